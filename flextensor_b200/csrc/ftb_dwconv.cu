@@ -1,0 +1,204 @@
+// Depthwise conv2d NCHW fp32: a bandwidth-bound stencil, no tensor cores.
+//
+// One CTA owns a strip of `strip_h` output rows of one input plane (n, c) and produces
+// the strip for all `factor` output channels fed by that plane.  The input rows the
+// strip needs are staged once in shared memory with 16-byte loads, zero padding is
+// written into the staging tile (the reference's separate padding op disappears),
+// each thread then produces four adjacent outputs of a row and stores them as one
+// 16-byte vector.  Algorithmic traffic: input read once, output written once.
+#include "ftb_host.h"
+
+namespace ftb {
+
+constexpr int kMaxTaps = 49;
+
+struct DwParams {
+  const float* in;
+  const float* w;
+  const float* bias;
+  float* out;
+  int N, C, H, W, F, R, S, P, Q;
+  int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int strip_h, strips;  // output rows per CTA, strips per plane
+  int tile_rows;        // input rows staged per strip
+  int tile_pitch;       // floats per staged row (multiple of 4)
+  int lead;             // staged column of input column 0 (multiple of 4, >= pad_w)
+};
+
+// Staging tile: row i holds input row (h_in0 + i); column (lead + x) holds input column x.
+template <bool K3S1>
+__global__ void dwconv_kernel(const DwParams p) {
+  extern __shared__ __align__(16) float tile[];
+  __shared__ float wsm[kMaxTaps];
+
+  const int strip = blockIdx.x % p.strips;
+  const int plane = blockIdx.x / p.strips;  // n * C + c
+  const int c = plane % p.C;
+  const int n = plane / p.C;
+  const int oh0 = strip * p.strip_h;
+  const int h_in0 = oh0 * p.stride_h - p.pad_h;
+  const float* src = p.in + static_cast<long long>(plane) * p.H * p.W;
+
+  // ---- stage input rows (zero outside the image)
+  const bool vec_in = (p.W % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.in) & 15) == 0);
+  const int pitch4 = p.tile_pitch / 4;
+  for (int i = threadIdx.x; i < p.tile_rows * pitch4; i += blockDim.x) {
+    const int row = i / pitch4;
+    const int col = (i - row * pitch4) * 4;  // staged column of this 4-wide group
+    const int h = h_in0 + row;
+    const int x = col - p.lead;              // input column of the group's first element
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (h >= 0 && h < p.H) {
+      const float* rp = src + static_cast<long long>(h) * p.W;
+      if (vec_in && x >= 0 && x + 3 < p.W) {
+        v = __ldg(reinterpret_cast<const float4*>(rp + x));
+      } else {
+        if (x >= 0 && x < p.W) v.x = __ldg(rp + x);
+        if (x + 1 >= 0 && x + 1 < p.W) v.y = __ldg(rp + x + 1);
+        if (x + 2 >= 0 && x + 2 < p.W) v.z = __ldg(rp + x + 2);
+        if (x + 3 >= 0 && x + 3 < p.W) v.w = __ldg(rp + x + 3);
+      }
+    }
+    *reinterpret_cast<float4*>(tile + row * p.tile_pitch + col) = v;
+  }
+
+  const int rows_here = min(p.strip_h, p.P - oh0);
+  const int q4 = (p.Q + 3) / 4;
+  const bool vec_out = (p.Q % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+
+  for (int f = 0; f < p.F; ++f) {
+    __syncthreads();  // tile staged (f == 0) / previous weights consumed (f > 0)
+    if (threadIdx.x < p.R * p.S)
+      wsm[threadIdx.x] = p.w[(static_cast<long long>(c) * p.F + f) * p.R * p.S + threadIdx.x];
+    __syncthreads();
+    const int co = c * p.F + f;
+    const float b = p.bias ? p.bias[co] : 0.f;
+    float* dst_plane = p.out + (static_cast<long long>(n) * p.C * p.F + co) * p.P * p.Q;
+
+    for (int i = threadIdx.x; i < rows_here * q4; i += blockDim.x) {
+      const int orow = i / q4;
+      const int ow = (i - orow * q4) * 4;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if constexpr (K3S1) {
+        // 3x3, stride 1, dilation 1: six staged values per row feed four outputs.
+        const int col0 = ow - p.pad_w + p.lead;  // staged column of tap s = 0 for output ow
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+          const float* tr = tile + (orow + r) * p.tile_pitch + col0;
+          float x[6];
+#pragma unroll
+          for (int j = 0; j < 6; ++j) x[j] = tr[j];
+#pragma unroll
+          for (int s = 0; s < 3; ++s) {
+            const float wv = wsm[r * 3 + s];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = fmaf(x[j + s], wv, acc[j]);
+          }
+        }
+      } else {
+        for (int r = 0; r < p.R; ++r) {
+          const float* tr = tile + (orow * p.stride_h + r * p.dil_h) * p.tile_pitch + p.lead - p.pad_w;
+          for (int s = 0; s < p.S; ++s) {
+            const float wv = wsm[r * p.S + s];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              // Outputs past Q read staged zeros or neighbours; they are never stored.
+              const int col = (ow + j) * p.stride_w + s * p.dil_w;
+              acc[j] = fmaf(tr[col], wv, acc[j]);
+            }
+          }
+        }
+      }
+      float* dst = dst_plane + static_cast<long long>(oh0 + orow) * p.Q + ow;
+      if (vec_out) {
+        *reinterpret_cast<float4*>(dst) = make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (ow + j < p.Q) dst[j] = acc[j] + b;
+      }
+    }
+  }
+}
+
+}  // namespace ftb
+
+extern "C" int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const float* bias, float* out,
+                                     int64_t n, int64_t c, int64_t h, int64_t w, int64_t factor, int64_t r,
+                                     int64_t s, int stride_h, int stride_w, int pad_h, int pad_w,
+                                     int dil_h, int dil_w, const ftb_config* cfg, int* status,
+                                     void* stream_v) {
+  using namespace ftb;
+  (void)status;  // no in-kernel waits: nothing to report
+  if (!in || !weight || !out) return FTB_E_BAD_ARG;
+  if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || factor <= 0 || r <= 0 || s <= 0) return FTB_E_BAD_ARG;
+  if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad_h < 0 || pad_w < 0) return FTB_E_BAD_ARG;
+  if (r * s > kMaxTaps) return FTB_E_UNSUPPORTED;
+  const int64_t P = (h + 2 * pad_h - dil_h * (r - 1) - 1) / stride_h + 1;
+  const int64_t Q = (w + 2 * pad_w - dil_w * (s - 1) - 1) / stride_w + 1;
+  if (P <= 0 || Q <= 0) return FTB_E_BAD_ARG;
+  if (n * c * h * w > (1ll << 31) || n * c * factor * P * Q > (1ll << 31)) return FTB_E_TOO_LARGE;
+  int rc = device_ok();
+  if (rc) return rc;
+
+  DwParams p;
+  memset(&p, 0, sizeof(p));
+  p.in = in; p.w = weight; p.bias = bias; p.out = out;
+  p.N = static_cast<int>(n); p.C = static_cast<int>(c); p.H = static_cast<int>(h); p.W = static_cast<int>(w);
+  p.F = static_cast<int>(factor); p.R = static_cast<int>(r); p.S = static_cast<int>(s);
+  p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);
+  p.stride_h = stride_h; p.stride_w = stride_w; p.pad_h = pad_h; p.pad_w = pad_w;
+  p.dil_h = dil_h; p.dil_w = dil_w;
+
+  // Staged row: [lead zeros/halo | W input columns | right halo], wide enough for the
+  // last 4-output group (which may run past Q) and rounded to 16 bytes.
+  p.lead = (pad_w + 3) / 4 * 4;
+  const int q_pad = static_cast<int>((Q + 3) / 4 * 4);
+  const int max_col = p.lead - pad_w + (q_pad - 1) * stride_w + (p.S - 1) * dil_w;
+  int pitch = max_col + 1;
+  if (pitch < p.lead + p.W) pitch = p.lead + p.W;
+  p.tile_pitch = (pitch + 3) / 4 * 4;
+
+  const int sms = sm_count();
+  int threads = cfg && cfg->threads > 0 ? cfg->threads : 256;
+  if (threads < 32 || threads > 1024 || threads % 32) return FTB_E_BAD_CONFIG;
+  if (threads < p.R * p.S) return FTB_E_BAD_CONFIG;
+  int strip_h = cfg && cfg->tile_h > 0 ? cfg->tile_h : 0;
+  if (strip_h == 0) {
+    // Default: the tallest strip that still gives every SM about four CTAs.
+    strip_h = p.P;
+    while (strip_h > 4 && static_cast<long long>(n) * c * ((p.P + strip_h - 1) / strip_h) < 4ll * sms)
+      strip_h = (strip_h + 1) / 2;
+  }
+  if (strip_h > p.P) strip_h = p.P;
+  const size_t kDynLimit = 200 * 1024;
+  auto rows_for = [&](int sh) { return (sh - 1) * stride_h + (p.R - 1) * dil_h + 1; };
+  while (strip_h > 1 && static_cast<size_t>(rows_for(strip_h)) * p.tile_pitch * 4 > kDynLimit)
+    strip_h = (strip_h + 1) / 2;
+  p.strip_h = strip_h;
+  p.strips = (p.P + strip_h - 1) / strip_h;
+  p.tile_rows = rows_for(strip_h);
+  const size_t smem = static_cast<size_t>(p.tile_rows) * p.tile_pitch * 4;
+  if (smem > kDynLimit) return FTB_E_UNSUPPORTED;
+
+  const bool k3s1 = (r == 3 && s == 3 && stride_h == 1 && stride_w == 1 && dil_h == 1 && dil_w == 1);
+  auto kern = k3s1 ? dwconv_kernel<true> : dwconv_kernel<false>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kDynLimit));
+    if (e != cudaSuccess) {
+      set_last_cuda_error(static_cast<int>(e));
+      return FTB_E_CUDA;
+    }
+  }
+  const long long blocks = static_cast<long long>(n) * c * p.strips;
+  if (blocks > 0x7fffffffll) return FTB_E_TOO_LARGE;
+  kern<<<static_cast<unsigned>(blocks), threads, smem, static_cast<cudaStream_t>(stream_v)>>>(p);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_cuda_error(static_cast<int>(e));
+    return FTB_E_CUDA;
+  }
+  return FTB_OK;
+}

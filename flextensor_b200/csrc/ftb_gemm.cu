@@ -1,0 +1,530 @@
+// Host side of the tcgen05 contraction kernel: tensor-map construction, knob
+// resolution/validation and the C-ABI launchers for GEMM fp32, batched GEMM bf16,
+// GEMM int8 and conv2d (implicit GEMM).
+#include "ftb_host.h"
+#include "ftb_umma_kernel.cuh"
+
+#include <cudaTypedefs.h>
+#include <mutex>
+
+namespace ftb {
+
+// ------------------------------------------------------------------ driver entry point
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+static std::once_flag g_encode_once;
+
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    else
+      set_last_cuda_error(static_cast<int>(e));
+  });
+  return g_encode;
+}
+
+// rank-`rank` tiled map with the 128-byte swizzle; strides in bytes for dims 1..rank-1.
+static int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base,
+                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                     const uint32_t* elem_strides) {
+  auto fn = encode_fn();
+  if (!fn) return FTB_E_CUDA;
+  CUresult r = fn(map, dt, rank, const_cast<void*>(base), dims, strides_bytes, box, elem_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_cuda_error(static_cast<int>(r));
+    return FTB_E_CUDA;
+  }
+  return FTB_OK;
+}
+
+// ------------------------------------------------------------------ per-dtype constants
+struct KindInfo {
+  int kind;         // KIND_*
+  int esize;        // bytes per input element
+  int kblk;         // K elements per stage (128 B)
+  int umma_k;       // K elements per tcgen05.mma
+  uint32_t ab_fmt;  // a_format / b_format field of the instruction descriptor
+  uint32_t c_fmt;   // c_format field
+  CUtensorMapDataType dt;
+};
+
+static KindInfo kind_info(int kind) {
+  switch (kind) {
+    case KIND_BF16: return {KIND_BF16, 2, 64, 16, 1u, 1u, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16};
+    case KIND_TF32: return {KIND_TF32, 4, 32, 8, 2u, 1u, CU_TENSOR_MAP_DATA_TYPE_FLOAT32};
+    default: return {KIND_I8, 1, 128, 32, 1u, 2u, CU_TENSOR_MAP_DATA_TYPE_UINT8};
+  }
+}
+
+// Instruction descriptor of tcgen05.mma for a dense M=128 x N=bn tile.
+static uint32_t make_idesc(const KindInfo& ki, int bn, int a_mn, int b_mn) {
+  uint32_t d = 0;
+  d |= ki.c_fmt << 4;
+  d |= ki.ab_fmt << 7;
+  d |= ki.ab_fmt << 10;
+  d |= static_cast<uint32_t>(a_mn ? 1 : 0) << 15;
+  d |= static_cast<uint32_t>(b_mn ? 1 : 0) << 16;
+  d |= static_cast<uint32_t>(bn >> 3) << 17;
+  d |= static_cast<uint32_t>(kTileM >> 4) << 24;
+  return d;
+}
+
+static size_t smem_needed(int bn, int stages, bool split3) {
+  return static_cast<size_t>(stages) * (kATileBytes + static_cast<size_t>(bn) * 128) * (split3 ? 2 : 1) +
+         1024;
+}
+constexpr size_t kSmemLimit = 227 * 1024 - 2048;  // leave room for the static barriers
+
+// N extent a single TMA box covers for an N-contiguous B operand.
+static int box_mn(const KindInfo& ki) { return 128 / ki.esize; }
+
+// Resolves tile_n / stages and checks every knob; `bn_mult` is the granularity B needs.
+static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split3, int b_mn,
+                          long long batch_tiles_m, long long n, int num_kb, bool f32_out, int num_sms,
+                          ftb_config* out) {
+  ftb_config c;
+  memset(&c, 0, sizeof(c));
+  if (user) c = *user;
+  const int gran = b_mn ? (box_mn(ki) > 32 ? box_mn(ki) : 32) : 32;
+  if (c.tile_n == 0) {
+    // Pick the widest tile that still fills the machine: compare useful work per wave.
+    double best = -1.0;
+    for (int bn = 256; bn >= gran; bn -= gran) {
+      if (bn != 256 && bn != 128 && bn != 64 && bn != 32) continue;
+      const long long tiles = batch_tiles_m * ((n + bn - 1) / bn);
+      const long long waves = (tiles + num_sms - 1) / num_sms;
+      const double useful = static_cast<double>(batch_tiles_m) * static_cast<double>(n);
+      const double paid = static_cast<double>(waves) * num_sms * bn;
+      const double eff = useful / paid;
+      if (eff > best + 1e-9) {
+        best = eff;
+        c.tile_n = bn;
+      }
+    }
+    if (c.tile_n == 0) c.tile_n = gran;
+  }
+  if (c.tile_n < 32 || c.tile_n > 256 || c.tile_n % gran != 0) return FTB_E_BAD_CONFIG;
+  if (c.stages == 0) {
+    c.stages = kMaxStages;
+    while (c.stages > 2 && smem_needed(c.tile_n, c.stages, split3) > kSmemLimit) --c.stages;
+    if (c.stages > num_kb + 1 && num_kb >= 1) c.stages = num_kb + 1 > 2 ? num_kb + 1 : 2;
+    if (c.stages > kMaxStages) c.stages = kMaxStages;
+  }
+  if (c.stages < 2 || c.stages > kMaxStages) return FTB_E_BAD_CONFIG;
+  if (smem_needed(c.tile_n, c.stages, split3) > kSmemLimit) return FTB_E_BAD_CONFIG;
+  if (c.raster < 0 || c.raster > 2) return FTB_E_BAD_CONFIG;
+  if (c.raster == 2 && c.group_m == 0) c.group_m = 8;
+  if (c.group_m < 0) return FTB_E_BAD_CONFIG;
+  if (c.split_k == 0) c.split_k = 1;
+  if (c.split_k < 1 || c.split_k > 64 || c.split_k > num_kb) return FTB_E_BAD_CONFIG;
+  if (c.split_k > 1 && !f32_out) return FTB_E_BAD_CONFIG;
+  if (c.ctas < 0) return FTB_E_BAD_CONFIG;
+  *out = c;
+  return FTB_OK;
+}
+
+template <int KIND, int OUT, bool SPLIT3>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const UmmaParams& p, int ctas,
+                  cudaStream_t stream) {
+  auto kern = umma_gemm_kernel<KIND, OUT, SPLIT3>;
+  const size_t smem = smem_needed(p.bn, p.stages, SPLIT3);
+  // The opt-in shared-memory size is a per-device attribute of the function.
+  static std::mutex mu;
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !done[dev]) {
+      cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  static_cast<int>(kSmemLimit));
+      if (attr_err != cudaSuccess) {
+        set_last_cuda_error(static_cast<int>(attr_err));
+        return FTB_E_CUDA;
+      }
+      done[dev] = true;
+    }
+  }
+  kern<<<ctas, SPLIT3 ? 320 : 192, smem, stream>>>(ta, tb, p);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_cuda_error(static_cast<int>(e));
+    return FTB_E_CUDA;
+  }
+  return FTB_OK;
+}
+
+static int dispatch(int kind, int out, bool split3, const CUtensorMap& ta, const CUtensorMap& tb,
+                    const UmmaParams& p, int ctas, cudaStream_t stream) {
+  if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false>(ta, tb, p, ctas, stream);
+  if (kind == KIND_BF16 && out == OUT_F32) return launch<KIND_BF16, OUT_F32, false>(ta, tb, p, ctas, stream);
+  if (kind == KIND_I8 && out == OUT_S32) return launch<KIND_I8, OUT_S32, false>(ta, tb, p, ctas, stream);
+  if (kind == KIND_TF32 && out == OUT_F32 && !split3) return launch<KIND_TF32, OUT_F32, false>(ta, tb, p, ctas, stream);
+  if (kind == KIND_TF32 && out == OUT_F32 && split3) return launch<KIND_TF32, OUT_F32, true>(ta, tb, p, ctas, stream);
+  return FTB_E_BAD_ARG;
+}
+
+// Fills the operand-staging fields for a plain (batched) GEMM operand.
+static void operand_layout(const KindInfo& ki, int mn_major, int tile_extent, int* boxes, int* box_extent,
+                           uint32_t* box_bytes, uint32_t* lbo, uint32_t* sbo, uint32_t* kadv) {
+  if (mn_major) {
+    *box_extent = box_mn(ki);
+    *boxes = tile_extent / *box_extent;
+    *box_bytes = static_cast<uint32_t>(ki.kblk) * 128u;
+    *lbo = *box_bytes;
+    *sbo = 1024;
+    *kadv = static_cast<uint32_t>(ki.umma_k) * 128u;
+  } else {
+    *box_extent = tile_extent;
+    *boxes = 1;
+    *box_bytes = static_cast<uint32_t>(tile_extent) * 128u;
+    *lbo = 16;
+    *sbo = 1024;
+    *kadv = static_cast<uint32_t>(ki.umma_k * ki.esize);
+  }
+}
+
+int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64_t batch, int64_t m,
+                 int64_t n, int64_t k, int trans_a, int trans_b, const ftb_config* user, int* status,
+                 void* stream_v) {
+  if (!a || !b || !c) return FTB_E_BAD_ARG;
+  if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return FTB_E_BAD_ARG;
+  if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30) || batch > (1ll << 24)) return FTB_E_TOO_LARGE;
+  int rc = device_ok();
+  if (rc) return rc;
+  const KindInfo ki = kind_info(kind);
+  const bool split3 = (kind == KIND_TF32) && user && user->fp32_mode == 1;
+  if (user && (user->fp32_mode < 0 || user->fp32_mode > 1)) return FTB_E_BAD_CONFIG;
+  const int a_mn = trans_a ? 1 : 0;  // A given as [K,M]: M contiguous
+  const int b_mn = trans_b ? 0 : 1;  // B given as [K,N]: N contiguous
+  // TMA addressing rules: 16-byte aligned bases and row pitches.
+  const int64_t a_pitch = (a_mn ? m : k) * ki.esize;
+  const int64_t b_pitch = (b_mn ? n : k) * ki.esize;
+  if ((a_pitch & 15) || (b_pitch & 15)) return FTB_E_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return FTB_E_UNSUPPORTED;
+
+  const int num_sms = sm_count();
+  const int tiles_m = static_cast<int>((m + kTileM - 1) / kTileM);
+  const int num_kb = static_cast<int>((k + ki.kblk - 1) / ki.kblk);
+  ftb_config cfg;
+  rc = resolve_config(user, ki, split3, b_mn, batch * tiles_m, n, num_kb, out == OUT_F32, num_sms, &cfg);
+  if (rc) return rc;
+
+  UmmaParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = static_cast<int>(m);
+  p.N = static_cast<int>(n);
+  p.K = static_cast<int>(k);
+  p.batch = static_cast<int>(batch);
+  p.bn = cfg.tile_n;
+  p.stages = cfg.stages;
+  p.num_kb = num_kb;
+  p.tiles_m = tiles_m;
+  p.tiles_n = static_cast<int>((n + p.bn - 1) / p.bn);
+  p.raster = cfg.raster;
+  p.group_m = cfg.group_m;
+  p.split_k = cfg.split_k;
+  p.kblk = ki.kblk;
+  p.idesc = make_idesc(ki, p.bn, a_mn, b_mn);
+  p.a_mn = a_mn;
+  p.b_mn = b_mn;
+  p.b_bytes = static_cast<uint32_t>(p.bn) * 128u;
+  operand_layout(ki, a_mn, kTileM, &p.a_boxes, &p.a_box_mn, &p.a_box_bytes, &p.a_lbo, &p.a_sbo, &p.a_kadv);
+  operand_layout(ki, b_mn, p.bn, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv);
+  p.mma_per_kb = ki.kblk / ki.umma_k;
+  p.C = c;
+  p.ldc = n;
+  p.c_batch_stride = m * n;
+  p.status = status ? status : fallback_status();
+  if (!p.status) return FTB_E_CUDA;
+
+  // Tensor maps: dim 0 is the contiguous one; batch is the outermost.
+  CUtensorMap ta, tb;
+  const uint32_t ones[3] = {1, 1, 1};
+  {
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    if (a_mn) {
+      dims[0] = m; dims[1] = k; dims[2] = batch;
+      box[0] = p.a_box_mn; box[1] = ki.kblk; box[2] = 1;
+    } else {
+      dims[0] = k; dims[1] = m; dims[2] = batch;
+      box[0] = ki.kblk; box[1] = kTileM; box[2] = 1;
+    }
+    strides[0] = dims[0] * ki.esize;
+    strides[1] = static_cast<uint64_t>(m) * k * ki.esize;
+    rc = make_tmap(&ta, ki.dt, 3, a, dims, strides, box, ones);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    if (b_mn) {
+      dims[0] = n; dims[1] = k; dims[2] = batch;
+      box[0] = p.b_box_mn; box[1] = ki.kblk; box[2] = 1;
+    } else {
+      dims[0] = k; dims[1] = n; dims[2] = batch;
+      box[0] = ki.kblk; box[1] = p.bn; box[2] = 1;
+    }
+    strides[0] = dims[0] * ki.esize;
+    strides[1] = static_cast<uint64_t>(n) * k * ki.esize;
+    rc = make_tmap(&tb, ki.dt, 3, b, dims, strides, box, ones);
+    if (rc) return rc;
+  }
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (p.split_k > 1) {
+    cudaError_t e = cudaMemsetAsync(c, 0, static_cast<size_t>(batch) * m * n * 4, stream);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(static_cast<int>(e));
+      return FTB_E_CUDA;
+    }
+  }
+  const long long total = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n * p.split_k;
+  if (total > 0x7fffffffll) return FTB_E_TOO_LARGE;
+  int ctas = cfg.ctas > 0 ? cfg.ctas : num_sms;
+  if (ctas > total) ctas = static_cast<int>(total);
+  return dispatch(kind, out, split3, ta, tb, p, ctas, stream);
+}
+
+// ------------------------------------------------------------------ conv2d as implicit GEMM
+// Workspace layout: [input as N,H,W,Cp floats][weights as K, R*S*cchunks*32 floats],
+// Cp = C rounded up to 4 (TMA pitch rule), both regions 1024-byte aligned.
+static int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+struct ConvWs {
+  int64_t cp, cchunks, in_bytes, w_bytes;
+};
+static ConvWs conv_ws(int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s,
+                      int64_t groups) {
+  ConvWs ws;
+  const int64_t cg = c / groups;
+  ws.cp = round_up(c, 4);
+  ws.cchunks = (cg + 31) / 32;
+  ws.in_bytes = round_up(n * h * w * ws.cp * 4, 1024);
+  ws.w_bytes = round_up(k * r * s * ws.cchunks * 32 * 4, 1024);
+  return ws;
+}
+
+// One launch: blocks [0, in_blocks) transpose NCHW -> NHWC(Cp) through a 32x33 tile,
+// the rest pack weights [K][Cg][R][S] -> [K][R][S][cchunks*32] (zero padded).
+__global__ void conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
+                                    float* __restrict__ in_nhwc, float* __restrict__ w_packed, int N,
+                                    int C, int HW, int Cp, int K, int Cg, int RS, int cchunks,
+                                    int hw_tiles, int c_tiles, int in_blocks) {
+  __shared__ float tile[32][33];
+  const int bid = blockIdx.x;
+  if (bid < in_blocks) {
+    const int ct = bid % c_tiles;
+    const int ht = (bid / c_tiles) % hw_tiles;
+    const int img = bid / (c_tiles * hw_tiles);
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    for (int j = ty; j < 32; j += 8) {
+      const int c = ct * 32 + j, hw = ht * 32 + tx;
+      tile[j][tx] = (c < C && hw < HW) ? in[(static_cast<long long>(img) * C + c) * HW + hw] : 0.0f;
+    }
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8) {
+      const int hw = ht * 32 + j, c = ct * 32 + tx;
+      if (hw < HW && c < Cp) in_nhwc[(static_cast<long long>(img) * HW + hw) * Cp + c] = tile[tx][j];
+    }
+  } else {
+    const long long kdim = static_cast<long long>(RS) * cchunks * 32;
+    const long long total = static_cast<long long>(K) * kdim;
+    const long long nb = gridDim.x - in_blocks;
+    for (long long i = static_cast<long long>(bid - in_blocks) * blockDim.x + threadIdx.x; i < total;
+         i += nb * blockDim.x) {
+      const int c = static_cast<int>(i % (cchunks * 32));
+      const int rs = static_cast<int>((i / (cchunks * 32)) % RS);
+      const int ko = static_cast<int>(i / kdim);
+      w_packed[i] = (c < Cg) ? wgt[(static_cast<long long>(ko) * Cg + c) * RS + rs] : 0.0f;
+    }
+  }
+}
+
+int conv2d_generic(const float* in, const float* weight, const float* bias, float* out, int64_t n,
+                   int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,
+                   int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
+                   const ftb_config* user, void* workspace, size_t workspace_bytes, int* status,
+                   void* stream_v) {
+  if (!in || !weight || !out) return FTB_E_BAD_ARG;
+  if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || k <= 0 || r <= 0 || s <= 0 || groups <= 0) return FTB_E_BAD_ARG;
+  if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad_h < 0 || pad_w < 0) return FTB_E_BAD_ARG;
+  if (c % groups || k % groups) return FTB_E_BAD_ARG;
+  const int64_t P = (h + 2 * pad_h - dil_h * (r - 1) - 1) / stride_h + 1;
+  const int64_t Q = (w + 2 * pad_w - dil_w * (s - 1) - 1) / stride_w + 1;
+  if (P <= 0 || Q <= 0) return FTB_E_BAD_ARG;
+  if (n * c * h * w > (1ll << 31) || n * k * P * Q > (1ll << 31)) return FTB_E_TOO_LARGE;
+  int rc = device_ok();
+  if (rc) return rc;
+  const int64_t cg = c / groups, kg = k / groups;
+  if (groups > 1 && (cg % 4)) return FTB_E_UNSUPPORTED;  // group base must stay 16-byte aligned
+  const ConvWs ws = conv_ws(n, c, h, w, k, r, s, groups);
+  if (!workspace || workspace_bytes < static_cast<size_t>(ws.in_bytes + ws.w_bytes)) return FTB_E_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FTB_E_WORKSPACE;
+  float* in_nhwc = static_cast<float*>(workspace);
+  float* w_packed = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ws.in_bytes);
+
+  const KindInfo ki = kind_info(KIND_TF32);
+  const bool split3 = user && user->fp32_mode == 1;
+  if (user && (user->fp32_mode < 0 || user->fp32_mode > 1)) return FTB_E_BAD_CONFIG;
+  const int num_sms = sm_count();
+
+  // Output tile of the implicit GEMM: tile_h x tile_w pixels (<= 128) of one image.
+  int tile_w = static_cast<int>(Q < 128 ? Q : 128);
+  if (tile_w * stride_w > 256) tile_w = 256 / stride_w;
+  int tile_h = user && user->tile_h > 0 ? user->tile_h : 128 / tile_w;
+  if (tile_h > P) tile_h = static_cast<int>(P);
+  if (tile_h < 1 || tile_h * tile_w > 128 || tile_h * stride_h > 256) return FTB_E_BAD_CONFIG;
+  const int tiles_w = static_cast<int>((Q + tile_w - 1) / tile_w);
+  const int tiles_h = static_cast<int>((P + tile_h - 1) / tile_h);
+  const int num_kb = static_cast<int>(r * s * ws.cchunks);
+  const long long tiles_m = static_cast<long long>(n) * tiles_h * tiles_w;
+  ftb_config cfg;
+  rc = resolve_config(user, ki, split3, 0, tiles_m, kg, num_kb, true, num_sms, &cfg);
+  if (rc) return rc;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  {
+    const int HW = static_cast<int>(h * w);
+    const int hw_tiles = (HW + 31) / 32, c_tiles = static_cast<int>((ws.cp + 31) / 32);
+    const int in_blocks = static_cast<int>(n) * hw_tiles * c_tiles;
+    const long long wtotal = k * r * s * ws.cchunks * 32;
+    int w_blocks = static_cast<int>((wtotal + 255) / 256);
+    if (w_blocks > 4 * num_sms) w_blocks = 4 * num_sms;
+    conv_prepass_kernel<<<in_blocks + w_blocks, 256, 0, stream>>>(
+        in, weight, in_nhwc, w_packed, static_cast<int>(n), static_cast<int>(c), HW,
+        static_cast<int>(ws.cp), static_cast<int>(k), static_cast<int>(cg), static_cast<int>(r * s),
+        static_cast<int>(ws.cchunks), hw_tiles, c_tiles, in_blocks);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      set_last_cuda_error(static_cast<int>(e));
+      return FTB_E_CUDA;
+    }
+  }
+  if (cfg.split_k > 1) {
+    cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(n * k * P * Q) * 4, stream);
+    if (e != cudaSuccess) {
+      set_last_cuda_error(static_cast<int>(e));
+      return FTB_E_CUDA;
+    }
+  }
+
+  for (int g = 0; g < groups; ++g) {
+    UmmaParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = static_cast<int>(tiles_m) * kTileM;
+    p.N = static_cast<int>(kg);
+    p.K = num_kb * ki.kblk;
+    p.batch = 1;
+    p.bn = cfg.tile_n;
+    p.stages = cfg.stages;
+    p.num_kb = num_kb;
+    p.tiles_m = static_cast<int>(tiles_m);
+    p.tiles_n = static_cast<int>((kg + p.bn - 1) / p.bn);
+    p.raster = cfg.raster;
+    p.group_m = cfg.group_m;
+    p.split_k = cfg.split_k;
+    p.kblk = ki.kblk;
+    p.idesc = make_idesc(ki, p.bn, 0, 0);
+    p.b_bytes = static_cast<uint32_t>(p.bn) * 128u;
+    p.a_boxes = 1;
+    p.a_box_mn = kTileM;
+    p.a_box_bytes = static_cast<uint32_t>(tile_h * tile_w) * 128u;
+    p.a_lbo = 16; p.a_sbo = 1024; p.a_kadv = static_cast<uint32_t>(ki.umma_k * ki.esize);
+    operand_layout(ki, 0, p.bn, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv);
+    p.mma_per_kb = ki.kblk / ki.umma_k;
+    p.conv = 1;
+    p.conv_ktot = static_cast<int>(k);
+    p.conv_koff = static_cast<int>(g * kg);
+    p.C = out;
+    p.bias = bias;
+    p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);
+    p.tile_h = tile_h; p.tile_w = tile_w; p.tiles_h = tiles_h; p.tiles_w = tiles_w;
+    p.R = static_cast<int>(r); p.S = static_cast<int>(s); p.cchunks = static_cast<int>(ws.cchunks);
+    p.stride_h = stride_h; p.stride_w = stride_w; p.pad_h = pad_h; p.pad_w = pad_w;
+    p.dil_h = dil_h; p.dil_w = dil_w;
+    p.status = status ? status : fallback_status();
+    if (!p.status) return FTB_E_CUDA;
+
+    CUtensorMap ta, tb;
+    {
+      // (c, w, h, n) view of the channels-last copy; a group sees its own Cg channels.
+      uint64_t dims[4] = {static_cast<uint64_t>(groups > 1 ? cg : ws.cp), static_cast<uint64_t>(w),
+                          static_cast<uint64_t>(h), static_cast<uint64_t>(n)};
+      uint64_t strides[3] = {static_cast<uint64_t>(ws.cp) * 4, static_cast<uint64_t>(w) * ws.cp * 4,
+                             static_cast<uint64_t>(h) * w * ws.cp * 4};
+      uint32_t box[4] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(tile_w * stride_w),
+                         static_cast<uint32_t>(tile_h * stride_h), 1};
+      uint32_t es[4] = {1, static_cast<uint32_t>(stride_w), static_cast<uint32_t>(stride_h), 1};
+      rc = make_tmap(&ta, ki.dt, 4, in_nhwc + g * cg, dims, strides, box, es);
+      if (rc) return rc;
+    }
+    {
+      const uint64_t kdim = static_cast<uint64_t>(num_kb) * ki.kblk;
+      uint64_t dims[3] = {kdim, static_cast<uint64_t>(kg), 1};
+      uint64_t strides[2] = {kdim * 4, kdim * 4 * kg};
+      uint32_t box[3] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(p.bn), 1};
+      const uint32_t ones[3] = {1, 1, 1};
+      rc = make_tmap(&tb, ki.dt, 3, w_packed + static_cast<uint64_t>(g) * kg * kdim, dims, strides, box, ones);
+      if (rc) return rc;
+    }
+    const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.split_k;
+    if (total > 0x7fffffffll) return FTB_E_TOO_LARGE;
+    int ctas = cfg.ctas > 0 ? cfg.ctas : num_sms;
+    if (ctas > total) ctas = static_cast<int>(total);
+    rc = dispatch(KIND_TF32, OUT_F32, split3, ta, tb, p, ctas, stream);
+    if (rc) return rc;
+  }
+  return FTB_OK;
+}
+
+}  // namespace ftb
+
+// ------------------------------------------------------------------ C ABI
+extern "C" {
+
+int ftb_gemm_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int trans_a,
+                 int trans_b, const ftb_config* cfg, int* status, void* stream) {
+  return ftb::gemm_generic(ftb::KIND_TF32, ftb::OUT_F32, a, b, c, 1, m, n, k, trans_a, trans_b, cfg,
+                           status, stream);
+}
+
+int ftb_bgemm_bf16(const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n, int64_t k,
+                   int trans_a, int trans_b, int out_f32, const ftb_config* cfg, int* status,
+                   void* stream) {
+  return ftb::gemm_generic(ftb::KIND_BF16, out_f32 ? ftb::OUT_F32 : ftb::OUT_BF16, a, b, c, batch, m, n,
+                           k, trans_a, trans_b, cfg, status, stream);
+}
+
+int ftb_gemm_s8(const int8_t* a, const int8_t* b, int32_t* c, int64_t m, int64_t n, int64_t k,
+                int trans_a, int trans_b, const ftb_config* cfg, int* status, void* stream) {
+  return ftb::gemm_generic(ftb::KIND_I8, ftb::OUT_S32, a, b, c, 1, m, n, k, trans_a, trans_b, cfg,
+                           status, stream);
+}
+
+size_t ftb_conv2d_workspace_bytes(int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r,
+                                  int64_t s, int64_t groups) {
+  if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || k <= 0 || r <= 0 || s <= 0 || groups <= 0) return 0;
+  const ftb::ConvWs ws = ftb::conv_ws(n, c, h, w, k, r, s, groups);
+  return static_cast<size_t>(ws.in_bytes + ws.w_bytes);
+}
+
+int ftb_conv2d_nchw_f32(const float* in, const float* weight, const float* bias, float* out, int64_t n,
+                        int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,
+                        int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
+                        const ftb_config* cfg, void* workspace, size_t workspace_bytes, int* status,
+                        void* stream) {
+  return ftb::conv2d_generic(in, weight, bias, out, n, c, h, w, k, r, s, stride_h, stride_w, pad_h,
+                             pad_w, dil_h, dil_w, groups, cfg, workspace, workspace_bytes, status,
+                             stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,141 @@
+"""Compute definitions of the five hot-path operators, PyTorch conventions.
+
+Each function returns the output ``Tensor`` of a small op graph (see ``ir.py``), with the
+same argument meaning, shape checks, loop-axis names and output-size formulas as the
+reference's ``flextensor/nn/ops.py``:
+
+  zero_pad2d             ops.py:83-117
+  conv2d_nchw            ops.py:419-479   (pad -> conv [-> bias]: a 2- or 3-op graph)
+  depthwise_conv2d_nchw  ops.py:622-678   (weight layout [C, factor, kh, kw])
+  gemm                   ops.py:1074-1108 (four transpose variants)
+  batch_gemm             ops.py:1111-1158
+  gemm_int8              no ops.py symbol; contract of test/test_tvm/legacy/gemm_int8.py:15-21
+
+The reference is fp32 only; ``dtype`` follows the input tensors here so that the same
+index expressions serve bf16 (fp32 accumulate) and int8 (int32 accumulate).
+"""
+from ..ir import ComputeOp, Tensor, reduce_axis
+from ..utils import assert_print
+
+
+def _pair(value, what):
+    if isinstance(value, int):
+        return (value, value)
+    value = tuple(int(v) for v in value)
+    assert_print(len(value) == 2, "%s must be an int or a pair" % what)
+    return value
+
+
+def _acc_dtype(dtype):
+    return {"float32": "float32", "bfloat16": "float32", "int8": "int32"}.get(dtype, dtype)
+
+
+def zero_pad2d(inputs, padding=0):
+    """Zero padding of [batch, channel, height, width]; padding int, (h, w) or (up, down, left, right)."""
+    if isinstance(padding, int):
+        padding = (padding,) * 4
+    assert_print(isinstance(padding, tuple), "type(padding)={}".format(type(padding)))
+    if len(padding) == 2:
+        padding = (padding[0], padding[0], padding[1], padding[1])
+    assert_print(len(padding) == 4)
+    b, c, h, w = (int(s) for s in inputs.shape)
+    shape = (b, c, h + padding[0] + padding[1], w + padding[2] + padding[3])
+    op = ComputeOp("pad2d", "Padding", shape, inputs.dtype, [inputs], ("b", "c", "h", "w"),
+                   attrs={"padding": tuple(padding)})
+    return op.output(0)
+
+
+def _bias_add(output, bias):
+    op = ComputeOp("bias_add", "bias_add", tuple(int(s) for s in output.shape), output.dtype,
+                   [output, bias], ("b", "c", "h", "w"), attrs={"axis": 1})
+    return op.output(0)
+
+
+def conv2d_nchw(inputs, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    """inputs [N,C,H,W], weight [K, C/groups, kh, kw] -> [N, K, out_h, out_w]."""
+    n, c, in_h, in_w = (int(s) for s in inputs.shape)
+    k, cg, k_h, k_w = (int(s) for s in weight.shape)
+    assert_print(cg * groups == c)
+    kg = k // groups
+    assert_print(kg * groups == k)
+    stride, padding, dilation = _pair(stride, "stride"), _pair(padding, "padding"), _pair(dilation, "dilation")
+    out_h = (in_h + 2 * padding[0] - dilation[0] * (k_h - 1) - 1) // stride[0] + 1
+    out_w = (in_w + 2 * padding[1] - dilation[1] * (k_w - 1) - 1) // stride[1] + 1
+    rc = reduce_axis((0, cg), name="rc")
+    rh = reduce_axis((0, k_h), name="rh")
+    rw = reduce_axis((0, k_w), name="rw")
+    padded = zero_pad2d(inputs, padding=padding)
+    op = ComputeOp("conv2d", "compute", (n, k, out_h, out_w), _acc_dtype(inputs.dtype), [padded, weight],
+                   ("b", "c", "h", "w"), reduce_axes=[rc, rw, rh],
+                   attrs={"stride": stride, "padding": padding, "dilation": dilation, "groups": groups})
+    out = op.output(0)
+    if bias is not None:
+        out = _bias_add(out, bias)
+    return out
+
+
+def depthwise_conv2d_nchw(inputs, weight, bias=None, stride=1, padding=0, dilation=1):
+    """inputs [N,C,H,W], weight [C, factor, kh, kw] -> [N, C*factor, out_h, out_w]."""
+    n, c, in_h, in_w = (int(s) for s in inputs.shape)
+    c2, factor, k_h, k_w = (int(s) for s in weight.shape)
+    assert_print(c2 == c)
+    stride, padding, dilation = _pair(stride, "stride"), _pair(padding, "padding"), _pair(dilation, "dilation")
+    out_h = (in_h + 2 * padding[0] - dilation[0] * (k_h - 1) - 1) // stride[0] + 1
+    out_w = (in_w + 2 * padding[1] - dilation[1] * (k_w - 1) - 1) // stride[1] + 1
+    rh = reduce_axis((0, k_h), name="rh")
+    rw = reduce_axis((0, k_w), name="rw")
+    padded = zero_pad2d(inputs, padding=padding)
+    op = ComputeOp("depthwise_conv2d", "compute", (n, c * factor, out_h, out_w), _acc_dtype(inputs.dtype),
+                   [padded, weight], ("b", "c", "h", "w"), reduce_axes=[rw, rh],
+                   attrs={"stride": stride, "padding": padding, "dilation": dilation, "factor": factor})
+    out = op.output(0)
+    if bias is not None:
+        out = _bias_add(out, bias)
+    return out
+
+
+def _gemm_dims(a_shape, b_shape, transposeA, transposeB):
+    """(M, N, K) of op(A).op(B) for 2-d shapes, with the reference's shape assertion."""
+    if transposeA and transposeB:      # A[k,i], B[j,k]
+        assert_print(a_shape[0] == b_shape[1])
+        return a_shape[1], b_shape[0], b_shape[1]
+    if transposeA:                     # A[k,i], B[k,j]
+        assert_print(a_shape[0] == b_shape[0])
+        return a_shape[1], b_shape[1], b_shape[0]
+    if transposeB:                     # A[i,k], B[j,k]
+        assert_print(a_shape[1] == b_shape[1])
+        return a_shape[0], b_shape[0], b_shape[1]
+    assert_print(a_shape[1] == b_shape[0])  # A[i,k], B[k,j]
+    return a_shape[0], b_shape[1], b_shape[0]
+
+
+def gemm(A, B, transposeA=False, transposeB=False):
+    """C[i,j] = sum_k op(A)[i,k] * op(B)[k,j]."""
+    m, n, k = _gemm_dims([int(s) for s in A.shape], [int(s) for s in B.shape], transposeA, transposeB)
+    rk = reduce_axis((0, k), name="k")
+    op = ComputeOp("gemm", "compute", (m, n), _acc_dtype(A.dtype), [A, B], ("i", "j"), reduce_axes=[rk],
+                   attrs={"transposeA": bool(transposeA), "transposeB": bool(transposeB)})
+    return op.output(0)
+
+
+def batch_gemm(A, B, transposeA=False, transposeB=False, out_dtype=None):
+    """C[b,i,j] = sum_k op(A[b])[i,k] * op(B[b])[k,j]; ``out_dtype`` defaults to the input dtype
+    for bf16 (accumulation is always fp32) and to fp32 for fp32."""
+    a_shape, b_shape = [int(s) for s in A.shape], [int(s) for s in B.shape]
+    assert_print(a_shape[0] == b_shape[0])
+    m, n, k = _gemm_dims(a_shape[1:], b_shape[1:], transposeA, transposeB)
+    rk = reduce_axis((0, k), name="k")
+    dtype = out_dtype or A.dtype
+    op = ComputeOp("batch_gemm", "compute", (a_shape[0], m, n), dtype, [A, B], ("b", "i", "j"),
+                   reduce_axes=[rk], attrs={"transposeA": bool(transposeA), "transposeB": bool(transposeB)})
+    return op.output(0)
+
+
+def gemm_int8(A, B, transposeA=False, transposeB=False):
+    """int8 x int8 -> int32 GEMM; ``transposeB=True`` is the legacy script's B[n,k] layout."""
+    assert_print(A.dtype == "int8" and B.dtype == "int8", "gemm_int8 takes int8 tensors")
+    m, n, k = _gemm_dims([int(s) for s in A.shape], [int(s) for s in B.shape], transposeA, transposeB)
+    rk = reduce_axis((0, k), name="k")
+    op = ComputeOp("gemm_int8", "compute", (m, n), "int32", [A, B], ("i", "j"), reduce_axes=[rk],
+                   attrs={"transposeA": bool(transposeA), "transposeB": bool(transposeB)})
+    return op.output(0)

@@ -1,0 +1,111 @@
+/*
+ * ftb200 - C ABI of the B200 (sm_100a) kernel backend that stands where FlexTensor's
+ * TVM-built CUDA modules stood.
+ *
+ * The reference has no C boundary of its own: its boundary is the callable returned by
+ * `tvm.build(s, bufs, target)` (README.md:153-158, flextensor/optimize/common.py:34-48,
+ * flextensor/measure.py:87-110), called destination-passing with the arrays of `bufs`
+ * in order, output last.  Each launcher below is what that callable binds to for one
+ * operator of flextensor/nn/ops.py; the operator it replaces is cited beside it.
+ *
+ * Conventions
+ *   - every pointer is a device pointer owned by the caller; the library allocates no
+ *     device memory (it keeps two small `__device__` words per process for status);
+ *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous on it;
+ *   - return value: 0 on success, a negative FTB_E_* code otherwise; nothing throws,
+ *     exits or prints;
+ *   - `status` is a device int (may be NULL): kernels OR a non-zero FTB_DEV_* bit into it
+ *     when a bounded in-kernel wait ran out; read it after synchronising the stream;
+ *   - `cfg` may be NULL: every knob then takes its default (0 means "default" per field).
+ */
+#ifndef FTB200_H_
+#define FTB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FTB_VERSION 100
+
+enum ftb_error {
+  FTB_OK = 0,
+  FTB_E_BAD_ARG = -1,     /* null pointer, non-positive extent, unknown enum value      */
+  FTB_E_UNSUPPORTED = -2, /* shape/stride the TMA path cannot address (16-byte rules)   */
+  FTB_E_BAD_CONFIG = -3,  /* knob outside its range or over the shared-memory budget    */
+  FTB_E_WORKSPACE = -4,   /* workspace missing or too small                             */
+  FTB_E_CUDA = -5,        /* a CUDA runtime/driver call failed; see ftb_last_cuda_error */
+  FTB_E_NO_DEVICE = -6,   /* current device is not compute capability 10.x              */
+  FTB_E_TOO_LARGE = -7    /* size beyond a stated maximum of the entry point            */
+};
+
+/* Knobs of the kernels: the config space the scheduler searches
+ * (replaces the split/fuse/reorder/unroll factors of flextensor/templates/cuda.py:390-661). */
+typedef struct ftb_config {
+  int32_t tile_n;    /* accumulator columns per CTA tile: 32..256 step 32 (M tile is 128) */
+  int32_t stages;    /* shared-memory pipeline depth, 2..8                                */
+  int32_t raster;    /* tile order: 0 n-fastest, 1 m-fastest, 2 grouped-M                 */
+  int32_t group_m;   /* group height for raster 2                                         */
+  int32_t split_k;   /* K splits accumulated with atomics (fp32 outputs only)             */
+  int32_t fp32_mode; /* fp32 inputs: 0 = single-pass TF32, 1 = 3xTF32 (fp32-grade)        */
+  int32_t ctas;      /* persistent CTAs (default: one per SM)                             */
+  int32_t tile_h;    /* conv2d: output rows per tile; depthwise: output rows per strip    */
+  int32_t threads;   /* depthwise: threads per CTA                                        */
+  int32_t reserved[7];
+} ftb_config;
+
+int ftb_version(void);
+const char* ftb_strerror(int code);
+/* Last CUDA error code seen by a launcher of this process (cudaError_t / CUresult value). */
+int ftb_last_cuda_error(void);
+/* 0 when the current device can run the kernels (compute capability 10.x). */
+int ftb_device_check(void);
+/* Checks a knob set against the limits of an operator without launching:
+ * op = 0 gemm_f32, 1 bgemm_bf16, 2 gemm_s8, 3 conv2d, 4 depthwise
+ * (host-side counterpart of flextensor/scheduler.py:58-76 verify_code). */
+int ftb_validate(int op, const ftb_config* cfg, int64_t m, int64_t n, int64_t k);
+/* Number of kernels this library has launched in this process (all entry points). */
+int64_t ftb_launch_count(void);
+
+/* C[M,N] = op(A) . op(B), fp32 in/out, TF32 tensor cores (flextensor/nn/ops.py:1074-1108 gemm).
+ * trans_a = 0: A is [M,K] row-major, 1: A is [K,M]; trans_b = 0: B is [K,N], 1: B is [N,K]. */
+int ftb_gemm_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                 int trans_a, int trans_b, const ftb_config* cfg, int* status, void* stream);
+
+/* C[b,M,N] = op(A[b]) . op(B[b]); bf16 inputs, fp32 accumulate, output bf16 (out_f32 = 0) or
+ * fp32 (out_f32 = 1) (flextensor/nn/ops.py:1111-1158 batch_gemm, extended to bf16). */
+int ftb_bgemm_bf16(const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n,
+                   int64_t k, int trans_a, int trans_b, int out_f32, const ftb_config* cfg,
+                   int* status, void* stream);
+
+/* C[M,N] (int32) = op(A) . op(B), int8 inputs, exact int32 accumulation
+ * (contract of flextensor/test/test_tvm/legacy/gemm_int8.py:15-21,143-148; trans_b = 1 is its
+ * B[N,K] layout, trans_b = 0 the numpy `A @ B` layout). */
+int ftb_gemm_s8(const int8_t* a, const int8_t* b, int32_t* c, int64_t m, int64_t n, int64_t k,
+                int trans_a, int trans_b, const ftb_config* cfg, int* status, void* stream);
+
+/* out[N,K,P,Q] = conv2d(in[N,C,H,W], w[K,C/groups,R,S]) (+ bias[K]), cross-correlation with
+ * zero padding folded into the loads (flextensor/nn/ops.py:83-117 zero_pad2d + :419-479
+ * conv2d_nchw).  `workspace` holds the channels-last copy of the input and the packed
+ * weights; its size comes from ftb_conv2d_workspace_bytes. */
+size_t ftb_conv2d_workspace_bytes(int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r,
+                                  int64_t s, int64_t groups);
+int ftb_conv2d_nchw_f32(const float* in, const float* weight, const float* bias, float* out,
+                        int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s,
+                        int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                        int groups, const ftb_config* cfg, void* workspace, size_t workspace_bytes,
+                        int* status, void* stream);
+
+/* out[N,C*f,P,Q] = depthwise conv of in[N,C,H,W] with w[C,f,R,S] (+ bias[C*f])
+ * (flextensor/nn/ops.py:622-678 depthwise_conv2d_nchw; note the [C,f,R,S] weight layout). */
+int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const float* bias, float* out,
+                          int64_t n, int64_t c, int64_t h, int64_t w, int64_t factor, int64_t r,
+                          int64_t s, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h,
+                          int dil_w, const ftb_config* cfg, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FTB200_H_ */
