@@ -39,10 +39,12 @@ class FtbConfig(ctypes.Structure):
         ("ctas", ctypes.c_int32),
         ("tile_h", ctypes.c_int32),
         ("threads", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 7),
+        ("cluster", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 6),
     ]
 
-    KNOBS = ("tile_n", "stages", "raster", "group_m", "split_k", "fp32_mode", "ctas", "tile_h", "threads")
+    KNOBS = ("tile_n", "stages", "raster", "group_m", "split_k", "fp32_mode", "ctas", "tile_h", "threads",
+             "cluster")
 
     @classmethod
     def from_dict(cls, knobs):

@@ -26,14 +26,14 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return g_encode;
 }
 
-// rank-`rank` tiled map with the 128-byte swizzle; strides in bytes for dims 1..rank-1.
+// rank-`rank` tiled map (128-byte swizzle unless told otherwise); strides in bytes for dims 1..rank-1.
 static int make_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base,
                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
-                     const uint32_t* elem_strides) {
+                     const uint32_t* elem_strides, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   auto fn = encode_fn();
   if (!fn) return FTB_E_CUDA;
   CUresult r = fn(map, dt, rank, const_cast<void*>(base), dims, strides_bytes, box, elem_strides,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_last_cuda_error(static_cast<int>(r));
@@ -62,7 +62,7 @@ static KindInfo kind_info(int kind) {
 }
 
 // Instruction descriptor of tcgen05.mma for a dense M=128 x N=bn tile.
-static uint32_t make_idesc(const KindInfo& ki, int bn, int a_mn, int b_mn) {
+static uint32_t make_idesc(const KindInfo& ki, int bn, int a_mn, int b_mn, int mma_m = kTileM) {
   uint32_t d = 0;
   d |= ki.c_fmt << 4;
   d |= ki.ab_fmt << 7;
@@ -70,7 +70,7 @@ static uint32_t make_idesc(const KindInfo& ki, int bn, int a_mn, int b_mn) {
   d |= static_cast<uint32_t>(a_mn ? 1 : 0) << 15;
   d |= static_cast<uint32_t>(b_mn ? 1 : 0) << 16;
   d |= static_cast<uint32_t>(bn >> 3) << 17;
-  d |= static_cast<uint32_t>(kTileM >> 4) << 24;
+  d |= static_cast<uint32_t>(mma_m >> 4) << 24;
   return d;
 }
 
@@ -83,40 +83,75 @@ constexpr size_t kSmemLimit = 227 * 1024 - 2048;  // leave room for the static b
 // N extent a single TMA box covers for an N-contiguous B operand.
 static int box_mn(const KindInfo& ki) { return 128 / ki.esize; }
 
-// Resolves tile_n / stages and checks every knob; `bn_mult` is the granularity B needs.
-static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split3, int b_mn,
-                          long long batch_tiles_m, long long n, int num_kb, bool f32_out, int num_sms,
-                          ftb_config* out) {
+// Relative per-SM throughput of a (cluster, tile_n) choice on a long K loop, from
+// measurement; used only to rank defaults.
+static double tile_rate(int cluster, int bn) {
+  if (cluster == 2) return bn >= 256 ? 1.0 : bn >= 128 ? 0.65 : bn >= 64 ? 0.35 : 0.2;
+  return bn >= 256 ? 0.7 : bn >= 128 ? 0.4 : bn >= 64 ? 0.2 : 0.1;
+}
+
+// Resolves cluster / tile_n / stages and checks every knob.  `m_rows` = M of one batch
+// item, `batch` items; `allow_pair` is false for conv and 3xTF32.
+static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split3, int b_mn, bool allow_pair,
+                          long long batch, long long m_rows, long long n, int num_kb, bool f32_out,
+                          int num_sms, ftb_config* out) {
   ftb_config c;
   memset(&c, 0, sizeof(c));
   if (user) c = *user;
-  const int gran = b_mn ? (box_mn(ki) > 32 ? box_mn(ki) : 32) : 32;
-  if (c.tile_n == 0) {
-    // Pick the widest tile that still fills the machine: compare useful work per wave.
+  if (c.cluster < 0 || c.cluster > 2) return FTB_E_BAD_CONFIG;
+  if (c.cluster == 2 && !allow_pair) return FTB_E_BAD_CONFIG;
+  if (c.tile_n != 0 && (c.tile_n < 32 || c.tile_n > 256 || c.tile_n % 32)) return FTB_E_BAD_CONFIG;
+  // Granularity of tile_n: one TMA box of an N-contiguous B covers box_mn columns per CTA.
+  auto tile_ok = [&](int cluster, int bn) {
+    const int per_cta = bn / cluster;
+    if (per_cta < 16 || per_cta % 8) return false;
+    if (b_mn && per_cta % box_mn(ki)) return false;
+    return true;
+  };
+  if (c.cluster == 0 || c.tile_n == 0) {
     double best = -1.0;
-    for (int bn = 256; bn >= gran; bn -= gran) {
-      if (bn != 256 && bn != 128 && bn != 64 && bn != 32) continue;
-      const long long tiles = batch_tiles_m * ((n + bn - 1) / bn);
-      const long long waves = (tiles + num_sms - 1) / num_sms;
-      const double useful = static_cast<double>(batch_tiles_m) * static_cast<double>(n);
-      const double paid = static_cast<double>(waves) * num_sms * bn;
-      const double eff = useful / paid;
-      if (eff > best + 1e-9) {
-        best = eff;
-        c.tile_n = bn;
+    int best_cluster = 1, best_bn = 32;
+    for (int cluster = 2; cluster >= 1; --cluster) {
+      if (c.cluster != 0 && c.cluster != cluster) continue;
+      if (cluster == 2 && (!allow_pair || num_sms < 2)) continue;
+      for (int bn = 256; bn >= 32; bn /= 2) {
+        if (c.tile_n != 0 && c.tile_n != bn) continue;
+        if (!tile_ok(cluster, bn)) continue;
+        const long long tm = kTileM * cluster;
+        const long long tiles = batch * ((m_rows + tm - 1) / tm) * ((n + bn - 1) / bn);
+        const long long units = num_sms / cluster;
+        const long long waves = (tiles + units - 1) / units;
+        const double useful = static_cast<double>(batch) * m_rows * n;
+        const double paid = static_cast<double>(waves) * units * tm * bn;
+        const double score = useful / paid * tile_rate(cluster, bn);
+        if (score > best + 1e-9) {
+          best = score;
+          best_cluster = cluster;
+          best_bn = bn;
+        }
       }
     }
-    if (c.tile_n == 0) c.tile_n = gran;
+    if (best < 0) {
+      if (c.tile_n == 0 || c.cluster == 0) {
+        // no ranked candidate: fall back to the smallest legal single-CTA tile
+        c.cluster = c.cluster ? c.cluster : 1;
+        if (c.tile_n == 0) c.tile_n = b_mn && box_mn(ki) > 32 ? box_mn(ki) : 32;
+      }
+    } else {
+      c.cluster = best_cluster;
+      c.tile_n = best_bn;
+    }
   }
-  if (c.tile_n < 32 || c.tile_n > 256 || c.tile_n % gran != 0) return FTB_E_BAD_CONFIG;
+  if (!tile_ok(c.cluster, c.tile_n)) return FTB_E_BAD_CONFIG;
+  const int bn_cta = c.tile_n / c.cluster;
   if (c.stages == 0) {
     c.stages = kMaxStages;
-    while (c.stages > 2 && smem_needed(c.tile_n, c.stages, split3) > kSmemLimit) --c.stages;
+    while (c.stages > 2 && smem_needed(bn_cta, c.stages, split3) > kSmemLimit) --c.stages;
     if (c.stages > num_kb + 1 && num_kb >= 1) c.stages = num_kb + 1 > 2 ? num_kb + 1 : 2;
     if (c.stages > kMaxStages) c.stages = kMaxStages;
   }
   if (c.stages < 2 || c.stages > kMaxStages) return FTB_E_BAD_CONFIG;
-  if (smem_needed(c.tile_n, c.stages, split3) > kSmemLimit) return FTB_E_BAD_CONFIG;
+  if (smem_needed(bn_cta, c.stages, split3) > kSmemLimit) return FTB_E_BAD_CONFIG;
   if (c.raster < 0 || c.raster > 2) return FTB_E_BAD_CONFIG;
   if (c.raster == 2 && c.group_m == 0) c.group_m = 8;
   if (c.group_m < 0) return FTB_E_BAD_CONFIG;
@@ -128,11 +163,11 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
   return FTB_OK;
 }
 
-template <int KIND, int OUT, bool SPLIT3>
+template <int KIND, int OUT, bool SPLIT3, bool PAIR>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const UmmaParams& p, int ctas,
                   cudaStream_t stream) {
-  auto kern = umma_gemm_kernel<KIND, OUT, SPLIT3>;
-  const size_t smem = smem_needed(p.bn, p.stages, SPLIT3);
+  auto kern = umma_gemm_kernel<KIND, OUT, SPLIT3, PAIR>;
+  const size_t smem = smem_needed(p.b_bytes / 128, p.stages, SPLIT3);
   // The opt-in shared-memory size is a per-device attribute of the function.
   static std::mutex mu;
   static bool done[64] = {false};
@@ -150,9 +185,24 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const UmmaParams
       done[dev] = true;
     }
   }
-  kern<<<ctas, SPLIT3 ? 320 : 192, smem, stream>>>(ta, tb, p);
+  cudaLaunchConfig_t lc;
+  memset(&lc, 0, sizeof(lc));
+  lc.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
+  lc.blockDim = dim3(SPLIT3 ? 320 : 192, 1, 1);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (PAIR) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&lc, kern, ta, tb, p);
   count_launch();
-  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_cuda_error(static_cast<int>(e));
     return FTB_E_CUDA;
@@ -160,26 +210,45 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const UmmaParams
   return FTB_OK;
 }
 
-static int dispatch(int kind, int out, bool split3, const CUtensorMap& ta, const CUtensorMap& tb,
+static int dispatch(int kind, int out, bool split3, bool pair, const CUtensorMap& ta, const CUtensorMap& tb,
                     const UmmaParams& p, int ctas, cudaStream_t stream) {
-  if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false>(ta, tb, p, ctas, stream);
-  if (kind == KIND_BF16 && out == OUT_F32) return launch<KIND_BF16, OUT_F32, false>(ta, tb, p, ctas, stream);
-  if (kind == KIND_I8 && out == OUT_S32) return launch<KIND_I8, OUT_S32, false>(ta, tb, p, ctas, stream);
-  if (kind == KIND_TF32 && out == OUT_F32 && !split3) return launch<KIND_TF32, OUT_F32, false>(ta, tb, p, ctas, stream);
-  if (kind == KIND_TF32 && out == OUT_F32 && split3) return launch<KIND_TF32, OUT_F32, true>(ta, tb, p, ctas, stream);
+  if (pair) {
+    if (split3) return FTB_E_BAD_CONFIG;
+    if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false, true>(ta, tb, p, ctas, stream);
+    if (kind == KIND_BF16 && out == OUT_F32) return launch<KIND_BF16, OUT_F32, false, true>(ta, tb, p, ctas, stream);
+    if (kind == KIND_I8 && out == OUT_S32) return launch<KIND_I8, OUT_S32, false, true>(ta, tb, p, ctas, stream);
+    if (kind == KIND_TF32 && out == OUT_F32) return launch<KIND_TF32, OUT_F32, false, true>(ta, tb, p, ctas, stream);
+    return FTB_E_BAD_ARG;
+  }
+  if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false, false>(ta, tb, p, ctas, stream);
+  if (kind == KIND_BF16 && out == OUT_F32) return launch<KIND_BF16, OUT_F32, false, false>(ta, tb, p, ctas, stream);
+  if (kind == KIND_I8 && out == OUT_S32) return launch<KIND_I8, OUT_S32, false, false>(ta, tb, p, ctas, stream);
+  if (kind == KIND_TF32 && out == OUT_F32 && !split3) return launch<KIND_TF32, OUT_F32, false, false>(ta, tb, p, ctas, stream);
+  if (kind == KIND_TF32 && out == OUT_F32 && split3) return launch<KIND_TF32, OUT_F32, true, false>(ta, tb, p, ctas, stream);
   return FTB_E_BAD_ARG;
 }
 
-// Fills the operand-staging fields for a plain (batched) GEMM operand.
+// Fills the operand-staging fields for a plain (batched) GEMM operand of which one CTA
+// stages `tile_extent` rows (K-major) or columns (MN-major).
 static void operand_layout(const KindInfo& ki, int mn_major, int tile_extent, int* boxes, int* box_extent,
-                           uint32_t* box_bytes, uint32_t* lbo, uint32_t* sbo, uint32_t* kadv) {
+                           uint32_t* box_bytes, uint32_t* lbo, uint32_t* sbo, uint32_t* kadv,
+                           uint32_t* layout, CUtensorMapSwizzle* swizzle) {
+  *layout = 2;
+  *swizzle = CU_TENSOR_MAP_SWIZZLE_128B;
   if (mn_major) {
     *box_extent = box_mn(ki);
     *boxes = tile_extent / *box_extent;
     *box_bytes = static_cast<uint32_t>(ki.kblk) * 128u;
-    *lbo = *box_bytes;
-    *sbo = 1024;
+    *lbo = *box_bytes;  // next 128-byte wide block along M/N
+    *sbo = 1024;        // next group of 8 K rows
     *kadv = static_cast<uint32_t>(ki.umma_k) * 128u;
+    if (ki.esize == 4) {
+      // 32-bit MN-major operands exist only in the layout that swizzles 32-byte units:
+      // the pattern repeats every 4 K rows.
+      *layout = 1;
+      *swizzle = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+      *sbo = 512;
+    }
   } else {
     *box_extent = tile_extent;
     *boxes = 1;
@@ -210,11 +279,13 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return FTB_E_UNSUPPORTED;
 
   const int num_sms = sm_count();
-  const int tiles_m = static_cast<int>((m + kTileM - 1) / kTileM);
   const int num_kb = static_cast<int>((k + ki.kblk - 1) / ki.kblk);
   ftb_config cfg;
-  rc = resolve_config(user, ki, split3, b_mn, batch * tiles_m, n, num_kb, out == OUT_F32, num_sms, &cfg);
+  rc = resolve_config(user, ki, split3, b_mn, !split3, batch, m, n, num_kb, out == OUT_F32, num_sms, &cfg);
   if (rc) return rc;
+  const bool pair = cfg.cluster == 2;
+  const int tile_m = pair ? 2 * kTileM : kTileM;
+  const int tiles_m = static_cast<int>((m + tile_m - 1) / tile_m);
 
   UmmaParams p;
   memset(&p, 0, sizeof(p));
@@ -231,13 +302,17 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   p.group_m = cfg.group_m;
   p.split_k = cfg.split_k;
   p.kblk = ki.kblk;
-  p.idesc = make_idesc(ki, p.bn, a_mn, b_mn);
+  p.idesc = make_idesc(ki, p.bn, a_mn, b_mn, tile_m);
   p.a_mn = a_mn;
   p.b_mn = b_mn;
-  p.b_bytes = static_cast<uint32_t>(p.bn) * 128u;
-  operand_layout(ki, a_mn, kTileM, &p.a_boxes, &p.a_box_mn, &p.a_box_bytes, &p.a_lbo, &p.a_sbo, &p.a_kadv);
-  operand_layout(ki, b_mn, p.bn, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv);
-  p.mma_per_kb = ki.kblk / ki.umma_k;
+  p.pair_m = tile_m;
+  p.b_rows = pair ? p.bn / 2 : p.bn;
+  p.b_bytes = static_cast<uint32_t>(p.b_rows) * 128u;
+  CUtensorMapSwizzle a_swz, b_swz;
+  operand_layout(ki, a_mn, kTileM, &p.a_boxes, &p.a_box_mn, &p.a_box_bytes, &p.a_lbo, &p.a_sbo, &p.a_kadv,
+                 &p.a_layout, &a_swz);
+  operand_layout(ki, b_mn, p.b_rows, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv,
+                 &p.b_layout, &b_swz);
   p.C = c;
   p.ldc = n;
   p.c_batch_stride = m * n;
@@ -259,7 +334,7 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
     }
     strides[0] = dims[0] * ki.esize;
     strides[1] = static_cast<uint64_t>(m) * k * ki.esize;
-    rc = make_tmap(&ta, ki.dt, 3, a, dims, strides, box, ones);
+    rc = make_tmap(&ta, ki.dt, 3, a, dims, strides, box, ones, a_swz);
     if (rc) return rc;
   }
   {
@@ -270,11 +345,11 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
       box[0] = p.b_box_mn; box[1] = ki.kblk; box[2] = 1;
     } else {
       dims[0] = k; dims[1] = n; dims[2] = batch;
-      box[0] = ki.kblk; box[1] = p.bn; box[2] = 1;
+      box[0] = ki.kblk; box[1] = p.b_rows; box[2] = 1;
     }
     strides[0] = dims[0] * ki.esize;
     strides[1] = static_cast<uint64_t>(n) * k * ki.esize;
-    rc = make_tmap(&tb, ki.dt, 3, b, dims, strides, box, ones);
+    rc = make_tmap(&tb, ki.dt, 3, b, dims, strides, box, ones, b_swz);
     if (rc) return rc;
   }
 
@@ -289,8 +364,14 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   const long long total = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n * p.split_k;
   if (total > 0x7fffffffll) return FTB_E_TOO_LARGE;
   int ctas = cfg.ctas > 0 ? cfg.ctas : num_sms;
-  if (ctas > total) ctas = static_cast<int>(total);
-  return dispatch(kind, out, split3, ta, tb, p, ctas, stream);
+  if (pair) {
+    if (ctas / 2 > total) ctas = static_cast<int>(total) * 2;
+    ctas &= ~1;
+    if (ctas < 2) ctas = 2;
+  } else if (ctas > total) {
+    ctas = static_cast<int>(total);
+  }
+  return dispatch(kind, out, split3, pair, ta, tb, p, ctas, stream);
 }
 
 // ------------------------------------------------------------------ conv2d as implicit GEMM
@@ -367,7 +448,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   if (groups > 1 && (cg % 4)) return FTB_E_UNSUPPORTED;  // group base must stay 16-byte aligned
   const ConvWs ws = conv_ws(n, c, h, w, k, r, s, groups);
   if (!workspace || workspace_bytes < static_cast<size_t>(ws.in_bytes + ws.w_bytes)) return FTB_E_WORKSPACE;
-  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FTB_E_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return FTB_E_WORKSPACE;
   float* in_nhwc = static_cast<float*>(workspace);
   float* w_packed = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ws.in_bytes);
 
@@ -387,7 +468,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   const int num_kb = static_cast<int>(r * s * ws.cchunks);
   const long long tiles_m = static_cast<long long>(n) * tiles_h * tiles_w;
   ftb_config cfg;
-  rc = resolve_config(user, ki, split3, 0, tiles_m, kg, num_kb, true, num_sms, &cfg);
+  rc = resolve_config(user, ki, split3, 0, false, tiles_m, kTileM, kg, num_kb, true, num_sms, &cfg);
   if (rc) return rc;
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
@@ -439,8 +520,12 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.a_box_mn = kTileM;
     p.a_box_bytes = static_cast<uint32_t>(tile_h * tile_w) * 128u;
     p.a_lbo = 16; p.a_sbo = 1024; p.a_kadv = static_cast<uint32_t>(ki.umma_k * ki.esize);
-    operand_layout(ki, 0, p.bn, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv);
-    p.mma_per_kb = ki.kblk / ki.umma_k;
+    CUtensorMapSwizzle b_swz;
+    operand_layout(ki, 0, p.bn, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv,
+                   &p.b_layout, &b_swz);
+    p.a_layout = 2;
+    p.pair_m = kTileM;
+    p.b_rows = p.bn;
     p.conv = 1;
     p.conv_ktot = static_cast<int>(k);
     p.conv_koff = static_cast<int>(g * kg);
@@ -480,7 +565,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     if (total > 0x7fffffffll) return FTB_E_TOO_LARGE;
     int ctas = cfg.ctas > 0 ? cfg.ctas : num_sms;
     if (ctas > total) ctas = static_cast<int>(total);
-    rc = dispatch(KIND_TF32, OUT_F32, split3, ta, tb, p, ctas, stream);
+    rc = dispatch(KIND_TF32, OUT_F32, split3, false, ta, tb, p, ctas, stream);
     if (rc) return rc;
   }
   return FTB_OK;

@@ -65,9 +65,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 #endif
 
 // Bounded wait. `abort_flag` is a shared-memory word every role polls so that one
-// role giving up makes the others leave too.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (int i = 0; i < 2048; ++i)
+// role giving up makes the others leave too.  The common case (phase already complete)
+// costs one try_wait; the polling loop is kept out of line so the hot loops stay short.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (int i = 0; i < 4096; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   while (true) {
@@ -77,6 +78,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (global_timer_ns() - t0 > FTB_WAIT_LIMIT_NS) return false;
     __nanosleep(64);
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag);
 }
 
 // ---------------------------------------------------------------- TMA (tiled loads, no cluster forms)
@@ -97,6 +102,42 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, 
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// ---------------------------------------------------------------- CTA pairs (cluster of 2)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The two forms below take a cluster-window barrier address (possibly the peer CTA's).
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// TMA load issued by one CTA of a pair: data lands in this CTA, completion bytes are
+// reported to `bar`, which may live in the peer CTA.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0,
+                                                 int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 
@@ -125,32 +166,53 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                : "memory");
 }
 
+// cta_group::2 forms: both CTAs of a pair allocate / free together; the leader CTA
+// issues the MMAs and the commits (a commit may target a barrier of either CTA).
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar_cluster_addr)
+               : "memory");
+}
+
 enum { KIND_BF16 = 0, KIND_TF32 = 1, KIND_I8 = 2 };
 
-// D[tmem] (+)= A[smem desc] * B[smem desc]; `accumulate` = 0 overwrites D.
-template <int KIND>
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                     uint32_t accumulate) {
+// D[tmem] (+)= A[smem desc] * B[smem desc]; `accumulate` = 0 overwrites D.  The 64-bit
+// shared-memory descriptors are passed as (lo, hi) halves: only `lo` (the start address)
+// changes inside a main loop, so the issuing thread does 32-bit adds only.
+// GROUP 1 = one CTA (M = 128); GROUP 2 = CTA pair (M = 256), issued by the leader CTA:
+// each CTA supplies its 128 rows of A and its half of B.
+#define FTB_UMMA_ASM(GROUP, KINDSTR)                                                              \
+  asm volatile(                                                                                   \
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"                                             \
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\tsetp.ne.b32 p, %6, 0;\n\t"               \
+      "tcgen05.mma.cta_group::" GROUP ".kind::" KINDSTR " [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem), \
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)                     \
+      : "memory")
+
+template <int KIND, bool PAIR>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                     uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
   if constexpr (KIND == KIND_BF16) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (PAIR) FTB_UMMA_ASM("2", "f16"); else FTB_UMMA_ASM("1", "f16");
   } else if constexpr (KIND == KIND_TF32) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (PAIR) FTB_UMMA_ASM("2", "tf32"); else FTB_UMMA_ASM("1", "tf32");
   } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (PAIR) FTB_UMMA_ASM("2", "i8"); else FTB_UMMA_ASM("1", "i8");
   }
 }
+#undef FTB_UMMA_ASM
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets TMEM lane
 // (quarter*32 + t), register j gets column (col0 + j).
@@ -177,15 +239,27 @@ __device__ __forceinline__ void tmem_ld_wait() {
 //                     `lbo` is not used by the hardware in this mode.
 //   MN-major operand: 128-B wide column blocks; `lbo` = bytes between successive
 //                     blocks along M/N, `sbo` = bytes between 8-row groups along K.
+//   `layout_type`  : 2 = 128-byte swizzle of 16-byte units (every case but one),
+//                     1 = 128-byte swizzle of 32-byte units, the only layout the tensor
+//                         core accepts for an MN-major 32-bit (TF32) operand.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes, uint32_t layout_type) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= static_cast<uint64_t>(1) << 46;  // descriptor version for sm_100
-  d |= static_cast<uint64_t>(2) << 61;  // 128-byte swizzle
+  d |= static_cast<uint64_t>(layout_type & 7) << 61;
   return d;
+}
+
+// High word of a descriptor (everything but the start address) and the encoding of an
+// address / byte offset for the low word.
+__device__ __forceinline__ uint32_t smem_desc_hi(uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
+  return static_cast<uint32_t>(make_smem_desc(0, lbo_bytes, sbo_bytes, layout_type) >> 32);
+}
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
 }
 
 }  // namespace ftb

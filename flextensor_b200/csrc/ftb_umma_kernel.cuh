@@ -7,9 +7,20 @@
 //   warps 2-5   epilogue         tcgen05.ld -> convert -> global stores
 //   warps 6-9   split stage      only for 3xTF32: rewrites a stage as (hi, lo) pairs
 //
-// A CTA owns 128 accumulator rows (UMMA M = 128, one row per TMEM lane) by `bn`
-// columns (UMMA N = bn), and walks the tile list with a stride of gridDim.x.  The
-// two TMEM buffers let the epilogue of tile i overlap the main loop of tile i+1.
+// A CTA owns 128 accumulator rows (one row per TMEM lane) by `bn` columns and walks
+// the tile list with a stride of the number of CTAs (or CTA pairs).  The two TMEM
+// buffers let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// PAIR = true runs two CTAs of a cluster as one tcgen05 `cta_group::2` unit on a
+// 256 x bn tile: each CTA stages its own 128 rows of A and its own half of B (so every
+// byte of B is fetched once per pair instead of once per CTA), the leader CTA issues
+// the MMAs for both, and each CTA drains its own 128 accumulator rows.  Each CTA issues
+// plain TMA loads for its own halves.
+//
+// The producer and the MMA issuer are single threads, so their loops are latency-bound
+// scalar code: everything that does not change per K block is hoisted into registers and
+// the per-block work is a handful of adds (ring counters instead of div/mod, 32-bit
+// descriptor halves instead of 64-bit arithmetic).
 #pragma once
 #include "ftb_ptx.cuh"
 #include <cuda_bf16.h>
@@ -21,6 +32,7 @@ constexpr int kTileM = 128;
 constexpr uint32_t kATileBytes = kTileM * 128;  // 128 rows x 128 B
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccStride = 256;            // columns between the two accumulators
+constexpr int kMmaPerKb = 4;                    // a stage holds 128 B of K = 4 tcgen05.mma steps
 
 enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_S32 = 2 };
 
@@ -32,13 +44,15 @@ struct UmmaParams {
   int kblk;  // K elements held by one stage (128 B / element size)
   uint32_t idesc;
   // operand staging
-  int a_mn, b_mn;          // 1 = operand is M/N-contiguous in global memory
-  int a_boxes, b_boxes;    // TMA boxes per stage
-  int a_box_mn, b_box_mn;  // M/N elements covered by one box (M/N-contiguous operands)
+  int a_mn, b_mn;               // 1 = operand is M/N-contiguous in global memory
+  uint32_t a_layout, b_layout;  // descriptor layout type (2, or 1 for MN-major TF32)
+  int pair_m;                   // rows of one tile: 128, or 256 for a CTA pair
+  int b_rows;                   // B rows (K-major) or columns (MN-major) staged per CTA
+  int a_boxes, b_boxes;         // TMA boxes per stage
+  int a_box_mn, b_box_mn;       // M/N elements covered by one box (M/N-contiguous operands)
   uint32_t a_box_bytes, b_box_bytes, b_bytes;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
   uint32_t a_kadv, b_kadv;  // bytes added to the descriptor start per UMMA-K step
-  int mma_per_kb;
   // output
   void* C;
   long long ldc, c_batch_stride;
@@ -79,10 +93,10 @@ __device__ __forceinline__ TileCoord decode_tile(const UmmaParams& p, int t) {
   return c;
 }
 
-template <int KIND, int OUT, bool SPLIT3>
+template <int KIND, int OUT, bool SPLIT3, bool PAIR>
 __global__ void __launch_bounds__(SPLIT3 ? 320 : 192, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const UmmaParams p) {
+                 const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
@@ -95,19 +109,25 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t stage_bytes = (kATileBytes + p.b_bytes) * (SPLIT3 ? 2u : 1u);
-  const uint32_t lo_off = kATileBytes + p.b_bytes;  // offset of the (Alo, Blo) pair in a stage
+  const uint32_t pair_bytes = kATileBytes + p.b_bytes;  // one (A, B) pair of a stage
+  const uint32_t stage_bytes = pair_bytes * (SPLIT3 ? 2u : 1u);
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;  // 0 = leader of a pair
+  const int unit = PAIR ? (blockIdx.x >> 1) : blockIdx.x;   // tile-walking unit (CTA or pair)
+  const int units = PAIR ? (gridDim.x >> 1) : gridDim.x;
+  const uint32_t stages = p.stages;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < p.stages; ++s) {
+    // In a pair the leader's `full` barrier counts the bytes of both CTAs' loads and its
+    // `tempty` barrier the epilogue warps of both.
+    for (uint32_t s = 0; s < stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
       mbar_init(smem_u32(&bar_split[s]), 4);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
-      mbar_init(smem_u32(&bar_tempty[a]), 4);
+      mbar_init(smem_u32(&bar_tempty[a]), PAIR ? 8 : 4);
     }
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -115,81 +135,146 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     prefetch_tmap(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(&tmem_base_slot), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // peer barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
   const int total_tiles = p.batch * p.tiles_m * p.tiles_n * p.split_k;
-  const int kb_per_split = (p.num_kb + p.split_k - 1) / p.split_k;
+  const int num_kb = p.num_kb;
+  const int kb_per_split = (num_kb + p.split_k - 1) / p.split_k;
+  const uint32_t full0 = smem_u32(&bar_full[0]);
+  const uint32_t empty0 = smem_u32(&bar_empty[0]);
+  const uint32_t split0 = smem_u32(&bar_split[0]);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
+      const int kblk = p.kblk;
+      const int a_boxes = p.a_boxes, b_boxes = p.b_boxes;
+      const int a_box_mn = p.a_box_mn, b_box_mn = p.b_box_mn;
+      const uint32_t a_box_bytes = p.a_box_bytes, b_box_bytes = p.b_box_bytes;
+      const uint32_t tx = a_boxes * a_box_bytes + b_boxes * b_box_bytes;
+      const bool a_mn = p.a_mn != 0, b_mn = p.b_mn != 0, conv = p.conv != 0;
+      // In a pair every completion is reported to the leader's barrier.
+      const uint32_t full_sig0 = PAIR ? map_to_cta(full0, 0) : full0;
+      uint32_t s = 0, ph = 0, sa = smem_base;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += units) {
         const TileCoord tc = decode_tile(p, t);
         const int kb0 = tc.ks * kb_per_split;
-        const int kb1 = min(p.num_kb, kb0 + kb_per_split);
-        int img = 0, h0 = 0, w0 = 0;
-        if (p.conv) {
+        const int kb1 = min(num_kb, kb0 + kb_per_split);
+        const int m0 = tc.m * p.pair_m + static_cast<int>(cta_rank) * kTileM;
+        const int n0 = tc.n * p.bn + static_cast<int>(cta_rank) * p.b_rows;
+        // conv: walking (r, s, channel chunk) with counters instead of div/mod per block
+        int img = 0, h0 = 0, w0 = 0, cc = 0, ts = 0, tr = 0;
+        if (conv) {
           const int tw = tc.m % p.tiles_w;
           const int th = (tc.m / p.tiles_w) % p.tiles_h;
           img = tc.m / (p.tiles_w * p.tiles_h);
           h0 = th * p.tile_h * p.stride_h - p.pad_h;
           w0 = tw * p.tile_w * p.stride_w - p.pad_w;
+          cc = kb0 % p.cchunks;
+          const int rs = kb0 / p.cchunks;
+          ts = rs % p.S;
+          tr = rs / p.S;
         }
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const uint32_t s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1u;
-          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, &abort_flag)) {
+        int kc = kb0 * kblk;  // K coordinate of the block
+        for (int kb = kb0; kb < kb1; ++kb, kc += kblk) {
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, &abort_flag)) {
             atomicOr(p.status, FTB_DEV_WAIT_EMPTY);
             abort_flag = 1;
             ok = false;
             break;
           }
-          const uint32_t full = smem_u32(&bar_full[s]);
-          const uint32_t sa = smem_base + s * stage_bytes;
           const uint32_t sb = sa + kATileBytes;
-          mbar_expect_tx(full, p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes);
-          if (p.conv) {
-            const int cc = kb % p.cchunks;
-            const int rs = kb / p.cchunks;
-            const int s_ = rs % p.S, r_ = rs / p.S;
-            tma_load_4d(sa, &tmap_a, full, cc * p.kblk, w0 + s_ * p.dil_w, h0 + r_ * p.dil_h, img);
-          } else if (p.a_mn) {
-            for (int i = 0; i < p.a_boxes; ++i)
-              tma_load_3d(sa + i * p.a_box_bytes, &tmap_a, full, tc.m * kTileM + i * p.a_box_mn,
-                          kb * p.kblk, tc.b);
+          const uint32_t full = full_sig0 + 8 * s;
+          if constexpr (PAIR) {
+            // The leader arms the phase for the two equal halves.  (Bytes of the peer may be
+            // reported before that; the phase still cannot complete until the leader's
+            // own arrival.)
+            if (cta_rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * tx);
+            if (a_mn) {
+              for (int i = 0; i < a_boxes; ++i)
+                tma_load_3d_pair(sa + i * a_box_bytes, &tmap_a, full, m0 + i * a_box_mn, kc, tc.b);
+            } else {
+              tma_load_3d_pair(sa, &tmap_a, full, kc, m0, tc.b);
+            }
+            if (b_mn) {
+              for (int i = 0; i < b_boxes; ++i)
+                tma_load_3d_pair(sb + i * b_box_bytes, &tmap_b, full, n0 + i * b_box_mn, kc, tc.b);
+            } else {
+              tma_load_3d_pair(sb, &tmap_b, full, kc, n0, tc.b);
+            }
           } else {
-            tma_load_3d(sa, &tmap_a, full, kb * p.kblk, tc.m * kTileM, tc.b);
+            mbar_expect_tx(full, tx);
+            if (conv) {
+              tma_load_4d(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
+              if (++cc == p.cchunks) {
+                cc = 0;
+                if (++ts == p.S) {
+                  ts = 0;
+                  ++tr;
+                }
+              }
+            } else if (a_mn) {
+              for (int i = 0; i < a_boxes; ++i)
+                tma_load_3d(sa + i * a_box_bytes, &tmap_a, full, m0 + i * a_box_mn, kc, tc.b);
+            } else {
+              tma_load_3d(sa, &tmap_a, full, kc, m0, tc.b);
+            }
+            if (b_mn) {
+              for (int i = 0; i < b_boxes; ++i)
+                tma_load_3d(sb + i * b_box_bytes, &tmap_b, full, n0 + i * b_box_mn, kc, tc.b);
+            } else {
+              tma_load_3d(sb, &tmap_b, full, kc, n0, tc.b);
+            }
           }
-          if (p.b_mn) {
-            for (int i = 0; i < p.b_boxes; ++i)
-              tma_load_3d(sb + i * p.b_box_bytes, &tmap_b, full, tc.n * p.bn + i * p.b_box_mn,
-                          kb * p.kblk, tc.b);
-          } else {
-            tma_load_3d(sb, &tmap_b, full, kb * p.kblk, tc.n * p.bn, tc.b);
+          sa += stage_bytes;
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+            sa = smem_base;
           }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      uint32_t it = 0;
+    // ------------------------------------------------------------ MMA issuer (leader CTA only in a pair)
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc = p.idesc;
+      const uint32_t a_hi = smem_desc_hi(p.a_lbo, p.a_sbo, p.a_layout);
+      const uint32_t b_hi = smem_desc_hi(p.b_lbo, p.b_sbo, p.b_layout);
+      const uint32_t a_lo0 = smem_desc_lo(smem_base, p.a_lbo);
+      const uint32_t b_off = kATileBytes >> 4;
+      const uint32_t b_lbo_delta = smem_desc_lo(0, p.b_lbo) - smem_desc_lo(0, p.a_lbo);
+      const uint32_t a_k = p.a_kadv >> 4, b_k = p.b_kadv >> 4;
+      const uint32_t stage_enc = stage_bytes >> 4;
+      const uint32_t lo_enc = pair_bytes >> 4;  // (A_lo, B_lo) pair of a 3xTF32 stage
+      const uint32_t ready0 = SPLIT3 ? split0 : full0;
+      // Barriers the commits arrive on; in a pair both CTAs' copies are signalled.
+      const uint32_t empty_l = PAIR ? map_to_cta(empty0, 0) : empty0;
+      const uint32_t empty_r = PAIR ? map_to_cta(empty0, 1) : 0u;
+      const uint32_t tfull_l = PAIR ? map_to_cta(smem_u32(&bar_tfull[0]), 0) : smem_u32(&bar_tfull[0]);
+      const uint32_t tfull_r = PAIR ? map_to_cta(smem_u32(&bar_tfull[0]), 1) : 0u;
+      uint32_t s = 0, ph = 0, a_lo = a_lo0;
       int local = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-        const TileCoord tc = decode_tile(p, t);
-        const int kb0 = tc.ks * kb_per_split;
-        const int kb1 = min(p.num_kb, kb0 + kb_per_split);
-        const int acc = local & 1;
+      for (int t = unit; t < total_tiles && ok; t += units, ++local) {
+        const int ks = (p.split_k > 1) ? (t % p.split_k) : 0;
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(num_kb, kb0 + kb_per_split);
+        const uint32_t acc = local & 1;
         const uint32_t aph = (local >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, &abort_flag)) {
           atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
@@ -199,48 +284,64 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
         uint32_t accumulate = 0;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const uint32_t s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1u;
-          const uint32_t ready = SPLIT3 ? smem_u32(&bar_split[s]) : smem_u32(&bar_full[s]);
-          if (!mbar_wait(ready, ph, &abort_flag)) {
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(ready0 + 8 * s, ph, &abort_flag)) {
             atomicOr(p.status, SPLIT3 ? FTB_DEV_WAIT_XFORM : FTB_DEV_WAIT_FULL);
             abort_flag = 1;
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_base + s * stage_bytes;
-          const uint32_t sb = sa + kATileBytes;
-          const uint64_t da = make_smem_desc(sa, p.a_lbo, p.a_sbo);
-          const uint64_t db = make_smem_desc(sb, p.b_lbo, p.b_sbo);
-          for (int k = 0; k < p.mma_per_kb; ++k) {
-            const uint64_t ak = da + ((static_cast<uint64_t>(k) * p.a_kadv) >> 4);
-            const uint64_t bk = db + ((static_cast<uint64_t>(k) * p.b_kadv) >> 4);
-            umma<KIND>(d_tmem, ak, bk, p.idesc, accumulate);
+          const uint32_t b_lo = a_lo + b_off + b_lbo_delta;
+#pragma unroll
+          for (int k = 0; k < kMmaPerKb; ++k) {
+            const uint32_t ak = a_lo + k * a_k;
+            const uint32_t bk = b_lo + k * b_k;
+            umma<KIND, PAIR>(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
             accumulate = 1;
             if constexpr (SPLIT3) {
-              const uint64_t lo = lo_off >> 4;
-              umma<KIND>(d_tmem, ak + lo, bk, p.idesc, 1);  // A_lo * B_hi
-              umma<KIND>(d_tmem, ak, bk + lo, p.idesc, 1);  // A_hi * B_lo
+              umma<KIND, PAIR>(d_tmem, ak + lo_enc, a_hi, bk, b_hi, idesc, 1);  // A_lo * B_hi
+              umma<KIND, PAIR>(d_tmem, ak, a_hi, bk + lo_enc, b_hi, idesc, 1);  // A_hi * B_lo
             }
           }
-          tc_commit(smem_u32(&bar_empty[s]));  // frees the stage once these MMAs have read it
+          // Free the stage (in both CTAs of a pair) once these MMAs have read it.
+          if constexpr (PAIR) {
+            tc_commit_pair(empty_l + 8 * s);
+            tc_commit_pair(empty_r + 8 * s);
+          } else {
+            tc_commit(empty_l + 8 * s);
+          }
+          a_lo += stage_enc;
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+            a_lo = a_lo0;
+          }
         }
-        if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
+        if (ok) {
+          if constexpr (PAIR) {
+            tc_commit_pair(tfull_l + 8 * acc);
+            tc_commit_pair(tfull_r + 8 * acc);
+          } else {
+            tc_commit(tfull_l + 8 * acc);
+          }
+        }
       }
     }
     __syncwarp();
   } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int row = quarter * 32 + lane;  // accumulator row owned by this thread
+    const int bn = p.bn, N = p.N;
+    const uint32_t tempty_sig0 =
+        PAIR ? map_to_cta(smem_u32(&bar_tempty[0]), 0) : smem_u32(&bar_tempty[0]);
     int local = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+    for (int t = unit; t < total_tiles; t += units, ++local) {
       const TileCoord tc = decode_tile(p, t);
-      const int acc = local & 1;
+      const uint32_t acc = local & 1;
       const uint32_t aph = (local >> 1) & 1u;
-      const int kb0 = tc.ks * kb_per_split;
-      const bool has_work = kb0 < p.num_kb;  // a split beyond the K range contributes nothing
+      const bool has_work = tc.ks * kb_per_split < num_kb;  // a split past the K range adds nothing
       const bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull[acc]), aph, &abort_flag));
       if (!got) {
         if (lane == 0) {
@@ -250,9 +351,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         break;
       }
       tc_fence_after();
-      const int row = quarter * 32 + lane;  // accumulator row owned by this thread
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kAccStride;
-      const int n0 = tc.n * p.bn;
+      const int n0 = tc.n * bn;
 
       // Where this thread's row goes in the output.
       bool row_ok;
@@ -269,31 +369,34 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         row_off = (static_cast<long long>(img) * p.conv_ktot + p.conv_koff) * col_stride +
                   static_cast<long long>(oh) * p.Q + ow;
       } else {
-        const int gm = tc.m * kTileM + row;
+        const int gm = tc.m * p.pair_m + static_cast<int>(cta_rank) * kTileM + row;
         row_ok = gm < p.M;
         row_off = tc.b * p.c_batch_stride + static_cast<long long>(gm) * p.ldc;
       }
       row_ok = row_ok && has_work;
 
-      for (int c = 0; c < p.bn; c += 32) {
+      for (int c = 0; c < bn; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(taddr + c, v);
         tmem_ld_wait();
-        if (c + 32 >= p.bn) {
+        if (c + 32 >= bn) {
           // Last read of this accumulator: hand it back before the stores go out.
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_cluster(tempty_sig0 + 8 * acc);
+            else mbar_arrive(tempty_sig0 + 8 * acc);
+          }
         }
         if (!row_ok) continue;
         const int nbase = n0 + c;
-        if (nbase >= p.N) continue;
+        if (nbase >= N) continue;
         if (p.conv) {
           float* out = reinterpret_cast<float*>(p.C);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int n = nbase + j;
-            if (n < p.N) {
+            if (n < N) {
               float x = __uint_as_float(v[j]);
               if (p.bias != nullptr && tc.ks == 0) x += p.bias[p.conv_koff + n];
               float* dst = out + row_off + n * col_stride;
@@ -303,7 +406,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         } else if constexpr (OUT == OUT_BF16) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row_off + nbase;
-          const bool vec = (nbase + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+          const bool vec = (nbase + 32 <= N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
           if (vec) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -319,7 +422,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (nbase + j < p.N) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
+              if (nbase + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(v[j]));
           }
         } else {
           // fp32 and int32 results leave TMEM as raw 32-bit words.
@@ -327,9 +430,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (OUT == OUT_F32 && p.split_k > 1) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (nbase + j < p.N) atomicAdd(reinterpret_cast<float*>(dst) + j, __uint_as_float(v[j]));
+              if (nbase + j < N) atomicAdd(reinterpret_cast<float*>(dst) + j, __uint_as_float(v[j]));
           } else {
-            const bool vec = (nbase + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+            const bool vec = (nbase + 32 <= N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
             if (vec) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
@@ -337,7 +440,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (nbase + j < p.N) dst[j] = v[j];
+                if (nbase + j < N) dst[j] = v[j];
             }
           }
         }
@@ -348,17 +451,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ------------------------------------------------------------ 3xTF32 split stage
     if constexpr (SPLIT3) {
       const int tid = threadIdx.x - 192;  // 0..127
-      uint32_t it = 0;
+      uint32_t s = 0, ph = 0;
       bool ok = true;
-      const uint32_t pair_bytes = kATileBytes + p.b_bytes;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileCoord tc = decode_tile(p, t);
-        const int kb0 = tc.ks * kb_per_split;
-        const int kb1 = min(p.num_kb, kb0 + kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const uint32_t s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1u;
-          const bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_full[s]), ph, &abort_flag));
+      uint8_t* const stage0 = smem_raw + (smem_base - smem_u32(smem_raw));
+      for (int t = unit; t < total_tiles && ok; t += units) {
+        const int ks = (p.split_k > 1) ? (t % p.split_k) : 0;
+        const int kb0 = ks * kb_per_split;
+        const int kb1 = min(num_kb, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          const bool got = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, ph, &abort_flag));
           if (!got) {
             if (lane == 0) {
               atomicOr(p.status, FTB_DEV_WAIT_FULL);
@@ -369,7 +470,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           // x = hi + lo with hi exactly representable in TF32 (low 13 mantissa bits
           // cleared); the elementwise rewrite keeps every value at its swizzled place.
-          uint8_t* base = smem_raw + (smem_base - smem_u32(smem_raw)) + s * stage_bytes;
+          uint8_t* base = stage0 + s * stage_bytes;
           for (uint32_t off = tid * 16; off < pair_bytes; off += 128 * 16) {
             float4 x = *reinterpret_cast<float4*>(base + off);
             float4 hi, lo;
@@ -382,11 +483,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             lo.z = x.z - hi.z;
             lo.w = x.w - hi.w;
             *reinterpret_cast<float4*>(base + off) = hi;
-            *reinterpret_cast<float4*>(base + lo_off + off) = lo;
+            *reinterpret_cast<float4*>(base + pair_bytes + off) = lo;
           }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core reads
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bar_split[s]));
+          if (lane == 0) mbar_arrive(split0 + 8 * s);
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+          }
         }
       }
       __syncwarp();
@@ -401,9 +506,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's shared memory and TMEM stay alive until both are done
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 

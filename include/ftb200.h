@@ -53,7 +53,8 @@ typedef struct ftb_config {
   int32_t ctas;      /* persistent CTAs (default: one per SM)                             */
   int32_t tile_h;    /* conv2d: output rows per tile; depthwise: output rows per strip    */
   int32_t threads;   /* depthwise: threads per CTA                                        */
-  int32_t reserved[7];
+  int32_t cluster;   /* 1 = one CTA per 128-row tile, 2 = CTA pair on a 256-row tile       */
+  int32_t reserved[6];
 } ftb_config;
 
 int ftb_version(void);
