@@ -1,0 +1,419 @@
+"""Benchmark of the hot path: batched GEMM bf16 (fp32 accumulate) B=64, M=N=K=2048, the
+batch sharded over the ranks, the output returned to every rank by one NCCL all-gather.
+
+  python bench.py --gpus 1 --steps 20 --warmup 5
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+  python bench.py --impl reference ...     CPU arm: the llvm-template loop nest on the host cores
+
+One JSON line on rank 0.  A step is one pass over the whole batch: every rank runs the
+tcgen05 kernel on its 64/N items (and, for N > 1, all-gathers the output).  `value` is
+whole-job TFLOP/s with the operands resident in HBM; `e2e` is the same step through
+Task -> schedule_with_config -> build -> func(*arrays) with pinned host buffers, the
+host->device copy of the operands and the device->host read of the result inside the timed
+region.  Inputs (1 GiB) are larger than L2, so consecutive steps do not find them cached.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BATCH, DIM = 64, 2048
+FLOP_PER_ITEM = 2.0 * DIM ** 3
+METRIC = "TFLOP/s batched GEMM bf16 (fp32 accumulate) B=64 M=N=K=2048"
+WORKLOAD = "batched GEMM bf16 B=64 M=N=K=2048, fp32 accumulate, normal(0,0.02) inputs, bf16 output"
+FALLBACK_BF16_TFLOPS = 1590.0
+# DRAM bytes of one full-batch launch of the dominant kernel (dram__bytes_read.sum +
+# dram__bytes_write.sum from profiles/umma_gemm_bf16_pair.md, scaled from the captured
+# 6-item launch to 64 items by the items processed); None until such a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+KNOBS = {"cluster": 2, "tile_n": 256, "raster": 2, "group_m": 4}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            peaks = json.load(f)
+        return float(peaks["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except Exception:
+        return FALLBACK_BF16_TFLOPS, "fallback"
+
+
+class ClockSampler(object):
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        clocks, reasons, mx = [], set(), None
+        for s in self.samples:
+            try:
+                clocks.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ---------------------------------------------------------------------- CPU arm / CPU baseline
+def cpu_items(count, seed=3):
+    import numpy as np
+    from oracle import ft_oracle as O
+    a = np.empty((count, DIM, DIM), dtype=np.uint16)
+    b = np.empty((count, DIM, DIM), dtype=np.uint16)
+    for i in range(count):
+        ai, bi = O.batch_gemm_item(i, DIM, DIM, DIM, seed=seed)
+        a[i] = O.to_bf16_bits(ai)
+        b[i] = O.to_bf16_bits(bi)
+    return a, b
+
+
+def cpu_step_time(a, b, out, tiles):
+    from oracle import c_oracle as CO
+    t0 = time.perf_counter()
+    CO.bgemm_bf16_tiled(a, b, *tiles, out=out)
+    return time.perf_counter() - t0
+
+
+def pick_cpu_tiles(a, b, out):
+    """Small sweep over tile factors of the loop nest, as a short search over split factors
+    would do; returns the fastest (ti, tj, tk)."""
+    best, best_t = None, float("inf")
+    for tiles in ((8, 64, 64), (4, 64, 256), (8, 64, 256), (16, 64, 64)):
+        t = cpu_step_time(a[:1], b[:1], out[:1], tiles)
+        if t < best_t:
+            best, best_t = tiles, t
+    return best
+
+
+def run_reference(args, rank):
+    """`--impl reference`: the reference has no runnable CPU path here (it needs an un-vendored
+    TVM fork), so the arm times the C restatement of the loop nest its llvm template emits, with
+    all host threads, one batch item (2048^3) per step - a bounded sample of the workload."""
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import c_oracle as CO
+    cores = CO.max_threads()
+    a, b = cpu_items(1)
+    out = np.empty((1, DIM, DIM), dtype=np.uint16)
+    tiles = pick_cpu_tiles(a, b, out)
+    for _ in range(args.warmup):
+        cpu_step_time(a, b, out, tiles)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step_time(a, b, out, tiles)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = FLOP_PER_ITEM / dt / 1e12
+    sample = "1 of 64 batch items (2048^3) per step, tile factors %s" % (tiles,)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_leg(budget_s=12.0):
+    import numpy as np
+    from oracle import c_oracle as CO
+    a, b = cpu_items(1)
+    out = np.empty((1, DIM, DIM), dtype=np.uint16)
+    tiles = pick_cpu_tiles(a, b, out)
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 8 and (time.perf_counter() - t_start < budget_s or not times):
+        times.append(cpu_step_time(a, b, out, tiles))
+    dt = sorted(times)[len(times) // 2]
+    return {"value": FLOP_PER_ITEM / dt / 1e12, "unit": "TFLOP/s", "cores": CO.max_threads(), "kind": "port",
+            "sample": "1 of 64 batch items (2048^3), median of %d runs, tile factors %s, scaled linearly" %
+                      (len(times), tiles)}
+
+
+# ---------------------------------------------------------------------- other operators (N = 1 only)
+def per_op_lines(peak_bf16, hbm_gbs):
+    """Kernel-only device time of the other four configurations, CUDA-graph replay of 20
+    back-to-back launches (these are microsecond-sized: a single launch is latency-bound)."""
+    import numpy as np
+    import torch
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config
+    from flextensor_b200.utils import Config
+    from oracle import ft_oracle as O
+    out = {}
+
+    def dev(x):
+        return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+    def timed(key, arrays, nops, precision=None, cfgs=None):
+        s, bufs = schedule_with_config(key, cfgs or Config([{}] * nops, None), precision=precision)
+        func = build(s, bufs)
+        res = func.time_evaluator(func.entry_name, None, number=20, repeat=5)(*arrays)
+        return res.median
+
+    a, b = O.gemm_inputs(1024, 1024, 1024, seed=0)
+    arrays = [dev(a), dev(b), torch.empty(1024, 1024, device="cuda")]
+    for mode in ("3xtf32", "tf32"):
+        t = timed("gemm_gemm_(1024, 1024, 1024)_cuda(0)", arrays, 1, precision=mode)
+        out["gemm_f32_1024_" + mode] = {"us": t * 1e6, "tflops": 2 * 1024 ** 3 / t / 1e12}
+    x, w = O.conv2d_inputs(1, 64, 56, 56, 64, 3, 3, seed=1)
+    arrays = [dev(x), dev(w), torch.empty(1, 64, 56, 56, device="cuda")]
+    t = timed("conv2d_res_b13_(1, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)", arrays, 2)
+    out["conv2d_c64_56_k64_tf32"] = {"us": t * 1e6, "tflops": 231211008 / t / 1e12}
+    x, w = O.depthwise_inputs(1, 256, 56, 56, 1, 3, 3, seed=2)
+    arrays = [dev(x), dev(w), torch.empty(1, 256, 56, 56, device="cuda")]
+    t = timed("conv2d_depthwise_(1, 256, 56, 56, 1, 3, 1, 1, 1)_cuda(0)", arrays, 2)
+    out["depthwise_c256_56"] = {"us": t * 1e6, "gbs": 6431744 / t / 1e9, "frac_of_hbm_peak": 6431744 / t / 1e9 / hbm_gbs,
+                                "note": "L2-warm graph replay; 6.4 MB working set"}
+    a8 = torch.randint(-127, 128, (8192, 8192), device="cuda", dtype=torch.int8)
+    b8 = torch.randint(-127, 128, (8192, 8192), device="cuda", dtype=torch.int8)
+    arrays = [a8, b8, torch.empty(8192, 8192, device="cuda", dtype=torch.int32)]
+    t = timed("gemm_gemm_int8_(8192, 8192, 8192)_cuda(0)", arrays, 1)
+    out["gemm_int8_8192"] = {"us": t * 1e6, "tops": 2 * 8192 ** 3 / t / 1e12,
+                             "frac_of_2x_bf16_measured": 2 * 8192 ** 3 / t / 1e12 / (2 * peak_bf16)}
+    return out
+
+
+# ---------------------------------------------------------------------- GPU arm
+def run_ours(args, rank, world, local_rank):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from flextensor_b200 import backend
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config
+    from flextensor_b200.sharded import BatchSharded, shard_range
+    from flextensor_b200.task import Task, batch_gemm, register_task
+    from flextensor_b200.templates import knobs_to_config
+    from flextensor_b200.utils import Config
+    from oracle import ft_oracle as O
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    assert BATCH % world == 0, "the batch of 64 shards over 1, 2, 4 or 8 ranks"
+    lo, hi = shard_range(BATCH, world, rank)
+    local = hi - lo
+
+    # The reference-facing path: a Task for this rank's shard, planned and built once.
+    task = Task("gemm", "batch_gemm", batch_gemm, (local, DIM, DIM, DIM), "cuda", local_rank)
+    register_task(task)
+    op = task.func(*task.args)[0][0]
+    s, bufs = schedule_with_config(task.key, Config([knobs_to_config(KNOBS, op)], None))
+    func = build(s, bufs, "cuda")
+
+    # Synthetic operands: normal(0, 0.02) rounded to bf16; the first item of the shard is the
+    # oracle's item (checked below), the rest are drawn on the device with a per-item seed.
+    a = torch.empty(local, DIM, DIM, device=device, dtype=torch.bfloat16)
+    b = torch.empty(local, DIM, DIM, device=device, dtype=torch.bfloat16)
+    gen = torch.Generator(device=device)
+    for i in range(local):
+        gen.manual_seed(3 * 1_000_003 + lo + i)
+        a[i] = (torch.randn(DIM, DIM, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+        b[i] = (torch.randn(DIM, DIM, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+    a0, b0 = O.batch_gemm_item(lo, DIM, DIM, DIM, seed=3)
+    a[0] = torch.from_numpy(a0).to(device).to(torch.bfloat16)
+    b[0] = torch.from_numpy(b0).to(device).to(torch.bfloat16)
+    c_local = torch.empty(local, DIM, DIM, device=device, dtype=torch.bfloat16)
+    c_full = torch.empty(BATCH, DIM, DIM, device=device, dtype=torch.bfloat16) if world > 1 else c_local
+    sharder = BatchSharded(BATCH) if world > 1 else None
+
+    def compute(lo_, hi_):
+        assert (lo_, hi_) == (0, local)
+        func(a, b, c_local)
+
+    def step():
+        if sharder is None:
+            func(a, b, c_local)
+        else:
+            sharder.run(compute, c_local, c_full, chunks=1)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # parity of what is being timed
+    step()
+    func.check()
+    got = c_local[0].float().cpu().numpy()
+    assert O.bf16_output_ok(got, O.gemm(a0, b0, out_dtype=np.float64)), "bench output does not match the oracle"
+    if world > 1:
+        assert torch.equal(c_full[lo:hi], c_local)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    stream = torch.cuda.current_stream()
+    launches0 = backend.launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    kern_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    ev[0].record(stream)
+    for i in range(args.steps):
+        kern_ev[i][0].record(stream)
+        func(a, b, c_local)
+        kern_ev[i][1].record(stream)
+        if sharder is not None:
+            sharder.gather(c_local, c_full)
+    ev[1].record(stream)
+    barrier()
+    launches = backend.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    func.check()
+    total_ms = ev[0].elapsed_time(ev[1])
+    kernel_ms = sum(s0.elapsed_time(s1) for s0, s1 in kern_ev) / args.steps
+    t = torch.tensor([total_ms, kernel_ms, float(launches)], device=device, dtype=torch.float64)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        total_ms, kernel_ms, launches = float(tmax[0]), float(tmax[1]), int(tsum[2])
+    ms_per_step = total_ms / args.steps
+    value = BATCH * FLOP_PER_ITEM / (ms_per_step * 1e-3) / 1e12
+    compute_only = BATCH * FLOP_PER_ITEM / (kernel_ms * 1e-3) / 1e12
+
+    # ---- end to end: pinned host operands -> device -> kernel -> (gather) -> host
+    ha = torch.empty(local, DIM, DIM, dtype=torch.bfloat16).pin_memory()
+    hb = torch.empty(local, DIM, DIM, dtype=torch.bfloat16).pin_memory()
+    hc = torch.empty(local, DIM, DIM, dtype=torch.bfloat16).pin_memory()
+    ha.copy_(a)
+    hb.copy_(b)
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        a.copy_(ha, non_blocking=True)
+        b.copy_(hb, non_blocking=True)
+        step()
+        hc.copy_(c_local, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t[0])
+    assert torch.equal(hc[0], c_local[0].cpu())
+    e2e_value = BATCH * FLOP_PER_ITEM / (e2e_ms * 1e-3) / 1e12
+    elem = 2
+    h2d = 2 * BATCH * DIM * DIM * elem
+    d2h = BATCH * DIM * DIM * elem
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        hbm = 6536.0
+        try:
+            hbm = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+        except Exception:
+            pass
+        # the dominant kernel processes 64/N items per launch on each rank
+        achieved = local * FLOP_PER_ITEM / (kernel_ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sharding": "batch 64/%d items per GPU" % world,
+                       "collective": "none" if world == 1 else "NCCL all-gather of the bf16 output (512 MiB total)",
+                       "l2": "inputs (1 GiB) larger than L2; no flush needed", "knobs": KNOBS,
+                       "kernel": "umma_gemm_kernel<bf16, bf16 out, cta_group::2>"},
+            "compute_only_value": compute_only,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_2250": achieved / 2250.0,
+                         "kernel_ms": kernel_ms, "flop_per_launch": local * FLOP_PER_ITEM,
+                         "traffic": (NCU_TRAFFIC_BYTES_PER_LAUNCH * local / BATCH) if NCU_TRAFFIC_BYTES_PER_LAUNCH else None},
+            "clocks": clocks,
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline_leg()
+            if not args.no_extra:
+                line["per_op"] = per_op_lines(peak, hbm)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the per-operator lines of the other four configs")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus))
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -100,6 +100,8 @@ def lib():
         handle.ftb_validate.argtypes = [i32, cfgp, i64, i64, i64]
         handle.ftb_gemm_f32.restype = i32
         handle.ftb_gemm_f32.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, cfgp, vp, vp]
+        handle.ftb_bgemm_f32.restype = i32
+        handle.ftb_bgemm_f32.argtypes = [vp, vp, vp, i64, i64, i64, i64, i32, i32, cfgp, vp, vp]
         handle.ftb_bgemm_bf16.restype = i32
         handle.ftb_bgemm_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i32, i32, i32, cfgp, vp, vp]
         handle.ftb_gemm_s8.restype = i32
@@ -117,7 +119,7 @@ def lib():
 
 EXPORTED_SYMBOLS = (
     "ftb_version", "ftb_strerror", "ftb_last_cuda_error", "ftb_device_check", "ftb_validate",
-    "ftb_launch_count", "ftb_gemm_f32", "ftb_bgemm_bf16", "ftb_gemm_s8",
+    "ftb_launch_count", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_gemm_s8",
     "ftb_conv2d_workspace_bytes", "ftb_conv2d_nchw_f32", "ftb_dwconv2d_nchw_f32",
 )
 
@@ -187,6 +189,22 @@ def gemm_f32(a, b, c, trans_a=False, trans_b=False, cfg=None, status=None, strea
                                 _cfg_ptr(cfg), _status_ptr(status), _stream_ptr(stream))
     if rc:
         raise FtbError(rc, "ftb_gemm_f32")
+
+
+def bgemm_f32(a, b, c, trans_a=False, trans_b=False, cfg=None, status=None, stream=None):
+    """c[B,M,N] = op(a[b]) @ op(b[b]) in fp32 on TF32 tensor cores (3xTF32 when cfg.fp32_mode == 1)."""
+    for t, nm in ((a, "a"), (b, "b"), (c, "c")):
+        _check(t, torch.float32, nm)
+    batch, m, n = c.shape
+    k = a.shape[1] if trans_a else a.shape[2]
+    if (tuple(a.shape) != ((batch, k, m) if trans_a else (batch, m, k)) or
+            tuple(b.shape) != ((batch, n, k) if trans_b else (batch, k, n))):
+        raise ValueError("bgemm_f32: shapes do not agree: %s %s -> %s" % (a.shape, b.shape, c.shape))
+    with torch.cuda.device(c.device):
+        rc = lib().ftb_bgemm_f32(a.data_ptr(), b.data_ptr(), c.data_ptr(), batch, m, n, k, int(trans_a),
+                                 int(trans_b), _cfg_ptr(cfg), _status_ptr(status), _stream_ptr(stream))
+    if rc:
+        raise FtbError(rc, "ftb_bgemm_f32")
 
 
 def bgemm_bf16(a, b, c, trans_a=False, trans_b=False, cfg=None, status=None, stream=None):

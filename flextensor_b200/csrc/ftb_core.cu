@@ -106,11 +106,15 @@ int ftb_validate(int op, const ftb_config* cfg, int64_t m, int64_t n, int64_t k)
   const int esize = op == 1 ? 2 : (op == 2 ? 1 : 4);
   const bool split3 = (op == 0 || op == 3) && cfg->fp32_mode == 1;
   if (cfg->fp32_mode < 0 || cfg->fp32_mode > 1) return FTB_E_BAD_CONFIG;
-  if (cfg->tile_n != 0 && (cfg->tile_n < 32 || cfg->tile_n > 256 || cfg->tile_n % 32)) return FTB_E_BAD_CONFIG;
+  if (cfg->tile_n != 0 && cfg->tile_n != 32 && cfg->tile_n != 64 && cfg->tile_n != 128 && cfg->tile_n != 256)
+    return FTB_E_BAD_CONFIG;
   if (cfg->stages != 0 && (cfg->stages < 2 || cfg->stages > 8)) return FTB_E_BAD_CONFIG;
+  if (cfg->cluster < 0 || cfg->cluster > 2) return FTB_E_BAD_CONFIG;
+  if (cfg->cluster == 2 && (op == 3 || split3)) return FTB_E_BAD_CONFIG;
+  if (cfg->cluster == 2 && cfg->tile_n != 0 && cfg->tile_n < 64) return FTB_E_BAD_CONFIG;
   if (cfg->tile_n != 0 && cfg->stages != 0) {
-    const size_t smem = static_cast<size_t>(cfg->stages) * (16384 + static_cast<size_t>(cfg->tile_n) * 128) *
-                            (split3 ? 2 : 1) + 1024;
+    const size_t per_cta = static_cast<size_t>(cfg->tile_n) / (cfg->cluster == 2 ? 2 : 1);
+    const size_t smem = static_cast<size_t>(cfg->stages) * (16384 + per_cta * 128) * (split3 ? 2 : 1) + 1024;
     if (smem > 227 * 1024 - 2048) return FTB_E_BAD_CONFIG;
   }
   if (cfg->raster < 0 || cfg->raster > 2 || cfg->group_m < 0) return FTB_E_BAD_CONFIG;

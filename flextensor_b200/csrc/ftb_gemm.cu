@@ -582,6 +582,12 @@ int ftb_gemm_f32(const float* a, const float* b, float* c, int64_t m, int64_t n,
                            status, stream);
 }
 
+int ftb_bgemm_f32(const float* a, const float* b, float* c, int64_t batch, int64_t m, int64_t n, int64_t k,
+                  int trans_a, int trans_b, const ftb_config* cfg, int* status, void* stream) {
+  return ftb::gemm_generic(ftb::KIND_TF32, ftb::OUT_F32, a, b, c, batch, m, n, k, trans_a, trans_b, cfg,
+                           status, stream);
+}
+
 int ftb_bgemm_bf16(const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n, int64_t k,
                    int trans_a, int trans_b, int out_f32, const ftb_config* cfg, int* status,
                    void* stream) {

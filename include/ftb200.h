@@ -44,7 +44,7 @@ enum ftb_error {
 /* Knobs of the kernels: the config space the scheduler searches
  * (replaces the split/fuse/reorder/unroll factors of flextensor/templates/cuda.py:390-661). */
 typedef struct ftb_config {
-  int32_t tile_n;    /* accumulator columns per CTA tile: 32..256 step 32 (M tile is 128) */
+  int32_t tile_n;    /* accumulator columns per tile: 32, 64, 128 or 256                  */
   int32_t stages;    /* shared-memory pipeline depth, 2..8                                */
   int32_t raster;    /* tile order: 0 n-fastest, 1 m-fastest, 2 grouped-M                 */
   int32_t group_m;   /* group height for raster 2                                         */
@@ -74,6 +74,11 @@ int64_t ftb_launch_count(void);
  * trans_a = 0: A is [M,K] row-major, 1: A is [K,M]; trans_b = 0: B is [K,N], 1: B is [N,K]. */
 int ftb_gemm_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                  int trans_a, int trans_b, const ftb_config* cfg, int* status, void* stream);
+
+/* C[b,M,N] = op(A[b]) . op(B[b]) in fp32 (flextensor/nn/ops.py:1111-1158 batch_gemm as the
+ * reference defines it: fp32 placeholders). */
+int ftb_bgemm_f32(const float* a, const float* b, float* c, int64_t batch, int64_t m, int64_t n, int64_t k,
+                  int trans_a, int trans_b, const ftb_config* cfg, int* status, void* stream);
 
 /* C[b,M,N] = op(A[b]) . op(B[b]); bf16 inputs, fp32 accumulate, output bf16 (out_f32 = 0) or
  * fp32 (out_f32 = 1) (flextensor/nn/ops.py:1111-1158 batch_gemm, extended to bf16). */

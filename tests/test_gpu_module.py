@@ -1,0 +1,124 @@
+"""The reference-facing path on a GPU: Task -> schedule_with_config / schedule -> build ->
+callable, the timing interface, and the measurer (host-side failure handling included)."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ft_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def test_readme_flow_gemm(native_lib):
+    """README.md:131-158 with this backend: key -> schedule_with_config -> build -> func(*arrays)."""
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config
+    from flextensor_b200.task import Task
+    from flextensor_b200.utils import Config
+    key = Task("gemm", "gemm", None, (1024, 1024, 1024), "cuda", 0).key
+    s, bufs = schedule_with_config(key, Config([{}], None))
+    func = build(s, bufs, "cuda")
+    a, b = O.gemm_inputs(1024, 1024, 1024, seed=0)
+    c = torch.zeros(1024, 1024, device="cuda")
+    func(dev(a), dev(b), c)
+    func.check()
+    assert O.normalised_error(c.cpu().numpy(), O.gemm(a, b)) <= O.TOLERANCE["gemm_f32_3xtf32"]
+    res = func.time_evaluator(func.entry_name, None, number=5)(dev(a), dev(b), c)
+    assert 0 < res.mean < 1e-2
+    assert json.loads(func.imported_modules[0].get_source())["steps"][0]["op"] == "gemm"
+    with pytest.raises(ValueError):
+        func(dev(a), dev(b))
+    with pytest.raises(TypeError):
+        func(dev(a), dev(b), c.double())
+
+
+def test_module_conv_depthwise_int8_bf16(native_lib):
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config, schedule_with_config_ops
+    from flextensor_b200.ir import placeholder
+    from flextensor_b200.nn import ops
+    from flextensor_b200.utils import Config
+    key = "conv2d_res_b13_(1, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)"
+    s, bufs = schedule_with_config(key, Config([{}, {}], {"inline": [[1, 0]]}))
+    x, w = O.conv2d_inputs(1, 64, 56, 56, 64, 3, 3, seed=1)
+    out = torch.zeros(1, 64, 56, 56, device="cuda")
+    func = build(s, bufs)
+    func(dev(x), dev(w), out)
+    func.check()
+    assert O.normalised_error(out.cpu().numpy(), O.conv2d_nchw(x, w, None, 1, 1, 1)) <= O.TOLERANCE["conv2d_tf32"]
+    # conv with bias: three stages in the graph, one kernel
+    xi, wi, bi = placeholder((2, 8, 10, 10)), placeholder((12, 8, 3, 3)), placeholder((12,))
+    yo = ops.conv2d_nchw(xi, wi, bi, stride=1, padding=1)
+    plan, bufs = schedule_with_config_ops([yo.op], [xi, wi, bi, yo], Config([], None), precision="3xtf32")
+    x, w = O.conv2d_inputs(2, 8, 10, 10, 12, 3, 3, seed=7)
+    b = np.linspace(-1, 1, 12).astype(np.float32)
+    out = torch.zeros(2, 12, 10, 10, device="cuda")
+    plan.build()(dev(x), dev(w), dev(b), out)
+    assert O.normalised_error(out.cpu().numpy(), O.conv2d_nchw(x, w, b, 1, 1, 1)) <= O.TOLERANCE["conv2d_3xtf32"]
+    # depthwise
+    key = "conv2d_depthwise_(1, 256, 56, 56, 1, 3, 1, 1, 1)_cuda(0)"
+    s, bufs = schedule_with_config(key, Config([{}, {}], None))
+    x, w = O.depthwise_inputs(1, 256, 56, 56, 1, 3, 3, seed=2)
+    out = torch.zeros(1, 256, 56, 56, device="cuda")
+    build(s, bufs)(dev(x), dev(w), out)
+    assert O.normalised_error(out.cpu().numpy(), O.depthwise_conv2d_nchw(x, w, None, 1, 1, 1)) <= 1e-5
+    # int8
+    key = "gemm_gemm_int8_(256, 512, 384)_cuda(0)"
+    s, bufs = schedule_with_config(key, Config([{}], None))
+    a, b = O.gemm_int8_inputs(256, 384, 512, seed=4)
+    c = torch.zeros(256, 384, device="cuda", dtype=torch.int32)
+    build(s, bufs)(dev(a), dev(b), c)
+    assert (c.cpu().numpy() == O.gemm_int8(a, b)).all()
+    # bf16 batched
+    key = "gemm_batch_gemm_(4, 256, 512, 384)_cuda(0)"
+    s, bufs = schedule_with_config(key, Config([{}], None))
+    items = [O.batch_gemm_item(i, 256, 384, 512) for i in range(4)]
+    a = np.stack([i[0] for i in items])
+    b = np.stack([i[1] for i in items])
+    c = torch.zeros(4, 256, 384, device="cuda", dtype=torch.bfloat16)
+    build(s, bufs)(dev(a).bfloat16(), dev(b).bfloat16(), c)
+    assert O.bf16_output_ok(c.float().cpu().numpy(), O.batch_gemm(a, b))
+
+
+def test_search_on_device_in_process(native_lib):
+    """A short real search: candidates are measured on the GPU (no compile per candidate)."""
+    from flextensor_b200 import scheduler as S
+    from flextensor_b200.measure import InProcessMeasurer
+    from flextensor_b200.runtime import build
+    S.VERBOSE = False
+    np.random.seed(0)
+    torch.manual_seed(0)
+    measurer = InProcessMeasurer(0)
+    key = "gemm_batch_gemm_(8, 1024, 1024, 1024)_cuda(0)"
+    plan, bufs, configs = S.schedule(key, op_trial=3, op_stop=2, timeout=10, parallel=1, number=3, measurer=measurer)
+    assert plan.steps[0].knobs["tile_n"] in (64, 128, 256)
+    items = [O.batch_gemm_item(i, 1024, 1024, 1024) for i in range(2)]
+    a = torch.stack([dev(i[0]).bfloat16() for i in items] * 4)
+    b = torch.stack([dev(i[1]).bfloat16() for i in items] * 4)
+    c = torch.zeros(8, 1024, 1024, device="cuda", dtype=torch.bfloat16)
+    build(plan, bufs)(a, b, c)
+    assert O.bf16_output_ok(c[1].float().cpu().numpy(), O.gemm(items[1][0], items[1][1], out_dtype=np.float64))
+
+
+def test_gpu_pool_measurer_and_failures(native_lib):
+    """One worker per GPU; a candidate the library rejects scores inf, the pool keeps working."""
+    from flextensor_b200.measure import GpuPoolMeasurer
+    from flextensor_b200.templates import knobs_to_config
+    from flextensor_b200.task import TASK_TABLE
+    from flextensor_b200.utils import Config
+    key = "gemm_batch_gemm_(4, 256, 512, 384)_cuda(0)"
+    op = TASK_TABLE[key].func(*TASK_TABLE[key].args)[0][0]
+    good = Config([knobs_to_config({"tile_n": 128, "cluster": 1, "stages": 3}, op)], None)
+    bad = Config([knobs_to_config({"tile_n": 256, "cluster": 1, "stages": 8}, op)], None)  # over the smem budget
+    pool = GpuPoolMeasurer(devices=[0])
+    try:
+        res = pool([(key, good, None), (key, bad, None), (key, good, None)], number=3, timeout=60, parallel=1)
+    finally:
+        pool.close()
+    assert 0 < res[0] < 100 and res[1] == float("inf") and 0 < res[2] < 100

@@ -1,0 +1,343 @@
+"""Parity of the sm_100a kernels, called through the C ABI, against the oracle.
+
+Tolerances (stated once in oracle/ft_oracle.py:TOLERANCE):
+  int8 GEMM                     bit-exact
+  GEMM fp32, 3xTF32             normalised error <= 1e-4   (|x-y| / max(|y|, rms(y)))
+  GEMM fp32, single-pass TF32   normalised error <= 5e-3   (reported mode, not the default)
+  conv2d TF32 / 3xTF32          5e-3 / 1e-4
+  depthwise fp32                1e-5
+  batched GEMM bf16             |x-y| <= 2^-7 |y| + 2^-8 rms(y) for bf16 output; 1e-5 for fp32 output
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_DIR
+from oracle import ft_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = O.TOLERANCE
+
+
+@pytest.fixture(scope="module")
+def B(native_lib):
+    from flextensor_b200 import backend
+    assert backend.lib().ftb_device_check() == 0, "the current device is not sm_100"
+    return backend
+
+
+@pytest.fixture()
+def status(B):
+    st = B.new_status()
+    yield st
+    B.check_status(st)  # no kernel may have given up a wait
+
+
+def _load(name):
+    return np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def bf16_dev(values_f32):
+    return dev(values_f32).to(torch.bfloat16)
+
+
+# ---------------------------------------------------------------- GEMM fp32
+def run_gemm_f32(B, a, b, ta=False, tb=False, cfg=None, status=None):
+    m = a.shape[1] if ta else a.shape[0]
+    n = b.shape[0] if tb else b.shape[1]
+    c = torch.full((m, n), float("nan"), device="cuda")
+    B.gemm_f32(dev(a), dev(b), c, ta, tb, cfg=cfg, status=status)
+    torch.cuda.synchronize()
+    return c.cpu().numpy()
+
+
+def test_gemm_f32_golden(B, status):
+    g = _load("gemm_f32")
+    got = run_gemm_f32(B, g["a"], g["b"], cfg={"fp32_mode": 1}, status=status)
+    assert O.normalised_error(got, g["y"]) <= TOL["gemm_f32_3xtf32"]
+    got = run_gemm_f32(B, g["a"], g["b"], cfg={"fp32_mode": 0}, status=status)
+    assert O.normalised_error(got, g["y"]) <= TOL["gemm_f32_tf32"]
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_gemm_f32_transposes_ragged(B, status, ta, tb, mode):
+    a, b = O.gemm_inputs(196, 132, 260, seed=21)
+    want = O.gemm(a, b)
+    got = run_gemm_f32(B, a.T.copy() if ta else a, b.T.copy() if tb else b, ta, tb, cfg={"fp32_mode": mode},
+                       status=status)
+    assert O.normalised_error(got, want) <= (TOL["gemm_f32_3xtf32"] if mode else TOL["gemm_f32_tf32"])
+
+
+@pytest.mark.parametrize("cfg", [
+    {"fp32_mode": 1}, {"fp32_mode": 1, "tile_n": 64}, {"fp32_mode": 1, "tile_n": 128, "stages": 2},
+    {"fp32_mode": 0}, {"fp32_mode": 0, "cluster": 2, "tile_n": 128}, {"fp32_mode": 0, "tile_n": 64, "split_k": 4},
+    {"fp32_mode": 0, "tile_n": 256, "raster": 1}, {"fp32_mode": 0, "raster": 2, "group_m": 4, "ctas": 74},
+])
+def test_gemm_f32_1024_every_knob(B, status, cfg):
+    """The README task: C[1024,1024] = A.B, uniform[-1,1) inputs from seed 0."""
+    a, b = O.gemm_inputs(1024, 1024, 1024, seed=0)
+    want = O.gemm(a, b)
+    got = run_gemm_f32(B, a, b, cfg=cfg, status=status)
+    err = O.normalised_error(got, want)
+    assert err <= (TOL["gemm_f32_3xtf32"] if cfg["fp32_mode"] else TOL["gemm_f32_tf32"]), err
+
+
+def test_gemm_f32_tiny_and_k_tail(B, status):
+    for (m, n, k) in [(1, 4, 4), (4, 8, 36), (129, 260, 100), (300, 36, 4)]:
+        a, b = O.gemm_inputs(m, n, k, seed=m + n + k)
+        got = run_gemm_f32(B, a, b, cfg={"fp32_mode": 1}, status=status)
+        assert O.normalised_error(got, O.gemm(a, b)) <= TOL["gemm_f32_3xtf32"], (m, n, k)
+
+
+def test_batched_gemm_f32(B, status):
+    rng = np.random.default_rng(5)
+    a = rng.uniform(-1, 1, (3, 72, 40)).astype(np.float32)
+    b = rng.uniform(-1, 1, (3, 40, 56)).astype(np.float32)
+    c = torch.full((3, 72, 56), float("nan"), device="cuda")
+    B.bgemm_f32(dev(a), dev(b), c, cfg={"fp32_mode": 1}, status=status)
+    assert O.normalised_error(c.cpu().numpy(), O.batch_gemm(a, b)) <= TOL["gemm_f32_3xtf32"]
+
+
+def test_unaligned_shapes_are_refused_not_miscomputed(B):
+    a = torch.zeros(8, 6, device="cuda")   # K = 6 floats = 24 bytes per row: not a multiple of 16
+    b = torch.zeros(6, 8, device="cuda")
+    c = torch.zeros(8, 8, device="cuda")
+    with pytest.raises(B.FtbError) as err:
+        B.gemm_f32(a, b, c)
+    assert err.value.code == -2
+    with pytest.raises(B.FtbError) as err:
+        B.gemm_f32(torch.zeros(8, 8, device="cuda"), torch.zeros(8, 8, device="cuda"), c, cfg={"tile_n": 48})
+    assert err.value.code == -3
+    with pytest.raises(TypeError):
+        B.gemm_f32(a.cpu(), b, c)
+
+
+# ---------------------------------------------------------------- batched GEMM bf16
+def test_bgemm_bf16_golden(B, status):
+    g = _load("bgemm_bf16")
+    a, b = O.from_bf16_bits(g["a_bits"]), O.from_bf16_bits(g["b_bits"])
+    c = torch.full(g["y"].shape, float("nan"), device="cuda", dtype=torch.bfloat16)
+    B.bgemm_bf16(bf16_dev(a), bf16_dev(b), c, status=status)
+    assert O.bf16_output_ok(c.float().cpu().numpy(), g["y"])
+    c32 = torch.full(g["y"].shape, float("nan"), device="cuda")
+    B.bgemm_bf16(bf16_dev(a), bf16_dev(b), c32, status=status)
+    assert O.normalised_error(c32.cpu().numpy(), g["y"]) <= TOL["bgemm_bf16_out_f32"]
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("cfg", [{"cluster": 1}, {"cluster": 2, "tile_n": 256}, {"cluster": 2, "tile_n": 128, "stages": 3},
+                                 {"cluster": 1, "tile_n": 64, "raster": 2, "group_m": 2}])
+def test_bgemm_bf16_layouts_and_tails(B, status, ta, tb, cfg):
+    items = [O.batch_gemm_item(i, 328, 264, 136, seed=31) for i in range(3)]
+    a = np.stack([i[0] for i in items])
+    b = np.stack([i[1] for i in items])
+    want = O.batch_gemm(a, b)
+    a_in = np.ascontiguousarray(np.swapaxes(a, 1, 2)) if ta else a
+    b_in = np.ascontiguousarray(np.swapaxes(b, 1, 2)) if tb else b
+    c = torch.full(want.shape, float("nan"), device="cuda")
+    B.bgemm_bf16(bf16_dev(a_in), bf16_dev(b_in), c, ta, tb, cfg=cfg, status=status)
+    assert O.normalised_error(c.cpu().numpy(), want) <= TOL["bgemm_bf16_out_f32"]
+
+
+def test_bgemm_bf16_full_size_properties(B, status):
+    """B=64, M=N=K=2048 (the batch-sharded headline shape): two items against the oracle, every
+    item through the row-sum identity (A.B).1 = A.(B.1), and run-to-run bit equality."""
+    batch, n = 64, 2048
+    a = torch.empty(batch, n, n, device="cuda", dtype=torch.bfloat16)
+    b = torch.empty(batch, n, n, device="cuda", dtype=torch.bfloat16)
+    host = {}
+    for i in range(batch):
+        ai, bi = O.batch_gemm_item(i, n, n, n, seed=3)
+        a[i] = bf16_dev(ai)
+        b[i] = bf16_dev(bi)
+        if i in (0, 63):
+            host[i] = (ai, bi)
+    c = torch.full((batch, n, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    B.bgemm_bf16(a, b, c, status=status)
+    torch.cuda.synchronize()
+    for i, (ai, bi) in host.items():
+        assert O.bf16_output_ok(c[i].float().cpu().numpy(), O.gemm(ai, bi, out_dtype=np.float64))
+    row_sums = c.double().sum(dim=2)
+    want = torch.bmm(a.double(), b.double().sum(dim=2, keepdim=True)).squeeze(2)
+    # 2048 bf16 roundings of magnitude <= 2^-9 |c| each, summed: well inside 2^-7 of the absolute row mass
+    mass = c.double().abs().sum(dim=2)
+    assert bool(((row_sums - want).abs() <= 2.0 ** -7 * mass).all())
+    c2 = torch.empty_like(c)
+    B.bgemm_bf16(a, b, c2, status=status)
+    assert torch.equal(c, c2)
+
+
+# ---------------------------------------------------------------- int8 GEMM
+def run_gemm_s8(B, a, b, ta=False, tb=False, cfg=None, status=None):
+    m = a.shape[1] if ta else a.shape[0]
+    n = b.shape[0] if tb else b.shape[1]
+    c = torch.full((m, n), -7, device="cuda", dtype=torch.int32)
+    B.gemm_s8(dev(a), dev(b), c, ta, tb, cfg=cfg, status=status)
+    torch.cuda.synchronize()
+    return c.cpu().numpy()
+
+
+def test_gemm_s8_golden_and_layouts(B, status):
+    g = _load("gemm_int8")
+    assert (run_gemm_s8(B, g["a"], g["b"], status=status) == g["y"]).all()
+    a, b = O.gemm_int8_inputs(272, 384, 400, seed=41)
+    want = O.gemm_int8(a, b)
+    for ta in (False, True):
+        for tb in (False, True):
+            got = run_gemm_s8(B, a.T.copy() if ta else a, b.T.copy() if tb else b, ta, tb, status=status)
+            assert (got == want).all(), (ta, tb)
+    for cfg in ({"cluster": 2, "tile_n": 256}, {"cluster": 1, "tile_n": 128, "stages": 3}, {"raster": 1}):
+        assert (run_gemm_s8(B, a, b, cfg=cfg, status=status) == want).all(), cfg
+
+
+def test_gemm_s8_extremes(B, status):
+    k = 4096
+    a = np.full((128, k), 127, dtype=np.int8)
+    b = np.full((k, 256), -127, dtype=np.int8)
+    assert (run_gemm_s8(B, a, b, status=status) == -127 * 127 * k).all()
+
+
+def test_gemm_s8_8192_bit_exact(B, status):
+    """M=N=K=8192, values uniform in [-127,127] from seed 4: a random 256x256 block against a
+    literal int32 matmul, every row through the exact checksum C.1 = A.(B.1)."""
+    n = 8192
+    a, b = O.gemm_int8_inputs(n, n, n, seed=4)
+    ad, bd = dev(a), dev(b)
+    c = torch.full((n, n), -7, device="cuda", dtype=torch.int32)
+    B.gemm_s8(ad, bd, c, status=status)
+    torch.cuda.synchronize()
+    r0, c0 = 3072 + 17, 5120 + 33
+    block = c[r0:r0 + 256, c0:c0 + 256].cpu().numpy()
+    assert (block == O.gemm_int8_direct(a[r0:r0 + 256], b[:, c0:c0 + 256])).all()
+    b_row_sums = b.astype(np.int64).sum(axis=1)
+    want = a.astype(np.int64) @ b_row_sums
+    got = c.to(torch.int64).sum(dim=1).cpu().numpy()
+    assert (got == want).all()
+    c2 = torch.empty_like(c)
+    B.gemm_s8(ad, bd, c2, cfg={"cluster": 1, "tile_n": 256}, status=status)
+    assert torch.equal(c, c2)                      # another tiling, the same integers
+
+
+# ---------------------------------------------------------------- conv2d
+def run_conv(B, x, w, bias=None, stride=1, padding=0, dilation=1, groups=1, cfg=None, status=None):
+    n, c, h, wd = x.shape
+    k, _, r, s = w.shape
+    p = O.out_size(h, r, stride, padding, dilation)
+    q = O.out_size(wd, s, stride, padding, dilation)
+    out = torch.full((n, k, p, q), float("nan"), device="cuda")
+    ws = torch.empty(B.conv2d_workspace_bytes(n, c, h, wd, k, r, s, groups), dtype=torch.uint8, device="cuda")
+    B.conv2d_nchw_f32(dev(x), dev(w), out, dev(bias) if bias is not None else None, (stride, stride),
+                      (padding, padding), (dilation, dilation), groups, cfg=cfg, workspace=ws, status=status)
+    torch.cuda.synchronize()
+    return out.cpu().numpy()
+
+
+def test_conv2d_golden(B, status):
+    g = _load("conv2d_grouped")
+    stride, pad, dil, groups = (int(v) for v in g["params"])
+    # 2 input channels per group: the group base is not 16-byte aligned -> refused, not miscomputed
+    with pytest.raises(B.FtbError):
+        run_conv(B, g["x"], g["w"], g["b"], stride, pad, dil, groups)
+    g = _load("conv2d_3x3")
+    for mode, tol in ((0, TOL["conv2d_tf32"]), (1, TOL["conv2d_3xtf32"])):
+        got = run_conv(B, g["x"], g["w"], None, 1, 1, 1, 1, cfg={"fp32_mode": mode}, status=status)
+        assert O.normalised_error(got, g["y"]) <= tol
+
+
+@pytest.mark.parametrize("case", [
+    dict(n=2, c=24, h=14, w=14, k=36, r=3, stride=1, pad=1, dil=1, groups=3, bias=True),
+    dict(n=2, c=32, h=29, w=31, k=64, r=3, stride=2, pad=2, dil=2, groups=1, bias=True),
+    dict(n=1, c=40, h=20, w=24, k=48, r=3, stride=1, pad=1, dil=1, groups=1, bias=False),
+    dict(n=3, c=64, h=9, w=9, k=40, r=1, stride=1, pad=0, dil=1, groups=1, bias=False),
+    dict(n=1, c=8, h=33, w=130, k=16, r=5, stride=1, pad=2, dil=1, groups=1, bias=True),
+    dict(n=1, c=3, h=32, w=32, k=8, r=7, stride=2, pad=3, dil=1, groups=1, bias=False),
+])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_conv2d_cases(B, status, case, mode):
+    x, w = O.conv2d_inputs(case["n"], case["c"], case["h"], case["w"], case["k"], case["r"], case["r"],
+                           groups=case["groups"], seed=51)
+    bias = np.random.default_rng(52).standard_normal(case["k"]).astype(np.float32) if case["bias"] else None
+    want = O.conv2d_nchw(x, w, bias, case["stride"], case["pad"], case["dil"], case["groups"])
+    got = run_conv(B, x, w, bias, case["stride"], case["pad"], case["dil"], case["groups"],
+                   cfg={"fp32_mode": mode}, status=status)
+    assert got.shape == want.shape
+    assert O.normalised_error(got, want) <= (TOL["conv2d_3xtf32"] if mode else TOL["conv2d_tf32"])
+
+
+@pytest.mark.parametrize("cfg", [{"fp32_mode": 0}, {"fp32_mode": 1}, {"fp32_mode": 0, "tile_n": 32},
+                                 {"fp32_mode": 0, "tile_h": 1}, {"fp32_mode": 0, "split_k": 3},
+                                 {"fp32_mode": 1, "split_k": 9, "tile_n": 32}])
+def test_conv2d_resnet_stage2(B, status, cfg):
+    """N=1, C=64, 56x56, K=64, 3x3, stride 1, pad 1; normal(0,1) input and weights from seed 1."""
+    x, w = O.conv2d_inputs(1, 64, 56, 56, 64, 3, 3, seed=1)
+    want = O.conv2d_nchw(x, w, None, 1, 1, 1, 1)
+    got = run_conv(B, x, w, None, 1, 1, 1, 1, cfg=cfg, status=status)
+    assert O.normalised_error(got, want) <= (TOL["conv2d_3xtf32"] if cfg["fp32_mode"] else TOL["conv2d_tf32"])
+
+
+def test_conv2d_workspace_is_required(B):
+    x = torch.zeros(1, 8, 8, 8, device="cuda")
+    w = torch.zeros(8, 8, 3, 3, device="cuda")
+    out = torch.zeros(1, 8, 6, 6, device="cuda")
+    with pytest.raises(ValueError):
+        B.conv2d_nchw_f32(x, w, out, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+    rc = B.lib().ftb_conv2d_nchw_f32(x.data_ptr(), w.data_ptr(), None, out.data_ptr(), 1, 8, 8, 8, 8, 3, 3, 1, 1, 0,
+                                     0, 1, 1, 1, None, None, 0, None, None)
+    assert rc == -4
+
+
+# ---------------------------------------------------------------- depthwise conv2d
+def run_dw(B, x, w, bias=None, stride=1, padding=0, dilation=1, cfg=None):
+    n, c, h, wd = x.shape
+    _, f, r, s = w.shape
+    p = O.out_size(h, r, stride, padding, dilation)
+    q = O.out_size(wd, s, stride, padding, dilation)
+    out = torch.full((n, c * f, p, q), float("nan"), device="cuda")
+    B.dwconv2d_nchw_f32(dev(x), dev(w), out, dev(bias) if bias is not None else None, (stride, stride),
+                        (padding, padding), (dilation, dilation), cfg=cfg)
+    torch.cuda.synchronize()
+    return out.cpu().numpy()
+
+
+def test_depthwise_golden(B):
+    g = _load("depthwise_f3")
+    stride, pad, dil = (int(v) for v in g["params"])
+    got = run_dw(B, g["x"], g["w"], g["b"], stride, pad, dil)
+    assert O.normalised_error(got, g["y"]) <= TOL["depthwise_f32"]
+
+
+@pytest.mark.parametrize("cfg", [None, {"tile_h": 7}, {"tile_h": 14, "threads": 128}, {"tile_h": 56, "threads": 512},
+                                 {"tile_h": 1, "threads": 64}])
+def test_depthwise_c256_56(B, cfg):
+    """N=1, C=256, 56x56, 3x3, stride 1, pad 1, multiplier 1; uniform[-1,1) from seed 2."""
+    x, w = O.depthwise_inputs(1, 256, 56, 56, 1, 3, 3, seed=2)
+    got = run_dw(B, x, w, None, 1, 1, 1, cfg=cfg)
+    assert O.normalised_error(got, O.depthwise_conv2d_nchw(x, w, None, 1, 1, 1)) <= TOL["depthwise_f32"]
+
+
+@pytest.mark.parametrize("shape", [(2, 6, 19, 23, 2, 5, 2, 3, 2), (1, 32, 112, 112, 1, 3, 1, 1, 1),
+                                   (8, 16, 112, 112, 6, 3, 2, 1, 1), (2, 160, 7, 7, 6, 3, 1, 1, 1),
+                                   (1, 3, 5, 5, 1, 3, 1, 0, 1), (1, 4, 30, 33, 1, 7, 1, 3, 1)])
+def test_depthwise_shapes(B, shape):
+    n, c, h, w_, f, r, stride, pad, dil = shape
+    x, w = O.depthwise_inputs(n, c, h, w_, f, r, r, seed=61)
+    bias = np.random.default_rng(62).standard_normal(c * f).astype(np.float32)
+    got = run_dw(B, x, w, bias, stride, pad, dil)
+    want = O.depthwise_conv2d_nchw(x, w, bias, stride, pad, dil)
+    assert got.shape == want.shape
+    assert O.normalised_error(got, want) <= TOL["depthwise_f32"]
+
+
+def test_launch_counter_counts_our_kernels(B):
+    before = B.launch_count()
+    x, w = O.depthwise_inputs(1, 4, 8, 8, 1, 3, 3)
+    run_dw(B, x, w, None, 1, 1, 1)
+    assert B.launch_count() == before + 1

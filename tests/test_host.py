@@ -1,0 +1,357 @@
+"""Host-side mirror of the reference interface: helpers, op definitions, task registry,
+config space, walkers, search (with a pure-Python cost function standing in for the GPU),
+templates and the log-line format.  Runs without a GPU."""
+import json
+import math
+import os
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from flextensor_b200 import scheduler as S
+from flextensor_b200 import space as SP
+from flextensor_b200.ir import placeholder
+from flextensor_b200.model import WalkerGroup, Walker, PerformanceModel, rank_loss
+from flextensor_b200.nn import ops
+from flextensor_b200.scheduler import schedule, schedule_with_config, flatten_graph
+from flextensor_b200.task import Task, TASK_TABLE, register_task, conv2d, gemm
+from flextensor_b200.templates import config_to_knobs, knobs_to_config
+from flextensor_b200.utils import (Config, any_factor_split, get_factor_lst, gen_enum, gen_group, test_allclose,
+                                   assert_print, to_tuple)
+
+S.VERBOSE = False
+
+
+# ---------------------------------------------------------------- utils
+def test_factor_helpers():
+    assert get_factor_lst(16) == [1, 16, 2, 8, 4]
+    assert get_factor_lst(12) == [1, 12, 2, 6, 3, 4]
+    assert get_factor_lst(1) == [1]
+    splits = any_factor_split(1024, 4)
+    assert len(splits) == 286                      # C(10+3, 3): space size of a 1024-extent axis
+    assert all(math.prod(s) == 1024 for s in splits)
+    assert len(any_factor_split(1024, 3)) == 66
+    assert len(any_factor_split(8192, 4)) == 560 and len(any_factor_split(8192, 3)) == 105
+    assert [1, 1, 1, 7] in any_factor_split(7, 4)
+    assert gen_enum([1, 0], 2) == [[1, 1], [1, 0], [0, 1], [0, 0]]
+    assert gen_group(["a", "b", "c", "d"], most_groups=3) == [[1, 2, 4], [1, 3, 4], [2, 3, 4]]
+    assert gen_group(["a", "b"], most_groups=3) == [[1, 2, 2]]
+    assert test_allclose(np.ones(3), np.ones(3) * (1 + 1e-7)) == 1
+    assert test_allclose(np.ones(3), np.ones(3) * 1.1) == 0
+    with pytest.raises(AssertionError):
+        assert_print(False, "x")
+    assert to_tuple(placeholder((3, 4)).shape) == (3, 4)
+
+
+# ---------------------------------------------------------------- op definitions
+def test_op_definitions_shapes_and_axes():
+    x = placeholder((1, 64, 56, 56))
+    w = placeholder((64, 64, 3, 3))
+    out = ops.conv2d_nchw(x, w, stride=1, padding=1)
+    assert to_tuple(out.shape) == (1, 64, 56, 56)
+    assert [a.var.name for a in out.op.axis] == ["b", "c", "h", "w"]
+    assert [(a.var.name, a.dom.extent.value) for a in out.op.reduce_axis] == [("rc", 64), ("rw", 3), ("rh", 3)]
+    padded = out.op.input_tensors[0]
+    assert padded.op.name == "Padding" and to_tuple(padded.shape) == (1, 64, 58, 58)
+    out = ops.conv2d_nchw(placeholder((4, 6, 7, 7)), placeholder((9, 2, 3, 3)), placeholder((9,)), stride=2,
+                          padding=1, dilation=2, groups=3)
+    assert to_tuple(out.shape) == (4, 9, 3, 3) and out.op.kind == "bias_add"
+    with pytest.raises(AssertionError):
+        ops.conv2d_nchw(placeholder((1, 6, 7, 7)), placeholder((9, 4, 3, 3)), groups=3)
+    dw = ops.depthwise_conv2d_nchw(placeholder((4, 6, 7, 7)), placeholder((6, 3, 3, 3)), stride=2, padding=1,
+                                   dilation=2)
+    assert to_tuple(dw.shape) == (4, 18, 3, 3)
+    a, b = placeholder((8, 16)), placeholder((16, 4))
+    assert to_tuple(ops.gemm(a, b).shape) == (8, 4)
+    assert to_tuple(ops.gemm(placeholder((16, 8)), b, transposeA=True).shape) == (8, 4)
+    assert to_tuple(ops.gemm(a, placeholder((4, 16)), transposeB=True).shape) == (8, 4)
+    assert to_tuple(ops.gemm(placeholder((16, 8)), placeholder((4, 16)), True, True).shape) == (8, 4)
+    with pytest.raises(AssertionError):
+        ops.gemm(a, placeholder((15, 4)))
+    bg = ops.batch_gemm(placeholder((3, 8, 16), "bfloat16"), placeholder((3, 16, 4), "bfloat16"))
+    assert to_tuple(bg.shape) == (3, 8, 4) and bg.dtype == "bfloat16"
+    with pytest.raises(AssertionError):
+        ops.batch_gemm(placeholder((3, 8, 16)), placeholder((2, 16, 4)))
+    i8 = ops.gemm_int8(placeholder((8, 16), "int8"), placeholder((16, 4), "int8"))
+    assert i8.dtype == "int32"
+    with pytest.raises(AssertionError):
+        ops.gemm_int8(a, b)
+
+
+def test_flatten_graph_is_producer_first():
+    ops_, bufs = conv2d(1, 8, 6, 6, 4, 3, 1, 1, 1, 1)
+    op_lst, down = flatten_graph(ops_)
+    assert [op.kind for op in op_lst] == ["pad2d", "conv2d"]
+    assert SP.able_inline(op_lst[0], down) and not SP.able_inline(op_lst[1], down)
+
+
+# ---------------------------------------------------------------- task registry
+def test_task_keys_and_registry():
+    t = Task("gemm", "gemm", None, (1024, 1024, 1024), "cuda", 0)
+    assert t.key == "gemm_gemm_(1024, 1024, 1024)_cuda(0)"
+    assert t.key in TASK_TABLE and TASK_TABLE[t.key].func is gemm
+    assert "conv2d_res5_(64, 256, 56, 56, 512, 1, 2, 0, 1, 1)_cuda(3)" in TASK_TABLE
+    assert "conv2d_res_b13_(1, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)" in TASK_TABLE
+    assert "conv2d_depthwise_(1, 256, 56, 56, 1, 3, 1, 1, 1)_cuda(0)" in TASK_TABLE
+    assert "gemm_batch_gemm_(64, 2048, 2048, 2048)_cuda(7)" in TASK_TABLE
+    assert "gemm_gemm_int8_(8192, 8192, 8192)_cuda(0)" in TASK_TABLE
+    marker = Task("gemm", "gemm", "replaced", (32, 32, 32), "cuda", 0)
+    old = TASK_TABLE[marker.key]
+    register_task(marker)                          # silent overwrite, as in the reference
+    assert TASK_TABLE[marker.key].func == "replaced"
+    register_task(old)
+    t.set_specific_space("layout", "enum", [[0, 0], [1, 0]])
+    assert len(t.special_space["layout"]) == 2
+    with pytest.raises(RuntimeError):
+        t.set_specific_space("x", "grid", [])
+
+
+# ---------------------------------------------------------------- space
+def test_split_space_invariants_and_moves():
+    sp = SP.SplitSpace(4, 1024)
+    assert len(sp) == 286 and sp.num_direction == 12
+    assert all(math.prod(e) == 1024 for e in sp.static_entities)
+    pos = sp.static_entities.index([1, 1, 1, 1024])
+    nxt = sp.next_entity(pos, (0, 3))             # move a factor from part 3 to part 0
+    assert sp.static_entities[nxt] == [2, 1, 1, 512]
+    assert sp.next_entity(pos, (3, 0)) == pos      # nothing left to take from part 0
+    assert sp.next_entity(5, (1,)) == 6 and sp.next_entity(0, (-1,)) == len(sp) - 1
+    sp7 = SP.SplitSpace(3, 7)
+    assert all(math.prod(e) == 7 for e in sp7.static_entities)
+    p2 = SP.SplitSpace(2, 6, allow_non_divisible="power2")
+    assert [4, 1] in p2.static_entities or [4, 2] in p2.static_entities
+
+
+def test_reference_style_space_sizes():
+    ops_, _ = gemm(1024, 1024, 1024)
+    space = SP.generate_space_intra_op(ops_[0], {}, slevel=4, rlevel=3, groups=3, target="llvm")
+    sizes = space.length()
+    assert sizes["split_i_0"] == 286 and sizes["split_j_1"] == 286 and sizes["split_k_0"] == 66
+    assert sizes["reorder"] == 3 and sizes["unroll"] == 8
+    assert space.dim == 3 + 4 + 4 + 3 + 1 + 2     # fuse (3 cut positions) + splits + reorder + unroll
+
+
+def test_b200_space_per_family():
+    ops_, _ = gemm(1024, 1024, 1024)
+    space = SP.generate_space_intra_op(ops_[0], {}, target="cuda")
+    assert list(space.subspaces) == ["tile_n", "cluster", "stages", "split_k", "raster", "ctas"]
+    assert space.types["spatial"] == ["tile_n", "cluster"] and space.types["reduce"] == ["stages", "split_k"]
+    assert [e[0] for e in space.subspaces["tile_n"].static_entities] == [32, 64, 128, 256]
+    for sub in space.subspaces.values():          # every sub-space speaks the walker protocol
+        assert sub.num_direction == len(sub.directions) == 2 and len(sub) == len(sub.static_entities) > 0
+        assert all(len(e) == sub.dim for e in sub.static_entities)
+        assert sub.next_entity(len(sub) - 1, (1,)) == 0
+    from flextensor_b200.task import gemm_int8, batch_gemm, depthwise_conv2d
+    i8 = SP.generate_space_intra_op(gemm_int8(512, 512, 512)[0][0], {}, target="cuda")
+    assert [e[0] for e in i8.subspaces["tile_n"].static_entities] == [128, 256]   # N-contiguous int8 B: 128-wide boxes
+    assert [e[0] for e in i8.subspaces["split_k"].static_entities] == [1]         # integer output: no atomics
+    bg = SP.generate_space_intra_op(batch_gemm(4, 256, 256, 256)[0][0], {}, target="cuda")
+    assert [e[0] for e in bg.subspaces["tile_n"].static_entities] == [64, 128, 256]
+    ops_, _ = conv2d(1, 64, 56, 56, 64, 3, 1, 1, 1, 1)
+    op_lst, down = flatten_graph(ops_)
+    assert len(SP.generate_space_intra_op(op_lst[0], down, target="cuda").subspaces) == 0   # padding: no kernel
+    cv = SP.generate_space_intra_op(op_lst[1], down, target="cuda")
+    assert [e[0] for e in cv.subspaces["tile_h"].static_entities] == [1, 2]
+    assert 9 in [e[0] for e in cv.subspaces["split_k"].static_entities]
+    dw = SP.generate_space_intra_op(flatten_graph(depthwise_conv2d(1, 256, 56, 56, 1, 3, 1, 1, 1)[0])[0][1], {},
+                                    target="cuda")
+    assert list(dw.subspaces) == ["tile_h", "threads"]
+    inter = SP.generate_space_inter_op(op_lst, down)
+    assert inter.subspaces["inline"].static_entities == [[1, 0], [0, 0]]
+    assert SP.generate_space_inter_op(op_lst, down, force_inline=True).subspaces["inline"].static_entities == [[1, 0]]
+
+
+# ---------------------------------------------------------------- templates
+def test_config_knob_round_trip():
+    ops_, _ = gemm(1024, 1024, 1024)
+    op = ops_[0]
+    knobs = {"tile_n": 128, "cluster": 2, "stages": 6, "split_k": 1, "raster": 2, "group_m": 8}
+    cfg = knobs_to_config(knobs, op)
+    assert cfg["spatial"] == [[128], [2]] and cfg["reduce"] == [[6], [1]] and cfg["reorder"] == [[2, 8]]
+    assert config_to_knobs(cfg, op) == knobs
+    assert config_to_knobs({}, op) == {}
+    assert config_to_knobs({"spatial": [[64]]}, op) == {"tile_n": 64}
+
+
+# ---------------------------------------------------------------- walkers and models
+def _toy_space():
+    space = SP.Space()
+    space.add_subspace("a", SP.KnobSpace("a", [1, 2, 4, 8]), "spatial")
+    space.add_subspace("b", SP.KnobSpace("b", [[0, 0], [1, 0], [2, 4]]), "reorder")
+    return space
+
+
+def test_walker_group_memory_and_moves():
+    np.random.seed(1)
+    torch.manual_seed(1)
+    group = WalkerGroup("toy", _toy_space())
+    assert group.top1() == {} and group.top1_value() == float("inf") and not group.has_more()
+    group.record({"a": 0, "b": 0}, 3.0)
+    group.record({"a": 1, "b": 0}, 1.0)
+    group.record({"a": 2, "b": 1}, 2.0)
+    assert group.top1() == {"a": 1, "b": 0} and group.top1_value() == 1.0
+    assert group.ever_met({"a": 0, "b": 0}) and not group.ever_met({"a": 3, "b": 2})
+    assert group.flatten({"a": 2, "b": 2}) == [4, 2, 4]
+    assert group.to_config({"a": 3, "b": 1})["spatial"] == [[8]]
+    assert group.to_config({"a": 3, "b": 1})["reorder"] == [[1, 0]]
+    nxt, acts = group.full_walk({"a": 1, "b": 0}, no_repeat=True)
+    assert {"a": 0, "b": 0} not in nxt and {"a": 2, "b": 0} in nxt and len(nxt) == len(acts)
+    assert group.topk(2) == [{"a": 1, "b": 0}, {"a": 2, "b": 1}] and group.mem_size == 3
+    assert group.topk(2, modify=True, with_value=True)[0][1] == 1.0 and group.mem_size == 1
+    assert group.pop_top().value == 3.0 and group.pop_top().value == float("inf")
+    # a much worse point is (almost surely) rejected when random_reject is on
+    group.record({"a": 1, "b": 0}, 1.0)
+    before = group.mem_size
+    for _ in range(20):
+        group.record({"a": 3, "b": 2}, 1e6, random_reject=True)
+    assert group.mem_size == before
+    frm, nxt, acts = group.walk([({"a": 1, "b": 0}, 1.0)], trial=0)
+    assert len(frm) == len(nxt) == len(acts) and all(not group.ever_met(n) or True for n in nxt)
+
+
+def test_walker_training_and_persistence(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    torch.manual_seed(0)
+    np.random.seed(0)
+    group = WalkerGroup("persist", _toy_space())
+    for i in range(40):
+        pre = {"a": i % 4, "b": i % 3}
+        post = {"a": (i + 1) % 4, "b": i % 3}
+        group.add_data("a", pre, (1,), post, 0.5)
+        group.add_data("b", pre, 0, {"a": i % 4, "b": (i + 2) % 3}, 0.1)
+    group.train_walkers(save=True, verbose=False)
+    walker = group.walkers["a"]
+    assert os.path.exists(walker.model_path)
+    q_before = walker.pre_judger(torch.ones(group.space.dim)).detach().clone()
+    fresh = WalkerGroup("persist", _toy_space())
+    fresh.load_walker_model()
+    assert torch.allclose(fresh.walkers["a"].pre_judger(torch.ones(group.space.dim)), q_before)
+    assert torch.allclose(fresh.walkers["a"].post_judger(torch.ones(group.space.dim)), q_before)  # target synced
+    group.dump_data()
+    fresh.load_walker_data()
+    assert fresh.walkers["a"].mem_size == 40
+    # performance model: rank loss trains towards the right order
+    group.add_perf_data([{"a": 0, "b": 0}, {"a": 3, "b": 2}, {"a": 1, "b": 1}], [3.0, 1.0, 2.0])
+    group.train_on_perf(save=True, verbose=False)
+    assert len(group.query_performance([{"a": 0, "b": 0}, {"a": 3, "b": 2}])) == 2
+    y = torch.tensor([3.0, 1.0])
+    assert rank_loss(y, torch.tensor([3.0, 1.0])) < rank_loss(y, torch.tensor([1.0, 3.0]))
+    assert PerformanceModel(5)(torch.zeros(2, 5)).shape == (2, 1)
+
+
+# ---------------------------------------------------------------- search with a fake measurer
+def _fake_measurer(log=None):
+    def measure(jobs, number=1, timeout=1.0, parallel=1):
+        out = []
+        for task_key, cfg, op_pos in jobs:
+            plan, _ = schedule_with_config(task_key, cfg, op_pos=op_pos)
+            kn = plan.steps[-1].knobs if plan.steps else {}
+            cost = (1.0 + abs(kn.get("tile_n", 64) - 128) / 64 + abs(kn.get("stages", 4) - 5) * 0.1 +
+                    (0.5 if kn.get("cluster", 1) == 1 else 0.0) + 0.05 * kn.get("split_k", 1))
+            if kn.get("stages") == 8:
+                cost = float("inf")                # a candidate that "fails to run"
+            out.append(cost)
+            if log is not None:
+                log.append((task_key, op_pos, parallel))
+        return out
+    return measure
+
+
+GEMM_KEY = "gemm_batch_gemm_(4, 256, 512, 384)_cuda(0)"
+
+
+@pytest.mark.parametrize("method", ["searching", "random"])
+def test_schedule_finds_the_optimum_of_a_fake_cost(method):
+    np.random.seed(0)
+    torch.manual_seed(0)
+    plan, bufs, configs = schedule(GEMM_KEY, op_trial=12, op_stop=6, timeout=1, parallel=4, method=method,
+                                   measurer=_fake_measurer())
+    knobs = plan.steps[0].knobs
+    assert knobs["tile_n"] == 128 and knobs["cluster"] == 2 and knobs["stages"] in (4, 5, 6)
+    assert isinstance(configs, Config) and len(configs.op_config_lst) == 1
+    assert [to_tuple(b.shape) for b in bufs] == [(4, 256, 512), (4, 512, 384), (4, 256, 384)]
+
+
+def test_schedule_is_deterministic_under_a_seed():
+    results = []
+    for _ in range(2):
+        np.random.seed(123)
+        torch.manual_seed(123)
+        _, _, configs = schedule(GEMM_KEY, op_trial=4, op_stop=3, timeout=1, parallel=2, method="searching",
+                                 measurer=_fake_measurer())
+        results.append(json.dumps(configs))
+    assert results[0] == results[1]
+
+
+def test_q_method_runs_and_trains(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)                    # walker checkpoints land in the working directory
+    np.random.seed(0)
+    torch.manual_seed(0)
+    plan, _, _ = schedule(GEMM_KEY, op_trial=5, op_stop=5, timeout=1, parallel=2, method="q",
+                          measurer=_fake_measurer())
+    assert plan.steps[0].knobs["tile_n"] in (64, 128, 256)
+    assert any(f.startswith("walker_judger_model_") for f in os.listdir(tmp_path))
+
+
+def test_conv_graph_search_and_log_round_trip():
+    np.random.seed(0)
+    torch.manual_seed(0)
+    key = "conv2d_res_b13_(1, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)"
+    log = []
+    plan, bufs, configs = schedule(key, op_trial=6, op_stop=3, timeout=1, parallel=2, trials=[1, 6],
+                                   measurer=_fake_measurer(log))
+    assert configs.op_config_lst[0] == {}          # the padding stage has no kernel of its own
+    assert [s.op.kind for s in plan.steps] == ["conv2d"]
+    assert any(p == 1 for _, _, p in log)          # leaders were re-measured serially
+    line = key + ":" + json.dumps(configs)         # the drivers' log line
+    name, string = line.split(":", 1)
+    obj = json.loads(string)
+    replay, _ = schedule_with_config(name, Config(obj[0], obj[1]))
+    assert replay.steps[0].knobs == plan.steps[0].knobs
+    # defaults when no config is given
+    default_plan, _ = schedule_with_config(key, Config([{}, {}], None))
+    assert default_plan.steps[0].knobs == {"fp32_mode": 0}
+    strict, _ = schedule_with_config(key, Config([{}, {}], None), precision="3xtf32")
+    assert strict.steps[0].knobs == {"fp32_mode": 1}
+
+
+def test_all_candidates_failing_gives_up_cleanly():
+    def broken(jobs, number=1, timeout=1.0, parallel=1):
+        return [float("inf")] * len(jobs)
+    sched = S.OpScheduler(GEMM_KEY, 0, SP.generate_space_intra_op(TASK_TABLE[GEMM_KEY].func(
+        *TASK_TABLE[GEMM_KEY].args)[0][0], {}, target="cuda"), parallel=2, timeout=1.0, trial=2, measurer=broken)
+    sched._warm_up(1, 3, Config([], None), [], max_repeat=3)
+    assert sched.walker_group.top1() == {} and sched.timeout == 1.0     # timeout restored after the doubling
+
+
+def test_bias_is_folded_and_unsupported_targets_refused():
+    x, w, b = placeholder((1, 8, 6, 6)), placeholder((4, 8, 3, 3)), placeholder((4,))
+    out = ops.conv2d_nchw(x, w, b, padding=1)
+    plan, _ = S.schedule_with_config_ops([out.op], [x, w, b, out], Config([], None))
+    assert [s.op.kind for s in plan.steps] == ["conv2d"] and plan.steps[0].bias is b and plan.steps[0].out is out
+    llvm_plan, _ = schedule_with_config("gemm_gemm_(32, 32, 32)_llvm(0)", Config([{}], None))
+    with pytest.raises(RuntimeError):
+        llvm_plan.build()
+    with pytest.raises(RuntimeError):
+        schedule_with_config(GEMM_KEY, Config([{}], None), rewrite=True)
+
+
+# ---------------------------------------------------------------- measurement plumbing (host-side failures)
+def _sleepy(seconds):
+    time.sleep(seconds)
+    return 42.0
+
+
+def _raiser():
+    raise ValueError("candidate failed")
+
+
+def test_master_routine_timeout_and_failure():
+    from flextensor_b200.measure import master_routine
+    assert master_routine(20, _sleepy, 0.01) == 42.0
+    res = master_routine(0.5, _sleepy, 30)
+    assert isinstance(res, Exception)
+    res = master_routine(20, _raiser)
+    assert isinstance(res, ValueError)
