@@ -29,10 +29,12 @@ FLOP_PER_ITEM = 2.0 * DIM ** 3
 METRIC = "TFLOP/s batched GEMM bf16 (fp32 accumulate) B=64 M=N=K=2048"
 WORKLOAD = "batched GEMM bf16 B=64 M=N=K=2048, fp32 accumulate, normal(0,0.02) inputs, bf16 output"
 FALLBACK_BF16_TFLOPS = 1590.0
-# DRAM bytes of one full-batch launch of the dominant kernel (dram__bytes_read.sum +
-# dram__bytes_write.sum from profiles/umma_gemm_bf16_pair.md, scaled from the captured
-# 6-item launch to 64 items by the items processed); None until such a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes of one full-batch launch of the dominant kernel: dram__bytes_read.sum +
+# dram__bytes_write.sum of a 6-item launch (profiles/umma_gemm_bf16_pair_b6_2048.md), scaled to
+# 64 items by the items processed (traffic grows in proportion: every item is read once).  The
+# 6-item capture still holds half of its output in L2 when the kernel ends, so the write part
+# is a lower bound; the algorithmic figure is 1.61e9.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = (100.73e6 + 24.08e6) * 64 / 6
 KNOBS = {"cluster": 2, "tile_n": 256, "raster": 2, "group_m": 4}
 
 
@@ -47,56 +49,78 @@ def measured_peak():
 
 
 class ClockSampler(object):
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while a region runs (read-only
+    NVML queries every few milliseconds; nvidia-smi every 100 ms when NVML cannot be loaded)."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20),
+               ("hw_thermal_slowdown", 0x40))
 
     def __init__(self, index):
         self.index = index
-        self.samples = []
-        self.proc = None
-        self.thread = None
+        self.clocks = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._mode = None
+
+    def _nvml_loop(self):
+        import pynvml
+        handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        while not self._stop.is_set():
+            try:
+                self.clocks.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                mask = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                for name, bit in self.REASONS:
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def _smi_loop(self):
+        fields = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.sw_power_cap,"
+                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.hw_thermal_slowdown")
+        proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + fields,
+                                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                stderr=subprocess.DEVNULL, text=True)
+        try:
+            for line in proc.stdout:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) >= 6:
+                    try:
+                        self.clocks.append(float(parts[0]))
+                        self.max_mhz = float(parts[1])
+                    except ValueError:
+                        continue
+                    for (name, _), val in zip(self.REASONS, parts[2:6]):
+                        if val.lower().startswith("active"):
+                            self.reasons.add(name)
+                if self._stop.is_set():
+                    break
+        finally:
+            proc.terminate()
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self._mode = "nvml"
+            self._thread = threading.Thread(target=self._nvml_loop, daemon=True)
         except Exception:
-            self.proc = None
-            return
-        self.thread = threading.Thread(target=self._read, daemon=True)
-        self.thread.start()
-
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 6:
-                self.samples.append(parts)
+            self._mode = "nvidia-smi"
+            self._thread = threading.Thread(target=self._smi_loop, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
-        clocks, reasons, mx = [], set(), None
-        for s in self.samples:
-            try:
-                clocks.append(float(s[0]))
-                mx = float(s[1])
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        clocks.sort()
-        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(clocks)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        clocks = sorted(self.clocks)
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(clocks), "source": self._mode}
 
 
 # ---------------------------------------------------------------------- CPU arm / CPU baseline
@@ -251,15 +275,12 @@ def run_ours(args, rank, world, local_rank):
     s, bufs = schedule_with_config(task.key, Config([knobs_to_config(KNOBS, op)], None))
     func = build(s, bufs, "cuda")
 
-    # Synthetic operands: normal(0, 0.02) rounded to bf16; the first item of the shard is the
-    # oracle's item (checked below), the rest are drawn on the device with a per-item seed.
-    a = torch.empty(local, DIM, DIM, device=device, dtype=torch.bfloat16)
-    b = torch.empty(local, DIM, DIM, device=device, dtype=torch.bfloat16)
+    # Synthetic operands: normal(0, 0.02) rounded to bf16, drawn on the device with a per-rank
+    # seed; the first item of the shard is replaced by the oracle's item, which is checked below.
     gen = torch.Generator(device=device)
-    for i in range(local):
-        gen.manual_seed(3 * 1_000_003 + lo + i)
-        a[i] = (torch.randn(DIM, DIM, device=device, generator=gen) * 0.02).to(torch.bfloat16)
-        b[i] = (torch.randn(DIM, DIM, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+    gen.manual_seed(3 * 1_000_003 + lo)
+    a = (torch.randn(local, DIM, DIM, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+    b = (torch.randn(local, DIM, DIM, device=device, generator=gen) * 0.02).to(torch.bfloat16)
     a0, b0 = O.batch_gemm_item(lo, DIM, DIM, DIM, seed=3)
     a[0] = torch.from_numpy(a0).to(device).to(torch.bfloat16)
     b[0] = torch.from_numpy(b0).to(device).to(torch.bfloat16)

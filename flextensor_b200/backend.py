@@ -60,11 +60,19 @@ class FtbConfig(ctypes.Structure):
 
 
 class FtbError(RuntimeError):
-    def __init__(self, code, where):
+    """A launcher returned a negative FTB_E_* code (``.code``)."""
+
+    def __init__(self, code, where, message=None):
         self.code = code
-        detail = lib().ftb_strerror(code).decode()
-        cuda = lib().ftb_last_cuda_error()
-        super().__init__("%s failed: %s (code %d, last CUDA error %d)" % (where, detail, code, cuda))
+        self.where = where
+        if message is None:
+            detail = lib().ftb_strerror(code).decode()
+            cuda = lib().ftb_last_cuda_error()
+            message = "%s failed: %s (code %d, last CUDA error %d)" % (where, detail, code, cuda)
+        super().__init__(message)
+
+    def __reduce__(self):  # crosses process boundaries (measurement workers)
+        return (FtbError, (self.code, self.where, str(self)))
 
 
 def lib_path():

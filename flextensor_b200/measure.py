@@ -102,8 +102,8 @@ def _worker_main(dev_id, jobs, results):
         job_id, job, number = item
         try:
             value = _evaluate_job(job, number, dev_id)
-        except Exception as exc:
-            value = exc
+        except Exception as exc:  # sent as text: any exception type survives the queue
+            value = RuntimeError("%s: %s" % (type(exc).__name__, exc))
         results.put((job_id, value))
 
 
