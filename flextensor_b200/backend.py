@@ -119,6 +119,8 @@ def lib():
         handle.ftb_conv2d_nchw_f32.restype = i32
         handle.ftb_conv2d_nchw_f32.argtypes = ([vp] * 4 + [i64] * 7 + [i32] * 7 +
                                                [cfgp, vp, ctypes.c_size_t, vp, vp])
+        handle.ftb_conv2d_nchw_f32_noalloc.restype = i32
+        handle.ftb_conv2d_nchw_f32_noalloc.argtypes = [vp] * 4 + [i64] * 7 + [i32] * 7 + [cfgp, vp, vp]
         handle.ftb_dwconv2d_nchw_f32.restype = i32
         handle.ftb_dwconv2d_nchw_f32.argtypes = [vp] * 4 + [i64] * 7 + [i32] * 6 + [cfgp, vp, vp]
         _lib = handle
@@ -128,7 +130,7 @@ def lib():
 EXPORTED_SYMBOLS = (
     "ftb_version", "ftb_strerror", "ftb_last_cuda_error", "ftb_device_check", "ftb_validate",
     "ftb_launch_count", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_gemm_s8",
-    "ftb_conv2d_workspace_bytes", "ftb_conv2d_nchw_f32", "ftb_dwconv2d_nchw_f32",
+    "ftb_conv2d_workspace_bytes", "ftb_conv2d_nchw_f32", "ftb_conv2d_nchw_f32_noalloc", "ftb_dwconv2d_nchw_f32",
 )
 
 
@@ -282,6 +284,36 @@ def conv2d_nchw_f32(x, weight, out, bias=None, stride=(1, 1), padding=(0, 0), di
             _status_ptr(status), _stream_ptr(stream))
     if rc:
         raise FtbError(rc, "ftb_conv2d_nchw_f32")
+
+
+NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024
+
+
+def conv2d_nchw_f32_noalloc(x, weight, out, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1,
+                            cfg=None, status=None, stream=None):
+    """conv2d for callers that may not allocate device memory (no workspace argument).
+
+    Meant for code that is handed its buffers by another runtime, or runs where allocation is
+    banned after start-up.  The workspace is a fixed 8 MiB array inside the library; shapes that
+    need more raise ``FtbError`` with code -7.  Calls share that array: do not let two of them
+    overlap on one GPU.  The first call on a device does a one-time address lookup and should
+    happen before any stream capture begins.
+    """
+    for t, nm in ((x, "x"), (weight, "weight"), (out, "out")):
+        _check(t, torch.float32, nm)
+    if bias is not None:
+        _check(bias, torch.float32, "bias")
+    n, c, h, w = x.shape
+    k, cg, r, s = weight.shape
+    if cg * groups != c:
+        raise ValueError("conv2d: weight channels %d x groups %d != input channels %d" % (cg, groups, c))
+    with torch.cuda.device(out.device):
+        rc = lib().ftb_conv2d_nchw_f32_noalloc(
+            x.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(),
+            n, c, h, w, k, r, s, stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
+            groups, _cfg_ptr(cfg), _status_ptr(status), _stream_ptr(stream))
+    if rc:
+        raise FtbError(rc, "ftb_conv2d_nchw_f32_noalloc")
 
 
 def dwconv2d_nchw_f32(x, weight, out, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), cfg=None,

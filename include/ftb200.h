@@ -104,6 +104,29 @@ int ftb_conv2d_nchw_f32(const float* in, const float* weight, const float* bias,
                         int groups, const ftb_config* cfg, void* workspace, size_t workspace_bytes,
                         int* status, void* stream);
 
+/* conv2d without a caller workspace - no counterpart in the reference.
+ *
+ * For callers that cannot allocate device memory: code that receives its input and output
+ * buffers from another runtime and has no allocator of its own, or a serving loop that bans
+ * allocation after start-up (cudaMalloc synchronises the device and may fail when memory is
+ * tight).  Same computation and arguments as ftb_conv2d_nchw_f32 minus the workspace: the
+ * channels-last copy of the input and the packed weights go into a fixed array of
+ * FTB_NOALLOC_SCRATCH_BYTES that the library keeps in device global memory (every GPU that loads
+ * the library holds it until the process exits).  The call allocates and frees nothing.
+ *
+ *   - a shape whose workspace (ftb_conv2d_workspace_bytes) exceeds FTB_NOALLOC_SCRATCH_BYTES is
+ *     refused with FTB_E_TOO_LARGE;
+ *   - the first call on a device looks up the array's device address (once per device, with that
+ *     device current); make that first call before starting any stream capture;
+ *   - all calls share the one array and it keeps what the last call wrote; nothing in it needs
+ *     clearing (each call rewrites every byte it later reads), but two calls that overlap in time
+ *     on the same GPU - different streams, or different threads - race on it: serialise them. */
+#define FTB_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024)
+int ftb_conv2d_nchw_f32_noalloc(const float* in, const float* weight, const float* bias, float* out,
+                                int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r,
+                                int64_t s, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h,
+                                int dil_w, int groups, const ftb_config* cfg, int* status, void* stream);
+
 /* out[N,C*f,P,Q] = depthwise conv of in[N,C,H,W] with w[C,f,R,S] (+ bias[C*f])
  * (flextensor/nn/ops.py:622-678 depthwise_conv2d_nchw; note the [C,f,R,S] weight layout). */
 int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const float* bias, float* out,
