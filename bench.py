@@ -237,6 +237,22 @@ def per_op_lines(peak_bf16, hbm_gbs):
     t = timed("conv2d_depthwise_(1, 256, 56, 56, 1, 3, 1, 1, 1)_cuda(0)", arrays, 2)
     out["depthwise_c256_56"] = {"us": t * 1e6, "gbs": 6431744 / t / 1e9, "frac_of_hbm_peak": 6431744 / t / 1e9 / hbm_gbs,
                                 "note": "L2-warm graph replay; 6.4 MB working set"}
+    # The same two kernels on batched variants of the shapes (batch 64), where the work is large
+    # enough for the bound to show: HBM traffic for depthwise, tensor time for conv2d.
+    from flextensor_b200.task import Task, depthwise_conv2d, register_task
+    big = Task("conv2d", "depthwise", depthwise_conv2d, (64, 256, 56, 56, 1, 3, 1, 1, 1), "cuda", 0)
+    register_task(big)
+    arrays = [torch.rand(64, 256, 56, 56, device="cuda"), dev(w), torch.empty(64, 256, 56, 56, device="cuda")]
+    t = timed(big.key, arrays, 2)
+    out["depthwise_c256_56_batch64"] = {"us": t * 1e6, "gbs": 64 * 6422528 / t / 1e9,
+                                        "frac_of_hbm_peak": 64 * 6422528 / t / 1e9 / hbm_gbs,
+                                        "note": "411 MB of input+output per launch, larger than L2"}
+    x64 = torch.randn(64, 64, 56, 56, device="cuda")
+    w64 = torch.randn(64, 64, 3, 3, device="cuda")
+    arrays = [x64, w64, torch.empty(64, 64, 56, 56, device="cuda")]
+    t = timed("conv2d_res3_(64, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)", arrays, 2)
+    out["conv2d_c64_56_k64_batch64_tf32"] = {"us": t * 1e6, "tflops": 64 * 231211008 / t / 1e12}
+    del arrays, x64, w64
     a8 = torch.randint(-127, 128, (8192, 8192), device="cuda", dtype=torch.int8)
     b8 = torch.randint(-127, 128, (8192, 8192), device="cuda", dtype=torch.int8)
     arrays = [a8, b8, torch.empty(8192, 8192, device="cuda", dtype=torch.int32)]
