@@ -162,7 +162,7 @@ def run_reference(args, rank):
         return
     import numpy as np
     from oracle import c_oracle as CO
-    cores = CO.max_threads()
+    cores = CO.use_all_cores()
     a, b = cpu_items(1)
     out = np.empty((1, DIM, DIM), dtype=np.uint16)
     tiles = pick_cpu_tiles(a, b, out)
@@ -189,6 +189,7 @@ def run_reference(args, rank):
 def cpu_baseline_leg(budget_s=12.0):
     import numpy as np
     from oracle import c_oracle as CO
+    CO.use_all_cores()
     a, b = cpu_items(1)
     out = np.empty((1, DIM, DIM), dtype=np.uint16)
     tiles = pick_cpu_tiles(a, b, out)
@@ -270,7 +271,7 @@ def run_ours(args, rank, world, local_rank):
     from flextensor_b200 import backend
     from flextensor_b200.runtime import build
     from flextensor_b200.scheduler import schedule_with_config
-    from flextensor_b200.sharded import BatchSharded, shard_range
+    from flextensor_b200.sharded import BatchSharded, PeerGatheredOutput, shard_range
     from flextensor_b200.task import Task, batch_gemm, register_task
     from flextensor_b200.templates import knobs_to_config
     from flextensor_b200.utils import Config
@@ -303,14 +304,35 @@ def run_ours(args, rank, world, local_rank):
     c_local = torch.empty(local, DIM, DIM, device=device, dtype=torch.bfloat16)
     c_full = torch.empty(BATCH, DIM, DIM, device=device, dtype=torch.bfloat16) if world > 1 else c_local
     sharder = BatchSharded(BATCH) if world > 1 else None
+    # N > 1: the gather is fused into the GEMM epilogue (bulk stores into every rank's copy of the
+    # output over NVLink) when symmetric memory is available, else one NCCL all-gather per step.
+    peer_out, fused_why = None, None
+    if world > 1 and not args.nccl_gather:
+        try:
+            peer_out = PeerGatheredOutput(BATCH, DIM, DIM, torch.bfloat16)
+            dst_ptrs = peer_out.slice_ptrs(lo)
+            c_full = peer_out.tensor
+            c_local = c_full[lo:hi]
+            status_word = backend.new_status(device)
+        except Exception as exc:  # reported in the JSON line, the NCCL path is used instead
+            peer_out, fused_why = None, "%s: %s" % (type(exc).__name__, exc)
 
     def compute(lo_, hi_):
         assert (lo_, hi_) == (0, local)
         func(a, b, c_local)
 
+    def kernel_only():
+        if peer_out is not None:
+            backend.bgemm_bf16_multi(a, b, dst_ptrs, DIM, DIM, cfg=KNOBS, status=status_word)
+        else:
+            func(a, b, c_local)
+
     def step():
         if sharder is None:
             func(a, b, c_local)
+        elif peer_out is not None:
+            kernel_only()
+            peer_out.barrier()
         else:
             sharder.run(compute, c_local, c_full, chunks=1)
 
@@ -325,7 +347,14 @@ def run_ours(args, rank, world, local_rank):
     got = c_local[0].float().cpu().numpy()
     assert O.bf16_output_ok(got, O.gemm(a0, b0, out_dtype=np.float64)), "bench output does not match the oracle"
     if world > 1:
+        barrier()
         assert torch.equal(c_full[lo:hi], c_local)
+        # every rank's first item is the oracle's item of that index: the gathered copy must hold them all
+        for r in range(world):
+            first = shard_range(BATCH, world, r)[0]
+            ar, br = O.batch_gemm_item(first, DIM, DIM, DIM, seed=3)
+            assert O.bf16_output_ok(c_full[first].float().cpu().numpy(), O.gemm(ar, br, out_dtype=np.float64)), \
+                "rank %d does not hold rank %d's slice" % (rank, r)
 
     for _ in range(args.warmup):
         step()
@@ -340,15 +369,19 @@ def run_ours(args, rank, world, local_rank):
     ev[0].record(stream)
     for i in range(args.steps):
         kern_ev[i][0].record(stream)
-        func(a, b, c_local)
+        kernel_only()
         kern_ev[i][1].record(stream)
-        if sharder is not None:
+        if peer_out is not None:
+            peer_out.barrier()
+        elif sharder is not None:
             sharder.gather(c_local, c_full)
     ev[1].record(stream)
     barrier()
     launches = backend.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     func.check()
+    if peer_out is not None:
+        backend.check_status(status_word)
     total_ms = ev[0].elapsed_time(ev[1])
     kernel_ms = sum(s0.elapsed_time(s1) for s0, s1 in kern_ev) / args.steps
     t = torch.tensor([total_ms, kernel_ms, float(launches)], device=device, dtype=torch.float64)
@@ -409,7 +442,11 @@ def run_ours(args, rank, world, local_rank):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "sharding": "batch 64/%d items per GPU" % world,
-                       "collective": "none" if world == 1 else "NCCL all-gather of the bf16 output (512 MiB total)",
+                       "collective": ("none" if world == 1 else
+                                      "fused: epilogue bulk stores into every rank's output over NVLink + one barrier"
+                                      if peer_out is not None else
+                                      "NCCL all-gather of the bf16 output (512 MiB total)" +
+                                      (" [fused path unavailable: %s]" % fused_why if fused_why else "")),
                        "l2": "inputs (1 GiB) larger than L2; no flush needed", "knobs": KNOBS,
                        "kernel": "umma_gemm_kernel<bf16, bf16 out, cta_group::2>"},
             "compute_only_value": compute_only,
@@ -439,6 +476,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the per-operator lines of the other four configs")
+    ap.add_argument("--nccl-gather", action="store_true", help="N > 1: return the output with an NCCL all-gather "
+                    "instead of the fused epilogue stores")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

@@ -112,6 +112,9 @@ def lib():
         handle.ftb_bgemm_f32.argtypes = [vp, vp, vp, i64, i64, i64, i64, i32, i32, cfgp, vp, vp]
         handle.ftb_bgemm_bf16.restype = i32
         handle.ftb_bgemm_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i32, i32, i32, cfgp, vp, vp]
+        handle.ftb_bgemm_bf16_multi.restype = i32
+        handle.ftb_bgemm_bf16_multi.argtypes = [vp, vp, ctypes.POINTER(vp), i32, i64, i64, i64, i64, i32, i32, i32,
+                                                cfgp, vp, vp]
         handle.ftb_gemm_s8.restype = i32
         handle.ftb_gemm_s8.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, cfgp, vp, vp]
         handle.ftb_conv2d_workspace_bytes.restype = ctypes.c_size_t
@@ -129,7 +132,7 @@ def lib():
 
 EXPORTED_SYMBOLS = (
     "ftb_version", "ftb_strerror", "ftb_last_cuda_error", "ftb_device_check", "ftb_validate",
-    "ftb_launch_count", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_gemm_s8",
+    "ftb_launch_count", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_bgemm_bf16_multi", "ftb_gemm_s8",
     "ftb_conv2d_workspace_bytes", "ftb_conv2d_nchw_f32", "ftb_conv2d_nchw_f32_noalloc", "ftb_dwconv2d_nchw_f32",
 )
 
@@ -235,6 +238,31 @@ def bgemm_bf16(a, b, c, trans_a=False, trans_b=False, cfg=None, status=None, str
                                   _status_ptr(status), _stream_ptr(stream))
     if rc:
         raise FtbError(rc, "ftb_bgemm_bf16")
+
+
+def bgemm_bf16_multi(a, b, dst_ptrs, m, n, trans_a=False, trans_b=False, out_f32=False, cfg=None, status=None,
+                     stream=None):
+    """Batched bf16 GEMM whose result goes to several buffers at once.
+
+    ``dst_ptrs``: 1..8 device addresses (ints), each of a [batch, m, n] buffer on this GPU or a
+    mapped buffer of a peer GPU (e.g. ``symm_mem`` buffer pointers plus the slice offset).
+    """
+    _check(a, torch.bfloat16, "a")
+    _check(b, torch.bfloat16, "b")
+    batch = a.shape[0]
+    k = a.shape[1] if trans_a else a.shape[2]
+    if (tuple(a.shape) != ((batch, k, m) if trans_a else (batch, m, k)) or
+            tuple(b.shape) != ((batch, n, k) if trans_b else (batch, k, n))):
+        raise ValueError("bgemm_bf16_multi: shapes do not agree: %s %s -> (%d, %d, %d)" % (a.shape, b.shape, batch, m, n))
+    if not 1 <= len(dst_ptrs) <= 8:
+        raise ValueError("between 1 and 8 destinations")
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*[ctypes.c_void_p(int(p)) for p in dst_ptrs])
+    with torch.cuda.device(a.device):
+        rc = lib().ftb_bgemm_bf16_multi(a.data_ptr(), b.data_ptr(), arr, len(dst_ptrs), batch, m, n, k,
+                                        int(trans_a), int(trans_b), int(out_f32), _cfg_ptr(cfg),
+                                        _status_ptr(status), _stream_ptr(stream))
+    if rc:
+        raise FtbError(rc, "ftb_bgemm_bf16_multi")
 
 
 def gemm_s8(a, b, c, trans_a=False, trans_b=False, cfg=None, status=None, stream=None):

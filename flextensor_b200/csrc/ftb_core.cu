@@ -114,7 +114,9 @@ int ftb_validate(int op, const ftb_config* cfg, int64_t m, int64_t n, int64_t k)
   if (cfg->cluster == 2 && cfg->tile_n != 0 && cfg->tile_n < 64) return FTB_E_BAD_CONFIG;
   if (cfg->tile_n != 0 && cfg->stages != 0) {
     const size_t per_cta = static_cast<size_t>(cfg->tile_n) / (cfg->cluster == 2 ? 2 : 1);
-    const size_t smem = static_cast<size_t>(cfg->stages) * (16384 + per_cta * 128) * (split3 ? 2 : 1) + 1024;
+    // GEMM kernels also hold two 16 KB output slabs for the bulk-store epilogue
+    const size_t smem = static_cast<size_t>(cfg->stages) * (16384 + per_cta * 128) * (split3 ? 2 : 1) + 1024 +
+                        (op == 3 ? 0 : 32768);
     if (smem > 227 * 1024 - 2048) return FTB_E_BAD_CONFIG;
   }
   if (cfg->raster < 0 || cfg->raster > 2 || cfg->group_m < 0) return FTB_E_BAD_CONFIG;

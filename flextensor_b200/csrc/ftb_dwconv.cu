@@ -121,6 +121,65 @@ __global__ void dwconv_kernel(const DwParams p) {
   }
 }
 
+// 3x3, stride 1, dilation 1, pad_w = 1, W % 4 == 0: no staging at all.  A thread owns a
+// 4-wide, RH-tall block of outputs of one input plane: it loads RH + 2 input rows as one
+// aligned 16-byte vector each plus the two halo scalars (which hit in L1: the neighbouring
+// threads load those lines as vectors), keeps them in registers and writes RH vectors.  Every
+// load of a thread is issued before the first use, so a CTA keeps (RH + 2) * 16 B per thread in
+// flight - what a bandwidth-bound kernel needs - and there is no barrier anywhere.
+template <int RH>
+__global__ void __launch_bounds__(256) dwconv3x3_direct_kernel(const DwParams p, long long items, int vcols,
+                                                               int rblocks) {
+  const long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (item >= items) return;
+  const int vc = static_cast<int>(item % vcols);
+  const int rb = static_cast<int>((item / vcols) % rblocks);
+  const long long plane = item / (static_cast<long long>(vcols) * rblocks);  // n * C + c
+  const int c = static_cast<int>(plane % p.C);
+  const long long n = plane / p.C;
+  const int ow = vc * 4;
+  const int oh0 = rb * RH;
+  const float* src = p.in + plane * p.H * p.W;
+
+  float x[RH + 2][6];
+#pragma unroll
+  for (int i = 0; i < RH + 2; ++i) {
+    const int h = oh0 + i - p.pad_h;
+    const bool row_ok = h >= 0 && h < p.H && (oh0 + i - 2 < p.P);  // rows past the last output are not needed
+    const float* rp = src + static_cast<long long>(row_ok ? h : 0) * p.W + ow;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    float left = 0.f, right = 0.f;
+    if (row_ok) {
+      v = __ldg(reinterpret_cast<const float4*>(rp));
+      if (ow > 0) left = __ldg(rp - 1);
+      if (ow + 4 < p.W) right = __ldg(rp + 4);
+    }
+    x[i][0] = left; x[i][1] = v.x; x[i][2] = v.y; x[i][3] = v.z; x[i][4] = v.w; x[i][5] = right;
+  }
+
+  for (int f = 0; f < p.F; ++f) {
+    const int co = c * p.F + f;
+    float wv[9];
+#pragma unroll
+    for (int t = 0; t < 9; ++t) wv[t] = __ldg(p.w + static_cast<long long>(co) * 9 + t);
+    const float b = p.bias ? __ldg(p.bias + co) : 0.f;
+    float* dst = p.out + ((n * p.C * p.F + co) * p.P + oh0) * p.Q + ow;
+#pragma unroll
+    for (int i = 0; i < RH; ++i) {
+      if (oh0 + i >= p.P) break;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < 3; ++r)
+#pragma unroll
+        for (int s = 0; s < 3; ++s)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[j] = fmaf(x[i + r][j + s], wv[r * 3 + s], acc[j]);
+      *reinterpret_cast<float4*>(dst + static_cast<long long>(i) * p.Q) =
+          make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b);
+    }
+  }
+}
+
 }  // namespace ftb
 
 extern "C" int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const float* bias, float* out,
@@ -158,6 +217,35 @@ extern "C" int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const
   int pitch = max_col + 1;
   if (pitch < p.lead + p.W) pitch = p.lead + p.W;
   p.tile_pitch = (pitch + 3) / 4 * 4;
+
+  // Register-tiled path: 3x3, stride 1, dilation 1, pad_w 1, 16-byte aligned rows.
+  // cfg->tile_h selects the rows per thread (4 or 8; other values keep the staged kernel).
+  const bool direct_ok = r == 3 && s == 3 && stride_h == 1 && stride_w == 1 && dil_h == 1 && dil_w == 1 &&
+                         pad_w == 1 && (w % 4 == 0) && Q == w &&
+                         ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const int want_rows = cfg ? cfg->tile_h : 0;
+  if (direct_ok && (want_rows == 0 || want_rows == 4 || want_rows == 8)) {
+    int threads_d = cfg && cfg->threads > 0 ? cfg->threads : 128;
+    if (threads_d < 32 || threads_d > 256 || threads_d % 32) return FTB_E_BAD_CONFIG;
+    const int rh = want_rows == 4 ? 4 : 8;
+    const int vcols = p.W / 4;
+    const int rblocks = (p.P + rh - 1) / rh;
+    const long long items = static_cast<long long>(n) * c * vcols * rblocks;
+    const long long blocks_d = (items + threads_d - 1) / threads_d;
+    if (blocks_d > 0x7fffffffll) return FTB_E_TOO_LARGE;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (rh == 4)
+      dwconv3x3_direct_kernel<4><<<static_cast<unsigned>(blocks_d), threads_d, 0, stream>>>(p, items, vcols, rblocks);
+    else
+      dwconv3x3_direct_kernel<8><<<static_cast<unsigned>(blocks_d), threads_d, 0, stream>>>(p, items, vcols, rblocks);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      set_last_cuda_error(static_cast<int>(e));
+      return FTB_E_CUDA;
+    }
+    return FTB_OK;
+  }
 
   const int sms = sm_count();
   int threads = cfg && cfg->threads > 0 ? cfg->threads : 256;

@@ -74,10 +74,12 @@ static uint32_t make_idesc(const KindInfo& ki, int bn, int a_mn, int b_mn, int m
   return d;
 }
 
-static size_t smem_needed(int bn, int stages, bool split3) {
+// `bn` = B rows/columns staged per CTA; `epilogue_bytes` = staging of the TMA-store epilogue.
+static size_t smem_needed(int bn, int stages, bool split3, size_t epilogue_bytes = 0) {
   return static_cast<size_t>(stages) * (kATileBytes + static_cast<size_t>(bn) * 128) * (split3 ? 2 : 1) +
-         1024;
+         1024 + epilogue_bytes;
 }
+constexpr size_t kEpilogueStaging = 2 * kEpiBufBytes;
 constexpr size_t kSmemLimit = 227 * 1024 - 2048;  // leave room for the static barriers
 
 // N extent a single TMA box covers for an N-contiguous B operand.
@@ -94,7 +96,7 @@ static double tile_rate(int cluster, int bn) {
 // item, `batch` items; `allow_pair` is false for conv and 3xTF32.
 static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split3, int b_mn, bool allow_pair,
                           long long batch, long long m_rows, long long n, int num_kb, bool f32_out,
-                          int num_sms, ftb_config* out) {
+                          int num_sms, ftb_config* out, size_t epilogue_bytes = 0) {
   ftb_config c;
   memset(&c, 0, sizeof(c));
   if (user) c = *user;
@@ -146,12 +148,12 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
   const int bn_cta = c.tile_n / c.cluster;
   if (c.stages == 0) {
     c.stages = kMaxStages;
-    while (c.stages > 2 && smem_needed(bn_cta, c.stages, split3) > kSmemLimit) --c.stages;
+    while (c.stages > 2 && smem_needed(bn_cta, c.stages, split3, epilogue_bytes) > kSmemLimit) --c.stages;
     if (c.stages > num_kb + 1 && num_kb >= 1) c.stages = num_kb + 1 > 2 ? num_kb + 1 : 2;
     if (c.stages > kMaxStages) c.stages = kMaxStages;
   }
   if (c.stages < 2 || c.stages > kMaxStages) return FTB_E_BAD_CONFIG;
-  if (smem_needed(bn_cta, c.stages, split3) > kSmemLimit) return FTB_E_BAD_CONFIG;
+  if (smem_needed(bn_cta, c.stages, split3, epilogue_bytes) > kSmemLimit) return FTB_E_BAD_CONFIG;
   if (c.raster < 0 || c.raster > 2) return FTB_E_BAD_CONFIG;
   if (c.raster == 2 && c.group_m == 0) c.group_m = 8;
   if (c.group_m < 0) return FTB_E_BAD_CONFIG;
@@ -164,10 +166,10 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
 }
 
 template <int KIND, int OUT, bool SPLIT3, bool PAIR>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const UmmaParams& p, int ctas,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps& tc, const UmmaParams& p,
+                  int ctas, cudaStream_t stream) {
   auto kern = umma_gemm_kernel<KIND, OUT, SPLIT3, PAIR>;
-  const size_t smem = smem_needed(p.b_bytes / 128, p.stages, SPLIT3);
+  const size_t smem = smem_needed(p.b_bytes / 128, p.stages, SPLIT3, p.tma_store ? kEpilogueStaging : 0);
   // The opt-in shared-memory size is a per-device attribute of the function.
   static std::mutex mu;
   static bool done[64] = {false};
@@ -200,7 +202,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const UmmaParams
     lc.attrs = attr;
     lc.numAttrs = 1;
   }
-  cudaError_t e = cudaLaunchKernelEx(&lc, kern, ta, tb, p);
+  cudaError_t e = cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p);
   count_launch();
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -211,20 +213,20 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const UmmaParams
 }
 
 static int dispatch(int kind, int out, bool split3, bool pair, const CUtensorMap& ta, const CUtensorMap& tb,
-                    const UmmaParams& p, int ctas, cudaStream_t stream) {
+                    const StoreMaps& tc, const UmmaParams& p, int ctas, cudaStream_t stream) {
   if (pair) {
     if (split3) return FTB_E_BAD_CONFIG;
-    if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false, true>(ta, tb, p, ctas, stream);
-    if (kind == KIND_BF16 && out == OUT_F32) return launch<KIND_BF16, OUT_F32, false, true>(ta, tb, p, ctas, stream);
-    if (kind == KIND_I8 && out == OUT_S32) return launch<KIND_I8, OUT_S32, false, true>(ta, tb, p, ctas, stream);
-    if (kind == KIND_TF32 && out == OUT_F32) return launch<KIND_TF32, OUT_F32, false, true>(ta, tb, p, ctas, stream);
+    if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false, true>(ta, tb, tc, p, ctas, stream);
+    if (kind == KIND_BF16 && out == OUT_F32) return launch<KIND_BF16, OUT_F32, false, true>(ta, tb, tc, p, ctas, stream);
+    if (kind == KIND_I8 && out == OUT_S32) return launch<KIND_I8, OUT_S32, false, true>(ta, tb, tc, p, ctas, stream);
+    if (kind == KIND_TF32 && out == OUT_F32) return launch<KIND_TF32, OUT_F32, false, true>(ta, tb, tc, p, ctas, stream);
     return FTB_E_BAD_ARG;
   }
-  if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false, false>(ta, tb, p, ctas, stream);
-  if (kind == KIND_BF16 && out == OUT_F32) return launch<KIND_BF16, OUT_F32, false, false>(ta, tb, p, ctas, stream);
-  if (kind == KIND_I8 && out == OUT_S32) return launch<KIND_I8, OUT_S32, false, false>(ta, tb, p, ctas, stream);
-  if (kind == KIND_TF32 && out == OUT_F32 && !split3) return launch<KIND_TF32, OUT_F32, false, false>(ta, tb, p, ctas, stream);
-  if (kind == KIND_TF32 && out == OUT_F32 && split3) return launch<KIND_TF32, OUT_F32, true, false>(ta, tb, p, ctas, stream);
+  if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false, false>(ta, tb, tc, p, ctas, stream);
+  if (kind == KIND_BF16 && out == OUT_F32) return launch<KIND_BF16, OUT_F32, false, false>(ta, tb, tc, p, ctas, stream);
+  if (kind == KIND_I8 && out == OUT_S32) return launch<KIND_I8, OUT_S32, false, false>(ta, tb, tc, p, ctas, stream);
+  if (kind == KIND_TF32 && out == OUT_F32 && !split3) return launch<KIND_TF32, OUT_F32, false, false>(ta, tb, tc, p, ctas, stream);
+  if (kind == KIND_TF32 && out == OUT_F32 && split3) return launch<KIND_TF32, OUT_F32, true, false>(ta, tb, tc, p, ctas, stream);
   return FTB_E_BAD_ARG;
 }
 
@@ -261,8 +263,11 @@ static void operand_layout(const KindInfo& ki, int mn_major, int tile_extent, in
 
 int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64_t batch, int64_t m,
                  int64_t n, int64_t k, int trans_a, int trans_b, const ftb_config* user, int* status,
-                 void* stream_v) {
+                 void* stream_v, void* const* extra_dst, int num_extra) {
   if (!a || !b || !c) return FTB_E_BAD_ARG;
+  if (num_extra < 0 || num_extra > kMaxDst - 1 || (num_extra > 0 && !extra_dst)) return FTB_E_BAD_ARG;
+  for (int d = 0; d < num_extra; ++d)
+    if (!extra_dst[d]) return FTB_E_BAD_ARG;
   if (batch <= 0 || m <= 0 || n <= 0 || k <= 0) return FTB_E_BAD_ARG;
   if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30) || batch > (1ll << 24)) return FTB_E_TOO_LARGE;
   int rc = device_ok();
@@ -278,10 +283,20 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   if ((a_pitch & 15) || (b_pitch & 15)) return FTB_E_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return FTB_E_UNSUPPORTED;
 
+  // The staged (bulk tensor store) epilogue needs 16-byte aligned output rows and bases.
+  const int out_esize = out == OUT_BF16 ? 2 : 4;
+  bool store_ok = ((n * out_esize) & 15) == 0 && (reinterpret_cast<uintptr_t>(c) & 15) == 0;
+  for (int d = 0; d < num_extra; ++d) store_ok = store_ok && (reinterpret_cast<uintptr_t>(extra_dst[d]) & 15) == 0;
+  {
+    const char* e = getenv("FTB_EPILOGUE");  // "direct" forces per-thread global stores (diagnostics)
+    if (e && strcmp(e, "direct") == 0) store_ok = false;
+  }
+
   const int num_sms = sm_count();
   const int num_kb = static_cast<int>((k + ki.kblk - 1) / ki.kblk);
   ftb_config cfg;
-  rc = resolve_config(user, ki, split3, b_mn, !split3, batch, m, n, num_kb, out == OUT_F32, num_sms, &cfg);
+  rc = resolve_config(user, ki, split3, b_mn, !split3, batch, m, n, num_kb, out == OUT_F32, num_sms, &cfg,
+                      kEpilogueStaging);
   if (rc) return rc;
   const bool pair = cfg.cluster == 2;
   const int tile_m = pair ? 2 * kTileM : kTileM;
@@ -318,10 +333,28 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   p.c_batch_stride = m * n;
   p.status = status ? status : fallback_status();
   if (!p.status) return FTB_E_CUDA;
+  p.slab_cols = 128 / out_esize;
+  p.tma_store = (store_ok && p.split_k == 1 && p.bn % p.slab_cols == 0) ? 1 : 0;
+  p.num_dst = 1 + num_extra;
+  if (num_extra > 0 && !p.tma_store) return FTB_E_UNSUPPORTED;  // several destinations only through bulk stores
 
   // Tensor maps: dim 0 is the contiguous one; batch is the outermost.
   CUtensorMap ta, tb;
+  StoreMaps tc;
+  memset(&tc, 0, sizeof(tc));
   const uint32_t ones[3] = {1, 1, 1};
+  if (p.tma_store) {
+    const CUtensorMapDataType odt = out == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                  : out == OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                   : CU_TENSOR_MAP_DATA_TYPE_INT32;
+    uint64_t dims[3] = {static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(batch)};
+    uint64_t strides[2] = {static_cast<uint64_t>(n) * out_esize, static_cast<uint64_t>(m) * n * out_esize};
+    uint32_t box[3] = {static_cast<uint32_t>(p.slab_cols), static_cast<uint32_t>(kTileM), 1};
+    for (int d = 0; d < p.num_dst; ++d) {
+      rc = make_tmap(&tc.dst[d], odt, 3, d == 0 ? c : extra_dst[d - 1], dims, strides, box, ones);
+      if (rc) return rc;
+    }
+  }
   {
     uint64_t dims[3], strides[2];
     uint32_t box[3];
@@ -371,7 +404,7 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   } else if (ctas > total) {
     ctas = static_cast<int>(total);
   }
-  return dispatch(kind, out, split3, pair, ta, tb, p, ctas, stream);
+  return dispatch(kind, out, split3, pair, ta, tb, tc, p, ctas, stream);
 }
 
 // ------------------------------------------------------------------ conv2d as implicit GEMM
@@ -565,7 +598,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     if (total > 0x7fffffffll) return FTB_E_TOO_LARGE;
     int ctas = cfg.ctas > 0 ? cfg.ctas : num_sms;
     if (ctas > total) ctas = static_cast<int>(total);
-    rc = dispatch(KIND_TF32, OUT_F32, split3, false, ta, tb, p, ctas, stream);
+    StoreMaps tc;
+    memset(&tc, 0, sizeof(tc));
+    rc = dispatch(KIND_TF32, OUT_F32, split3, false, ta, tb, tc, p, ctas, stream);
     if (rc) return rc;
   }
   return FTB_OK;
@@ -579,26 +614,34 @@ extern "C" {
 int ftb_gemm_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int trans_a,
                  int trans_b, const ftb_config* cfg, int* status, void* stream) {
   return ftb::gemm_generic(ftb::KIND_TF32, ftb::OUT_F32, a, b, c, 1, m, n, k, trans_a, trans_b, cfg,
-                           status, stream);
+                           status, stream, nullptr, 0);
 }
 
 int ftb_bgemm_f32(const float* a, const float* b, float* c, int64_t batch, int64_t m, int64_t n, int64_t k,
                   int trans_a, int trans_b, const ftb_config* cfg, int* status, void* stream) {
   return ftb::gemm_generic(ftb::KIND_TF32, ftb::OUT_F32, a, b, c, batch, m, n, k, trans_a, trans_b, cfg,
-                           status, stream);
+                           status, stream, nullptr, 0);
 }
 
 int ftb_bgemm_bf16(const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n, int64_t k,
                    int trans_a, int trans_b, int out_f32, const ftb_config* cfg, int* status,
                    void* stream) {
   return ftb::gemm_generic(ftb::KIND_BF16, out_f32 ? ftb::OUT_F32 : ftb::OUT_BF16, a, b, c, batch, m, n,
-                           k, trans_a, trans_b, cfg, status, stream);
+                           k, trans_a, trans_b, cfg, status, stream, nullptr, 0);
+}
+
+int ftb_bgemm_bf16_multi(const void* a, const void* b, void* const* c_dst, int num_dst, int64_t batch, int64_t m,
+                         int64_t n, int64_t k, int trans_a, int trans_b, int out_f32, const ftb_config* cfg,
+                         int* status, void* stream) {
+  if (!c_dst || num_dst < 1 || num_dst > ftb::kMaxDst) return FTB_E_BAD_ARG;
+  return ftb::gemm_generic(ftb::KIND_BF16, out_f32 ? ftb::OUT_F32 : ftb::OUT_BF16, a, b, c_dst[0], batch, m, n,
+                           k, trans_a, trans_b, cfg, status, stream, c_dst + 1, num_dst - 1);
 }
 
 int ftb_gemm_s8(const int8_t* a, const int8_t* b, int32_t* c, int64_t m, int64_t n, int64_t k,
                 int trans_a, int trans_b, const ftb_config* cfg, int* status, void* stream) {
   return ftb::gemm_generic(ftb::KIND_I8, ftb::OUT_S32, a, b, c, 1, m, n, k, trans_a, trans_b, cfg,
-                           status, stream);
+                           status, stream, nullptr, 0);
 }
 
 size_t ftb_conv2d_workspace_bytes(int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r,

@@ -16,9 +16,10 @@ int sm_count();
 // Device address of the library's own status word, used when the caller passes none.
 int* fallback_status();
 
+// `extra_dst`: further buffers (num_extra of them) that receive the same result as `c`.
 int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64_t batch, int64_t m,
                  int64_t n, int64_t k, int trans_a, int trans_b, const ftb_config* user, int* status,
-                 void* stream);
+                 void* stream, void* const* extra_dst, int num_extra);
 
 int conv2d_generic(const float* in, const float* weight, const float* bias, float* out, int64_t n,
                    int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,

@@ -62,6 +62,19 @@ struct UmmaParams {
   int conv_ktot, conv_koff;  // output channels of the whole conv / first channel of this group
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int* status;
+  // TMA-store epilogue: tma_store != 0 stages 128-byte wide output slabs in shared memory and
+  // writes each with one bulk tensor store per destination.
+  int tma_store, num_dst, slab_cols;
+};
+
+constexpr int kMaxDst = 8;
+constexpr uint32_t kEpiBufBytes = kTileM * 128;  // one staged output slab: 128 rows x 128 B
+
+// Tensor maps of the output for the TMA-store epilogue: one per destination buffer (the
+// result can be written to several buffers at once, e.g. the same slice of every rank's
+// gathered output over NVLink).
+struct StoreMaps {
+  CUtensorMap dst[kMaxDst];
 };
 
 struct TileCoord {
@@ -96,7 +109,7 @@ __device__ __forceinline__ TileCoord decode_tile(const UmmaParams& p, int t) {
 template <int KIND, int OUT, bool SPLIT3, bool PAIR>
 __global__ void __launch_bounds__(SPLIT3 ? 320 : 192, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ UmmaParams p) {
+                 const __grid_constant__ StoreMaps tmap_c, const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
@@ -336,13 +349,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int bn = p.bn, N = p.N;
     const uint32_t tempty_sig0 =
         PAIR ? map_to_cta(smem_u32(&bar_tempty[0]), 0) : smem_u32(&bar_tempty[0]);
+    const uint32_t epi_base = smem_base + stages * stage_bytes;  // two output slabs after the stages
+    uint32_t slab_seq = 0;
     int local = 0;
     for (int t = unit; t < total_tiles; t += units, ++local) {
       const TileCoord tc = decode_tile(p, t);
       const uint32_t acc = local & 1;
       const uint32_t aph = (local >> 1) & 1u;
       const bool has_work = tc.ks * kb_per_split < num_kb;  // a split past the K range adds nothing
-      const bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull[acc]), aph, &abort_flag));
+      bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull[acc]), aph, &abort_flag));
+      // The staged epilogue synchronises the four warps with each other: they must agree.
+      if (p.tma_store) got = named_barrier_all(2, 128, got);
       if (!got) {
         if (lane == 0) {
           atomicOr(p.status, FTB_DEV_WAIT_TMEMFULL);
@@ -374,6 +391,67 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         row_off = tc.b * p.c_batch_stride + static_cast<long long>(gm) * p.ldc;
       }
       row_ok = row_ok && has_work;
+
+      if (p.tma_store) {
+        // ---- staged epilogue: TMEM -> registers -> swizzled shared slab -> bulk tensor store(s)
+        const int slab_cols = p.slab_cols;  // 64 for bf16 output, 32 for 32-bit output
+        const bool leader = (warp == 2 && lane == 0);
+        const int m0 = tc.m * p.pair_m + static_cast<int>(cta_rank) * kTileM;
+        const uint32_t swz = static_cast<uint32_t>(row & 7);
+        for (int c = 0; c < bn; c += slab_cols, ++slab_seq) {
+          const uint32_t buf = epi_base + (slab_seq & 1u) * kEpiBufBytes;
+          // The store that used this buffer two slabs ago must have finished reading it.
+          if (leader) bulk_wait_group_read<1>();
+          named_barrier_sync(1, 128);
+          const uint32_t row_addr = buf + static_cast<uint32_t>(row) * 128u;
+          if constexpr (OUT == OUT_BF16) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t v[32];
+              tmem_ld_32x32(taddr + c + half * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * q]),
+                                                            __uint_as_float(v[j * 8 + 2 * q + 1]));
+                  w[q] = *reinterpret_cast<uint32_t*>(&h2);
+                }
+                const uint32_t chunk = static_cast<uint32_t>(half * 4 + j);
+                st_shared_v4(row_addr + ((chunk ^ swz) << 4), w[0], w[1], w[2], w[3]);
+              }
+            }
+          } else {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ swz) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2],
+                           v[4 * j + 3]);
+          }
+          if (c + slab_cols >= bn) {
+            // Last read of this accumulator: hand it back to the MMA issuer.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (PAIR) mbar_arrive_cluster(tempty_sig0 + 8 * acc);
+              else mbar_arrive(tempty_sig0 + 8 * acc);
+            }
+          }
+          fence_proxy_async_smem();  // the slab must be visible to the bulk-copy engine
+          named_barrier_sync(1, 128);
+          if (leader) {
+            if (has_work && n0 + c < N) {
+              for (int d = 0; d < p.num_dst; ++d) tma_store_3d(&tmap_c.dst[d], buf, n0 + c, m0, tc.b);
+            }
+            bulk_commit_group();
+          }
+        }
+        continue;
+      }
 
       for (int c = 0; c < bn; c += 32) {
         uint32_t v[32];
@@ -446,6 +524,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     }
+    // Every bulk store of this CTA has been performed before the kernel ends.
+    if (p.tma_store && warp == 2 && lane == 0) bulk_wait_group<0>();
     __syncwarp();
   } else {
     // ------------------------------------------------------------ 3xTF32 split stage

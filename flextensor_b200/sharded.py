@@ -9,6 +9,12 @@ NVLink via ``torch.distributed``).  ``run`` can overlap that gather with compute
 splitting the local slice into chunks: chunk i is gathered on a side stream while chunk
 i+1 is computed.
 
+``PeerGatheredOutput`` removes the collective altogether: the gathered output lives in
+symmetric memory (every rank maps every rank's buffer over NVLink) and the GEMM epilogue writes
+each finished slab of a rank's slice into all ranks' buffers with bulk tensor stores
+(``ftb_bgemm_bf16_multi``), so the transfer overlaps the math tile by tile; what is left of the
+all-gather is one barrier after the kernel.  Plain peer stores only (no multicast objects).
+
 One process per GPU; ``torch.distributed`` must be initialised by the caller.
 """
 import torch
@@ -89,3 +95,35 @@ class BatchSharded(object):
                 outs = [full_view[r, lo:hi] for r in range(self.world)]
                 dist.all_gather(outs, out_local[lo:hi], group=self.group)
         main.wait_stream(comm)
+
+
+class PeerGatheredOutput(object):
+    """A [batch, m, n] output buffer present on every rank and writable by every rank.
+
+    ``slice_ptrs(lo)`` gives, own rank first, the device address of batch item ``lo`` in each
+    rank's buffer - the destination list of ``backend.bgemm_bf16_multi``.  ``barrier()`` must
+    follow the launch on the same stream before any rank reads the gathered result: it orders
+    every rank's stores before every rank's reads.
+    """
+
+    def __init__(self, batch, m, n, dtype=torch.bfloat16, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.shape = (batch, m, n)
+        self.tensor = symm_mem.empty(batch, m, n, dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.item_bytes = m * n * self.tensor.element_size()
+        if len(self.ptrs) != self.world:
+            raise RuntimeError("symmetric memory gave %d buffers for %d ranks" % (len(self.ptrs), self.world))
+
+    def slice_ptrs(self, lo):
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        return [self.ptrs[r] + lo * self.item_bytes for r in order]
+
+    def barrier(self):
+        self.handle.barrier()

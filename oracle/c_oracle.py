@@ -55,6 +55,16 @@ def max_threads():
     return int(lib().fto_max_threads())
 
 
+def use_all_cores():
+    """Let the tiled nests use every core this process may run on; returns the thread count."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().fto_set_threads(ctypes.c_int(n))
+    return max_threads()
+
+
 def gemm_f32_naive(a, b, ta=False, tb=False, acc64=True):
     m = a.shape[1] if ta else a.shape[0]
     k = a.shape[0] if ta else a.shape[1]

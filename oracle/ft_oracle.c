@@ -47,6 +47,16 @@ int fto_max_threads(void) {
 #endif
 }
 
+/* Number of OpenMP threads the tiled nests use from now on (launchers such as torchrun export
+ * OMP_NUM_THREADS=1; the timed CPU baseline asks for every core it is allowed to run on). */
+void fto_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------ part 1: naive */
 
 /* C[i,j] = sum_k opA(i,k) * opB(k,j); double accumulation when acc64 != 0. */

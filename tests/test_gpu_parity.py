@@ -175,6 +175,39 @@ def test_bgemm_bf16_full_size_properties(B, status):
     assert torch.equal(c, c2)
 
 
+def test_bgemm_bf16_several_destinations(B, status):
+    """One launch, the result in three buffers (stands for: the same slice of every rank's gathered
+    output; here all three are local), each at its own batch offset of a larger buffer."""
+    items = [O.batch_gemm_item(i, 200, 136, 72, seed=33) for i in range(2)]
+    a = np.stack([i[0] for i in items])
+    b = np.stack([i[1] for i in items])
+    want = O.batch_gemm(a, b)
+    full = [torch.full((5, 200, 136), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    offsets = [0, 1, 3]
+    ptrs = [f[o:].data_ptr() for f, o in zip(full, offsets)]
+    B.bgemm_bf16_multi(bf16_dev(a), bf16_dev(b), ptrs, 200, 136, cfg={"cluster": 2, "tile_n": 128}, status=status)
+    torch.cuda.synchronize()
+    for f, o in zip(full, offsets):
+        assert O.bf16_output_ok(f[o:o + 2].float().cpu().numpy(), want)
+        untouched = torch.cat([f[:o], f[o + 2:]])
+        assert bool(torch.isnan(untouched.float()).all())            # nothing written outside the slice
+    assert torch.equal(full[0][0:2], full[1][1:3]) and torch.equal(full[0][0:2], full[2][3:5])
+
+
+def test_epilogues_agree(B, status, monkeypatch):
+    """The staged bulk-store epilogue and the per-thread store epilogue give the same bits."""
+    items = [O.batch_gemm_item(i, 328, 264, 136, seed=34) for i in range(2)]
+    a = bf16_dev(np.stack([i[0] for i in items]))
+    b = bf16_dev(np.stack([i[1] for i in items]))
+    c1 = torch.full((2, 328, 264), float("nan"), device="cuda", dtype=torch.bfloat16)
+    c2 = torch.full((2, 328, 264), float("nan"), device="cuda", dtype=torch.bfloat16)
+    B.bgemm_bf16(a, b, c1, status=status)
+    monkeypatch.setenv("FTB_EPILOGUE", "direct")
+    B.bgemm_bf16(a, b, c2, status=status)
+    torch.cuda.synchronize()
+    assert torch.equal(c1, c2)
+
+
 # ---------------------------------------------------------------- int8 GEMM
 def run_gemm_s8(B, a, b, ta=False, tb=False, cfg=None, status=None):
     m = a.shape[1] if ta else a.shape[0]
@@ -314,7 +347,8 @@ def test_depthwise_golden(B):
     assert O.normalised_error(got, g["y"]) <= TOL["depthwise_f32"]
 
 
-@pytest.mark.parametrize("cfg", [None, {"tile_h": 7}, {"tile_h": 14, "threads": 128}, {"tile_h": 56, "threads": 512},
+@pytest.mark.parametrize("cfg", [None, {"tile_h": 4}, {"tile_h": 8, "threads": 256}, {"tile_h": 7},
+                                 {"tile_h": 14, "threads": 128}, {"tile_h": 56, "threads": 512},
                                  {"tile_h": 1, "threads": 64}])
 def test_depthwise_c256_56(B, cfg):
     """N=1, C=256, 56x56, 3x3, stride 1, pad 1, multiplier 1; uniform[-1,1) from seed 2."""
@@ -325,7 +359,8 @@ def test_depthwise_c256_56(B, cfg):
 
 @pytest.mark.parametrize("shape", [(2, 6, 19, 23, 2, 5, 2, 3, 2), (1, 32, 112, 112, 1, 3, 1, 1, 1),
                                    (8, 16, 112, 112, 6, 3, 2, 1, 1), (2, 160, 7, 7, 6, 3, 1, 1, 1),
-                                   (1, 3, 5, 5, 1, 3, 1, 0, 1), (1, 4, 30, 33, 1, 7, 1, 3, 1)])
+                                   (1, 3, 5, 5, 1, 3, 1, 0, 1), (1, 4, 30, 33, 1, 7, 1, 3, 1),
+                                   (2, 8, 21, 24, 3, 3, 1, 1, 1), (1, 5, 9, 132, 1, 3, 1, 1, 1)])
 def test_depthwise_shapes(B, shape):
     n, c, h, w_, f, r, stride, pad, dil = shape
     x, w = O.depthwise_inputs(n, c, h, w_, f, r, r, seed=61)
