@@ -81,6 +81,23 @@ def build_and_eval(lib, s, bufs, target, dev_id, rpc_info=None, number=1):
         return evaluator(*arrays).mean * 1e3
 
 
+def _evaluate(s, bufs, target, dev_id, number=1, q=None):
+    """In-process timing of a plan with uniform(-10, 10) inputs (flextensor/measure.py:29-52);
+    milliseconds, also put on ``q`` when a queue is given."""
+    import torch
+    from .runtime import build
+    device = torch.device("cuda", dev_id)
+    with torch.cuda.device(device):
+        func = build(s, bufs, target)
+        arrays = make_inputs(bufs, device, low=-10.0, high=10.0)
+        func(*arrays)
+        func.check()
+        cost = func.time_evaluator(func.entry_name, None, number=max(int(number), 1))(*arrays).mean * 1e3
+    if q is not None:
+        q.put(cost)
+    return cost
+
+
 def _evaluate_job(job, number, dev_id):
     """One candidate: (task_key, Config, op_pos) -> milliseconds on GPU ``dev_id``."""
     from .scheduler import schedule_with_config
