@@ -48,79 +48,106 @@ def measured_peak():
         return FALLBACK_BF16_TFLOPS, "fallback"
 
 
+_SAMPLER_CHILD = r"""
+import sys, time
+import pynvml
+pynvml.nvmlInit()
+h = pynvml.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+print("max", pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM), flush=True)
+while True:
+    try:
+        print(time.time(), pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM),
+              pynvml.nvmlDeviceGetCurrentClocksEventReasons(h), flush=True)
+    except Exception:
+        pass
+    time.sleep(0.003)
+"""
+
+
 class ClockSampler(object):
-    """Samples the SM clock and the throttle reasons of one GPU while a region runs (read-only
-    NVML queries every few milliseconds; nvidia-smi every 100 ms when NVML cannot be loaded)."""
+    """Samples the SM clock and the throttle reasons of one GPU while a region runs.
+
+    Read-only NVML queries every few milliseconds from a CHILD process (queries made from the
+    benchmarking process itself contend with its kernel launches for the driver and stretch a
+    launch-bound step); only samples stamped inside [mark_start, mark_end] are used.  Falls
+    back to `nvidia-smi -lms 100` when the NVML module cannot be loaded.
+    """
 
     REASONS = (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20),
                ("hw_thermal_slowdown", 0x40))
+    SMI_FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.sw_power_cap,"
+                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.hw_thermal_slowdown")
 
     def __init__(self, index):
         self.index = index
-        self.clocks = []
-        self.reasons = set()
-        self.max_mhz = None
-        self._stop = threading.Event()
-        self._thread = None
-        self._mode = None
-
-    def _nvml_loop(self):
-        import pynvml
-        handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
-        while not self._stop.is_set():
-            try:
-                self.clocks.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
-                mask = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
-                for name, bit in self.REASONS:
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            time.sleep(0.002)
-
-    def _smi_loop(self):
-        fields = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.sw_power_cap,"
-                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.hw_thermal_slowdown")
-        proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + fields,
-                                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
-                                stderr=subprocess.DEVNULL, text=True)
-        try:
-            for line in proc.stdout:
-                parts = [p.strip() for p in line.split(",")]
-                if len(parts) >= 6:
-                    try:
-                        self.clocks.append(float(parts[0]))
-                        self.max_mhz = float(parts[1])
-                    except ValueError:
-                        continue
-                    for (name, _), val in zip(self.REASONS, parts[2:6]):
-                        if val.lower().startswith("active"):
-                            self.reasons.add(name)
-                if self._stop.is_set():
-                    break
-        finally:
-            proc.terminate()
+        self.lines = []
+        self.proc = None
+        self.thread = None
+        self.mode = None
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
-            self._mode = "nvml"
-            self._thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            import pynvml  # noqa: F401  (only to know the child can import it)
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_CHILD, str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.mode = "nvml (child process)"
         except Exception:
-            self._mode = "nvidia-smi"
-            self._thread = threading.Thread(target=self._smi_loop, daemon=True)
-        self._thread.start()
+            try:
+                self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.SMI_FIELDS,
+                                              "--format=csv,noheader,nounits", "-lms", "100"],
+                                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                self.mode = "nvidia-smi"
+            except Exception:
+                self.proc = None
+                return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def stop(self):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join(timeout=2)
-        clocks = sorted(self.clocks)
-        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(clocks), "source": self._mode}
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source"], "samples": 0}
+        time.sleep(0.02)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        clocks, all_clocks, reasons, mx = [], [], set(), None
+        for stamp, line in self.lines:
+            parts = line.replace(",", " ").split()
+            try:
+                if self.mode == "nvidia-smi":
+                    when, clock, mx = stamp, float(parts[0]), float(parts[1])
+                    mask = sum(bit for (name, bit), val in zip(self.REASONS, parts[2:6]) if val.lower().startswith("active"))
+                elif parts[0] == "max":
+                    mx = float(parts[1])
+                    continue
+                else:
+                    when, clock, mask = float(parts[0]), float(parts[1]), int(parts[2])
+            except (ValueError, IndexError):
+                continue
+            all_clocks.append(clock)
+            if self.t0 is not None and self.t1 is not None and not (self.t0 - 0.005 <= when <= self.t1 + 0.005):
+                continue
+            clocks.append(clock)
+            for name, bit in self.REASONS:
+                if mask & bit:
+                    reasons.add(name)
+        used = sorted(clocks) if clocks else sorted(all_clocks)
+        return {"sm_mhz": used[len(used) // 2] if used else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clocks), "source": self.mode,
+                "window": "timed region" if clocks else "whole run (no sample fell inside the timed region)"}
 
 
 # ---------------------------------------------------------------------- CPU arm / CPU baseline
@@ -279,6 +306,9 @@ def run_ours(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # a child process; it is up and polling long before the timed region
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     assert BATCH % world == 0, "the batch of 64 shards over 1, 2, 4 or 8 ranks"
@@ -359,13 +389,11 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     stream = torch.cuda.current_stream()
     launches0 = backend.launch_count()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     kern_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    sampler.mark_start()
     ev[0].record(stream)
     for i in range(args.steps):
         kern_ev[i][0].record(stream)
@@ -377,6 +405,7 @@ def run_ours(args, rank, world, local_rank):
             sharder.gather(c_local, c_full)
     ev[1].record(stream)
     barrier()
+    sampler.mark_end()
     launches = backend.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     func.check()
