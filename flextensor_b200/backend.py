@@ -106,6 +106,8 @@ def lib():
         handle.ftb_launch_count.argtypes = []
         handle.ftb_validate.restype = i32
         handle.ftb_validate.argtypes = [i32, cfgp, i64, i64, i64]
+        handle.ftb_selftest_bounded_wait.restype = i32
+        handle.ftb_selftest_bounded_wait.argtypes = [vp, vp]
         handle.ftb_gemm_f32.restype = i32
         handle.ftb_gemm_f32.argtypes = [vp, vp, vp, i64, i64, i64, i32, i32, cfgp, vp, vp]
         handle.ftb_bgemm_f32.restype = i32
@@ -132,7 +134,7 @@ def lib():
 
 EXPORTED_SYMBOLS = (
     "ftb_version", "ftb_strerror", "ftb_last_cuda_error", "ftb_device_check", "ftb_validate",
-    "ftb_launch_count", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_bgemm_bf16_multi", "ftb_gemm_s8",
+    "ftb_launch_count", "ftb_selftest_bounded_wait", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_bgemm_bf16_multi", "ftb_gemm_s8",
     "ftb_conv2d_workspace_bytes", "ftb_conv2d_nchw_f32", "ftb_conv2d_nchw_f32_noalloc", "ftb_dwconv2d_nchw_f32",
 )
 
@@ -187,6 +189,14 @@ def validate(op, cfg, m, n, k):
 
 def launch_count():
     return int(lib().ftb_launch_count())
+
+
+def selftest_bounded_wait(status, stream=None):
+    """Launch the wait self-test (about two seconds on the device); ``status`` gets bit 1."""
+    with torch.cuda.device(status.device):
+        rc = lib().ftb_selftest_bounded_wait(_status_ptr(status), _stream_ptr(stream))
+    if rc:
+        raise FtbError(rc, "ftb_selftest_bounded_wait")
 
 
 def gemm_f32(a, b, c, trans_a=False, trans_b=False, cfg=None, status=None, stream=None):

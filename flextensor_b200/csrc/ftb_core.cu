@@ -1,6 +1,7 @@
 // Process-wide state of the library (error code, launch counter, device facts) and
 // the small query entry points of the C ABI.
 #include "ftb_host.h"
+#include "ftb_ptx.cuh"
 
 #include <atomic>
 #include <mutex>
@@ -68,9 +69,36 @@ int* fallback_status() {
   return g_dev_status[dev];
 }
 
+// One thread waits, with the kernels' own bounded wait, on a barrier that nothing ever
+// completes: the wait must run out, set its status bit and return normally.
+__global__ void selftest_wait_kernel(int* status) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+    if (!mbar_wait(smem_u32(&bar), 0, &abort_flag)) atomicOr(status, FTB_DEV_WAIT_FULL);
+  }
+}
+
 }  // namespace ftb
 
 extern "C" {
+
+int ftb_selftest_bounded_wait(int* status, void* stream) {
+  if (!status) return FTB_E_BAD_ARG;
+  int rc = ftb::device_ok();
+  if (rc) return rc;
+  ftb::selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status);
+  ftb::count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    ftb::set_last_cuda_error(static_cast<int>(e));
+    return FTB_E_CUDA;
+  }
+  return FTB_OK;
+}
 
 int ftb_version(void) { return FTB_VERSION; }
 
@@ -110,7 +138,7 @@ int ftb_validate(int op, const ftb_config* cfg, int64_t m, int64_t n, int64_t k)
     return FTB_E_BAD_CONFIG;
   if (cfg->stages != 0 && (cfg->stages < 2 || cfg->stages > 8)) return FTB_E_BAD_CONFIG;
   if (cfg->cluster < 0 || cfg->cluster > 2) return FTB_E_BAD_CONFIG;
-  if (cfg->cluster == 2 && (op == 3 || split3)) return FTB_E_BAD_CONFIG;
+  if (cfg->cluster == 2 && split3) return FTB_E_BAD_CONFIG;
   if (cfg->cluster == 2 && cfg->tile_n != 0 && cfg->tile_n < 64) return FTB_E_BAD_CONFIG;
   if (cfg->tile_n != 0 && cfg->stages != 0) {
     const size_t per_cta = static_cast<size_t>(cfg->tile_n) / (cfg->cluster == 2 ? 2 : 1);

@@ -111,8 +111,14 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
     return true;
   };
   if (c.cluster == 0 || c.tile_n == 0) {
+    // Two regimes.  Many waves of tiles: rank by useful work per wave times the tile's steady-state
+    // rate (big tiles win).  A problem that fits in one wave is latency-bound: its time is a fixed
+    // cost plus K blocks times a per-block cost that shrinks with the tile, so the candidate that
+    // spreads over the most SMs wins (ties go to the larger tile).
     double best = -1.0;
     int best_cluster = 1, best_bn = 32;
+    long long best_ctas = -1;
+    int wave_cluster = 0, wave_bn = 0;
     for (int cluster = 2; cluster >= 1; --cluster) {
       if (c.cluster != 0 && c.cluster != cluster) continue;
       if (cluster == 2 && (!allow_pair || num_sms < 2)) continue;
@@ -131,13 +137,33 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
           best_cluster = cluster;
           best_bn = bn;
         }
+        if (waves == 1) {
+          const long long ctas_used = tiles * cluster;
+          if (ctas_used > best_ctas) {
+            best_ctas = ctas_used;
+            wave_cluster = cluster;
+            wave_bn = bn;
+          }
+        }
       }
     }
     if (best < 0) {
-      if (c.tile_n == 0 || c.cluster == 0) {
-        // no ranked candidate: fall back to the smallest legal single-CTA tile
-        c.cluster = c.cluster ? c.cluster : 1;
-        if (c.tile_n == 0) c.tile_n = b_mn && box_mn(ki) > 32 ? box_mn(ki) : 32;
+      // no ranked candidate: fall back to the smallest legal single-CTA tile
+      c.cluster = c.cluster ? c.cluster : 1;
+      if (c.tile_n == 0) c.tile_n = b_mn && box_mn(ki) > 32 ? box_mn(ki) : 32;
+    } else if (best_ctas >= 0) {
+      bool best_is_single_wave;
+      {
+        const long long tm = kTileM * best_cluster;
+        const long long tiles = batch * ((m_rows + tm - 1) / tm) * ((n + best_bn - 1) / best_bn);
+        best_is_single_wave = tiles <= num_sms / best_cluster;
+      }
+      if (best_is_single_wave) {
+        c.cluster = wave_cluster;
+        c.tile_n = wave_bn;
+      } else {
+        c.cluster = best_cluster;
+        c.tile_n = best_bn;
       }
     } else {
       c.cluster = best_cluster;
@@ -501,8 +527,21 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   const int num_kb = static_cast<int>(r * s * ws.cchunks);
   const long long tiles_m = static_cast<long long>(n) * tiles_h * tiles_w;
   ftb_config cfg;
-  rc = resolve_config(user, ki, split3, 0, false, tiles_m, kTileM, kg, num_kb, true, num_sms, &cfg);
+  rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg);
   if (rc) return rc;
+  const bool pair = cfg.cluster == 2;
+  const long long tiles_m_launch = pair ? (tiles_m + 1) / 2 : tiles_m;
+  if ((!user || user->split_k == 0) && groups == 1) {
+    // A short tile list leaves SMs idle: split the reduction (whole filter taps per split) so that
+    // about all SMs get work; measured best at 2-4 splits, more only adds atomics.
+    const long long tiles = tiles_m_launch * ((kg + cfg.tile_n - 1) / cfg.tile_n);
+    int want = static_cast<int>((num_sms / (pair ? 2 : 1)) / (tiles > 0 ? tiles : 1));
+    if (want > 4) want = 4;
+    int pick = 1;
+    for (int d = 2; d <= want; ++d)
+      if (num_kb % d == 0) pick = d;
+    cfg.split_k = pick;
+  }
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   {
@@ -541,24 +580,25 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.bn = cfg.tile_n;
     p.stages = cfg.stages;
     p.num_kb = num_kb;
-    p.tiles_m = static_cast<int>(tiles_m);
+    p.tiles_m = static_cast<int>(tiles_m_launch);
+    p.conv_tiles = static_cast<int>(tiles_m);
     p.tiles_n = static_cast<int>((kg + p.bn - 1) / p.bn);
     p.raster = cfg.raster;
     p.group_m = cfg.group_m;
     p.split_k = cfg.split_k;
     p.kblk = ki.kblk;
-    p.idesc = make_idesc(ki, p.bn, 0, 0);
-    p.b_bytes = static_cast<uint32_t>(p.bn) * 128u;
+    p.idesc = make_idesc(ki, p.bn, 0, 0, pair ? 2 * kTileM : kTileM);
+    p.b_rows = pair ? p.bn / 2 : p.bn;
+    p.b_bytes = static_cast<uint32_t>(p.b_rows) * 128u;
     p.a_boxes = 1;
     p.a_box_mn = kTileM;
     p.a_box_bytes = static_cast<uint32_t>(tile_h * tile_w) * 128u;
     p.a_lbo = 16; p.a_sbo = 1024; p.a_kadv = static_cast<uint32_t>(ki.umma_k * ki.esize);
     CUtensorMapSwizzle b_swz;
-    operand_layout(ki, 0, p.bn, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv,
+    operand_layout(ki, 0, p.b_rows, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv,
                    &p.b_layout, &b_swz);
     p.a_layout = 2;
-    p.pair_m = kTileM;
-    p.b_rows = p.bn;
+    p.pair_m = pair ? 2 * kTileM : kTileM;
     p.conv = 1;
     p.conv_ktot = static_cast<int>(k);
     p.conv_koff = static_cast<int>(g * kg);
@@ -589,7 +629,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       const uint64_t kdim = static_cast<uint64_t>(num_kb) * ki.kblk;
       uint64_t dims[3] = {kdim, static_cast<uint64_t>(kg), 1};
       uint64_t strides[2] = {kdim * 4, kdim * 4 * kg};
-      uint32_t box[3] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(p.bn), 1};
+      uint32_t box[3] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(p.b_rows), 1};
       const uint32_t ones[3] = {1, 1, 1};
       rc = make_tmap(&tb, ki.dt, 3, w_packed + static_cast<uint64_t>(g) * kg * kdim, dims, strides, box, ones);
       if (rc) return rc;
@@ -597,10 +637,16 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.split_k;
     if (total > 0x7fffffffll) return FTB_E_TOO_LARGE;
     int ctas = cfg.ctas > 0 ? cfg.ctas : num_sms;
-    if (ctas > total) ctas = static_cast<int>(total);
+    if (pair) {
+      if (ctas / 2 > total) ctas = static_cast<int>(total) * 2;
+      ctas &= ~1;
+      if (ctas < 2) ctas = 2;
+    } else if (ctas > total) {
+      ctas = static_cast<int>(total);
+    }
     StoreMaps tc;
     memset(&tc, 0, sizeof(tc));
-    rc = dispatch(KIND_TF32, OUT_F32, split3, false, ta, tb, tc, p, ctas, stream);
+    rc = dispatch(KIND_TF32, OUT_F32, split3, pair, ta, tb, tc, p, ctas, stream);
     if (rc) return rc;
   }
   return FTB_OK;

@@ -60,6 +60,7 @@ struct UmmaParams {
   // implicit-GEMM conv geometry (conv != 0)
   int conv, P, Q, tile_h, tile_w, tiles_h, tiles_w, R, S, cchunks;
   int conv_ktot, conv_koff;  // output channels of the whole conv / first channel of this group
+  int conv_tiles;            // number of 128-pixel tiles (a CTA pair takes two consecutive ones)
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int* status;
   // TMA-store epilogue: tma_store != 0 stages 128-byte wide output slabs in shared memory and
@@ -191,9 +192,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // conv: walking (r, s, channel chunk) with counters instead of div/mod per block
         int img = 0, h0 = 0, w0 = 0, cc = 0, ts = 0, tr = 0;
         if (conv) {
-          const int tw = tc.m % p.tiles_w;
-          const int th = (tc.m / p.tiles_w) % p.tiles_h;
-          img = tc.m / (p.tiles_w * p.tiles_h);
+          // this CTA's 128-pixel tile; one past the end (odd tile count in a pair) lands outside
+          // the tensor and loads zeros
+          const int mt = PAIR ? tc.m * 2 + static_cast<int>(cta_rank) : tc.m;
+          const int tw = mt % p.tiles_w;
+          const int th = (mt / p.tiles_w) % p.tiles_h;
+          img = mt / (p.tiles_w * p.tiles_h);
           h0 = th * p.tile_h * p.stride_h - p.pad_h;
           w0 = tw * p.tile_w * p.stride_w - p.pad_w;
           cc = kb0 % p.cchunks;
@@ -216,7 +220,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // reported before that; the phase still cannot complete until the leader's
             // own arrival.)
             if (cta_rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * tx);
-            if (a_mn) {
+            if (conv) {
+              tma_load_4d_pair(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
+              if (++cc == p.cchunks) {
+                cc = 0;
+                if (++ts == p.S) {
+                  ts = 0;
+                  ++tr;
+                }
+              }
+            } else if (a_mn) {
               for (int i = 0; i < a_boxes; ++i)
                 tma_load_3d_pair(sa + i * a_box_bytes, &tmap_a, full, m0 + i * a_box_mn, kc, tc.b);
             } else {
@@ -376,12 +389,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       long long row_off;  // element offset of (row, column 0 of the problem)
       long long col_stride = 1;
       if (p.conv) {
-        const int tw = tc.m % p.tiles_w;
-        const int th = (tc.m / p.tiles_w) % p.tiles_h;
-        const int img = tc.m / (p.tiles_w * p.tiles_h);
+        const int mt = PAIR ? tc.m * 2 + static_cast<int>(cta_rank) : tc.m;
+        const int tw = mt % p.tiles_w;
+        const int th = (mt / p.tiles_w) % p.tiles_h;
+        const int img = mt / (p.tiles_w * p.tiles_h);
         const int oh = th * p.tile_h + row / p.tile_w;
         const int ow = tw * p.tile_w + row % p.tile_w;
-        row_ok = row < p.tile_h * p.tile_w && oh < p.P && ow < p.Q;
+        row_ok = mt < p.conv_tiles && row < p.tile_h * p.tile_w && oh < p.P && ow < p.Q;
         col_stride = static_cast<long long>(p.P) * p.Q;
         row_off = (static_cast<long long>(img) * p.conv_ktot + p.conv_koff) * col_stride +
                   static_cast<long long>(oh) * p.Q + ow;

@@ -14,7 +14,7 @@ ftb_config``).  ``generate_space_intra_op`` builds, per op kind:
 
   type key   sub-space (entity)                      reference knob it takes the place of
   spatial    tile_n [n]      cluster [c]             thread x serial tile / vthread split
-             tile_h [h]      threads [t]             (conv rows per tile; depthwise strip, CTA size)
+             tile_h [h]      threads [t]             (conv rows per tile; depthwise rows per thread/strip, CTA size)
   reduce     stages [s]      split_k [k]             reduce split [outer, mid, inner]
   reorder    raster [mode, group_m]                  reorder position
   unroll     ctas   [fraction of SMs in eighths]     unroll depth (how much work is in flight)
@@ -292,7 +292,7 @@ def generate_space_intra_op_llvm(op, down_graph, slevel=4, rlevel=3, groups=3, s
 B200_LAYOUT = {
     "contraction": {"spatial": ["tile_n", "cluster"], "reduce": ["stages", "split_k"], "reorder": ["raster"],
                     "unroll": ["ctas"]},
-    "conv2d": {"spatial": ["tile_n", "tile_h"], "reduce": ["stages", "split_k"], "reorder": ["raster"],
+    "conv2d": {"spatial": ["tile_n", "tile_h", "cluster"], "reduce": ["stages", "split_k"], "reorder": ["raster"],
                "unroll": ["ctas"]},
     "depthwise_conv2d": {"spatial": ["tile_h", "threads"], "reduce": [], "reorder": [], "unroll": []},
 }
@@ -350,6 +350,7 @@ def generate_space_intra_op_b200(op, down_graph=None):
         tile_w = min(out_w, 128)
         max_h = max(1, 128 // tile_w)
         space.add_subspace("tile_h", KnobSpace("tile_h", [h for h in range(1, max_h + 1) if h <= out_h]), "spatial")
+        space.add_subspace("cluster", KnobSpace("cluster", [1, 2]), "spatial")
         rc = op.reduce_axis[0].dom.extent.value
         taps = op.reduce_axis[1].dom.extent.value * op.reduce_axis[2].dom.extent.value
         num_kb = taps * math.ceil(rc / 32)

@@ -70,6 +70,12 @@ int ftb_validate(int op, const ftb_config* cfg, int64_t m, int64_t n, int64_t k)
 /* Number of kernels this library has launched in this process (all entry points). */
 int64_t ftb_launch_count(void);
 
+/* Self-test of the failure path (no counterpart in the reference): launches one thread that waits,
+ * with the same bounded wait every kernel uses, on a barrier nothing completes.  After about two
+ * seconds the wait gives up, ORs FTB_DEV bit 1 into *status and the kernel ends normally; the
+ * context stays usable.  Lets a host verify that a stuck pipeline surfaces as a status, not a hang. */
+int ftb_selftest_bounded_wait(int* status, void* stream);
+
 /* C[M,N] = op(A) . op(B), fp32 in/out, TF32 tensor cores (flextensor/nn/ops.py:1074-1108 gemm).
  * trans_a = 0: A is [M,K] row-major, 1: A is [K,M]; trans_b = 0: B is [K,N], 1: B is [N,K]. */
 int ftb_gemm_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,

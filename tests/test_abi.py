@@ -56,7 +56,8 @@ def test_validate(native_lib):
     assert ok(backend.OP_GEMM_F32, {"split_k": 64}, 64, 64, 64) == -3        # more splits than K blocks
     assert ok(backend.OP_GEMM_F32, {"fp32_mode": 1, "cluster": 2}, 512, 512, 512) == -3
     assert ok(backend.OP_GEMM_F32, {"fp32_mode": 2}, 512, 512, 512) == -3
-    assert ok(backend.OP_CONV2D, {"cluster": 2}, 512, 64, 576) == -3
+    assert ok(backend.OP_CONV2D, {"cluster": 2}, 512, 64, 576) == 0
+    assert ok(backend.OP_CONV2D, {"cluster": 2, "fp32_mode": 1}, 512, 64, 576) == -3
     assert ok(backend.OP_DWCONV2D, {"threads": 100}, 1, 1, 1) == -3
     assert ok(backend.OP_DWCONV2D, {"threads": 128, "tile_h": 7}, 1, 1, 1) == 0
     assert ok(9, None, 1, 1, 1) == -1

@@ -316,6 +316,20 @@ def test_conv2d_resnet_stage2(B, status, cfg):
     assert O.normalised_error(got, want) <= (TOL["conv2d_3xtf32"] if cfg["fp32_mode"] else TOL["conv2d_tf32"])
 
 
+@pytest.mark.parametrize("shape", [(3, 64, 9, 9, 40, 1, 0), (1, 64, 56, 56, 64, 3, 1), (5, 16, 12, 10, 24, 3, 1)])
+@pytest.mark.parametrize("cfg", [{"cluster": 2}, {"cluster": 2, "tile_n": 32, "split_k": 1}, {"cluster": 2, "split_k": 3},
+                                 {"cluster": 1, "split_k": 1}])
+def test_conv2d_cta_pairs(B, status, shape, cfg):
+    """Two CTAs on two consecutive 128-pixel tiles (odd tile counts included)."""
+    n, c, hw1, hw2, k, r, pad = shape
+    x, w = O.conv2d_inputs(n, c, hw1, hw2, k, r, r, seed=53)
+    want = O.conv2d_nchw(x, w, None, 1, pad, 1, 1)
+    if cfg.get("split_k", 1) > r * r * ((c + 31) // 32):
+        pytest.skip("more splits than K blocks")
+    got = run_conv(B, x, w, None, 1, pad, 1, 1, cfg=dict(cfg, fp32_mode=0), status=status)
+    assert O.normalised_error(got, want) <= TOL["conv2d_tf32"]
+
+
 def test_conv2d_workspace_is_required(B):
     x = torch.zeros(1, 8, 8, 8, device="cuda")
     w = torch.zeros(8, 8, 3, 3, device="cuda")
@@ -369,6 +383,20 @@ def test_depthwise_shapes(B, shape):
     want = O.depthwise_conv2d_nchw(x, w, bias, stride, pad, dil)
     assert got.shape == want.shape
     assert O.normalised_error(got, want) <= TOL["depthwise_f32"]
+
+
+def test_a_wait_that_runs_out_is_reported_not_hung(B):
+    """A barrier nothing completes: the bounded wait gives up, the status word says so, and the
+    device keeps working afterwards."""
+    st = B.new_status()
+    B.selftest_bounded_wait(st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 1
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        B.check_status(st)
+    a, b = O.gemm_inputs(64, 64, 64, seed=1)
+    got = run_gemm_f32(B, a, b, cfg={"fp32_mode": 1})
+    assert O.normalised_error(got, O.gemm(a, b)) <= TOL["gemm_f32_3xtf32"]
 
 
 def test_launch_counter_counts_our_kernels(B):

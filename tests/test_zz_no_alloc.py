@@ -6,7 +6,8 @@ runtime, or run where allocation is forbidden once serving has started - so they
 the regular conv2d its workspace.  ``ftb_conv2d_nchw_f32_noalloc`` keeps a fixed 8 MiB
 workspace inside the library instead.  Here it is called through the C ABI twice in a row, on
 two different shapes, and each result is compared with the regular entry point's.  The two
-paths run the same kernels with the same knobs, so the outputs must be bit-identical; the
+paths run the same kernels with the same knobs (no K split, so no atomics), so the outputs must
+be bit-identical; the
 second call also shows that what the first one left in the shared workspace does no harm.
 """
 import numpy as np
@@ -28,11 +29,11 @@ def _both(B, x, w, bias, stride, pad, dil, groups, status):
     args = (bd, (stride, stride), (pad, pad), (dil, dil), groups)
     ref = torch.full((n, k, p, q), float("nan"), device="cuda")
     ws = torch.empty(B.conv2d_workspace_bytes(n, c, h, wd, k, r, s, groups), dtype=torch.uint8, device="cuda")
-    B.conv2d_nchw_f32(xd, wdv, ref, *args, cfg={"fp32_mode": 1}, workspace=ws, status=status)
+    B.conv2d_nchw_f32(xd, wdv, ref, *args, cfg={"fp32_mode": 1, "split_k": 1}, workspace=ws, status=status)
     got = torch.full((n, k, p, q), float("nan"), device="cuda")
     torch.cuda.synchronize()
     allocated = torch.cuda.memory_allocated()
-    B.conv2d_nchw_f32_noalloc(xd, wdv, got, *args, cfg={"fp32_mode": 1}, status=status)
+    B.conv2d_nchw_f32_noalloc(xd, wdv, got, *args, cfg={"fp32_mode": 1, "split_k": 1}, status=status)
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == allocated     # torch's allocator was not touched either
     return got.cpu().numpy(), ref.cpu().numpy()
