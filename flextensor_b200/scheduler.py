@@ -297,8 +297,12 @@ class Scheduler(object):
         return group.to_config(best)
 
     def _dispatch(self, configs, type_keys, method, use_model):
-        if len(self.space) <= 1 and not self.space.subspaces:
+        if not self.space.subspaces:
             return {}
+        if len(self.space) == 1:
+            # a single point: nothing to search (the reference would measure it 400 times in warm-up)
+            only = {name: 0 for name in self.space.subspaces}
+            return self.walker_group.to_config(only)
         if method == "searching":
             return self._searching_schedule(configs, type_keys, use_model=use_model)
         if method == "q":

@@ -355,3 +355,38 @@ def test_master_routine_timeout_and_failure():
     assert isinstance(res, Exception)
     res = master_routine(20, _raiser)
     assert isinstance(res, ValueError)
+
+
+def test_offline_training_round_trip(tmp_path, monkeypatch):
+    """Search data dumped by one run trains the models another run searches against
+    (flextensor/train.py flow): dump -> train -> schedule(use the performance model, no measurements)."""
+    from flextensor_b200 import train
+    monkeypatch.chdir(tmp_path)
+    np.random.seed(0)
+    torch.manual_seed(0)
+    group = train.group_for(GEMM_KEY, 0)
+    measure = _fake_measurer()
+    names = list(group.walkers)
+    for i in range(12):
+        drawn = group.forward(4)
+        points = [{n: int(drawn[n][1][j]) for n in names} for j in range(4)]
+        costs = measure([(GEMM_KEY, Config([group.to_config(p)], None), 0) for p in points])
+        costs = [min(c, 50.0) for c in costs]
+        group.add_perf_data(points, costs)
+        for p in points:
+            nxt, acts = group.full_walk(p, no_repeat=False)
+            group.add_data(acts[0][0], p, acts[0][1], nxt[0], 0.25)
+    group.dump_data()
+    trained, loss = train.train_performance(GEMM_KEY, 0, verbose=False)
+    assert os.path.exists(trained.model_path) and loss >= 0.0
+    train.train_walkers(GEMM_KEY, 0, verbose=False)
+    calls = []
+
+    def counting(jobs, number=1, timeout=1.0, parallel=1):
+        calls.append(len(jobs))
+        return measure(jobs)
+
+    plan, _, _ = schedule(GEMM_KEY, op_trial=3, op_stop=2, timeout=1, parallel=2, measurer=counting,
+                          op_perf_model_path=[(0, trained.model_path)])
+    assert plan.steps[0].knobs["tile_n"] in (64, 128, 256)
+    assert sum(calls) <= 4      # the op search ran on the model; only the tiny graph search measured
