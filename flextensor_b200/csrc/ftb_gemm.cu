@@ -452,27 +452,52 @@ static ConvWs conv_ws(int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int
   return ws;
 }
 
-// One launch: blocks [0, in_blocks) transpose NCHW -> NHWC(Cp) through a 32x33 tile,
-// the rest pack weights [K][Cg][R][S] -> [K][R][S][cchunks*32] (zero padded).
-__global__ void conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
-                                    float* __restrict__ in_nhwc, float* __restrict__ w_packed, int N,
-                                    int C, int HW, int Cp, int K, int Cg, int RS, int cchunks,
-                                    int hw_tiles, int c_tiles, int in_blocks) {
-  __shared__ float tile[32][33];
+// One launch: blocks [0, in_blocks) transpose NCHW -> NHWC(Cp) through a shared-memory tile of
+// 32 channels x 128 pixels (16-byte loads along the pixels, 16-byte stores along the channels;
+// the 129-float row pitch keeps both phases free of bank conflicts), the rest pack weights
+// [K][Cg][R][S] -> [K][R][S][cchunks*32] (zero padded).
+constexpr int kPreCh = 32, kPrePx = 128;
+
+__global__ void __launch_bounds__(256)
+conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt, float* __restrict__ in_nhwc,
+                    float* __restrict__ w_packed, int N, int C, int HW, int Cp, int K, int Cg, int RS,
+                    int cchunks, int hw_tiles, int c_tiles, int in_blocks) {
+  __shared__ float tile[kPreCh][kPrePx + 1];
   const int bid = blockIdx.x;
   if (bid < in_blocks) {
     const int ct = bid % c_tiles;
     const int ht = (bid / c_tiles) % hw_tiles;
     const int img = bid / (c_tiles * hw_tiles);
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-    for (int j = ty; j < 32; j += 8) {
-      const int c = ct * 32 + j, hw = ht * 32 + tx;
-      tile[j][tx] = (c < C && hw < HW) ? in[(static_cast<long long>(img) * C + c) * HW + hw] : 0.0f;
+    const int c0 = ct * kPreCh, p0 = ht * kPrePx;
+    const float* src = in + static_cast<long long>(img) * C * HW;
+    const bool vec = (HW % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+    // load: thread -> (channel, 4 pixels)
+    for (int i = threadIdx.x; i < kPreCh * (kPrePx / 4); i += 256) {
+      const int ch = i / (kPrePx / 4), q = (i % (kPrePx / 4)) * 4;
+      const int c = c0 + ch, px = p0 + q;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < C && px < HW) {
+        const float* rp = src + static_cast<long long>(c) * HW + px;
+        if (vec && px + 3 < HW) {
+          v = __ldg(reinterpret_cast<const float4*>(rp));
+        } else {
+          v.x = __ldg(rp);
+          if (px + 1 < HW) v.y = __ldg(rp + 1);
+          if (px + 2 < HW) v.z = __ldg(rp + 2);
+          if (px + 3 < HW) v.w = __ldg(rp + 3);
+        }
+      }
+      tile[ch][q] = v.x; tile[ch][q + 1] = v.y; tile[ch][q + 2] = v.z; tile[ch][q + 3] = v.w;
     }
     __syncthreads();
-    for (int j = ty; j < 32; j += 8) {
-      const int hw = ht * 32 + j, c = ct * 32 + tx;
-      if (hw < HW && c < Cp) in_nhwc[(static_cast<long long>(img) * HW + hw) * Cp + c] = tile[tx][j];
+    // store: thread -> (pixel, 4 channels); Cp is a multiple of 4 and the copy is 16-byte aligned
+    float* dst = in_nhwc + static_cast<long long>(img) * HW * Cp;
+    for (int i = threadIdx.x; i < kPrePx * (kPreCh / 4); i += 256) {
+      const int cg = (i % (kPreCh / 4)) * 4, q = i / (kPreCh / 4);
+      const int c = c0 + cg, px = p0 + q;
+      if (px < HW && c < Cp)
+        *reinterpret_cast<float4*>(dst + static_cast<long long>(px) * Cp + c) =
+            make_float4(tile[cg][q], tile[cg + 1][q], tile[cg + 2][q], tile[cg + 3][q]);
     }
   } else {
     const long long kdim = static_cast<long long>(RS) * cchunks * 32;
@@ -546,7 +571,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   {
     const int HW = static_cast<int>(h * w);
-    const int hw_tiles = (HW + 31) / 32, c_tiles = static_cast<int>((ws.cp + 31) / 32);
+    const int hw_tiles = (HW + kPrePx - 1) / kPrePx, c_tiles = static_cast<int>((ws.cp + kPreCh - 1) / kPreCh);
     const int in_blocks = static_cast<int>(n) * hw_tiles * c_tiles;
     const long long wtotal = k * r * s * ws.cchunks * 32;
     int w_blocks = static_cast<int>((wtotal + 255) / 256);
