@@ -432,11 +432,50 @@ def run_ours(args, rank, world, local_rank):
     hb.copy_(b)
     e2e_steps = max(3, min(args.steps, 10))
 
+    # The step is pipelined over chunks of the local batch: chunk c+1 is copied host->device on one
+    # copy stream while chunk c is computed and chunk c-1 is read back on another (PCIe is full
+    # duplex).  Every chunk goes through the public callable of its own Task.
+    nchunks = max(1, min(8, local))
+    while local % nchunks:
+        nchunks -= 1
+    csz = local // nchunks
+    chunk_task = Task("gemm", "batch_gemm", batch_gemm, (csz, DIM, DIM, DIM), "cuda", local_rank)
+    register_task(chunk_task)
+    cop = chunk_task.func(*chunk_task.args)[0][0]
+    cs, cbufs = schedule_with_config(chunk_task.key, Config([knobs_to_config(KNOBS, cop)], None))
+    chunk_func = build(cs, cbufs, "cuda")
+    h2d_stream, d2h_stream = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+    ev_in = [torch.cuda.Event() for _ in range(nchunks)]
+    ev_cmp = [torch.cuda.Event() for _ in range(nchunks)]
+    ev_out = [torch.cuda.Event() for _ in range(nchunks)]
+    for e in ev_cmp + ev_out:
+        e.record(stream)
+
     def e2e_step():
-        a.copy_(ha, non_blocking=True)
-        b.copy_(hb, non_blocking=True)
-        step()
-        hc.copy_(c_local, non_blocking=True)
+        for c in range(nchunks):
+            sl = slice(c * csz, (c + 1) * csz)
+            with torch.cuda.stream(h2d_stream):
+                h2d_stream.wait_event(ev_cmp[c])      # the previous step is done reading this chunk's operands
+                a[sl].copy_(ha[sl], non_blocking=True)
+                b[sl].copy_(hb[sl], non_blocking=True)
+                ev_in[c].record(h2d_stream)
+            stream.wait_event(ev_in[c])
+            stream.wait_event(ev_out[c])              # the previous step's read-back of this chunk is done
+            if peer_out is not None:
+                backend.bgemm_bf16_multi(a[sl], b[sl], peer_out.slice_ptrs(lo + c * csz), DIM, DIM, cfg=KNOBS,
+                                         status=status_word)
+            else:
+                chunk_func(a[sl], b[sl], c_local[sl])
+            ev_cmp[c].record(stream)
+            with torch.cuda.stream(d2h_stream):
+                d2h_stream.wait_event(ev_cmp[c])
+                hc[sl].copy_(c_local[sl], non_blocking=True)
+                ev_out[c].record(d2h_stream)
+        if peer_out is not None:
+            peer_out.barrier()
+        elif sharder is not None:
+            sharder.gather(c_local, c_full)
+        stream.wait_stream(d2h_stream)
 
     e2e_step()
     barrier()
@@ -480,7 +519,8 @@ def run_ours(args, rank, world, local_rank):
                        "kernel": "umma_gemm_kernel<bf16, bf16 out, cta_group::2>"},
             "compute_only_value": compute_only,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+                    "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "pipeline": "%d chunks per rank; host->device, compute and device->host overlap" % nchunks},
             "gpu_launches": launches,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_2250": achieved / 2250.0,
@@ -488,6 +528,15 @@ def run_ours(args, rank, world, local_rank):
                          "traffic": (NCU_TRAFFIC_BYTES_PER_LAUNCH * local / BATCH) if NCU_TRAFFIC_BYTES_PER_LAUNCH else None},
             "clocks": clocks,
         }
+        if world > 1:
+            # fused compute + collective: the step cannot beat the slower of the math at the GEMM peak and
+            # the bytes every GPU must receive over NVLink at the measured peer-copy rate (770 GB/s)
+            link_bytes = (world - 1) * local * DIM * DIM * elem
+            t_math = local * FLOP_PER_ITEM / (peak * 1e12) * 1e3
+            t_link = link_bytes / 770e9 * 1e3
+            line["fused_collective"] = {"bound": "nvlink" if t_link > t_math else "tensor",
+                                        "nvlink_bytes_per_gpu_per_step": link_bytes, "target_ms": max(t_math, t_link),
+                                        "achieved_ms": ms_per_step, "frac": max(t_math, t_link) / ms_per_step}
         if world == 1:
             line["cpu_baseline"] = cpu_baseline_leg()
             if not args.no_extra:
