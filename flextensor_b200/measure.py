@@ -15,8 +15,6 @@ import os
 import queue as _queue
 import time
 
-import numpy as np
-
 mp = _mp.get_context("spawn")
 
 _DEFAULT = {"measurer": None}
@@ -44,23 +42,37 @@ def master_routine(timeout, func, *args, **kwargs):
     return ret
 
 
-def make_inputs(bufs, device, low=0.0, high=1.0, seed=None):
-    """Random arrays for the buffers of a task (uniform(0,1) floats as measure.py:98; small
-    integers for int8), output buffer included, as CUDA tensors."""
+_INPUT_CACHE = {}
+
+
+def make_inputs(bufs, device, low=0.0, high=1.0, seed=None, cache=True):
+    """Random arrays for the buffers of a task (uniform(low, high) floats as measure.py:98; integers in
+    [-127, 127] for int8), output buffer included, as CUDA tensors drawn on the device.
+
+    Candidates of one task differ only in their knobs, so the arrays of the last task are kept and
+    handed out again (``cache``): a worker does not redraw gigabytes per candidate.
+    """
     import torch
     from .runtime import torch_dtype
-    gen = np.random.default_rng(seed)
+    key = (str(device), float(low), float(high), seed,
+           tuple((tuple(int(s) for s in buf.shape), buf.dtype) for buf in bufs))
+    if cache and key in _INPUT_CACHE:
+        return _INPUT_CACHE[key]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(0 if seed is None else int(seed))
     arrays = []
     for buf in bufs:
         shape = tuple(int(s) for s in buf.shape)
         if buf.dtype == "int8":
-            host = gen.integers(-127, 128, size=shape, dtype=np.int8)
-            arrays.append(torch.from_numpy(host).to(device))
+            arrays.append(torch.randint(-127, 128, shape, device=device, dtype=torch.int8, generator=gen))
         elif buf.dtype == "int32":
             arrays.append(torch.zeros(shape, dtype=torch.int32, device=device))
         else:
-            host = gen.uniform(low, high, size=shape).astype(np.float32)
-            arrays.append(torch.from_numpy(host).to(device).to(torch_dtype(buf.dtype)))
+            t = torch.rand(shape, device=device, generator=gen, dtype=torch.float32) * (high - low) + low
+            arrays.append(t.to(torch_dtype(buf.dtype)))
+    if cache:
+        _INPUT_CACHE.clear()  # keep one task's arrays only
+        _INPUT_CACHE[key] = arrays
     return arrays
 
 

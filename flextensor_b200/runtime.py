@@ -198,6 +198,28 @@ class Module(object):
             else:
                 raise RuntimeError("no kernel for op kind %r" % (op.kind,))
 
+    def capture(self, *arrays):
+        """Record one call on these arrays into a CUDA graph; returns an object whose ``replay()``
+        re-runs it with a single launch from the host.
+
+        For microsecond-sized operators the Python and launch cost of ``func(*arrays)`` (tens of
+        microseconds) exceeds the kernels' own time; a serving loop that calls the operator on the
+        same buffers every step replays the graph instead.  The arrays must stay alive and keep
+        their addresses; their contents may change between replays.
+        """
+        stream = torch.cuda.current_stream()
+        self(*arrays)  # first call outside the capture: one-time set-up (attributes, workspaces)
+        stream.synchronize()
+        self.check()
+        side = torch.cuda.Stream(device=arrays[-1].device)
+        side.wait_stream(stream)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                self(*arrays)
+        stream.wait_stream(side)
+        return CapturedCall(self, graph, arrays)
+
     def check(self):
         """Synchronise and raise if a kernel of this module reported a failed in-kernel wait."""
         if self._status is not None:
@@ -275,6 +297,20 @@ class Module(object):
     def export_library(self, path, fcompile=None):
         with open(path, "w") as fout:
             fout.write(self.get_source())
+
+
+class CapturedCall(object):
+    """A call of a ``Module`` frozen into a CUDA graph (see ``Module.capture``)."""
+
+    def __init__(self, module, graph, arrays):
+        self.module = module
+        self.graph = graph
+        self.arrays = arrays  # keeps the buffers alive
+
+    def replay(self):
+        self.graph.replay()
+
+    __call__ = replay
 
 
 def build(s, bufs=None, target="cuda", target_host=None, name="default_function"):

@@ -95,8 +95,8 @@ int ftb_bgemm_bf16(const void* a, const void* b, void* c, int64_t batch, int64_t
 /* The same, with the result written to `num_dst` (1..8) buffers at once: c_dst is a host array of
  * device pointers, each to a [batch,M,N] buffer that may live on this GPU or be a mapped buffer
  * of a peer GPU.  Used by the batch-sharded path to place a rank's slice of the output directly
- * in every rank's gathered buffer (the all-gather the multi-GPU path of the north star asks for,
- * fused into the GEMM epilogue as bulk tensor stores over NVLink).  Needs N*elem_size % 16 == 0
+ * in every rank's gathered buffer (an all-gather fused into the GEMM epilogue as bulk tensor
+ * stores over NVLink).  Needs N*elem_size % 16 == 0
  * and 16-byte aligned destinations; no counterpart in the reference (it is single-device). */
 int ftb_bgemm_bf16_multi(const void* a, const void* b, void* const* c_dst, int num_dst, int64_t batch,
                          int64_t m, int64_t n, int64_t k, int trans_a, int trans_b, int out_f32,

@@ -38,6 +38,25 @@ def test_readme_flow_gemm(native_lib):
         func(dev(a), dev(b), c.double())
 
 
+def test_captured_call_replays(native_lib):
+    """A call frozen into a CUDA graph follows the contents of its buffers."""
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config
+    from flextensor_b200.utils import Config
+    key = "conv2d_depthwise_(1, 256, 56, 56, 1, 3, 1, 1, 1)_cuda(0)"
+    s, bufs = schedule_with_config(key, Config([{}, {}], None))
+    func = build(s, bufs)
+    x, w = O.depthwise_inputs(1, 256, 56, 56, 1, 3, 3, seed=2)
+    xd, wd, out = dev(x), dev(w), torch.zeros(1, 256, 56, 56, device="cuda")
+    call = func.capture(xd, wd, out)
+    x2, _ = O.depthwise_inputs(1, 256, 56, 56, 1, 3, 3, seed=99)
+    xd.copy_(dev(x2))
+    out.zero_()
+    call.replay()
+    torch.cuda.synchronize()
+    assert O.normalised_error(out.cpu().numpy(), O.depthwise_conv2d_nchw(x2, w, None, 1, 1, 1)) <= 1e-5
+
+
 def test_module_conv_depthwise_int8_bf16(native_lib):
     from flextensor_b200.runtime import build
     from flextensor_b200.scheduler import schedule_with_config, schedule_with_config_ops
