@@ -35,7 +35,7 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # 6-item capture still holds half of its output in L2 when the kernel ends, so the write part
 # is a lower bound; the algorithmic figure is 1.61e9.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = (100.73e6 + 24.08e6) * 64 / 6
-KNOBS = {"cluster": 2, "tile_n": 256, "raster": 2, "group_m": 4}
+KNOBS = {"cluster": 2, "tile_n": 256, "raster": 3, "group_m": 4}
 
 
 def measured_peak():

@@ -147,7 +147,7 @@ int ftb_validate(int op, const ftb_config* cfg, int64_t m, int64_t n, int64_t k)
                         (op == 3 ? 0 : 32768);
     if (smem > 227 * 1024 - 2048) return FTB_E_BAD_CONFIG;
   }
-  if (cfg->raster < 0 || cfg->raster > 2 || cfg->group_m < 0) return FTB_E_BAD_CONFIG;
+  if (cfg->raster < 0 || cfg->raster > 3 || cfg->group_m < 0) return FTB_E_BAD_CONFIG;
   const int64_t kblk = 128 / esize;
   const int64_t num_kb = (k + kblk - 1) / kblk;
   if (cfg->split_k != 0 && (cfg->split_k < 1 || cfg->split_k > 64 || cfg->split_k > num_kb)) return FTB_E_BAD_CONFIG;

@@ -180,8 +180,19 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
   }
   if (c.stages < 2 || c.stages > kMaxStages) return FTB_E_BAD_CONFIG;
   if (smem_needed(bn_cta, c.stages, split3, epilogue_bytes) > kSmemLimit) return FTB_E_BAD_CONFIG;
-  if (c.raster < 0 || c.raster > 2) return FTB_E_BAD_CONFIG;
-  if (c.raster == 2 && c.group_m == 0) c.group_m = 8;
+  if (c.raster < 0 || c.raster > 3) return FTB_E_BAD_CONFIG;
+  if (c.raster == 0) {
+    // auto: a B operand much larger than what stays in L2 next to A wants grouped-M order (a wave
+    // of tiles then touches a few panels of both operands instead of all of B); otherwise n-fastest
+    const double b_bytes = static_cast<double>(n) * num_kb * 128.0;
+    if (batch == 1 && b_bytes > 32.0 * 1024 * 1024) {
+      c.raster = 3;
+      if (c.group_m == 0) c.group_m = 8;
+    } else {
+      c.raster = 1;
+    }
+  }
+  if (c.raster == 3 && c.group_m == 0) c.group_m = 8;
   if (c.group_m < 0) return FTB_E_BAD_CONFIG;
   if (c.split_k == 0) c.split_k = 1;
   if (c.split_k < 1 || c.split_k > 64 || c.split_k > num_kb) return FTB_E_BAD_CONFIG;
@@ -339,7 +350,7 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   p.num_kb = num_kb;
   p.tiles_m = tiles_m;
   p.tiles_n = static_cast<int>((n + p.bn - 1) / p.bn);
-  p.raster = cfg.raster;
+  p.raster = cfg.raster - 1;  // kernel: 0 n-fastest, 1 m-fastest, 2 grouped-M
   p.group_m = cfg.group_m;
   p.split_k = cfg.split_k;
   p.kblk = ki.kblk;
@@ -608,7 +619,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.tiles_m = static_cast<int>(tiles_m_launch);
     p.conv_tiles = static_cast<int>(tiles_m);
     p.tiles_n = static_cast<int>((kg + p.bn - 1) / p.bn);
-    p.raster = cfg.raster;
+    p.raster = cfg.raster - 1;
     p.group_m = cfg.group_m;
     p.split_k = cfg.split_k;
     p.kblk = ki.kblk;

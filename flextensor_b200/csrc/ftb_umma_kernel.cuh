@@ -562,21 +562,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ok = false;
             break;
           }
-          // x = hi + lo with hi exactly representable in TF32 (low 13 mantissa bits
-          // cleared); the elementwise rewrite keeps every value at its swizzled place.
+          // x = hi + lo.  The tensor core reads an fp32 operand as TF32 by dropping the low 13
+          // mantissa bits, so the stage as it landed already serves as `hi`; only
+          // lo = x - (x with those bits cleared), which is exact in fp32, has to be written.  The
+          // rewrite is elementwise, so every value keeps its swizzled place.
           uint8_t* base = stage0 + s * stage_bytes;
           for (uint32_t off = tid * 16; off < pair_bytes; off += 128 * 16) {
-            float4 x = *reinterpret_cast<float4*>(base + off);
-            float4 hi, lo;
-            hi.x = __uint_as_float(__float_as_uint(x.x) & 0xffffe000u);
-            hi.y = __uint_as_float(__float_as_uint(x.y) & 0xffffe000u);
-            hi.z = __uint_as_float(__float_as_uint(x.z) & 0xffffe000u);
-            hi.w = __uint_as_float(__float_as_uint(x.w) & 0xffffe000u);
-            lo.x = x.x - hi.x;
-            lo.y = x.y - hi.y;
-            lo.z = x.z - hi.z;
-            lo.w = x.w - hi.w;
-            *reinterpret_cast<float4*>(base + off) = hi;
+            const float4 x = *reinterpret_cast<const float4*>(base + off);
+            float4 lo;
+            lo.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xffffe000u);
+            lo.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xffffe000u);
+            lo.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xffffe000u);
+            lo.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xffffe000u);
             *reinterpret_cast<float4*>(base + pair_bytes + off) = lo;
           }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core reads

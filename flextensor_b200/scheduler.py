@@ -97,7 +97,14 @@ class Scheduler(object):
         self.re_evalutate_number = 10
         self.warm_up_epoch = 20
         self.warm_up_number = 20
-        self.early_stop_eps = 0.02  # milliseconds, as in the reference
+        self.early_stop_eps = 0.02  # milliseconds, as in the reference (capped at 1 % of the best, see below)
+
+    def _stop_eps(self, best_value):
+        """'Best did not move' threshold of the early stop: the reference's 0.02 ms, but never more than
+        1 % of the best time - its kernels ran for milliseconds, these often run for microseconds."""
+        if best_value < float("inf") and best_value > 0:
+            return min(self.early_stop_eps, 0.01 * best_value)
+        return self.early_stop_eps
 
     # ------------------------------------------------------------ evaluation plumbing
     def parallel_evaluate(self, old_configs, new_configs, number=1):
@@ -213,7 +220,7 @@ class Scheduler(object):
             if empty_walks >= self.early_stop:
                 _log("Early stop after continuous no trials %d times" % empty_walks)
                 break
-            if math.fabs(best_value - last_best) < self.early_stop_eps:
+            if math.fabs(best_value - last_best) < self._stop_eps(best_value):
                 unchanged += 1
             else:
                 last_best = best_value
@@ -263,7 +270,7 @@ class Scheduler(object):
             if group.top1_value() < best_value:
                 best_value, best = group.top1_value(), group.top1()
             _log("No. %d | [%.6f] The best currently %.6f" % (trial, time.time(), best_value), best)
-            if math.fabs(best_value - last_best) < self.early_stop_eps:
+            if math.fabs(best_value - last_best) < self._stop_eps(best_value):
                 unchanged += 1
             else:
                 last_best, unchanged = best_value, 0

@@ -340,7 +340,7 @@ def generate_space_intra_op_b200(op, down_graph=None):
         f32_out = op.output(0).dtype == "float32"
         splits = [s for s in (1, 2, 4, 8) if s <= num_kb] if f32_out else [1]
         space.add_subspace("split_k", KnobSpace("split_k", splits), "reduce")
-        space.add_subspace("raster", KnobSpace("raster", [[0, 0], [1, 0], [2, 2], [2, 4], [2, 8], [2, 16]]), "reorder")
+        space.add_subspace("raster", KnobSpace("raster", [[1, 0], [2, 0], [3, 2], [3, 4], [3, 8], [3, 16]]), "reorder")
         space.add_subspace("ctas", KnobSpace("ctas", [8, 7, 6, 4]), "unroll")
     elif family == "conv2d":
         k_out = extents["c"] // op.attrs.get("groups", 1)
@@ -356,7 +356,7 @@ def generate_space_intra_op_b200(op, down_graph=None):
         num_kb = taps * math.ceil(rc / 32)
         space.add_subspace("stages", KnobSpace("stages", [2, 3, 4, 5, 6, 7, 8]), "reduce")
         space.add_subspace("split_k", KnobSpace("split_k", [s for s in (1, 2, 3, 4, 6, 9) if s <= num_kb]), "reduce")
-        space.add_subspace("raster", KnobSpace("raster", [[0, 0], [1, 0]]), "reorder")
+        space.add_subspace("raster", KnobSpace("raster", [[1, 0], [2, 0]]), "reorder")
         space.add_subspace("ctas", KnobSpace("ctas", [8, 6, 4]), "unroll")
     else:  # depthwise
         out_h = extents["h"]

@@ -46,8 +46,8 @@ enum ftb_error {
 typedef struct ftb_config {
   int32_t tile_n;    /* accumulator columns per tile: 32, 64, 128 or 256                  */
   int32_t stages;    /* shared-memory pipeline depth, 2..8                                */
-  int32_t raster;    /* tile order: 0 n-fastest, 1 m-fastest, 2 grouped-M                 */
-  int32_t group_m;   /* group height for raster 2                                         */
+  int32_t raster;    /* tile order: 0 auto, 1 n-fastest, 2 m-fastest, 3 grouped-M         */
+  int32_t group_m;   /* group height for raster 3                                         */
   int32_t split_k;   /* K splits accumulated with atomics (fp32 outputs only)             */
   int32_t fp32_mode; /* fp32 inputs: 0 = single-pass TF32, 1 = 3xTF32 (fp32-grade)        */
   int32_t ctas;      /* persistent CTAs (default: one per SM)                             */

@@ -79,7 +79,7 @@ def test_gemm_f32_transposes_ragged(B, status, ta, tb, mode):
 @pytest.mark.parametrize("cfg", [
     {"fp32_mode": 1}, {"fp32_mode": 1, "tile_n": 64}, {"fp32_mode": 1, "tile_n": 128, "stages": 2},
     {"fp32_mode": 0}, {"fp32_mode": 0, "cluster": 2, "tile_n": 128}, {"fp32_mode": 0, "tile_n": 64, "split_k": 4},
-    {"fp32_mode": 0, "tile_n": 256, "raster": 1}, {"fp32_mode": 0, "raster": 2, "group_m": 4, "ctas": 74},
+    {"fp32_mode": 0, "tile_n": 256, "raster": 2}, {"fp32_mode": 0, "raster": 3, "group_m": 4, "ctas": 74},
 ])
 def test_gemm_f32_1024_every_knob(B, status, cfg):
     """The README task: C[1024,1024] = A.B, uniform[-1,1) inputs from seed 0."""
@@ -134,7 +134,7 @@ def test_bgemm_bf16_golden(B, status):
 
 @pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("cfg", [{"cluster": 1}, {"cluster": 2, "tile_n": 256}, {"cluster": 2, "tile_n": 128, "stages": 3},
-                                 {"cluster": 1, "tile_n": 64, "raster": 2, "group_m": 2}])
+                                 {"cluster": 1, "tile_n": 64, "raster": 3, "group_m": 2}])
 def test_bgemm_bf16_layouts_and_tails(B, status, ta, tb, cfg):
     items = [O.batch_gemm_item(i, 328, 264, 136, seed=31) for i in range(3)]
     a = np.stack([i[0] for i in items])
@@ -227,7 +227,7 @@ def test_gemm_s8_golden_and_layouts(B, status):
         for tb in (False, True):
             got = run_gemm_s8(B, a.T.copy() if ta else a, b.T.copy() if tb else b, ta, tb, status=status)
             assert (got == want).all(), (ta, tb)
-    for cfg in ({"cluster": 2, "tile_n": 256}, {"cluster": 1, "tile_n": 128, "stages": 3}, {"raster": 1}):
+    for cfg in ({"cluster": 2, "tile_n": 256}, {"cluster": 1, "tile_n": 128, "stages": 3}, {"raster": 2}, {"raster": 1}):
         assert (run_gemm_s8(B, a, b, cfg=cfg, status=status) == want).all(), cfg
 
 

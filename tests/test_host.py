@@ -167,9 +167,9 @@ def test_b200_space_per_family():
 def test_config_knob_round_trip():
     ops_, _ = gemm(1024, 1024, 1024)
     op = ops_[0]
-    knobs = {"tile_n": 128, "cluster": 2, "stages": 6, "split_k": 1, "raster": 2, "group_m": 8}
+    knobs = {"tile_n": 128, "cluster": 2, "stages": 6, "split_k": 1, "raster": 3, "group_m": 8}
     cfg = knobs_to_config(knobs, op)
-    assert cfg["spatial"] == [[128], [2]] and cfg["reduce"] == [[6], [1]] and cfg["reorder"] == [[2, 8]]
+    assert cfg["spatial"] == [[128], [2]] and cfg["reduce"] == [[6], [1]] and cfg["reorder"] == [[3, 8]]
     assert config_to_knobs(cfg, op) == knobs
     assert config_to_knobs({}, op) == {}
     assert config_to_knobs({"spatial": [[64]]}, op) == {"tile_n": 64}
