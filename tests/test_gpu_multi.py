@@ -82,3 +82,30 @@ def test_sharded_bgemm_fused_and_nccl(native_lib):
         if p.is_alive():
             p.terminate()
     assert dict(results) == {r: (True, True, True) for r in range(world)}
+
+
+def test_measurement_pool_uses_every_gpu(native_lib):
+    """Candidates are measured one per GPU in parallel worker processes."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    from flextensor_b200.measure import GpuPoolMeasurer
+    from flextensor_b200.task import TASK_TABLE
+    from flextensor_b200.templates import knobs_to_config
+    from flextensor_b200.utils import Config
+    key = "gemm_batch_gemm_(4, 256, 512, 384)_cuda(0)"
+    op = TASK_TABLE[key].func(*TASK_TABLE[key].args)[0][0]
+    jobs = []
+    for i in range(3 * n):
+        knobs = {"tile_n": (64, 128, 256)[i % 3], "cluster": 1 + i % 2, "stages": 2 + i % 3}
+        jobs.append((key, Config([knobs_to_config(knobs, op)], None), None))
+    pool = GpuPoolMeasurer(devices=list(range(n)))
+    try:
+        results = pool(jobs, number=3, timeout=60, parallel=n)
+        serial = pool(jobs[:2], number=3, timeout=60, parallel=1)
+    finally:
+        pool.close()
+    assert all(0 < r < 100 for r in results), results
+    assert all(0 < r < 100 for r in serial)
+    assert {dev for _, _, _, dev in pool.trace[:len(jobs)]} == set(range(n))
+    assert {dev for _, _, _, dev in pool.trace[len(jobs):]} == {0}

@@ -390,3 +390,19 @@ def test_offline_training_round_trip(tmp_path, monkeypatch):
                           op_perf_model_path=[(0, trained.model_path)])
     assert plan.steps[0].knobs["tile_n"] in (64, 128, 256)
     assert sum(calls) <= 4      # the op search ran on the model; only the tiny graph search measured
+
+
+def test_saved_search_log_replays():
+    """flextensor_b200/optimize/b200-config.log holds `key:json(configs)` lines found by searches on a
+    B200; every line must plan (the drivers' --test path reads it the same way)."""
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "flextensor_b200", "optimize",
+                        "b200-config.log")
+    count = 0
+    with open(path) as fin:
+        for line in fin:
+            name, string = line.split(":", 1)
+            obj = json.loads(string)
+            plan, bufs = schedule_with_config(name, Config(obj[0], obj[1]))
+            assert plan.steps and name in TASK_TABLE
+            count += 1
+    assert count >= 5
