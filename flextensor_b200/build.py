@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libftb200.so")
-SOURCES = ["ftb_core.cu", "ftb_gemm.cu", "ftb_dwconv.cu", "ftb_noalloc.cu"]
+SOURCES = ["ftb_core.cu", "ftb_gemm.cu", "ftb_dwconv.cu", "ftb_noalloc.cu", "ftb_simt_gemm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
 

@@ -317,8 +317,15 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   // TMA addressing rules: 16-byte aligned bases and row pitches.
   const int64_t a_pitch = (a_mn ? m : k) * ki.esize;
   const int64_t b_pitch = (b_mn ? n : k) * ki.esize;
-  if ((a_pitch & 15) || (b_pitch & 15)) return FTB_E_UNSUPPORTED;
-  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) return FTB_E_UNSUPPORTED;
+  if ((a_pitch & 15) || (b_pitch & 15) || (reinterpret_cast<uintptr_t>(a) & 15) ||
+      (reinterpret_cast<uintptr_t>(b) & 15)) {
+    // Not addressable by TMA: the CUDA-core kernel takes it (one destination only).
+    if (num_extra > 0) return FTB_E_UNSUPPORTED;
+    if (user && ftb_validate(kind == KIND_TF32 ? 0 : kind == KIND_BF16 ? 1 : 2, user, m, n, k) != FTB_OK)
+      return FTB_E_BAD_CONFIG;
+    return simt_gemm(kind == KIND_BF16 ? 0 : kind == KIND_TF32 ? 1 : 2, out, a, b, c, batch, m, n, k, trans_a,
+                     trans_b, stream_v);
+  }
 
   // The staged (bulk tensor store) epilogue needs 16-byte aligned output rows and bases.
   const int out_esize = out == OUT_BF16 ? 2 : 4;

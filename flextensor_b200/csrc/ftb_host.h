@@ -21,6 +21,10 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
                  int64_t n, int64_t k, int trans_a, int trans_b, const ftb_config* user, int* status,
                  void* stream, void* const* extra_dst, int num_extra);
 
+// CUDA-core GEMM for operands whose pitches or bases break the 16-byte rules of TMA.
+int simt_gemm(int kind, int out, const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n,
+              int64_t k, int trans_a, int trans_b, void* stream);
+
 int conv2d_generic(const float* in, const float* weight, const float* bias, float* out, int64_t n,
                    int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,
                    int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,

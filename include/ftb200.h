@@ -33,7 +33,7 @@ extern "C" {
 enum ftb_error {
   FTB_OK = 0,
   FTB_E_BAD_ARG = -1,     /* null pointer, non-positive extent, unknown enum value      */
-  FTB_E_UNSUPPORTED = -2, /* shape/stride the TMA path cannot address (16-byte rules)   */
+  FTB_E_UNSUPPORTED = -2, /* shape the kernels cannot take (e.g. conv groups that break 16-byte alignment) */
   FTB_E_BAD_CONFIG = -3,  /* knob outside its range or over the shared-memory budget    */
   FTB_E_WORKSPACE = -4,   /* workspace missing or too small                             */
   FTB_E_CUDA = -5,        /* a CUDA runtime/driver call failed; see ftb_last_cuda_error */
@@ -75,6 +75,10 @@ int64_t ftb_launch_count(void);
  * seconds the wait gives up, ORs FTB_DEV bit 1 into *status and the kernel ends normally; the
  * context stays usable.  Lets a host verify that a stuck pipeline surfaces as a status, not a hang. */
 int ftb_selftest_bounded_wait(int* status, void* stream);
+
+/* GEMM entry points: operands whose row pitch or base address is not a multiple of 16 bytes cannot
+ * be read by TMA; such calls are served by a CUDA-core kernel (correct, roughly 10x slower; plain
+ * fp32 arithmetic for fp32 inputs).  Everything else runs on the tcgen05 kernel. */
 
 /* C[M,N] = op(A) . op(B), fp32 in/out, TF32 tensor cores (flextensor/nn/ops.py:1074-1108 gemm).
  * trans_a = 0: A is [M,K] row-major, 1: A is [K,M]; trans_b = 0: B is [K,N], 1: B is [N,K]. */

@@ -106,18 +106,34 @@ def test_batched_gemm_f32(B, status):
     assert O.normalised_error(c.cpu().numpy(), O.batch_gemm(a, b)) <= TOL["gemm_f32_3xtf32"]
 
 
-def test_unaligned_shapes_are_refused_not_miscomputed(B):
-    a = torch.zeros(8, 6, device="cuda")   # K = 6 floats = 24 bytes per row: not a multiple of 16
-    b = torch.zeros(6, 8, device="cuda")
+def test_shapes_tma_cannot_address_run_on_the_cuda_core_kernel(B, status):
+    """Row pitches that are not multiples of 16 bytes (K = 6 floats, bf16 N = 28, int8 K = 50):
+    served by the CUDA-core kernel, same results."""
+    for (m, n, k, ta, tb) in [(8, 8, 6, False, False), (70, 33, 45, False, True), (19, 27, 13, True, False)]:
+        a, b = O.gemm_inputs(m, n, k, seed=m * n)
+        got = run_gemm_f32(B, a.T.copy() if ta else a, b.T.copy() if tb else b, ta, tb, status=status)
+        assert O.normalised_error(got, O.gemm(a, b)) <= 1e-5, (m, n, k)      # plain fp32 arithmetic here
+    items = [O.batch_gemm_item(i, 28, 28, 1024, seed=35) for i in range(3)]   # the reference's (32, 28, 1024, 28) shape
+    a = np.stack([i[0] for i in items])
+    b = np.stack([i[1] for i in items])
+    c = torch.full((3, 28, 28), float("nan"), device="cuda", dtype=torch.bfloat16)
+    B.bgemm_bf16(bf16_dev(a), bf16_dev(b), c, status=status)
+    assert O.bf16_output_ok(c.float().cpu().numpy(), O.batch_gemm(a, b))
+    a8, b8 = O.gemm_int8_inputs(37, 20, 50, seed=36)
+    assert (run_gemm_s8(B, a8, b8, status=status) == O.gemm_int8(a8, b8)).all()
+    assert (run_gemm_s8(B, a8, b8.T.copy(), tb=True, status=status) == O.gemm_int8(a8, b8)).all()
+
+
+def test_bad_arguments_are_refused(B):
     c = torch.zeros(8, 8, device="cuda")
-    with pytest.raises(B.FtbError) as err:
-        B.gemm_f32(a, b, c)
-    assert err.value.code == -2
     with pytest.raises(B.FtbError) as err:
         B.gemm_f32(torch.zeros(8, 8, device="cuda"), torch.zeros(8, 8, device="cuda"), c, cfg={"tile_n": 48})
     assert err.value.code == -3
+    with pytest.raises(B.FtbError) as err:
+        B.gemm_f32(torch.zeros(8, 6, device="cuda"), torch.zeros(6, 8, device="cuda"), c, cfg={"tile_n": 48})
+    assert err.value.code == -3
     with pytest.raises(TypeError):
-        B.gemm_f32(a.cpu(), b, c)
+        B.gemm_f32(torch.zeros(8, 8), torch.zeros(8, 8, device="cuda"), c)
 
 
 # ---------------------------------------------------------------- batched GEMM bf16
