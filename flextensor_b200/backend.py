@@ -40,11 +40,12 @@ class FtbConfig(ctypes.Structure):
         ("tile_h", ctypes.c_int32),
         ("threads", ctypes.c_int32),
         ("cluster", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 6),
+        ("algo", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 5),
     ]
 
     KNOBS = ("tile_n", "stages", "raster", "group_m", "split_k", "fp32_mode", "ctas", "tile_h", "threads",
-             "cluster")
+             "cluster", "algo")
 
     @classmethod
     def from_dict(cls, knobs):

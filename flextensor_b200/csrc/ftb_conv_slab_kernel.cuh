@@ -1,0 +1,334 @@
+// conv2d (stride 1) on the tensor cores with the input staged once per channel chunk and
+// the filter held in shared memory for the whole kernel.
+//
+// The implicit-GEMM lowering in ftb_umma_kernel.cuh fetches one shifted copy of the input
+// tile per filter tap, so an R x S filter reads the same pixels R*S times from L2.  Here a
+// CTA loads, per chunk of 32 input channels, ONE slab of (tile_h + halo) x (tile_w + halo)
+// pixels (channels-last, 128 B per pixel, 128-byte swizzled by the TMA unit).  Because
+// successive pixels are successive 128-byte rows of the slab, the A operand of tap (r, s)
+// is the same slab read from a row offset of r*dil_h*slab_w + s*dil_w: only the start
+// address of the shared-memory descriptor moves.  Accumulator row m then stands for the
+// pixel (m / slab_w, m % slab_w) of the tile; rows with m % slab_w >= tile_w are junk
+// (they mix the end of one image row with the start of the next) and are never stored.
+//
+// The filter (this CTA's taps x channel chunks x bn output channels) is loaded once and
+// stays resident, so the steady-state traffic of a tile is the slab alone.
+//
+//   warp 0      TMA producer     filter once, then one slab per (tile, channel chunk)
+//   warp 1      MMA issuer       taps x 4 tcgen05.mma per slab, accumulators in TMEM
+//   warps 2-5   epilogue         tcgen05.ld -> NCHW stores (atomic adds when taps are split)
+//
+// CTAs with the same blockIdx.x % split share a subset of the taps and walk the tile list
+// with a stride of gridDim.x / split.
+#pragma once
+#include "ftb_umma_kernel.cuh"
+
+namespace ftb {
+
+constexpr int kSlabMaxStages = 4;
+
+struct ConvSlabParams {
+  int N;        // output channels of this launch
+  int bn;       // accumulator columns (>= N, multiple of 16)
+  int tiles;    // output tiles: images x tiles_h x tiles_w
+  int tiles_h, tiles_w, tile_h, tile_w, slab_w;
+  int R, S, cchunks, split, taps_per_split;
+  int dil_h, dil_w, pad_h, pad_w, P, Q;
+  int conv_ktot;  // output channels of the whole tensor
+  int a_stages;
+  // staged epilogue: epi_bufs (0 = off, 1 or 2) buffers of 32 channels x tile pixels after the slabs
+  int epi_bufs;
+  uint32_t epi_buf_bytes;
+  uint32_t slab_bytes;   // bytes one slab load delivers
+  uint32_t slab_alloc;   // bytes reserved per slab stage (covers the furthest tap's 128 rows)
+  uint32_t b_tile_bytes; // bn x 128 B
+  uint32_t idesc;
+  float* out;
+  const float* bias;
+  int* status;
+};
+
+__global__ void __launch_bounds__(192, 1)
+conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_constant__ CUtensorMap tmap_w,
+                 const __grid_constant__ CUtensorMap tmap_out,
+                 const __grid_constant__ ConvSlabParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_afull[kSlabMaxStages];
+  __shared__ __align__(8) uint64_t bar_aempty[kSlabMaxStages];
+  __shared__ __align__(8) uint64_t bar_bfull;
+  __shared__ __align__(8) uint64_t bar_tfull[2];
+  __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_stages = p.a_stages;
+
+  const int ks = static_cast<int>(blockIdx.x) % p.split;
+  const int walker = static_cast<int>(blockIdx.x) / p.split;
+  const int walkers = static_cast<int>(gridDim.x) / p.split;
+  const int taps = p.R * p.S;
+  const int tap0 = ks * p.taps_per_split;
+  const int tap1 = min(taps, tap0 + p.taps_per_split);
+  const int ntaps = tap1 - tap0;
+  // filter first, slabs after it
+  const uint32_t b_base = smem_base;
+  const uint32_t a_base = smem_base + static_cast<uint32_t>(p.taps_per_split * p.cchunks) * p.b_tile_bytes;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (uint32_t s = 0; s < a_stages; ++s) {
+      mbar_init(smem_u32(&bar_afull[s]), 1);
+      mbar_init(smem_u32(&bar_aempty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_bfull), 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&bar_tfull[a]), 1);
+      mbar_init(smem_u32(&bar_tempty[a]), 4);
+    }
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    prefetch_tmap(&tmap_in);
+    prefetch_tmap(&tmap_w);
+    if (p.epi_bufs) prefetch_tmap(&tmap_out);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t afull0 = smem_u32(&bar_afull[0]);
+  const uint32_t aempty0 = smem_u32(&bar_aempty[0]);
+  const uint32_t bfull = smem_u32(&bar_bfull);
+  const int tiles_per_img = p.tiles_h * p.tiles_w;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && ntaps > 0) {
+      mbar_expect_tx(bfull, static_cast<uint32_t>(ntaps * p.cchunks) * p.b_tile_bytes);
+      {
+        uint32_t dst = b_base;
+        int kc = tap0 * p.cchunks * 32;  // the packed filter is [k_out][tap][chunk][32]
+        for (int i = 0; i < ntaps * p.cchunks; ++i, dst += p.b_tile_bytes, kc += 32)
+          tma_load_3d(dst, &tmap_w, bfull, kc, 0, 0);
+      }
+      uint32_t s = 0, ph = 0, sa = a_base;
+      bool ok = true;
+      for (int t = walker; t < p.tiles && ok; t += walkers) {
+        const int img = t / tiles_per_img;
+        const int rem = t - img * tiles_per_img;
+        const int th = rem / p.tiles_w, tw = rem - th * p.tiles_w;
+        const int h0 = th * p.tile_h - p.pad_h, w0 = tw * p.tile_w - p.pad_w;
+        for (int cc = 0; cc < p.cchunks; ++cc) {
+          if (!mbar_wait(aempty0 + 8 * s, ph ^ 1u, &abort_flag)) {
+            atomicOr(p.status, FTB_DEV_WAIT_EMPTY);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(afull0 + 8 * s, p.slab_bytes);
+          tma_load_4d(sa, &tmap_in, afull0 + 8 * s, cc * 32, w0, h0, img);
+          sa += p.slab_alloc;
+          if (++s == a_stages) {
+            s = 0;
+            ph ^= 1u;
+            sa = a_base;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && ntaps > 0) {
+      const uint32_t idesc = p.idesc;
+      const uint32_t hi = smem_desc_hi(16, 1024, 2);
+      const uint32_t b_tile_enc = p.b_tile_bytes >> 4;
+      const uint32_t slab_enc = p.slab_alloc >> 4;
+      const uint32_t a_lo0 = smem_desc_lo(a_base, 16);
+      const uint32_t b_lo0 = smem_desc_lo(b_base, 16);
+      // first tap of this CTA as (row, column) of the filter
+      const int tr0 = tap0 / p.S, ts0 = tap0 - tr0 * p.S;
+      uint32_t s = 0, ph = 0, a_lo = a_lo0;
+      int local = 0;
+      bool ok = mbar_wait(bfull, 0, &abort_flag);
+      if (!ok) {
+        atomicOr(p.status, FTB_DEV_WAIT_FULL);
+        abort_flag = 1;
+      }
+      for (int t = walker; t < p.tiles && ok; t += walkers, ++local) {
+        const uint32_t acc = local & 1;
+        const uint32_t aph = (local >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, &abort_flag)) {
+          atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kAccStride;
+        uint32_t accumulate = 0;
+        for (int cc = 0; cc < p.cchunks; ++cc) {
+          if (!mbar_wait(afull0 + 8 * s, ph, &abort_flag)) {
+            atomicOr(p.status, FTB_DEV_WAIT_FULL);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          int tr = tr0, ts = ts0;
+          uint32_t b_lo = b_lo0 + static_cast<uint32_t>(cc) * b_tile_enc;
+          for (int tap = 0; tap < ntaps; ++tap) {
+            // The slab is read from `off` pixel rows in.  The tensor core applies the 128-byte
+            // swizzle to the absolute shared-memory address, exactly as the TMA unit did when it
+            // wrote the slab, so a start address that is not a multiple of the 1024-byte swizzle
+            // period needs nothing else in the descriptor (its base-offset field stays 0; measured:
+            // setting it to the row phase gives wrong sums).
+            const uint32_t off = static_cast<uint32_t>(tr * p.dil_h * p.slab_w + ts * p.dil_w);
+            const uint32_t ta_lo = a_lo + off * 8u;
+#pragma unroll
+            for (int k = 0; k < kMmaPerKb; ++k) {
+              umma<KIND_TF32, false>(d_tmem, ta_lo + 2u * k, hi, b_lo + 2u * k, hi, idesc, accumulate);
+              accumulate = 1;
+            }
+            b_lo += static_cast<uint32_t>(p.cchunks) * b_tile_enc;
+            if (++ts == p.S) {
+              ts = 0;
+              ++tr;
+            }
+          }
+          tc_commit(aempty0 + 8 * s);
+          a_lo += slab_enc;
+          if (++s == a_stages) {
+            s = 0;
+            ph ^= 1u;
+            a_lo = a_lo0;
+          }
+        }
+        if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int prow = row / p.slab_w, pcol = row - prow * p.slab_w;
+    const bool in_tile = prow < p.tile_h && pcol < p.tile_w;
+    const long long plane = static_cast<long long>(p.P) * p.Q;
+    int local = 0;
+    uint32_t epi_seq = 0;
+    const uint32_t epi_base = a_base + a_stages * p.slab_alloc;
+    if (ntaps > 0) {
+      for (int t = walker; t < p.tiles; t += walkers, ++local) {
+        const uint32_t acc = local & 1;
+        const uint32_t aph = (local >> 1) & 1u;
+        bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull[acc]), aph, &abort_flag));
+        // The staged epilogue synchronises the four warps with each other: they must agree.
+        if (p.epi_bufs) got = named_barrier_all(2, 128, got);
+        if (!got) {
+          if (lane == 0) {
+            atomicOr(p.status, FTB_DEV_WAIT_TMEMFULL);
+            abort_flag = 1;
+          }
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kAccStride;
+        const int img = t / tiles_per_img;
+        const int rem = t - img * tiles_per_img;
+        const int th = rem / p.tiles_w, tw = rem - th * p.tiles_w;
+        if (p.epi_bufs) {
+          // ---- TMEM -> registers -> [channel][tile_h][tile_w] in shared memory -> one bulk tensor
+          // store (or fp32 reduce-add when the taps are split) per 32 output channels.  Lanes hold
+          // consecutive pixels, so the shared-memory writes of one channel are conflict-free and
+          // global memory sees whole rows of every channel plane.
+          const bool leader = (warp == 2 && lane == 0);
+          const uint32_t px_off = static_cast<uint32_t>(prow * p.tile_w + pcol) * 4u;
+          const uint32_t ch_stride = static_cast<uint32_t>(p.tile_h * p.tile_w) * 4u;
+          for (int c = 0; c < p.bn; c += 32, ++epi_seq) {
+            const uint32_t buf = epi_base + (p.epi_bufs == 2 ? (epi_seq & 1u) : 0u) * p.epi_buf_bytes;
+            if (leader) {
+              if (p.epi_bufs == 2) bulk_wait_group_read<1>();
+              else bulk_wait_group_read<0>();
+            }
+            named_barrier_sync(1, 128);
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c, v);
+            tmem_ld_wait();
+            if (c + 32 >= p.bn) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+            }
+            if (in_tile) {
+              const bool add_bias = p.bias != nullptr && ks == 0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float x = __uint_as_float(v[j]);
+                if (add_bias && c + j < p.N) x += p.bias[c + j];
+                st_shared_f32(buf + static_cast<uint32_t>(j) * ch_stride + px_off, x);
+              }
+            }
+            fence_proxy_async_smem();
+            named_barrier_sync(1, 128);
+            if (leader) {
+              if (c < p.N) {
+                if (p.split > 1) tma_reduce_add_4d(&tmap_out, buf, tw * p.tile_w, th * p.tile_h, c, img);
+                else tma_store_4d(&tmap_out, buf, tw * p.tile_w, th * p.tile_h, c, img);
+              }
+              bulk_commit_group();
+            }
+          }
+          continue;
+        }
+        const int oh = th * p.tile_h + prow, ow = tw * p.tile_w + pcol;
+        const bool row_ok = in_tile && oh < p.P && ow < p.Q;
+        float* dst0 = p.out + static_cast<long long>(img) * p.conv_ktot * plane + static_cast<long long>(oh) * p.Q + ow;
+        for (int c = 0; c < p.bn; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+          if (c + 32 >= p.bn) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+          }
+          if (!row_ok) continue;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = c + j;
+            if (n < p.N) {
+              float x = __uint_as_float(v[j]);
+              if (p.bias != nullptr && ks == 0) x += p.bias[n];
+              float* dst = dst0 + n * plane;
+              if (p.split > 1) atomicAdd(dst, x);
+              else *dst = x;
+            }
+          }
+        }
+      }
+    }
+    // Every bulk store of this CTA has been performed before the kernel ends.
+    if (p.epi_bufs && warp == 2 && lane == 0) bulk_wait_group<0>();
+    __syncwarp();
+  }
+
+  // ------------------------------------------------------------ teardown
+  if (*reinterpret_cast<volatile int*>(&abort_flag)) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace ftb

@@ -3,8 +3,10 @@
 // GEMM int8 and conv2d (implicit GEMM).
 #include "ftb_host.h"
 #include "ftb_umma_kernel.cuh"
+#include "ftb_conv_slab_kernel.cuh"
 
 #include <cudaTypedefs.h>
+#include <cstdlib>
 #include <mutex>
 
 namespace ftb {
@@ -531,6 +533,166 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
   }
 }
 
+// Launches the layout pass both conv kernels read from (input to channels-last, filter packed).
+static int conv_prepass(const float* in, const float* weight, float* in_nhwc, float* w_packed, int64_t n, int64_t c,
+                        int64_t h, int64_t w, int64_t k, int64_t cg, int64_t r, int64_t s, const ConvWs& ws,
+                        int num_sms, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int HW = static_cast<int>(h * w);
+  const int hw_tiles = (HW + kPrePx - 1) / kPrePx, c_tiles = static_cast<int>((ws.cp + kPreCh - 1) / kPreCh);
+  const int in_blocks = static_cast<int>(n) * hw_tiles * c_tiles;
+  const long long wtotal = k * r * s * ws.cchunks * 32;
+  int w_blocks = static_cast<int>((wtotal + 255) / 256);
+  if (w_blocks > 4 * num_sms) w_blocks = 4 * num_sms;
+  conv_prepass_kernel<<<in_blocks + w_blocks, 256, 0, stream>>>(
+      in, weight, in_nhwc, w_packed, static_cast<int>(n), static_cast<int>(c), HW, static_cast<int>(ws.cp),
+      static_cast<int>(k), static_cast<int>(cg), static_cast<int>(r * s), static_cast<int>(ws.cchunks), hw_tiles,
+      c_tiles, in_blocks);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_cuda_error(static_cast<int>(e));
+    return FTB_E_CUDA;
+  }
+  return FTB_OK;
+}
+
+// Plan of the slab kernel (ftb_conv_slab_kernel.cuh) for one conv2d; `ok` is false when the
+// shape or the knobs do not fit it.
+struct SlabPlan {
+  bool ok;
+  ConvSlabParams p;
+  int ctas;
+  size_t smem;
+  uint32_t box_w, box_h;
+};
+
+static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t P, int64_t Q, int64_t r, int64_t s,
+                          int64_t cchunks, int dil_h, int dil_w, int pad_h, int pad_w, bool out_aligned,
+                          int num_sms) {
+  SlabPlan sp;
+  memset(&sp, 0, sizeof(sp));
+  if (kg > 256) return sp;
+  const int halo_w = static_cast<int>(s - 1) * dil_w, halo_h = static_cast<int>(r - 1) * dil_h;
+  if (halo_w >= 64 || halo_h >= 128) return sp;
+  // Bulk tensor stores of the result need 16-byte aligned rows and boxes.
+  const bool staged_ok = out_aligned && Q % 4 == 0;
+  int tile_w = static_cast<int>(Q < 128 - halo_w ? Q : 128 - halo_w);
+  if (tile_w < Q && staged_ok) tile_w &= ~3;
+  const int slab_w = tile_w + halo_w;
+  int tile_h = 128 / slab_w;
+  if (tile_h > P) tile_h = static_cast<int>(P);
+  if (user && user->tile_h > 0) {
+    if (user->tile_h > tile_h) return sp;
+    tile_h = user->tile_h;
+  }
+  const int slab_h = tile_h + halo_h;
+  if (slab_h > 256) return sp;
+  const int bn = static_cast<int>((kg + 15) / 16 * 16);
+  if (user && user->tile_n != 0 && user->tile_n < kg) return sp;  // the kernel keeps all output channels in one tile
+  const long long slab_rows = static_cast<long long>(slab_h) * slab_w;
+  // The furthest tap reads 128 rows from its offset: past the end of what was loaded it reads
+  // whatever follows in shared memory (into rows that are never stored), so the bytes after the
+  // last slab must exist.
+  long long reach_rows = static_cast<long long>(halo_h) * slab_w + halo_w + 128;
+  if (reach_rows < slab_rows) reach_rows = slab_rows;
+  const uint32_t slab_stride = static_cast<uint32_t>((slab_rows * 128 + 1023) / 1024 * 1024);
+  const size_t tail = static_cast<size_t>(reach_rows * 128 > slab_stride ? reach_rows * 128 - slab_stride : 0);
+  const uint32_t epi_buf = staged_ok ? static_cast<uint32_t>((32ll * tile_h * tile_w * 4 + 127) / 128 * 128) : 0u;
+  const int taps = static_cast<int>(r * s);
+  const int tiles_w = static_cast<int>((Q + tile_w - 1) / tile_w);
+  const int tiles_h = static_cast<int>((P + tile_h - 1) / tile_h);
+  const long long tiles = n * tiles_h * tiles_w;
+  if (tiles > 0x7fffffffll) return sp;
+  const uint32_t b_tile = static_cast<uint32_t>(bn) * 128u;
+  const size_t after_min = tail > epi_buf ? tail : epi_buf;
+  auto fits = [&](int split, int* a_stages, int* epi_bufs) {
+    const int tps = (taps + split - 1) / split;
+    const size_t b_bytes = static_cast<size_t>(tps) * cchunks * b_tile;
+    if (b_bytes + 2 * static_cast<size_t>(slab_stride) + after_min + 1024 > kSmemLimit) return false;
+    const size_t rest = kSmemLimit - 1024 - b_bytes;
+    size_t st = (rest - after_min) / slab_stride;
+    if (st > static_cast<size_t>(kSlabMaxStages)) st = kSlabMaxStages;
+    *a_stages = static_cast<int>(st);
+    *epi_bufs = epi_buf == 0 ? 0 : (rest - st * slab_stride >= 2 * static_cast<size_t>(epi_buf) ? 2 : 1);
+    return true;
+  };
+  int split = 0, a_stages = 0, epi_bufs = 0;
+  if (user && user->split_k > 0) {
+    split = user->split_k;
+    if (split > taps || !fits(split, &a_stages, &epi_bufs)) return sp;
+  } else {
+    // Splitting the taps over CTAs fills idle SMs when the tile list is short (at the price of
+    // adding partial sums in global memory) and shrinks the resident filter when it would not
+    // fit otherwise.
+    long long want = num_sms / (tiles > 0 ? tiles : 1);
+    if (want > 4) want = 4;
+    for (int d = 1; d <= taps; ++d) {
+      if ((d - 1) * ((taps + d - 1) / d) >= taps) continue;  // would leave a split without taps
+      if (!fits(d, &a_stages, &epi_bufs)) continue;
+      if (split == 0 || d <= want) split = d;
+      if (d >= want) break;
+    }
+    if (split == 0 || !fits(split, &a_stages, &epi_bufs)) return sp;
+  }
+  const int tps = (taps + split - 1) / split;
+  ConvSlabParams& p = sp.p;
+  p.N = static_cast<int>(kg);
+  p.bn = bn;
+  p.tiles = static_cast<int>(tiles);
+  p.tiles_h = tiles_h; p.tiles_w = tiles_w; p.tile_h = tile_h; p.tile_w = tile_w; p.slab_w = slab_w;
+  p.R = static_cast<int>(r); p.S = static_cast<int>(s); p.cchunks = static_cast<int>(cchunks);
+  p.split = split; p.taps_per_split = tps;
+  p.dil_h = dil_h; p.dil_w = dil_w; p.pad_h = pad_h; p.pad_w = pad_w;
+  p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);
+  p.a_stages = a_stages;
+  p.epi_bufs = epi_bufs;
+  p.epi_buf_bytes = epi_buf;
+  p.slab_bytes = static_cast<uint32_t>(slab_rows * 128);
+  p.slab_alloc = slab_stride;
+  p.b_tile_bytes = b_tile;
+  p.idesc = make_idesc(kind_info(KIND_TF32), bn, 0, 0, kTileM);
+  long long walkers = num_sms / split;
+  if (user && user->ctas > 0) walkers = user->ctas / split;
+  if (walkers > tiles) walkers = tiles;
+  if (walkers < 1) walkers = 1;
+  sp.ctas = static_cast<int>(walkers) * split;
+  const size_t after = static_cast<size_t>(epi_bufs) * epi_buf > tail ? static_cast<size_t>(epi_bufs) * epi_buf : tail;
+  sp.smem = static_cast<size_t>(tps) * cchunks * b_tile + static_cast<size_t>(a_stages) * slab_stride + after + 1024;
+  sp.box_w = static_cast<uint32_t>(slab_w);
+  sp.box_h = static_cast<uint32_t>(slab_h);
+  sp.ok = true;
+  return sp;
+}
+
+static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap& tout, const SlabPlan& sp,
+                       cudaStream_t stream) {
+  static std::mutex mu;
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !done[dev]) {
+      cudaError_t attr_err = cudaFuncSetAttribute(conv_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  static_cast<int>(kSmemLimit));
+      if (attr_err != cudaSuccess) {
+        set_last_cuda_error(static_cast<int>(attr_err));
+        return FTB_E_CUDA;
+      }
+      done[dev] = true;
+    }
+  }
+  conv_slab_kernel<<<sp.ctas, 192, sp.smem, stream>>>(tin, tw, tout, sp.p);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_cuda_error(static_cast<int>(e));
+    return FTB_E_CUDA;
+  }
+  return FTB_OK;
+}
+
 int conv2d_generic(const float* in, const float* weight, const float* bias, float* out, int64_t n,
                    int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,
                    int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
@@ -558,6 +720,72 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   const bool split3 = user && user->fp32_mode == 1;
   if (user && (user->fp32_mode < 0 || user->fp32_mode > 1)) return FTB_E_BAD_CONFIG;
   const int num_sms = sm_count();
+
+  // Filters with more than one tap at stride 1 go to the slab kernel when it can take them.
+  const int algo = user ? user->algo : 0;
+  if (algo < 0 || algo > 2) return FTB_E_BAD_CONFIG;
+  SlabPlan sp;
+  sp.ok = false;
+  if (algo != 1 && groups == 1 && stride_h == 1 && stride_w == 1 && !split3 && (r * s > 1 || algo == 2) &&
+      !(user && user->cluster == 2))
+    sp = plan_slab(user, n, kg, P, Q, r, s, ws.cchunks, dil_h, dil_w, pad_h, pad_w,
+                   (reinterpret_cast<uintptr_t>(out) & 15) == 0, num_sms);
+  if (algo == 2 && !sp.ok) return FTB_E_UNSUPPORTED;
+  if (sp.ok) {
+    if (user) {
+      rc = ftb_validate(3, user, n * P * Q, k, c * r * s);
+      if (rc) return rc;
+    }
+    rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v);
+    if (rc) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    if (sp.p.split > 1) {
+      cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(n * k * P * Q) * 4, stream);
+      if (e != cudaSuccess) {
+        set_last_cuda_error(static_cast<int>(e));
+        return FTB_E_CUDA;
+      }
+    }
+    sp.p.out = out;
+    sp.p.bias = bias;
+    sp.p.conv_ktot = static_cast<int>(k);
+    sp.p.status = status ? status : fallback_status();
+    if (!sp.p.status) return FTB_E_CUDA;
+    CUtensorMap tin, tw;
+    {
+      uint64_t dims[4] = {static_cast<uint64_t>(ws.cp), static_cast<uint64_t>(w), static_cast<uint64_t>(h),
+                          static_cast<uint64_t>(n)};
+      uint64_t strides[3] = {static_cast<uint64_t>(ws.cp) * 4, static_cast<uint64_t>(w) * ws.cp * 4,
+                             static_cast<uint64_t>(h) * w * ws.cp * 4};
+      uint32_t box[4] = {32, sp.box_w, sp.box_h, 1};
+      const uint32_t ones[4] = {1, 1, 1, 1};
+      rc = make_tmap(&tin, ki.dt, 4, in_nhwc, dims, strides, box, ones);
+      if (rc) return rc;
+    }
+    {
+      const uint64_t kdim = static_cast<uint64_t>(r * s * ws.cchunks) * 32;
+      uint64_t dims[3] = {kdim, static_cast<uint64_t>(kg), 1};
+      uint64_t strides[2] = {kdim * 4, kdim * 4 * kg};
+      uint32_t box[3] = {32, static_cast<uint32_t>(sp.p.bn), 1};
+      const uint32_t ones[3] = {1, 1, 1};
+      rc = make_tmap(&tw, ki.dt, 3, w_packed, dims, strides, box, ones);
+      if (rc) return rc;
+    }
+    CUtensorMap tout;
+    memset(&tout, 0, sizeof(tout));
+    if (sp.p.epi_bufs) {
+      // (w, h, channel, image) view of the NCHW result; a box is 32 channels of one output tile.
+      uint64_t dims[4] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(k),
+                          static_cast<uint64_t>(n)};
+      uint64_t strides[3] = {static_cast<uint64_t>(Q) * 4, static_cast<uint64_t>(P) * Q * 4,
+                             static_cast<uint64_t>(k) * P * Q * 4};
+      uint32_t box[4] = {static_cast<uint32_t>(sp.p.tile_w), static_cast<uint32_t>(sp.p.tile_h), 32, 1};
+      const uint32_t ones[4] = {1, 1, 1, 1};
+      rc = make_tmap(&tout, ki.dt, 4, out, dims, strides, box, ones, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    }
+    return launch_slab(tin, tw, tout, sp, stream);
+  }
 
   // Output tile of the implicit GEMM: tile_h x tile_w pixels (<= 128) of one image.
   int tile_w = static_cast<int>(Q < 128 ? Q : 128);
@@ -587,24 +815,8 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   }
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  {
-    const int HW = static_cast<int>(h * w);
-    const int hw_tiles = (HW + kPrePx - 1) / kPrePx, c_tiles = static_cast<int>((ws.cp + kPreCh - 1) / kPreCh);
-    const int in_blocks = static_cast<int>(n) * hw_tiles * c_tiles;
-    const long long wtotal = k * r * s * ws.cchunks * 32;
-    int w_blocks = static_cast<int>((wtotal + 255) / 256);
-    if (w_blocks > 4 * num_sms) w_blocks = 4 * num_sms;
-    conv_prepass_kernel<<<in_blocks + w_blocks, 256, 0, stream>>>(
-        in, weight, in_nhwc, w_packed, static_cast<int>(n), static_cast<int>(c), HW,
-        static_cast<int>(ws.cp), static_cast<int>(k), static_cast<int>(cg), static_cast<int>(r * s),
-        static_cast<int>(ws.cchunks), hw_tiles, c_tiles, in_blocks);
-    count_launch();
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) {
-      set_last_cuda_error(static_cast<int>(e));
-      return FTB_E_CUDA;
-    }
-  }
+  rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v);
+  if (rc) return rc;
   if (cfg.split_k > 1) {
     cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(n * k * P * Q) * 4, stream);
     if (e != cudaSuccess) {

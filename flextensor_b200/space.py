@@ -293,7 +293,7 @@ B200_LAYOUT = {
     "contraction": {"spatial": ["tile_n", "cluster"], "reduce": ["stages", "split_k"], "reorder": ["raster"],
                     "unroll": ["ctas"]},
     "conv2d": {"spatial": ["tile_n", "tile_h", "cluster"], "reduce": ["stages", "split_k"], "reorder": ["raster"],
-               "unroll": ["ctas"]},
+               "unroll": ["ctas"], "inline": ["algo"]},
     "depthwise_conv2d": {"spatial": ["tile_h", "threads"], "reduce": [], "reorder": [], "unroll": []},
 }
 
@@ -358,6 +358,11 @@ def generate_space_intra_op_b200(op, down_graph=None):
         space.add_subspace("split_k", KnobSpace("split_k", [s for s in (1, 2, 3, 4, 6, 9) if s <= num_kb]), "reduce")
         space.add_subspace("raster", KnobSpace("raster", [[1, 0], [2, 0]]), "reorder")
         space.add_subspace("ctas", KnobSpace("ctas", [8, 6, 4]), "unroll")
+        # 1 = one shifted input tile per filter tap; 2 = one input slab per channel chunk shared by
+        # all taps with the filter resident in shared memory (stride 1, one group, <= 256 channels out)
+        slab_ok = (taps > 1 and op.attrs.get("groups", 1) == 1 and k_out <= 256
+                   and tuple(op.attrs.get("stride", (1, 1))) == (1, 1))
+        space.add_subspace("algo", KnobSpace("algo", [1, 2] if slab_ok else [1]), "inline")
     else:  # depthwise
         out_h = extents["h"]
         strips = sorted(set(_divisor_like(out_h, [1, 2, 4, 7, 8, 14, 16, 28, 32, 56, 64, 112]) + [out_h]))

@@ -346,6 +346,43 @@ def test_conv2d_cta_pairs(B, status, shape, cfg):
     assert O.normalised_error(got, want) <= TOL["conv2d_tf32"]
 
 
+@pytest.mark.parametrize("shape", [
+    # n, c, h, w, k, r, pad, dil
+    (1, 64, 56, 56, 64, 3, 1, 1),      # bulk-store epilogue, filter taps split over CTAs
+    (5, 64, 56, 56, 64, 3, 1, 1),      # more tiles than CTAs: slab ring and both accumulators wrap
+    (2, 16, 128, 128, 40, 3, 1, 1),    # two tiles across the width, 40 of 48 accumulator columns used
+    (2, 32, 14, 14, 48, 3, 1, 1),      # rows that bulk stores cannot address -> per-thread stores
+    (1, 64, 56, 56, 64, 3, 2, 2),      # dilation 2
+    (1, 8, 33, 130, 16, 5, 2, 1),      # 5x5, 25 taps
+    (3, 40, 30, 30, 80, 3, 0, 1),      # no padding, channel count that is no multiple of 32
+])
+@pytest.mark.parametrize("cfg", [{"algo": 2}, {"algo": 2, "split_k": 3}, {"algo": 2, "tile_h": 1}, {"algo": 1}])
+def test_conv2d_slab_algorithm(B, status, shape, cfg):
+    """One input slab per channel chunk shared by all filter taps (algo 2) against the oracle and
+    against the per-tap lowering (algo 1)."""
+    n, c, h, wd, k, r, pad, dil = shape
+    x, w = O.conv2d_inputs(n, c, h, wd, k, r, r, seed=57)
+    bias = np.random.default_rng(58).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, 1, pad, dil, 1)
+    got = run_conv(B, x, w, bias, 1, pad, dil, 1, cfg=dict(cfg, fp32_mode=0), status=status)
+    assert got.shape == want.shape
+    assert O.normalised_error(got, want) <= TOL["conv2d_tf32"]
+    assert int(status.item()) == 0
+
+
+def test_conv2d_slab_algorithm_refuses_what_it_cannot_take(B, status):
+    x, w = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, seed=59)
+    for kwargs, cfg in ((dict(stride=2), {"algo": 2}),                 # stride 2
+                        (dict(stride=1), {"algo": 2, "fp32_mode": 1}),  # 3xTF32
+                        (dict(stride=1), {"algo": 2, "tile_n": 16}),                # not a tile width
+                        (dict(stride=1), {"algo": 3})):
+        with pytest.raises(B.FtbError):
+            run_conv(B, x, w, None, kwargs["stride"], 1, 1, 1, cfg=cfg, status=status)
+    xg, wg = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, groups=2, seed=59)
+    with pytest.raises(B.FtbError):
+        run_conv(B, xg, wg, None, 1, 1, 1, 2, cfg={"algo": 2}, status=status)
+
+
 def test_conv2d_workspace_is_required(B):
     x = torch.zeros(1, 8, 8, 8, device="cuda")
     w = torch.zeros(8, 8, 3, 3, device="cuda")

@@ -155,6 +155,12 @@ def test_b200_space_per_family():
     cv = SP.generate_space_intra_op(op_lst[1], down, target="cuda")
     assert [e[0] for e in cv.subspaces["tile_h"].static_entities] == [1, 2]
     assert 9 in [e[0] for e in cv.subspaces["split_k"].static_entities]
+    assert [e[0] for e in cv.subspaces["algo"].static_entities] == [1, 2] and cv.types["inline"] == ["algo"]
+    strided = flatten_graph(conv2d(1, 64, 56, 56, 64, 3, 2, 1, 1, 1)[0])
+    assert [e[0] for e in SP.generate_space_intra_op(strided[0][1], strided[1], target="cuda")
+            .subspaces["algo"].static_entities] == [1]                    # the slab kernel is stride 1 only
+    knobs = config_to_knobs({"spatial": [[64], [2], [1]], "inline": [[2]]}, op_lst[1])
+    assert knobs == {"tile_n": 64, "tile_h": 2, "cluster": 1, "algo": 2}
     dw = SP.generate_space_intra_op(flatten_graph(depthwise_conv2d(1, 256, 56, 56, 1, 3, 1, 1, 1)[0])[0][1], {},
                                     target="cuda")
     assert list(dw.subspaces) == ["tile_h", "threads"]
