@@ -302,8 +302,11 @@ static void operand_layout(const KindInfo& ki, int mn_major, int tile_extent, in
 
 int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64_t batch, int64_t m,
                  int64_t n, int64_t k, int trans_a, int trans_b, const ftb_config* user, int* status,
-                 void* stream_v, void* const* extra_dst, int num_extra) {
+                 void* stream_v, void* const* extra_dst, int num_extra, const GemmExtras* extras) {
   if (!a || !b || !c) return FTB_E_BAD_ARG;
+  const bool a_bcast = extras && extras->a_broadcast;
+  const float* row_bias = extras ? extras->row_bias : nullptr;
+  if (row_bias && out != OUT_F32) return FTB_E_BAD_ARG;
   if (num_extra < 0 || num_extra > kMaxDst - 1 || (num_extra > 0 && !extra_dst)) return FTB_E_BAD_ARG;
   for (int d = 0; d < num_extra; ++d)
     if (!extra_dst[d]) return FTB_E_BAD_ARG;
@@ -322,7 +325,7 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   if ((a_pitch & 15) || (b_pitch & 15) || (reinterpret_cast<uintptr_t>(a) & 15) ||
       (reinterpret_cast<uintptr_t>(b) & 15)) {
     // Not addressable by TMA: the CUDA-core kernel takes it (one destination only).
-    if (num_extra > 0) return FTB_E_UNSUPPORTED;
+    if (num_extra > 0 || extras) return FTB_E_UNSUPPORTED;
     if (user && ftb_validate(kind == KIND_TF32 ? 0 : kind == KIND_BF16 ? 1 : 2, user, m, n, k) != FTB_OK)
       return FTB_E_BAD_CONFIG;
     return simt_gemm(kind == KIND_BF16 ? 0 : kind == KIND_TF32 ? 1 : 2, out, a, b, c, batch, m, n, k, trans_a,
@@ -377,6 +380,8 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   p.C = c;
   p.ldc = n;
   p.c_batch_stride = m * n;
+  p.bias = row_bias;
+  p.a_bcast = a_bcast ? 1 : 0;
   p.status = status ? status : fallback_status();
   if (!p.status) return FTB_E_CUDA;
   p.slab_cols = 128 / out_esize;
@@ -405,10 +410,10 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
     uint64_t dims[3], strides[2];
     uint32_t box[3];
     if (a_mn) {
-      dims[0] = m; dims[1] = k; dims[2] = batch;
+      dims[0] = m; dims[1] = k; dims[2] = a_bcast ? 1 : batch;
       box[0] = p.a_box_mn; box[1] = ki.kblk; box[2] = 1;
     } else {
-      dims[0] = k; dims[1] = m; dims[2] = batch;
+      dims[0] = k; dims[1] = m; dims[2] = a_bcast ? 1 : batch;
       box[0] = ki.kblk; box[1] = kTileM; box[2] = 1;
     }
     strides[0] = dims[0] * ki.esize;
@@ -721,9 +726,32 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   if (user && (user->fp32_mode < 0 || user->fp32_mode > 1)) return FTB_E_BAD_CONFIG;
   const int num_sms = sm_count();
 
-  // Filters with more than one tap at stride 1 go to the slab kernel when it can take them.
   const int algo = user ? user->algo : 0;
-  if (algo < 0 || algo > 2) return FTB_E_BAD_CONFIG;
+  if (algo < 0 || algo > 3) return FTB_E_BAD_CONFIG;
+  // A 1x1 filter at stride 1 without padding is a batched GEMM on the NCHW tensors as they are:
+  // out[b] (K x HW) = weight (K x C) * in[b] (C x HW), the pixels being the contiguous dimension
+  // of both the B operand and the result.  No layout pass, no workspace traffic.
+  {
+    const bool is_gemm = r == 1 && s == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 &&
+                         groups == 1 && (h * w) % 4 == 0 && c % 4 == 0 &&
+                         ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+    if (algo == 3 && !is_gemm) return FTB_E_UNSUPPORTED;
+    if (is_gemm && (algo == 0 || algo == 3)) {
+      ftb_config gcfg;
+      memset(&gcfg, 0, sizeof(gcfg));
+      if (user) {
+        gcfg = *user;
+        gcfg.tile_h = 0;
+        gcfg.algo = 0;
+      }
+      GemmExtras ex;
+      ex.a_broadcast = 1;
+      ex.row_bias = bias;
+      return gemm_generic(KIND_TF32, OUT_F32, weight, in, out, n, k, h * w, c, 0, 0, user ? &gcfg : nullptr, status,
+                          stream_v, nullptr, 0, &ex);
+    }
+  }
+  // Filters with more than one tap at stride 1 go to the slab kernel when it can take them.
   SlabPlan sp;
   sp.ok = false;
   if (algo != 1 && groups == 1 && stride_h == 1 && stride_w == 1 && !split3 && (r * s > 1 || algo == 2) &&
@@ -798,7 +826,22 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   const int num_kb = static_cast<int>(r * s * ws.cchunks);
   const long long tiles_m = static_cast<long long>(n) * tiles_h * tiles_w;
   ftb_config cfg;
-  rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg);
+  // The result leaves through bulk tensor stores when they can address it (16-byte aligned rows
+  // and boxes) and the staging buffers fit beside the chosen pipeline depth.
+  bool staged = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && Q % 4 == 0 && tile_w % 4 == 0 &&
+                (P * Q * 4) % 16 == 0 && (groups == 1 || (kg * P * Q * 4) % 16 == 0);
+  {
+    const char* e = getenv("FTB_EPILOGUE");  // "direct" forces per-thread global stores (diagnostics)
+    if (e && strcmp(e, "direct") == 0) staged = false;
+  }
+  rc = FTB_E_BAD_CONFIG;
+  if (staged)
+    rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg,
+                        kEpilogueStaging);
+  if (rc) {
+    staged = false;
+    rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg);
+  }
   if (rc) return rc;
   const bool pair = cfg.cluster == 2;
   const long long tiles_m_launch = pair ? (tiles_m + 1) / 2 : tiles_m;
@@ -901,6 +944,20 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     }
     StoreMaps tc;
     memset(&tc, 0, sizeof(tc));
+    if (staged) {
+      // (w, h, channel, image) view of this group's planes of the NCHW result
+      p.tma_store = 1;
+      p.num_dst = 1;
+      uint64_t dims[4] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(kg),
+                          static_cast<uint64_t>(n)};
+      uint64_t strides[3] = {static_cast<uint64_t>(Q) * 4, static_cast<uint64_t>(P) * Q * 4,
+                             static_cast<uint64_t>(k) * P * Q * 4};
+      uint32_t box[4] = {static_cast<uint32_t>(tile_w), static_cast<uint32_t>(tile_h), 32, 1};
+      const uint32_t ones[4] = {1, 1, 1, 1};
+      rc = make_tmap(&tc.dst[0], ki.dt, 4, out + static_cast<int64_t>(g) * kg * P * Q, dims, strides, box, ones,
+                     CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    }
     rc = dispatch(KIND_TF32, OUT_F32, split3, pair, ta, tb, tc, p, ctas, stream);
     if (rc) return rc;
   }

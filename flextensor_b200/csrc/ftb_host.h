@@ -16,10 +16,16 @@ int sm_count();
 // Device address of the library's own status word, used when the caller passes none.
 int* fallback_status();
 
+// Options of gemm_generic beyond the plain (batched) product.
+struct GemmExtras {
+  int a_broadcast;        // 1: every batch entry multiplies the same A (A holds one matrix)
+  const float* row_bias;  // fp32 output only: bias[i] added to row i of every result, may be null
+};
+
 // `extra_dst`: further buffers (num_extra of them) that receive the same result as `c`.
 int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64_t batch, int64_t m,
                  int64_t n, int64_t k, int trans_a, int trans_b, const ftb_config* user, int* status,
-                 void* stream, void* const* extra_dst, int num_extra);
+                 void* stream, void* const* extra_dst, int num_extra, const GemmExtras* extras = nullptr);
 
 // CUDA-core GEMM for operands whose pitches or bases break the 16-byte rules of TMA.
 int simt_gemm(int kind, int out, const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n,

@@ -4,7 +4,8 @@
 //
 //   warp 0      TMA producer     global -> 128B-swizzled shared-memory stages
 //   warp 1      MMA issuer       tcgen05.mma, accumulators in TMEM (two buffers)
-//   warps 2-5   epilogue         tcgen05.ld -> convert -> global stores
+//   warps 2-5   epilogue         tcgen05.ld -> convert -> shared-memory slab -> bulk tensor stores
+//                                (or per-thread global stores where bulk stores cannot address the result)
 //   warps 6-9   split stage      only for 3xTF32: rewrites a stage as (hi, lo) pairs
 //
 // A CTA owns 128 accumulator rows (one row per TMEM lane) by `bn` columns and walks
@@ -56,7 +57,8 @@ struct UmmaParams {
   // output
   void* C;
   long long ldc, c_batch_stride;
-  const float* bias;  // conv only, may be null
+  const float* bias;  // conv: per output channel; GEMM (fp32 out): per row of the result; may be null
+  int a_bcast;        // GEMM: every batch entry reads A of batch 0
   // implicit-GEMM conv geometry (conv != 0)
   int conv, P, Q, tile_h, tile_w, tiles_h, tiles_w, R, S, cchunks;
   int conv_ktot, conv_koff;  // output channels of the whole conv / first channel of this group
@@ -189,6 +191,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int kb1 = min(num_kb, kb0 + kb_per_split);
         const int m0 = tc.m * p.pair_m + static_cast<int>(cta_rank) * kTileM;
         const int n0 = tc.n * p.bn + static_cast<int>(cta_rank) * p.b_rows;
+        const int ab = p.a_bcast ? 0 : tc.b;  // batch coordinate of A
         // conv: walking (r, s, channel chunk) with counters instead of div/mod per block
         int img = 0, h0 = 0, w0 = 0, cc = 0, ts = 0, tr = 0;
         if (conv) {
@@ -231,9 +234,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             } else if (a_mn) {
               for (int i = 0; i < a_boxes; ++i)
-                tma_load_3d_pair(sa + i * a_box_bytes, &tmap_a, full, m0 + i * a_box_mn, kc, tc.b);
+                tma_load_3d_pair(sa + i * a_box_bytes, &tmap_a, full, m0 + i * a_box_mn, kc, ab);
             } else {
-              tma_load_3d_pair(sa, &tmap_a, full, kc, m0, tc.b);
+              tma_load_3d_pair(sa, &tmap_a, full, kc, m0, ab);
             }
             if (b_mn) {
               for (int i = 0; i < b_boxes; ++i)
@@ -254,9 +257,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             } else if (a_mn) {
               for (int i = 0; i < a_boxes; ++i)
-                tma_load_3d(sa + i * a_box_bytes, &tmap_a, full, m0 + i * a_box_mn, kc, tc.b);
+                tma_load_3d(sa + i * a_box_bytes, &tmap_a, full, m0 + i * a_box_mn, kc, ab);
             } else {
-              tma_load_3d(sa, &tmap_a, full, kc, m0, tc.b);
+              tma_load_3d(sa, &tmap_a, full, kc, m0, ab);
             }
             if (b_mn) {
               for (int i = 0; i < b_boxes; ++i)
@@ -388,11 +391,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool row_ok;
       long long row_off;  // element offset of (row, column 0 of the problem)
       long long col_stride = 1;
+      int conv_mt = 0, conv_tw = 0, conv_th = 0, conv_img = 0;
       if (p.conv) {
         const int mt = PAIR ? tc.m * 2 + static_cast<int>(cta_rank) : tc.m;
         const int tw = mt % p.tiles_w;
         const int th = (mt / p.tiles_w) % p.tiles_h;
         const int img = mt / (p.tiles_w * p.tiles_h);
+        conv_mt = mt; conv_tw = tw; conv_th = th; conv_img = img;
         const int oh = th * p.tile_h + row / p.tile_w;
         const int ow = tw * p.tile_w + row % p.tile_w;
         row_ok = mt < p.conv_tiles && row < p.tile_h * p.tile_w && oh < p.P && ow < p.Q;
@@ -406,6 +411,53 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       row_ok = row_ok && has_work;
 
+      if (p.conv && p.tma_store) {
+        // ---- conv, staged: TMEM -> registers -> [channel][tile_h][tile_w] in shared memory -> one
+        // bulk tensor store (fp32 reduce-add under split-K) per 32 output channels.  Lanes hold
+        // consecutive pixels, so the shared-memory writes of a channel are conflict-free and global
+        // memory sees whole rows of every channel plane of the NCHW result.
+        const bool leader = (warp == 2 && lane == 0);
+        const bool in_tile = row < p.tile_h * p.tile_w;
+        const uint32_t ch_stride = static_cast<uint32_t>(p.tile_h * p.tile_w) * 4u;
+        const bool add_bias = p.bias != nullptr && tc.ks == 0;
+        const bool tile_ok = has_work && conv_mt < p.conv_tiles;
+        for (int c = 0; c < bn; c += 32, ++slab_seq) {
+          const uint32_t buf = epi_base + (slab_seq & 1u) * kEpiBufBytes;
+          if (leader) bulk_wait_group_read<1>();
+          named_barrier_sync(1, 128);
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+          if (c + 32 >= bn) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (PAIR) mbar_arrive_cluster(tempty_sig0 + 8 * acc);
+              else mbar_arrive(tempty_sig0 + 8 * acc);
+            }
+          }
+          if (in_tile) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = __uint_as_float(v[j]);
+              if (add_bias && n0 + c + j < N) x += p.bias[p.conv_koff + n0 + c + j];
+              st_shared_f32(buf + static_cast<uint32_t>(j) * ch_stride + static_cast<uint32_t>(row) * 4u, x);
+            }
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(1, 128);
+          if (leader) {
+            if (tile_ok && n0 + c < N) {
+              if (p.split_k > 1)
+                tma_reduce_add_4d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, conv_img);
+              else
+                tma_store_4d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, conv_img);
+            }
+            bulk_commit_group();
+          }
+        }
+        continue;
+      }
       if (p.tma_store) {
         // ---- staged epilogue: TMEM -> registers -> swizzled shared slab -> bulk tensor store(s)
         const int slab_cols = p.slab_cols;  // 64 for bf16 output, 32 for 32-bit output
@@ -441,6 +493,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t v[32];
             tmem_ld_32x32(taddr + c, v);
             tmem_ld_wait();
+            if constexpr (OUT == OUT_F32) {
+              if (p.bias != nullptr && m0 + row < p.M) {
+                const float bias = p.bias[m0 + row];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + bias);
+              }
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ swz) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2],
@@ -519,6 +578,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         } else {
           // fp32 and int32 results leave TMEM as raw 32-bit words.
           uint32_t* dst = reinterpret_cast<uint32_t*>(p.C) + row_off + nbase;
+          if constexpr (OUT == OUT_F32) {
+            if (p.bias != nullptr && tc.ks == 0) {
+              const float bias = p.bias[tc.m * p.pair_m + static_cast<int>(cta_rank) * kTileM + row];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + bias);
+            }
+          }
           if (OUT == OUT_F32 && p.split_k > 1) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)

@@ -359,10 +359,15 @@ def generate_space_intra_op_b200(op, down_graph=None):
         space.add_subspace("raster", KnobSpace("raster", [[1, 0], [2, 0]]), "reorder")
         space.add_subspace("ctas", KnobSpace("ctas", [8, 6, 4]), "unroll")
         # 1 = one shifted input tile per filter tap; 2 = one input slab per channel chunk shared by
-        # all taps with the filter resident in shared memory (stride 1, one group, <= 256 channels out)
-        slab_ok = (taps > 1 and op.attrs.get("groups", 1) == 1 and k_out <= 256
-                   and tuple(op.attrs.get("stride", (1, 1))) == (1, 1))
-        space.add_subspace("algo", KnobSpace("algo", [1, 2] if slab_ok else [1]), "inline")
+        # all taps with the filter resident in shared memory (stride 1, one group, <= 256 channels
+        # out); 3 = batched GEMM on the NCHW tensors as they are (1x1, stride 1, no padding)
+        unit_stride = tuple(op.attrs.get("stride", (1, 1))) == (1, 1)
+        one_group = op.attrs.get("groups", 1) == 1
+        slab_ok = taps > 1 and one_group and k_out <= 256 and unit_stride
+        # (the padding stage feeding this op is the identity when padding is 0)
+        gemm_ok = (taps == 1 and one_group and unit_stride and tuple(op.attrs.get("padding", (0, 0))) == (0, 0)
+                   and (out_h * out_w) % 4 == 0 and rc % 4 == 0)
+        space.add_subspace("algo", KnobSpace("algo", [1, 2] if slab_ok else ([1, 3] if gemm_ok else [1])), "inline")
     else:  # depthwise
         out_h = extents["h"]
         strips = sorted(set(_divisor_like(out_h, [1, 2, 4, 7, 8, 14, 16, 28, 32, 56, 64, 112]) + [out_h]))

@@ -54,9 +54,10 @@ typedef struct ftb_config {
   int32_t tile_h;    /* conv2d: output rows per tile; depthwise: output rows per strip    */
   int32_t threads;   /* depthwise: threads per CTA                                        */
   int32_t cluster;   /* 1 = one CTA per 128-row tile, 2 = CTA pair on a 256-row tile       */
-  int32_t algo;      /* conv2d: 0 auto, 1 one shifted input tile per filter tap, 2 one input slab
-                        per channel chunk shared by all taps, filter resident in shared memory
-                        (stride 1, groups 1, <= 256 output channels, single-pass TF32)        */
+  int32_t algo;      /* conv2d: 0 auto; 1 one shifted input tile per filter tap; 2 one input slab per
+                        channel chunk shared by all taps, filter resident in shared memory (stride 1,
+                        groups 1, <= 256 output channels, single-pass TF32); 3 batched GEMM on the
+                        NCHW tensors as they are (1x1 filter, stride 1, no padding, groups 1)        */
   int32_t reserved[5];
 } ftb_config;
 

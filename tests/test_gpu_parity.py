@@ -370,12 +370,33 @@ def test_conv2d_slab_algorithm(B, status, shape, cfg):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("shape", [(2, 64, 8, 8, 48), (3, 32, 14, 14, 256), (1, 256, 56, 56, 64), (2, 20, 6, 6, 130)])
+@pytest.mark.parametrize("cfg", [{}, {"algo": 3, "cluster": 1, "tile_n": 64}, {"algo": 3, "split_k": 2}, {"algo": 1},
+                                 {"fp32_mode": 1}])
+def test_conv2d_1x1_as_batched_gemm(B, status, shape, cfg):
+    """A 1x1 filter (stride 1, no padding) is out[b] = W * in[b] on the NCHW tensors as they are."""
+    n, c, h, wd, k = shape
+    x, w = O.conv2d_inputs(n, c, h, wd, k, 1, 1, seed=61)
+    bias = np.random.default_rng(62).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, 1, 0, 1, 1)
+    if cfg.get("split_k", 1) > (c + 31) // 32:
+        pytest.skip("more splits than K blocks")
+    launches = B.launch_count()
+    got = run_conv(B, x, w, bias, 1, 0, 1, 1, cfg=cfg, status=status)
+    if cfg.get("algo", 0) != 1:
+        assert B.launch_count() - launches == 1            # no layout pass in front of the kernel
+    assert O.normalised_error(got, want) <= (TOL["conv2d_3xtf32"] if cfg.get("fp32_mode") else TOL["conv2d_tf32"])
+    with pytest.raises(B.FtbError):                        # padded or strided 1x1: not a plain GEMM
+        run_conv(B, x, w, bias, 1, 1, 1, 1, cfg={"algo": 3}, status=status)
+
+
 def test_conv2d_slab_algorithm_refuses_what_it_cannot_take(B, status):
     x, w = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, seed=59)
     for kwargs, cfg in ((dict(stride=2), {"algo": 2}),                 # stride 2
                         (dict(stride=1), {"algo": 2, "fp32_mode": 1}),  # 3xTF32
                         (dict(stride=1), {"algo": 2, "tile_n": 16}),                # not a tile width
-                        (dict(stride=1), {"algo": 3})):
+                        (dict(stride=1), {"algo": 3}),                             # GEMM form of a 3x3
+                        (dict(stride=1), {"algo": 4})):
         with pytest.raises(B.FtbError):
             run_conv(B, x, w, None, kwargs["stride"], 1, 1, 1, cfg=cfg, status=status)
     xg, wg = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, groups=2, seed=59)
