@@ -89,7 +89,13 @@ static int box_mn(const KindInfo& ki) { return 128 / ki.esize; }
 
 // Relative per-SM throughput of a (cluster, tile_n) choice on a long K loop, from
 // measurement; used only to rank defaults.
-static double tile_rate(int cluster, int bn) {
+static double tile_rate(int cluster, int bn, int num_kb) {
+  if (num_kb <= 4) {
+    // A short K loop is bound by writing the result: single CTAs with wide tiles do best
+    // (measured on K = 64, M = 256, N = 3136, 64 batch entries, fp32 result).
+    if (cluster == 2) return bn >= 256 ? 0.79 : bn >= 128 ? 0.63 : bn >= 64 ? 0.43 : 0.3;
+    return bn >= 256 ? 1.0 : bn >= 128 ? 0.92 : bn >= 64 ? 0.7 : 0.43;
+  }
   if (cluster == 2) return bn >= 256 ? 1.0 : bn >= 128 ? 0.65 : bn >= 64 ? 0.35 : 0.2;
   return bn >= 256 ? 0.7 : bn >= 128 ? 0.4 : bn >= 64 ? 0.2 : 0.1;
 }
@@ -133,7 +139,7 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
         const long long waves = (tiles + units - 1) / units;
         const double useful = static_cast<double>(batch) * m_rows * n;
         const double paid = static_cast<double>(waves) * units * tm * bn;
-        const double score = useful / paid * tile_rate(cluster, bn);
+        const double score = useful / paid * tile_rate(cluster, bn, num_kb);
         if (score > best + 1e-9) {
           best = score;
           best_cluster = cluster;
