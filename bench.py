@@ -30,12 +30,12 @@ METRIC = "TFLOP/s batched GEMM bf16 (fp32 accumulate) B=64 M=N=K=2048"
 WORKLOAD = "batched GEMM bf16 B=64 M=N=K=2048, fp32 accumulate, normal(0,0.02) inputs, bf16 output"
 FALLBACK_BF16_TFLOPS = 1590.0
 # DRAM bytes of one full-batch launch of the dominant kernel: dram__bytes_read.sum +
-# dram__bytes_write.sum of a 6-item launch (profiles/umma_gemm_bf16_pair_b6_2048.md), scaled to
+# dram__bytes_write.sum of a 6-item launch (profiles/umma_gemm_bf16_wide_b6_2048.md), scaled to
 # 64 items by the items processed (traffic grows in proportion: every item is read once).  The
 # 6-item capture still holds half of its output in L2 when the kernel ends, so the write part
 # is a lower bound; the algorithmic figure is 1.61e9.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = (100.73e6 + 24.08e6) * 64 / 6
-KNOBS = {"cluster": 2, "tile_n": 256, "raster": 3, "group_m": 4}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = (104.52e6 + 24.33e6) * 64 / 6
+KNOBS = {"cluster": 2, "tile_n": 512, "raster": 3, "group_m": 8}
 
 
 def measured_peak():
@@ -516,7 +516,7 @@ def run_ours(args, rank, world, local_rank):
                                       "NCCL all-gather of the bf16 output (512 MiB total)" +
                                       (" [fused path unavailable: %s]" % fused_why if fused_why else "")),
                        "l2": "inputs (1 GiB) larger than L2; no flush needed", "knobs": KNOBS,
-                       "kernel": "umma_gemm_kernel<bf16, bf16 out, cta_group::2>"},
+                       "kernel": "umma_gemm_kernel<bf16, bf16 out, cta_group::2, 256x512 tile>"},
             "compute_only_value": compute_only,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,

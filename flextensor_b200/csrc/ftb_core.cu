@@ -134,8 +134,12 @@ int ftb_validate(int op, const ftb_config* cfg, int64_t m, int64_t n, int64_t k)
   const int esize = op == 1 ? 2 : (op == 2 ? 1 : 4);
   const bool split3 = (op == 0 || op == 3) && cfg->fp32_mode == 1;
   if (cfg->fp32_mode < 0 || cfg->fp32_mode > 1) return FTB_E_BAD_CONFIG;
-  if (cfg->tile_n != 0 && cfg->tile_n != 32 && cfg->tile_n != 64 && cfg->tile_n != 128 && cfg->tile_n != 256)
+  if (cfg->tile_n == 512) {
+    // 256 x 512 tile of a CTA pair: plain GEMMs only
+    if (cfg->cluster != 2 || op == 3 || split3) return FTB_E_BAD_CONFIG;
+  } else if (cfg->tile_n != 0 && cfg->tile_n != 32 && cfg->tile_n != 64 && cfg->tile_n != 128 && cfg->tile_n != 256) {
     return FTB_E_BAD_CONFIG;
+  }
   if (cfg->stages != 0 && (cfg->stages < 2 || cfg->stages > 8)) return FTB_E_BAD_CONFIG;
   if (cfg->cluster < 0 || cfg->cluster > 2) return FTB_E_BAD_CONFIG;
   if (cfg->cluster == 2 && split3) return FTB_E_BAD_CONFIG;

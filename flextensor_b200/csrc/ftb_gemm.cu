@@ -96,7 +96,7 @@ static double tile_rate(int cluster, int bn, int num_kb) {
     if (cluster == 2) return bn >= 256 ? 0.79 : bn >= 128 ? 0.63 : bn >= 64 ? 0.43 : 0.3;
     return bn >= 256 ? 1.0 : bn >= 128 ? 0.92 : bn >= 64 ? 0.7 : 0.43;
   }
-  if (cluster == 2) return bn >= 256 ? 1.0 : bn >= 128 ? 0.65 : bn >= 64 ? 0.35 : 0.2;
+  if (cluster == 2) return bn >= 512 ? 1.1 : bn >= 256 ? 1.0 : bn >= 128 ? 0.65 : bn >= 64 ? 0.35 : 0.2;
   return bn >= 256 ? 0.7 : bn >= 128 ? 0.4 : bn >= 64 ? 0.2 : 0.1;
 }
 
@@ -104,13 +104,18 @@ static double tile_rate(int cluster, int bn, int num_kb) {
 // item, `batch` items; `allow_pair` is false for conv and 3xTF32.
 static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split3, int b_mn, bool allow_pair,
                           long long batch, long long m_rows, long long n, int num_kb, bool f32_out,
-                          int num_sms, ftb_config* out, size_t epilogue_bytes = 0) {
+                          int num_sms, ftb_config* out, size_t epilogue_bytes = 0, bool allow_wide = false) {
   ftb_config c;
   memset(&c, 0, sizeof(c));
   if (user) c = *user;
   if (c.cluster < 0 || c.cluster > 2) return FTB_E_BAD_CONFIG;
   if (c.cluster == 2 && !allow_pair) return FTB_E_BAD_CONFIG;
-  if (c.tile_n != 0 && (c.tile_n < 32 || c.tile_n > 256 || c.tile_n % 32)) return FTB_E_BAD_CONFIG;
+  if (c.tile_n == 512) {
+    // 256 x 512 tile of a CTA pair (plain GEMMs only, no 3xTF32)
+    if (c.cluster != 2 || !allow_pair || split3 || !allow_wide) return FTB_E_BAD_CONFIG;
+  } else if (c.tile_n != 0 && (c.tile_n < 32 || c.tile_n > 256 || c.tile_n % 32)) {
+    return FTB_E_BAD_CONFIG;
+  }
   // Granularity of tile_n: one TMA box of an N-contiguous B covers box_mn columns per CTA.
   auto tile_ok = [&](int cluster, int bn) {
     const int per_cta = bn / cluster;
@@ -130,7 +135,9 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
     for (int cluster = 2; cluster >= 1; --cluster) {
       if (c.cluster != 0 && c.cluster != cluster) continue;
       if (cluster == 2 && (!allow_pair || num_sms < 2)) continue;
-      for (int bn = 256; bn >= 32; bn /= 2) {
+      // the 256 x 512 pair tile competes only on long K loops (its epilogue overlaps less)
+      const int bn_max = (cluster == 2 && allow_wide && !split3 && num_kb > 4) ? 512 : 256;
+      for (int bn = bn_max; bn >= 32; bn /= 2) {
         if (c.tile_n != 0 && c.tile_n != bn) continue;
         if (!tile_ok(cluster, bn)) continue;
         const long long tm = kTileM * cluster;
@@ -210,10 +217,10 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
   return FTB_OK;
 }
 
-template <int KIND, int OUT, bool SPLIT3, bool PAIR>
+template <int KIND, int OUT, bool SPLIT3, bool PAIR, bool WIDE = false>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps& tc, const UmmaParams& p,
                   int ctas, cudaStream_t stream) {
-  auto kern = umma_gemm_kernel<KIND, OUT, SPLIT3, PAIR>;
+  auto kern = umma_gemm_kernel<KIND, OUT, SPLIT3, PAIR, WIDE>;
   const size_t smem = smem_needed(p.b_bytes / 128, p.stages, SPLIT3, p.tma_store ? kEpilogueStaging : 0);
   // The opt-in shared-memory size is a per-device attribute of the function.
   static std::mutex mu;
@@ -258,7 +265,15 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps&
 }
 
 static int dispatch(int kind, int out, bool split3, bool pair, const CUtensorMap& ta, const CUtensorMap& tb,
-                    const StoreMaps& tc, const UmmaParams& p, int ctas, cudaStream_t stream) {
+                    const StoreMaps& tc, const UmmaParams& p, int ctas, cudaStream_t stream, bool wide = false) {
+  if (wide) {
+    if (!pair || split3) return FTB_E_BAD_CONFIG;
+    if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false, true, true>(ta, tb, tc, p, ctas, stream);
+    if (kind == KIND_BF16 && out == OUT_F32) return launch<KIND_BF16, OUT_F32, false, true, true>(ta, tb, tc, p, ctas, stream);
+    if (kind == KIND_I8 && out == OUT_S32) return launch<KIND_I8, OUT_S32, false, true, true>(ta, tb, tc, p, ctas, stream);
+    if (kind == KIND_TF32 && out == OUT_F32) return launch<KIND_TF32, OUT_F32, false, true, true>(ta, tb, tc, p, ctas, stream);
+    return FTB_E_BAD_ARG;
+  }
   if (pair) {
     if (split3) return FTB_E_BAD_CONFIG;
     if (kind == KIND_BF16 && out == OUT_BF16) return launch<KIND_BF16, OUT_BF16, false, true>(ta, tb, tc, p, ctas, stream);
@@ -351,7 +366,7 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   const int num_kb = static_cast<int>((k + ki.kblk - 1) / ki.kblk);
   ftb_config cfg;
   rc = resolve_config(user, ki, split3, b_mn, !split3, batch, m, n, num_kb, out == OUT_F32, num_sms, &cfg,
-                      kEpilogueStaging);
+                      kEpilogueStaging, true);
   if (rc) return rc;
   const bool pair = cfg.cluster == 2;
   const int tile_m = pair ? 2 * kTileM : kTileM;
@@ -372,7 +387,8 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   p.group_m = cfg.group_m;
   p.split_k = cfg.split_k;
   p.kblk = ki.kblk;
-  p.idesc = make_idesc(ki, p.bn, a_mn, b_mn, tile_m);
+  const bool wide = cfg.tile_n == 512;  // one MMA covers half of the tile's columns
+  p.idesc = make_idesc(ki, wide ? 256 : p.bn, a_mn, b_mn, tile_m);
   p.a_mn = a_mn;
   p.b_mn = b_mn;
   p.pair_m = tile_m;
@@ -383,6 +399,8 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
                  &p.a_layout, &a_swz);
   operand_layout(ki, b_mn, p.b_rows, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv,
                  &p.b_layout, &b_swz);
+  // second half of a CTA's B stage in a wide tile: 128 rows (K-major) or 128 columns (N-contiguous boxes)
+  p.b_half_enc = (b_mn ? static_cast<uint32_t>(128 / p.b_box_mn) * p.b_box_bytes : 128u * 128u) >> 4;
   p.C = c;
   p.ldc = n;
   p.c_batch_stride = m * n;
@@ -461,7 +479,7 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   } else if (ctas > total) {
     ctas = static_cast<int>(total);
   }
-  return dispatch(kind, out, split3, pair, ta, tb, tc, p, ctas, stream);
+  return dispatch(kind, out, split3, pair, ta, tb, tc, p, ctas, stream, wide);
 }
 
 // ------------------------------------------------------------------ conv2d as implicit GEMM

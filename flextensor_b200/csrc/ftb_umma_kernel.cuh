@@ -18,6 +18,13 @@
 // the MMAs for both, and each CTA drains its own 128 accumulator rows.  Each CTA issues
 // plain TMA loads for its own halves.
 //
+// WIDE = true (pairs only) doubles the tile to 256 x 512: the two TMEM accumulators then hold
+// the two column halves of ONE tile instead of two tiles.  Each CTA stages 256 rows/columns of
+// B per K block next to the same 128 rows of A, so a byte of A feeds twice the math (175
+// instead of 131 FLOP per byte moved from L2), at the price of an epilogue that overlaps the
+// next main loop only half by half.  CTA r supplies B columns [256 r, 256 r + 256) of the tile:
+// accumulator half h holds tile columns [128 h, 128 h + 128) and [256 + 128 h, 256 + 128 h + 128).
+//
 // The producer and the MMA issuer are single threads, so their loops are latency-bound
 // scalar code: everything that does not change per K block is hoisted into registers and
 // the per-block work is a handful of adds (ring counters instead of div/mod, 32-bit
@@ -54,6 +61,7 @@ struct UmmaParams {
   uint32_t a_box_bytes, b_box_bytes, b_bytes;
   uint32_t a_lbo, a_sbo, b_lbo, b_sbo;
   uint32_t a_kadv, b_kadv;  // bytes added to the descriptor start per UMMA-K step
+  uint32_t b_half_enc;      // wide tiles: descriptor offset (bytes >> 4) of the second half of a CTA's B stage
   // output
   void* C;
   long long ldc, c_batch_stride;
@@ -109,7 +117,7 @@ __device__ __forceinline__ TileCoord decode_tile(const UmmaParams& p, int t) {
   return c;
 }
 
-template <int KIND, int OUT, bool SPLIT3, bool PAIR>
+template <int KIND, int OUT, bool SPLIT3, bool PAIR, bool WIDE = false>
 __global__ void __launch_bounds__(SPLIT3 ? 320 : 192, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ StoreMaps tmap_c, const __grid_constant__ UmmaParams p) {
@@ -122,6 +130,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
+  static_assert(!WIDE || (PAIR && !SPLIT3), "the 256 x 512 tile exists for CTA pairs only");
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -303,8 +312,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int ks = (p.split_k > 1) ? (t % p.split_k) : 0;
         const int kb0 = ks * kb_per_split;
         const int kb1 = min(num_kb, kb0 + kb_per_split);
-        const uint32_t acc = local & 1;
-        const uint32_t aph = (local >> 1) & 1u;
+        // Plain tiles alternate between the two accumulators; a wide tile owns both (one per half).
+        const uint32_t acc = WIDE ? 0u : (local & 1);
+        const uint32_t aph = WIDE ? (local & 1u) : ((local >> 1) & 1u);
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, &abort_flag)) {
           atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
           abort_flag = 1;
@@ -322,15 +332,43 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           tc_fence_after();
           const uint32_t b_lo = a_lo + b_off + b_lbo_delta;
+          if constexpr (WIDE) {
+            const bool last = kb + 1 == kb1;
 #pragma unroll
-          for (int k = 0; k < kMmaPerKb; ++k) {
-            const uint32_t ak = a_lo + k * a_k;
-            const uint32_t bk = b_lo + k * b_k;
-            umma<KIND, PAIR>(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
+            for (int k = 0; k < kMmaPerKb; ++k)
+              umma<KIND, PAIR>(d_tmem, a_lo + k * a_k, a_hi, b_lo + k * b_k, b_hi, idesc, k > 0 ? 1u : accumulate);
+            // the first half is complete one K block's worth of MMAs before the second
+            if (last) {
+              tc_commit_pair(tfull_l);
+              tc_commit_pair(tfull_r);
+            }
+            if (kb == kb0) {
+              // the second half may still be draining the previous tile
+              if (!mbar_wait(smem_u32(&bar_tempty[1]), aph ^ 1u, &abort_flag)) {
+                atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+            }
+            const uint32_t b_half = b_lo + p.b_half_enc;
+#pragma unroll
+            for (int k = 0; k < kMmaPerKb; ++k)
+              umma<KIND, PAIR>(d_tmem + kAccStride, a_lo + k * a_k, a_hi, b_half + k * b_k, b_hi, idesc,
+                               k > 0 ? 1u : accumulate);
             accumulate = 1;
-            if constexpr (SPLIT3) {
-              umma<KIND, PAIR>(d_tmem, ak + lo_enc, a_hi, bk, b_hi, idesc, 1);  // A_lo * B_hi
-              umma<KIND, PAIR>(d_tmem, ak, a_hi, bk + lo_enc, b_hi, idesc, 1);  // A_hi * B_lo
+          } else {
+#pragma unroll
+            for (int k = 0; k < kMmaPerKb; ++k) {
+              const uint32_t ak = a_lo + k * a_k;
+              const uint32_t bk = b_lo + k * b_k;
+              umma<KIND, PAIR>(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
+              accumulate = 1;
+              if constexpr (SPLIT3) {
+                umma<KIND, PAIR>(d_tmem, ak + lo_enc, a_hi, bk, b_hi, idesc, 1);  // A_lo * B_hi
+                umma<KIND, PAIR>(d_tmem, ak, a_hi, bk + lo_enc, b_hi, idesc, 1);  // A_hi * B_lo
+              }
             }
           }
           // Free the stage (in both CTAs of a pair) once these MMAs have read it.
@@ -348,7 +386,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
         if (ok) {
-          if constexpr (PAIR) {
+          if constexpr (WIDE) {
+            tc_commit_pair(tfull_l + 8);
+            tc_commit_pair(tfull_r + 8);
+          } else if constexpr (PAIR) {
             tc_commit_pair(tfull_l + 8 * acc);
             tc_commit_pair(tfull_r + 8 * acc);
           } else {
@@ -362,16 +403,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     const int row = quarter * 32 + lane;  // accumulator row owned by this thread
-    const int bn = p.bn, N = p.N;
+    const int bn = WIDE ? 256 : p.bn, N = p.N;  // accumulator columns drained per pass
     const uint32_t tempty_sig0 =
         PAIR ? map_to_cta(smem_u32(&bar_tempty[0]), 0) : smem_u32(&bar_tempty[0]);
     const uint32_t epi_base = smem_base + stages * stage_bytes;  // two output slabs after the stages
     uint32_t slab_seq = 0;
     int local = 0;
-    for (int t = unit; t < total_tiles; t += units, ++local) {
+    bool alive = true;
+    for (int t = unit; t < total_tiles && alive; t += units, ++local) {
       const TileCoord tc = decode_tile(p, t);
-      const uint32_t acc = local & 1;
-      const uint32_t aph = (local >> 1) & 1u;
+     // a wide tile is drained in two passes, one per accumulator half
+#pragma unroll 1
+     for (int half = 0; half < (WIDE ? 2 : 1); ++half) {
+      const uint32_t acc = WIDE ? static_cast<uint32_t>(half) : (local & 1);
+      const uint32_t aph = WIDE ? (local & 1u) : ((local >> 1) & 1u);
       const bool has_work = tc.ks * kb_per_split < num_kb;  // a split past the K range adds nothing
       bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull[acc]), aph, &abort_flag));
       // The staged epilogue synchronises the four warps with each other: they must agree.
@@ -381,11 +426,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           atomicOr(p.status, FTB_DEV_WAIT_TMEMFULL);
           abort_flag = 1;
         }
+        alive = false;
         break;
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kAccStride;
-      const int n0 = tc.n * bn;
+      const int n0 = tc.n * p.bn;
+      // problem column of accumulator column c (a slab of 32 or 64 columns never straddles the
+      // boundary between the two CTAs' parts of a wide tile)
+      auto ncol = [&](int c) { return WIDE ? n0 + ((c & 128) << 1) + half * 128 + (c & 127) : n0 + c; };
 
       // Where this thread's row goes in the output.
       bool row_ok;
@@ -517,8 +566,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           fence_proxy_async_smem();  // the slab must be visible to the bulk-copy engine
           named_barrier_sync(1, 128);
           if (leader) {
-            if (has_work && n0 + c < N) {
-              for (int d = 0; d < p.num_dst; ++d) tma_store_3d(&tmap_c.dst[d], buf, n0 + c, m0, tc.b);
+            if (has_work && ncol(c) < N) {
+              for (int d = 0; d < p.num_dst; ++d) tma_store_3d(&tmap_c.dst[d], buf, ncol(c), m0, tc.b);
             }
             bulk_commit_group();
           }
@@ -540,7 +589,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
         if (!row_ok) continue;
-        const int nbase = n0 + c;
+        const int nbase = ncol(c);
         if (nbase >= N) continue;
         if (p.conv) {
           float* out = reinterpret_cast<float*>(p.C);
@@ -603,6 +652,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
+     }
     }
     // Every bulk store of this CTA has been performed before the kernel ends.
     if (p.tma_store && warp == 2 && lane == 0) bulk_wait_group<0>();

@@ -331,8 +331,10 @@ def generate_space_intra_op_b200(op, down_graph=None):
         # an N-contiguous B is staged in 128-byte wide column blocks per CTA
         gran = 32 if transposed_b else max(32, 128 // esize)
         tiles = [t for t in (32, 64, 128, 256) if t % gran == 0]
-        space.add_subspace("tile_n", KnobSpace("tile_n", tiles), "spatial")
         clusters = [1, 2] if m_extent > 128 else [1]
+        if 2 in clusters and n_extent > 256:
+            tiles.append(512)                       # 256 x 512 tile of a CTA pair (refused with cluster 1)
+        space.add_subspace("tile_n", KnobSpace("tile_n", tiles), "spatial")
         space.add_subspace("cluster", KnobSpace("cluster", clusters), "spatial")
         k_extent = op.reduce_axis[0].dom.extent.value
         num_kb = max(1, math.ceil(k_extent * esize / 128))

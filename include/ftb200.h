@@ -44,7 +44,7 @@ enum ftb_error {
 /* Knobs of the kernels: the config space the scheduler searches
  * (replaces the split/fuse/reorder/unroll factors of flextensor/templates/cuda.py:390-661). */
 typedef struct ftb_config {
-  int32_t tile_n;    /* accumulator columns per tile: 32, 64, 128 or 256                  */
+  int32_t tile_n;    /* accumulator columns per tile: 32, 64, 128 or 256; 512 with cluster 2 (GEMMs) */
   int32_t stages;    /* shared-memory pipeline depth, 2..8                                */
   int32_t raster;    /* tile order: 0 auto, 1 n-fastest, 2 m-fastest, 3 grouped-M         */
   int32_t group_m;   /* group height for raster 3                                         */

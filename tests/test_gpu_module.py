@@ -116,7 +116,7 @@ def test_search_on_device_in_process(native_lib):
     measurer = InProcessMeasurer(0)
     key = "gemm_batch_gemm_(8, 1024, 1024, 1024)_cuda(0)"
     plan, bufs, configs = S.schedule(key, op_trial=3, op_stop=2, timeout=10, parallel=1, number=3, measurer=measurer)
-    assert plan.steps[0].knobs["tile_n"] in (64, 128, 256)
+    assert plan.steps[0].knobs["tile_n"] in (64, 128, 256, 512)
     items = [O.batch_gemm_item(i, 1024, 1024, 1024) for i in range(2)]
     a = torch.stack([dev(i[0]).bfloat16() for i in items] * 4)
     b = torch.stack([dev(i[1]).bfloat16() for i in items] * 4)

@@ -150,7 +150,8 @@ def test_bgemm_bf16_golden(B, status):
 
 @pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("cfg", [{"cluster": 1}, {"cluster": 2, "tile_n": 256}, {"cluster": 2, "tile_n": 128, "stages": 3},
-                                 {"cluster": 1, "tile_n": 64, "raster": 3, "group_m": 2}])
+                                 {"cluster": 1, "tile_n": 64, "raster": 3, "group_m": 2}, {"cluster": 2, "tile_n": 512},
+                                 {"cluster": 2, "tile_n": 512, "stages": 2, "raster": 2}])
 def test_bgemm_bf16_layouts_and_tails(B, status, ta, tb, cfg):
     items = [O.batch_gemm_item(i, 328, 264, 136, seed=31) for i in range(3)]
     a = np.stack([i[0] for i in items])
@@ -210,6 +211,45 @@ def test_bgemm_bf16_several_destinations(B, status):
     assert torch.equal(full[0][0:2], full[1][1:3]) and torch.equal(full[0][0:2], full[2][3:5])
 
 
+@pytest.mark.parametrize("shape", [(2, 512, 1024, 256), (3, 300, 1000, 200), (1, 1000, 776, 96), (2, 256, 520, 128)])
+def test_bgemm_bf16_wide_pair_tile(B, status, shape):
+    """The 256 x 512 pair tile (two accumulator halves per tile) gives the bits of the 256 x 256 tile,
+    on whole tiles and on ragged M, N and K; the same through the several-destinations entry point
+    and with fp32 output."""
+    batch, m, n, k = shape
+    items = [O.batch_gemm_item(i, m, n, k, seed=35) for i in range(batch)]
+    a = bf16_dev(np.stack([i[0] for i in items]))
+    b = bf16_dev(np.stack([i[1] for i in items]))
+    want = O.batch_gemm(np.stack([i[0] for i in items]), np.stack([i[1] for i in items]))
+    c256 = torch.full((batch, m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    c512 = torch.full_like(c256, float("nan"))
+    B.bgemm_bf16(a, b, c256, cfg={"cluster": 2, "tile_n": 256}, status=status)
+    B.bgemm_bf16(a, b, c512, cfg={"cluster": 2, "tile_n": 512}, status=status)
+    torch.cuda.synchronize()
+    assert torch.equal(c256, c512)
+    assert O.bf16_output_ok(c512.float().cpu().numpy(), want)
+    two = [torch.full_like(c256, float("nan")) for _ in range(2)]
+    B.bgemm_bf16_multi(a, b, [t.data_ptr() for t in two], m, n, cfg={"cluster": 2, "tile_n": 512}, status=status)
+    torch.cuda.synchronize()
+    assert torch.equal(two[0], c512) and torch.equal(two[1], c512)
+    c32 = torch.full((batch, m, n), float("nan"), device="cuda")
+    B.bgemm_bf16(a, b, c32, cfg={"cluster": 2, "tile_n": 512}, status=status)
+    assert O.normalised_error(c32.cpu().numpy(), want) <= TOL["bgemm_bf16_out_f32"]
+    with pytest.raises(B.FtbError):                 # the wide tile exists for CTA pairs only
+        B.bgemm_bf16(a, b, c512, cfg={"cluster": 1, "tile_n": 512}, status=status)
+    assert int(status.item()) == 0
+
+
+def test_gemm_f32_wide_pair_tile(B, status):
+    a, b = O.gemm_inputs(520, 1100, 300, seed=36)
+    want = O.gemm(a, b)
+    for split_k in (1, 2):                          # split-K adds the halves' partial sums with atomics
+        got = run_gemm_f32(B, a, b, cfg={"cluster": 2, "tile_n": 512, "fp32_mode": 0, "split_k": split_k}, status=status)
+        assert O.normalised_error(got, want) <= TOL["gemm_f32_tf32"]
+    with pytest.raises(B.FtbError):                 # no 3xTF32 on pairs, wide or not
+        run_gemm_f32(B, a, b, cfg={"cluster": 2, "tile_n": 512, "fp32_mode": 1}, status=status)
+
+
 def test_epilogues_agree(B, status, monkeypatch):
     """The staged bulk-store epilogue and the per-thread store epilogue give the same bits."""
     items = [O.batch_gemm_item(i, 328, 264, 136, seed=34) for i in range(2)]
@@ -243,8 +283,13 @@ def test_gemm_s8_golden_and_layouts(B, status):
         for tb in (False, True):
             got = run_gemm_s8(B, a.T.copy() if ta else a, b.T.copy() if tb else b, ta, tb, status=status)
             assert (got == want).all(), (ta, tb)
-    for cfg in ({"cluster": 2, "tile_n": 256}, {"cluster": 1, "tile_n": 128, "stages": 3}, {"raster": 2}, {"raster": 1}):
+    for cfg in ({"cluster": 2, "tile_n": 256}, {"cluster": 1, "tile_n": 128, "stages": 3}, {"raster": 2}, {"raster": 1},
+                {"cluster": 2, "tile_n": 512}):
         assert (run_gemm_s8(B, a, b, cfg=cfg, status=status) == want).all(), cfg
+    for tb in (False, True):                       # 256 x 512 tile, several tiles in both directions, ragged edges
+        a2, b2 = O.gemm_int8_inputs(600, 1300, 272, seed=42)
+        got = run_gemm_s8(B, a2, b2.T.copy() if tb else b2, False, tb, cfg={"cluster": 2, "tile_n": 512}, status=status)
+        assert (got == O.gemm_int8(a2, b2)).all(), tb
 
 
 def test_gemm_s8_extremes(B, status):

@@ -138,17 +138,17 @@ def test_b200_space_per_family():
     space = SP.generate_space_intra_op(ops_[0], {}, target="cuda")
     assert list(space.subspaces) == ["tile_n", "cluster", "stages", "split_k", "raster", "ctas"]
     assert space.types["spatial"] == ["tile_n", "cluster"] and space.types["reduce"] == ["stages", "split_k"]
-    assert [e[0] for e in space.subspaces["tile_n"].static_entities] == [32, 64, 128, 256]
+    assert [e[0] for e in space.subspaces["tile_n"].static_entities] == [32, 64, 128, 256, 512]
     for sub in space.subspaces.values():          # every sub-space speaks the walker protocol
         assert sub.num_direction == len(sub.directions) == 2 and len(sub) == len(sub.static_entities) > 0
         assert all(len(e) == sub.dim for e in sub.static_entities)
         assert sub.next_entity(len(sub) - 1, (1,)) == 0
     from flextensor_b200.task import gemm_int8, batch_gemm, depthwise_conv2d
     i8 = SP.generate_space_intra_op(gemm_int8(512, 512, 512)[0][0], {}, target="cuda")
-    assert [e[0] for e in i8.subspaces["tile_n"].static_entities] == [128, 256]   # N-contiguous int8 B: 128-wide boxes
+    assert [e[0] for e in i8.subspaces["tile_n"].static_entities] == [128, 256, 512]   # N-contiguous int8 B: 128-wide boxes
     assert [e[0] for e in i8.subspaces["split_k"].static_entities] == [1]         # integer output: no atomics
     bg = SP.generate_space_intra_op(batch_gemm(4, 256, 256, 256)[0][0], {}, target="cuda")
-    assert [e[0] for e in bg.subspaces["tile_n"].static_entities] == [64, 128, 256]
+    assert [e[0] for e in bg.subspaces["tile_n"].static_entities] == [64, 128, 256]          # N = 256: no room for a 512 tile
     ops_, _ = conv2d(1, 64, 56, 56, 64, 3, 1, 1, 1, 1)
     op_lst, down = flatten_graph(ops_)
     assert len(SP.generate_space_intra_op(op_lst[0], down, target="cuda").subspaces) == 0   # padding: no kernel
