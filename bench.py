@@ -36,6 +36,10 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # is a lower bound; the algorithmic figure is 1.61e9.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = (104.52e6 + 24.33e6) * 64 / 6
 KNOBS = {"cluster": 2, "tile_n": 512, "raster": 3, "group_m": 8}
+# N > 1 with the fused gather: the epilogue's bulk stores cross NVLink and take longer, and the
+# 256 x 512 tile overlaps its epilogue with the next main loop only half by half; the 256 x 256
+# tile (whole-tile overlap) is the faster one there (measured at N = 2: 0.48 ms against 0.66 ms).
+KNOBS_FUSED = {"cluster": 2, "tile_n": 256, "raster": 3, "group_m": 4}
 
 
 def measured_peak():
@@ -353,7 +357,7 @@ def run_ours(args, rank, world, local_rank):
 
     def kernel_only():
         if peer_out is not None:
-            backend.bgemm_bf16_multi(a, b, dst_ptrs, DIM, DIM, cfg=KNOBS, status=status_word)
+            backend.bgemm_bf16_multi(a, b, dst_ptrs, DIM, DIM, cfg=KNOBS_FUSED, status=status_word)
         else:
             func(a, b, c_local)
 
@@ -462,7 +466,7 @@ def run_ours(args, rank, world, local_rank):
             stream.wait_event(ev_in[c])
             stream.wait_event(ev_out[c])              # the previous step's read-back of this chunk is done
             if peer_out is not None:
-                backend.bgemm_bf16_multi(a[sl], b[sl], peer_out.slice_ptrs(lo + c * csz), DIM, DIM, cfg=KNOBS,
+                backend.bgemm_bf16_multi(a[sl], b[sl], peer_out.slice_ptrs(lo + c * csz), DIM, DIM, cfg=KNOBS_FUSED,
                                          status=status_word)
             else:
                 chunk_func(a[sl], b[sl], c_local[sl])
@@ -515,8 +519,10 @@ def run_ours(args, rank, world, local_rank):
                                       if peer_out is not None else
                                       "NCCL all-gather of the bf16 output (512 MiB total)" +
                                       (" [fused path unavailable: %s]" % fused_why if fused_why else "")),
-                       "l2": "inputs (1 GiB) larger than L2; no flush needed", "knobs": KNOBS,
-                       "kernel": "umma_gemm_kernel<bf16, bf16 out, cta_group::2, 256x512 tile>"},
+                       "l2": "inputs (1 GiB) larger than L2; no flush needed",
+                       "knobs": KNOBS_FUSED if peer_out is not None else KNOBS,
+                       "kernel": "umma_gemm_kernel<bf16, bf16 out, cta_group::2, %s tile>" %
+                                 ("256x256" if peer_out is not None else "256x512")},
             "compute_only_value": compute_only,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps,

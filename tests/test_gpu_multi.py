@@ -97,7 +97,9 @@ def test_measurement_pool_uses_every_gpu(native_lib):
     op = TASK_TABLE[key].func(*TASK_TABLE[key].args)[0][0]
     jobs = []
     for i in range(3 * n):
-        knobs = {"tile_n": (64, 128, 256)[i % 3], "cluster": 1 + i % 2, "stages": 2 + i % 3}
+        cluster = 1 + i % 2                       # a pair stages half of tile_n per CTA: at least one 64-wide box
+        knobs = {"tile_n": (128, 256)[i % 2] if cluster == 2 else (64, 128, 256)[i % 3], "cluster": cluster,
+                 "stages": 2 + i % 3}
         jobs.append((key, Config([knobs_to_config(knobs, op)], None), None))
     pool = GpuPoolMeasurer(devices=list(range(n)))
     try:
