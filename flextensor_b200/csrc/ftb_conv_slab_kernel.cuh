@@ -313,8 +313,9 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         }
       }
     }
-    // Every bulk store of this CTA has been performed before the kernel ends.
-    if (p.epi_bufs && warp == 2 && lane == 0) bulk_wait_group<0>();
+    // Shared memory must outlive the bulk stores' reads of it; their global writes are complete
+    // when the grid is.
+    if (p.epi_bufs && warp == 2 && lane == 0) bulk_wait_group_read<0>();
     __syncwarp();
   }
 

@@ -654,8 +654,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
      }
     }
-    // Every bulk store of this CTA has been performed before the kernel ends.
-    if (p.tma_store && warp == 2 && lane == 0) bulk_wait_group<0>();
+    // Shared memory must outlive the bulk stores' reads of it.  Their global writes are part of
+    // this grid's memory operations and are complete when the grid is; only stores into a peer
+    // GPU's memory (several destinations) are waited for in full before the CTA exits.
+    if (p.tma_store && warp == 2 && lane == 0) {
+      if (p.num_dst > 1) bulk_wait_group<0>();
+      else bulk_wait_group_read<0>();
+    }
     __syncwarp();
   } else {
     // ------------------------------------------------------------ 3xTF32 split stage
