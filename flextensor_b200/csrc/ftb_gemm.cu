@@ -94,7 +94,7 @@ static double tile_rate(int cluster, int bn, int num_kb) {
     // A short K loop is bound by writing the result: single CTAs with wide tiles do best
     // (measured on K = 64, M = 256, N = 3136, 64 batch entries, fp32 result).
     if (cluster == 2) return bn >= 256 ? 0.79 : bn >= 128 ? 0.63 : bn >= 64 ? 0.43 : 0.3;
-    return bn >= 256 ? 1.0 : bn >= 128 ? 0.92 : bn >= 64 ? 0.7 : 0.43;
+    return bn >= 256 ? 1.0 : bn >= 128 ? 0.88 : bn >= 64 ? 0.7 : 0.43;
   }
   if (cluster == 2) return bn >= 512 ? 1.1 : bn >= 256 ? 1.0 : bn >= 128 ? 0.65 : bn >= 64 ? 0.35 : 0.2;
   return bn >= 256 ? 0.7 : bn >= 128 ? 0.4 : bn >= 64 ? 0.2 : 0.1;
@@ -321,6 +321,54 @@ static void operand_layout(const KindInfo& ki, int mn_major, int tile_extent, in
   }
 }
 
+// Defaults for an fp32-output product that fits in one wave of CTAs.  Such a launch is not
+// latency-bound but bound by what each CTA has to pull through its L2 port and by its own
+// MMA chain, so wide tiles with the K loop split over otherwise idle SMs win even though the
+// partial sums then meet in global memory (bulk reduce-add into a zeroed result).  Cost model
+// per CTA, microseconds, constants measured on 1024^3 fp32 (single-pass and 3xTF32):
+//   K blocks x max(bytes staged / 60 GB/s, 4 MMAs x passes x time of a 128 x tile_n MMA)
+//   + result bytes / 35 GB/s + 2 us when the K loop is split (memset + adds) + 0.8 us for a CTA pair.
+// Returns true and fills `out` when the caller left tile_n, cluster and split_k open.
+static bool pick_small_f32(const ftb_config* user, const KindInfo& ki, bool split3, int b_mn, bool eligible,
+                           long long batch, long long m, long long n, int num_kb, int num_sms, ftb_config* out) {
+  if (!eligible) return false;
+  if (user && (user->tile_n != 0 || user->cluster != 0 || user->split_k != 0)) return false;
+  if (batch * ((m + 127) / 128) * ((n + 127) / 128) > num_sms) return false;  // more than one wave: not this regime
+  double best = 1e30;
+  int best_cluster = 0, best_bn = 0, best_split = 0;
+  for (int cluster = 1; cluster <= (split3 ? 1 : 2); ++cluster) {
+    for (int bn = 32; bn <= 256; bn *= 2) {
+      const int per_cta = bn / cluster;
+      if (per_cta < 32 || (b_mn && per_cta % box_mn(ki))) continue;
+      for (int split = 1; split <= 8; split *= 2) {
+        if (split > 1 && split * 2 > num_kb) break;
+        const long long ctas = batch * ((m + 128 * cluster - 1) / (128 * cluster)) * ((n + bn - 1) / bn) * split * cluster;
+        if (ctas > num_sms) break;
+        const int kb = (num_kb + split - 1) / split;
+        const double mma_us = (bn >= 256 ? 0.140 : bn >= 128 ? 0.090 : bn >= 64 ? 0.061 : 0.050) *
+                              (ki.kind == KIND_TF32 ? 1.0 : 0.5);
+        const double load = kb * (16384.0 + per_cta * 128.0) / 60e3;
+        const double math = kb * 4.0 * mma_us * (split3 ? 3.0 : 1.0);
+        const double cost = (load > math ? load : math) + 128.0 * bn * 4.0 / 35e3 + (split > 1 ? 2.0 : 0.0) +
+                            (cluster == 2 ? 0.8 : 0.0);  // a pair pays two cluster barriers
+        if (cost < best) {
+          best = cost;
+          best_cluster = cluster;
+          best_bn = bn;
+          best_split = split;
+        }
+      }
+    }
+  }
+  if (best_bn == 0) return false;
+  memset(out, 0, sizeof(*out));
+  if (user) *out = *user;
+  out->cluster = best_cluster;
+  out->tile_n = best_bn;
+  out->split_k = best_split;
+  return true;
+}
+
 int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64_t batch, int64_t m,
                  int64_t n, int64_t k, int trans_a, int trans_b, const ftb_config* user, int* status,
                  void* stream_v, void* const* extra_dst, int num_extra, const GemmExtras* extras) {
@@ -365,6 +413,9 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   const int num_sms = sm_count();
   const int num_kb = static_cast<int>((k + ki.kblk - 1) / ki.kblk);
   ftb_config cfg;
+  ftb_config tuned;
+  if (pick_small_f32(user, ki, split3, b_mn, out == OUT_F32 && num_extra == 0, batch, m, n, num_kb, num_sms, &tuned))
+    user = &tuned;
   rc = resolve_config(user, ki, split3, b_mn, !split3, batch, m, n, num_kb, out == OUT_F32, num_sms, &cfg,
                       kEpilogueStaging, true);
   if (rc) return rc;
@@ -409,7 +460,9 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   p.status = status ? status : fallback_status();
   if (!p.status) return FTB_E_CUDA;
   p.slab_cols = 128 / out_esize;
-  p.tma_store = (store_ok && p.split_k == 1 && p.bn % p.slab_cols == 0) ? 1 : 0;
+  // split-K goes through the staged epilogue as bulk fp32 reduce-adds (one destination only)
+  p.tma_store = (store_ok && p.bn % p.slab_cols == 0 &&
+                 (p.split_k == 1 || (out == OUT_F32 && num_extra == 0))) ? 1 : 0;
   p.num_dst = 1 + num_extra;
   if (num_extra > 0 && !p.tma_store) return FTB_E_UNSUPPORTED;  // several destinations only through bulk stores
 

@@ -543,7 +543,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tmem_ld_32x32(taddr + c, v);
             tmem_ld_wait();
             if constexpr (OUT == OUT_F32) {
-              if (p.bias != nullptr && m0 + row < p.M) {
+              if (p.bias != nullptr && tc.ks == 0 && m0 + row < p.M) {
                 const float bias = p.bias[m0 + row];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + bias);
@@ -567,7 +567,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           named_barrier_sync(1, 128);
           if (leader) {
             if (has_work && ncol(c) < N) {
-              for (int d = 0; d < p.num_dst; ++d) tma_store_3d(&tmap_c.dst[d], buf, ncol(c), m0, tc.b);
+              if (p.split_k > 1) {
+                // partial sums of the K splits meet in global memory (fp32 result, one destination)
+                tma_reduce_add_3d(&tmap_c.dst[0], buf, ncol(c), m0, tc.b);
+              } else {
+                for (int d = 0; d < p.num_dst; ++d) tma_store_3d(&tmap_c.dst[d], buf, ncol(c), m0, tc.b);
+              }
             }
             bulk_commit_group();
           }
