@@ -102,6 +102,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  // Launched as a programmatic dependent of the layout pass: everything above overlapped its tail.
+  grid_dependency_wait();
   const uint32_t afull0 = smem_u32(&bar_afull[0]);
   const uint32_t aempty0 = smem_u32(&bar_aempty[0]);
   const uint32_t bfull = smem_u32(&bar_bfull);

@@ -245,14 +245,24 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps&
   lc.blockDim = dim3(SPLIT3 ? 320 : 192, 1, 1);
   lc.dynamicSmemBytes = smem;
   lc.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int nattr = 0;
   if (PAIR) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = 2;
+    attr[nattr].val.clusterDim.y = 1;
+    attr[nattr].val.clusterDim.z = 1;
+    ++nattr;
+  }
+  if (p.pdl) {
+    // programmatic dependent of the kernel launched just before it on this stream
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  if (nattr) {
     lc.attrs = attr;
-    lc.numAttrs = 1;
+    lc.numAttrs = nattr;
   }
   cudaError_t e = cudaLaunchKernelEx(&lc, kern, ta, tb, tc, p);
   count_launch();
@@ -563,10 +573,27 @@ constexpr int kPreCh = 32, kPrePx = 128;
 __global__ void __launch_bounds__(256)
 conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt, float* __restrict__ in_nhwc,
                     float* __restrict__ w_packed, int N, int C, int HW, int Cp, int K, int Cg, int RS,
-                    int cchunks, int hw_tiles, int c_tiles, int in_blocks) {
+                    int cchunks, int hw_tiles, int c_tiles, int in_blocks, int w_blocks, float* __restrict__ zero,
+                    long long zero_n) {
   __shared__ float tile[kPreCh][kPrePx + 1];
+  // The conv kernel that follows is launched as a programmatic dependent: it may set itself up
+  // (barriers, tensor memory, descriptor fetch) while this grid runs, and waits for this grid's
+  // completion before it touches the workspace or the result.
+  grid_launch_dependents();
   const int bid = blockIdx.x;
-  if (bid < in_blocks) {
+  if (bid >= in_blocks + w_blocks) {
+    // zero the result for a conv whose partial sums meet in global memory (split reduction)
+    const long long nb = gridDim.x - in_blocks - w_blocks;
+    const long long t0 = static_cast<long long>(bid - in_blocks - w_blocks) * blockDim.x + threadIdx.x;
+    if ((reinterpret_cast<uintptr_t>(zero) & 15) == 0) {
+      float4* z4 = reinterpret_cast<float4*>(zero);
+      const long long n4 = zero_n / 4;
+      for (long long i = t0; i < n4; i += nb * blockDim.x) z4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (long long i = n4 * 4 + t0; i < zero_n; i += nb * blockDim.x) zero[i] = 0.f;
+    } else {
+      for (long long i = t0; i < zero_n; i += nb * blockDim.x) zero[i] = 0.f;
+    }
+  } else if (bid < in_blocks) {
     const int ct = bid % c_tiles;
     const int ht = (bid / c_tiles) % hw_tiles;
     const int img = bid / (c_tiles * hw_tiles);
@@ -604,7 +631,7 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
   } else {
     const long long kdim = static_cast<long long>(RS) * cchunks * 32;
     const long long total = static_cast<long long>(K) * kdim;
-    const long long nb = gridDim.x - in_blocks;
+    const long long nb = w_blocks;
     for (long long i = static_cast<long long>(bid - in_blocks) * blockDim.x + threadIdx.x; i < total;
          i += nb * blockDim.x) {
       const int c = static_cast<int>(i % (cchunks * 32));
@@ -616,9 +643,10 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
 }
 
 // Launches the layout pass both conv kernels read from (input to channels-last, filter packed).
+// `zero` (may be null): `zero_n` floats of the result to clear in the same launch.
 static int conv_prepass(const float* in, const float* weight, float* in_nhwc, float* w_packed, int64_t n, int64_t c,
                         int64_t h, int64_t w, int64_t k, int64_t cg, int64_t r, int64_t s, const ConvWs& ws,
-                        int num_sms, void* stream_v) {
+                        int num_sms, void* stream_v, float* zero = nullptr, long long zero_n = 0) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const int HW = static_cast<int>(h * w);
   const int hw_tiles = (HW + kPrePx - 1) / kPrePx, c_tiles = static_cast<int>((ws.cp + kPreCh - 1) / kPreCh);
@@ -626,10 +654,15 @@ static int conv_prepass(const float* in, const float* weight, float* in_nhwc, fl
   const long long wtotal = k * r * s * ws.cchunks * 32;
   int w_blocks = static_cast<int>((wtotal + 255) / 256);
   if (w_blocks > 4 * num_sms) w_blocks = 4 * num_sms;
-  conv_prepass_kernel<<<in_blocks + w_blocks, 256, 0, stream>>>(
+  int z_blocks = 0;
+  if (zero && zero_n > 0) {
+    const long long want = (zero_n / 4 + 255) / 256;
+    z_blocks = static_cast<int>(want < 1 ? 1 : want > 2 * num_sms ? 2 * num_sms : want);
+  }
+  conv_prepass_kernel<<<in_blocks + w_blocks + z_blocks, 256, 0, stream>>>(
       in, weight, in_nhwc, w_packed, static_cast<int>(n), static_cast<int>(c), HW, static_cast<int>(ws.cp),
       static_cast<int>(k), static_cast<int>(cg), static_cast<int>(r * s), static_cast<int>(ws.cchunks), hw_tiles,
-      c_tiles, in_blocks);
+      c_tiles, in_blocks, w_blocks, zero, zero_n);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -765,7 +798,19 @@ static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const CUte
       done[dev] = true;
     }
   }
-  conv_slab_kernel<<<sp.ctas, 192, sp.smem, stream>>>(tin, tw, tout, sp.p);
+  // Programmatic dependent of the layout pass launched just before it on this stream.
+  cudaLaunchConfig_t lc;
+  memset(&lc, 0, sizeof(lc));
+  lc.gridDim = dim3(static_cast<unsigned>(sp.ctas), 1, 1);
+  lc.blockDim = dim3(192, 1, 1);
+  lc.dynamicSmemBytes = sp.smem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  cudaLaunchKernelEx(&lc, conv_slab_kernel, tin, tw, tout, sp.p);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -841,16 +886,10 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       rc = ftb_validate(3, user, n * P * Q, k, c * r * s);
       if (rc) return rc;
     }
-    rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v);
+    rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v,
+                      sp.p.split > 1 ? out : nullptr, n * k * P * Q);
     if (rc) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    if (sp.p.split > 1) {
-      cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(n * k * P * Q) * 4, stream);
-      if (e != cudaSuccess) {
-        set_last_cuda_error(static_cast<int>(e));
-        return FTB_E_CUDA;
-      }
-    }
     sp.p.out = out;
     sp.p.bias = bias;
     sp.p.conv_ktot = static_cast<int>(k);
@@ -935,16 +974,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   }
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v);
+  rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v,
+                    cfg.split_k > 1 ? out : nullptr, n * k * P * Q);
   if (rc) return rc;
-  if (cfg.split_k > 1) {
-    cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(n * k * P * Q) * 4, stream);
-    if (e != cudaSuccess) {
-      set_last_cuda_error(static_cast<int>(e));
-      return FTB_E_CUDA;
-    }
-  }
-
   for (int g = 0; g < groups; ++g) {
     UmmaParams p;
     memset(&p, 0, sizeof(p));
@@ -975,6 +1007,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.a_layout = 2;
     p.pair_m = pair ? 2 * kTileM : kTileM;
     p.conv = 1;
+    p.pdl = (g == 0) ? 1 : 0;  // the first launch directly follows the layout pass
     p.conv_ktot = static_cast<int>(k);
     p.conv_koff = static_cast<int>(g * kg);
     p.C = out;

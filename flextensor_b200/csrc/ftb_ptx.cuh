@@ -30,6 +30,14 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running; `grid_dependency_wait` then blocks until that
+// kernel has completed and its writes are visible (a no-op for a normal launch), and
+// `grid_launch_dependents` in the earlier kernel lets the later one start early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

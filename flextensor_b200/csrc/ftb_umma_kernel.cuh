@@ -73,6 +73,7 @@ struct UmmaParams {
   int conv_tiles;            // number of 128-pixel tiles (a CTA pair takes two consecutive ones)
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int* status;
+  int pdl;  // launched as a programmatic dependent: wait for the previous kernel before touching memory
   // TMA-store epilogue: tma_store != 0 stages 128-byte wide output slabs in shared memory and
   // writes each with one bulk tensor store per destination.
   int tma_store, num_dst, slab_cols;
@@ -173,6 +174,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if constexpr (PAIR) cluster_sync_all();  // peer barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
+  if (p.pdl) grid_dependency_wait();  // everything above overlapped the previous kernel's tail
 
   const int total_tiles = p.batch * p.tiles_m * p.tiles_n * p.split_k;
   const int num_kb = p.num_kb;
