@@ -331,6 +331,18 @@ static void operand_layout(const KindInfo& ki, int mn_major, int tile_extent, in
   }
 }
 
+// Clears `n` floats (16-byte aligned base); the GEMM that adds its K splits into them is launched
+// as a programmatic dependent and sets itself up while this runs.
+__global__ void __launch_bounds__(256) zero_f32_kernel(float* __restrict__ dst, long long n) {
+  grid_launch_dependents();
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long t0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  float4* d4 = reinterpret_cast<float4*>(dst);
+  const long long n4 = n / 4;
+  for (long long i = t0; i < n4; i += stride) d4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long long i = n4 * 4 + t0; i < n; i += stride) dst[i] = 0.f;
+}
+
 // Defaults for an fp32-output product that fits in one wave of CTAs.  Such a launch is not
 // latency-bound but bound by what each CTA has to pull through its L2 port and by its own
 // MMA chain, so wide tiles with the K loop split over otherwise idle SMs win even though the
@@ -526,7 +538,19 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (p.split_k > 1) {
-    cudaError_t e = cudaMemsetAsync(c, 0, static_cast<size_t>(batch) * m * n * 4, stream);
+    const long long count = static_cast<long long>(batch) * m * n;
+    cudaError_t e;
+    if ((reinterpret_cast<uintptr_t>(c) & 15) == 0) {
+      long long blocks = (count / 4 + 255) / 256;
+      if (blocks > 4ll * num_sms) blocks = 4ll * num_sms;
+      if (blocks < 1) blocks = 1;
+      zero_f32_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<float*>(c), count);
+      count_launch();
+      e = cudaGetLastError();
+      p.pdl = 1;
+    } else {
+      e = cudaMemsetAsync(c, 0, static_cast<size_t>(count) * 4, stream);
+    }
     if (e != cudaSuccess) {
       set_last_cuda_error(static_cast<int>(e));
       return FTB_E_CUDA;
