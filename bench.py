@@ -285,6 +285,28 @@ def per_op_lines(peak_bf16, hbm_gbs):
     t = timed("conv2d_res3_(64, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)", arrays, 2)
     out["conv2d_c64_56_k64_batch64_tf32"] = {"us": t * 1e6, "tflops": 64 * 231211008 / t / 1e12}
     del arrays, x64, w64
+    # The reference's own conv2d benchmark: the 15 YOLO-v1 layers at batch 1
+    # (flextensor/configs/conv2d_config.py:18-45), library-default knobs, single-pass TF32.  Beside
+    # them the kernel times the reference published for its tuned fp32 CUDA kernels
+    # (testing/others/profile/compute_flops.py:17-33; GPU not named there, sibling files are V100).
+    from flextensor_b200.task import TASK_TABLE
+    published_ms = [0.1007, 0.2825, 0.0252, 0.2062, 0.0571, 0.7426, 0.0373, 0.2107, 0.0541, 0.7973, 0.0653,
+                    0.2498, 0.5610, 0.3801, 0.2718]
+    layers = []
+    for i in range(15):
+        key = next(k for k in TASK_TABLE if k.startswith("conv2d_yolo%d_" % i) and k.endswith("_cuda(0)"))
+        n_, c_, h_, w_, k_, r_, st_, pad_ = TASK_TABLE[key].args[:8]
+        out_hw = (h_ + 2 * pad_ - r_) // st_ + 1
+        arrays = [torch.randn(n_, c_, h_, w_, device="cuda"), torch.randn(k_, c_, r_, r_, device="cuda"),
+                  torch.empty(n_, k_, out_hw, out_hw, device="cuda")]
+        t = timed(key, arrays, 2)
+        flop = 2.0 * n_ * k_ * out_hw * out_hw * c_ * r_ * r_
+        layers.append({"layer": i + 1, "us": t * 1e6, "tflops": flop / t / 1e12,
+                       "published_reference_us": published_ms[i] * 1e3})
+        del arrays
+    out["conv2d_yolo_b1_tf32"] = {"layers": layers, "sum_us": sum(l["us"] for l in layers),
+                                  "published_reference_sum_us": sum(published_ms) * 1e3,
+                                  "note": "published figures: the reference's tuned fp32 kernels on its own GPU"}
     a8 = torch.randint(-127, 128, (8192, 8192), device="cuda", dtype=torch.int8)
     b8 = torch.randint(-127, 128, (8192, 8192), device="cuda", dtype=torch.int8)
     arrays = [a8, b8, torch.empty(8192, 8192, device="cuda", dtype=torch.int32)]

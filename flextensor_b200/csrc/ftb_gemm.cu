@@ -242,7 +242,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps&
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));
   lc.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
-  lc.blockDim = dim3(SPLIT3 ? 320 : 192, 1, 1);
+  lc.blockDim = dim3((SPLIT3 || WIDE) ? 320 : 192, 1, 1);
   lc.dynamicSmemBytes = smem;
   lc.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -599,7 +599,7 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
                     float* __restrict__ w_packed, int N, int C, int HW, int Cp, int K, int Cg, int RS,
                     int cchunks, int hw_tiles, int c_tiles, int in_blocks, int w_blocks, float* __restrict__ zero,
                     long long zero_n) {
-  __shared__ float tile[kPreCh][kPrePx + 1];
+  __shared__ __align__(16) float tile[kPreCh][kPrePx + 1];
   // The conv kernel that follows is launched as a programmatic dependent: it may set itself up
   // (barriers, tensor memory, descriptor fetch) while this grid runs, and waits for this grid's
   // completion before it touches the workspace or the result.
@@ -653,15 +653,59 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
             make_float4(tile[cg][q], tile[cg + 1][q], tile[cg + 2][q], tile[cg + 3][q]);
     }
   } else {
-    const long long kdim = static_cast<long long>(RS) * cchunks * 32;
-    const long long total = static_cast<long long>(K) * kdim;
-    const long long nb = w_blocks;
-    for (long long i = static_cast<long long>(bid - in_blocks) * blockDim.x + threadIdx.x; i < total;
-         i += nb * blockDim.x) {
-      const int c = static_cast<int>(i % (cchunks * 32));
-      const int rs = static_cast<int>((i / (cchunks * 32)) % RS);
-      const int ko = static_cast<int>(i / kdim);
-      w_packed[i] = (c < Cg) ? wgt[(static_cast<long long>(ko) * Cg + c) * RS + rs] : 0.0f;
+    // Filter [K][Cg][RS] -> [K][RS][cchunks*32]: a block takes, for one output channel, a run of
+    // `cpp` input channels x RS taps (contiguous in the source), turns it in shared memory and
+    // writes `cpp` contiguous channels per tap; both sides of the copy are coalesced.
+    float* buf = &tile[0][0];
+    constexpr int kBuf = kPreCh * (kPrePx + 1);
+    const int cpad = cchunks * 32;
+    // runs start on multiples of 4 channels so that both sides can move 16 bytes at a time
+    const int cpp = RS * 4 > kBuf ? 1 : ((kBuf / RS) & ~3) < cpad ? ((kBuf / RS) & ~3) : cpad;
+    const int pieces = (cpad + cpp - 1) / cpp;
+    const long long kdim = static_cast<long long>(RS) * cpad;
+    const long long work = static_cast<long long>(K) * pieces;
+    for (long long u = bid - in_blocks; u < work; u += w_blocks) {
+      const int ko = static_cast<int>(u / pieces);
+      const int c0 = static_cast<int>(u % pieces) * cpp;
+      const int nch = cpad - c0 < cpp ? cpad - c0 : cpp;
+      if (RS <= kBuf) {
+        const float* src = wgt + (static_cast<long long>(ko) * Cg + c0) * RS;
+        const int real = Cg - c0 < nch ? (Cg - c0 > 0 ? Cg - c0 : 0) : nch;  // channels that exist in the source
+        const int nreal = real * RS;
+        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+          const float4* src4 = reinterpret_cast<const float4*>(src);
+          float4* buf4 = reinterpret_cast<float4*>(buf);
+          for (int i = threadIdx.x; i < nreal / 4; i += blockDim.x) buf4[i] = __ldg(src4 + i);
+          for (int i = (nreal & ~3) + threadIdx.x; i < nch * RS; i += blockDim.x)
+            buf[i] = (i < nreal) ? __ldg(src + i) : 0.0f;
+        } else {
+          for (int i = threadIdx.x; i < nch * RS; i += blockDim.x) buf[i] = (i < nreal) ? __ldg(src + i) : 0.0f;
+        }
+        __syncthreads();
+        float* dst = w_packed + ko * kdim + c0;
+        if ((nch & 3) == 0 && cpp > 1) {
+          const int nq = nch >> 2;
+          for (int j = threadIdx.x; j < nq * RS; j += blockDim.x) {
+            const int rs = j / nq, cc = (j - rs * nq) * 4;
+            *reinterpret_cast<float4*>(dst + static_cast<long long>(rs) * cpad + cc) =
+                make_float4(buf[cc * RS + rs], buf[(cc + 1) * RS + rs], buf[(cc + 2) * RS + rs], buf[(cc + 3) * RS + rs]);
+          }
+        } else {
+          for (int j = threadIdx.x; j < nch * RS; j += blockDim.x) {
+            const int rs = j / nch, cc = j - rs * nch;
+            dst[static_cast<long long>(rs) * cpad + cc] = buf[cc * RS + rs];
+          }
+        }
+        __syncthreads();
+      } else {
+        // a filter with more taps than the buffer holds: plain gather
+        for (int j = threadIdx.x; j < nch * RS; j += blockDim.x) {
+          const int rs = j / nch, cc = j - rs * nch;
+          const int c = c0 + cc;
+          w_packed[ko * kdim + static_cast<long long>(rs) * cpad + c] =
+              (c < Cg) ? wgt[(static_cast<long long>(ko) * Cg + c) * RS + rs] : 0.0f;
+        }
+      }
     }
   }
 }
@@ -675,9 +719,11 @@ static int conv_prepass(const float* in, const float* weight, float* in_nhwc, fl
   const int HW = static_cast<int>(h * w);
   const int hw_tiles = (HW + kPrePx - 1) / kPrePx, c_tiles = static_cast<int>((ws.cp + kPreCh - 1) / kPreCh);
   const int in_blocks = static_cast<int>(n) * hw_tiles * c_tiles;
+  // one work unit of the filter packing = one output channel x one run of input channels
   const long long wtotal = k * r * s * ws.cchunks * 32;
-  int w_blocks = static_cast<int>((wtotal + 255) / 256);
-  if (w_blocks > 4 * num_sms) w_blocks = 4 * num_sms;
+  long long w_units = (wtotal + 2047) / 2048;
+  if (w_units < k) w_units = k;
+  int w_blocks = static_cast<int>(w_units > 8ll * num_sms ? 8ll * num_sms : w_units);
   int z_blocks = 0;
   if (zero && zero_n > 0) {
     const long long want = (zero_n / 4 + 255) / 256;
@@ -974,6 +1020,44 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     const char* e = getenv("FTB_EPILOGUE");  // "direct" forces per-thread global stores (diagnostics)
     if (e && strcmp(e, "direct") == 0) staged = false;
   }
+  // One wave of tiles or less, knobs left open: pick tile width and reduction split together by
+  // what a CTA has to stage and issue (same cost model as pick_small_f32: a short tile list is
+  // bound by per-CTA L2 traffic and MMA chain, not by latency).
+  ftb_config tuned;
+  bool conv_tuned = false;
+  if (groups == 1 && (!user || (user->tile_n == 0 && user->cluster == 0 && user->split_k == 0)) &&
+      tiles_m * ((kg + 127) / 128) <= num_sms) {
+    double best = 1e30;
+    int best_bn = 0, best_split = 1;
+    for (int bn = 32; bn <= 256; bn *= 2) {
+      if (bn > 32 && bn >= 2 * kg) break;  // wider than the output channels: pure padding
+      const long long tiles = tiles_m * ((kg + bn - 1) / bn);
+      if (tiles > num_sms) continue;
+      for (int split = 1; split <= 32 && split <= num_kb; ++split) {
+        if (num_kb % split) continue;
+        if (tiles * split > num_sms) break;
+        const int kb = num_kb / split;
+        const double mma_us = (bn >= 256 ? 0.140 : bn >= 128 ? 0.090 : bn >= 64 ? 0.061 : 0.050) * (split3 ? 3.0 : 1.0);
+        const double load = kb * (16384.0 + bn * 128.0) / 60e3;
+        const double math = kb * 4.0 * mma_us;
+        const double cost = (load > math ? load : math) + 128.0 * bn * 4.0 / 35e3 + (split > 1 ? 0.5 : 0.0);
+        if (cost < best) {
+          best = cost;
+          best_bn = bn;
+          best_split = split;
+        }
+      }
+    }
+    if (best_bn) {
+      memset(&tuned, 0, sizeof(tuned));
+      if (user) tuned = *user;
+      tuned.cluster = 1;
+      tuned.tile_n = best_bn;
+      tuned.split_k = best_split;
+      user = &tuned;
+      conv_tuned = true;
+    }
+  }
   rc = FTB_E_BAD_CONFIG;
   if (staged)
     rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg,
@@ -985,12 +1069,12 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   if (rc) return rc;
   const bool pair = cfg.cluster == 2;
   const long long tiles_m_launch = pair ? (tiles_m + 1) / 2 : tiles_m;
-  if ((!user || user->split_k == 0) && groups == 1) {
-    // A short tile list leaves SMs idle: split the reduction (whole filter taps per split) so that
-    // about all SMs get work; measured best at 2-4 splits, more only adds atomics.
+  if (!conv_tuned && (!user || user->split_k == 0) && groups == 1) {
+    // A short tile list leaves SMs idle: split the reduction so that about all SMs get work (the
+    // partial sums meet in global memory through bulk reduce-adds into the zeroed result).
     const long long tiles = tiles_m_launch * ((kg + cfg.tile_n - 1) / cfg.tile_n);
     int want = static_cast<int>((num_sms / (pair ? 2 : 1)) / (tiles > 0 ? tiles : 1));
-    if (want > 4) want = 4;
+    if (want > 32) want = 32;
     int pick = 1;
     for (int d = 2; d <= want; ++d)
       if (num_kb % d == 0) pick = d;

@@ -119,7 +119,7 @@ __device__ __forceinline__ TileCoord decode_tile(const UmmaParams& p, int t) {
 }
 
 template <int KIND, int OUT, bool SPLIT3, bool PAIR, bool WIDE = false>
-__global__ void __launch_bounds__(SPLIT3 ? 320 : 192, 1)
+__global__ void __launch_bounds__((SPLIT3 || WIDE) ? 320 : 192, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ StoreMaps tmap_c, const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -153,7 +153,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
-      mbar_init(smem_u32(&bar_tempty[a]), PAIR ? 8 : 4);
+      // every epilogue warp that reads an accumulator reports when it is done with it: four per
+      // CTA, eight where a wide tile is drained by two groups of warps
+      mbar_init(smem_u32(&bar_tempty[a]), (PAIR ? 8u : 4u) * ((WIDE && p.tma_store) ? 2u : 1u));
     }
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -401,8 +403,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
+  } else if (warp < 6 || (WIDE && p.tma_store != 0)) {
     // ------------------------------------------------------------ epilogue
+    // A wide tile's staged epilogue runs on two groups of four warps (2-5 and 6-9): both read the
+    // same accumulator half, each takes every other slab through its own staging buffer, so a half
+    // is drained, and handed back to the MMA issuer, in half the time.
+    const int grp = (WIDE && warp >= 6) ? 1 : 0;
+    const int bar_sync_id = 1 + 2 * grp, bar_vote_id = 2 + 2 * grp;
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     const int row = quarter * 32 + lane;  // accumulator row owned by this thread
     const int bn = WIDE ? 256 : p.bn, N = p.N;  // accumulator columns drained per pass
@@ -422,7 +429,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool has_work = tc.ks * kb_per_split < num_kb;  // a split past the K range adds nothing
       bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull[acc]), aph, &abort_flag));
       // The staged epilogue synchronises the four warps with each other: they must agree.
-      if (p.tma_store) got = named_barrier_all(2, 128, got);
+      if (p.tma_store) got = named_barrier_all(bar_vote_id, 128, got);
       if (!got) {
         if (lane == 0) {
           atomicOr(p.status, FTB_DEV_WAIT_TMEMFULL);
@@ -512,14 +519,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (p.tma_store) {
         // ---- staged epilogue: TMEM -> registers -> swizzled shared slab -> bulk tensor store(s)
         const int slab_cols = p.slab_cols;  // 64 for bf16 output, 32 for 32-bit output
-        const bool leader = (warp == 2 && lane == 0);
+        const bool leader = (warp == (grp ? 6 : 2) && lane == 0);
         const int m0 = tc.m * p.pair_m + static_cast<int>(cta_rank) * kTileM;
         const uint32_t swz = static_cast<uint32_t>(row & 7);
-        for (int c = 0; c < bn; c += slab_cols, ++slab_seq) {
-          const uint32_t buf = epi_base + (slab_seq & 1u) * kEpiBufBytes;
-          // The store that used this buffer two slabs ago must have finished reading it.
-          if (leader) bulk_wait_group_read<1>();
-          named_barrier_sync(1, 128);
+        const int c_step = WIDE ? 2 * slab_cols : slab_cols;
+        for (int c = grp * slab_cols; c < bn; c += c_step, ++slab_seq) {
+          // plain tiles alternate between the two buffers; a group of a wide tile owns one
+          const uint32_t buf = epi_base + (WIDE ? static_cast<uint32_t>(grp) : (slab_seq & 1u)) * kEpiBufBytes;
+          // The store that used this buffer before must have finished reading it.
+          if (leader) {
+            if constexpr (WIDE) bulk_wait_group_read<0>();
+            else bulk_wait_group_read<1>();
+          }
+          named_barrier_sync(bar_sync_id, 128);
           const uint32_t row_addr = buf + static_cast<uint32_t>(row) * 128u;
           if constexpr (OUT == OUT_BF16) {
 #pragma unroll
@@ -556,8 +568,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ swz) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2],
                            v[4 * j + 3]);
           }
-          if (c + slab_cols >= bn) {
-            // Last read of this accumulator: hand it back to the MMA issuer.
+          if (c + c_step >= bn) {
+            // Last read of this accumulator (by this group): hand it back to the MMA issuer.
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -566,7 +578,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           fence_proxy_async_smem();  // the slab must be visible to the bulk-copy engine
-          named_barrier_sync(1, 128);
+          named_barrier_sync(bar_sync_id, 128);
           if (leader) {
             if (has_work && ncol(c) < N) {
               if (p.split_k > 1) {
@@ -664,7 +676,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // Shared memory must outlive the bulk stores' reads of it.  Their global writes are part of
     // this grid's memory operations and are complete when the grid is; only stores into a peer
     // GPU's memory (several destinations) are waited for in full before the CTA exits.
-    if (p.tma_store && warp == 2 && lane == 0) {
+    if (p.tma_store && lane == 0 && (warp == 2 || (WIDE && warp == 6))) {
       if (p.num_dst > 1) bulk_wait_group<0>();
       else bulk_wait_group_read<0>();
     }
