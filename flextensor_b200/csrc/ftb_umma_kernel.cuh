@@ -161,6 +161,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     fence_proxy_async_smem();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
+    // the store maps too: their first use would otherwise pay the descriptor fetch in the epilogue
+    if (p.tma_store)
+      for (int d = 0; d < p.num_dst; ++d) prefetch_tmap(&tmap_c.dst[d]);
   }
   if (warp == 1) {
     if constexpr (PAIR) {
