@@ -537,21 +537,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           named_barrier_sync(bar_sync_id, 128);
           const uint32_t row_addr = buf + static_cast<uint32_t>(row) * 128u;
           if constexpr (OUT == OUT_BF16) {
+            // both 32-column loads are in flight before the one wait
+            uint32_t v[2][32];
+            tmem_ld_32x32(taddr + c, v[0]);
+            tmem_ld_32x32(taddr + c + 32, v[1]);
+            tmem_ld_wait();
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              uint32_t v[32];
-              tmem_ld_32x32(taddr + c + half * 32, v);
-              tmem_ld_wait();
+            for (int part = 0; part < 2; ++part) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 uint32_t w[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * q]),
-                                                            __uint_as_float(v[j * 8 + 2 * q + 1]));
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(v[part][j * 8 + 2 * q]),
+                                                            __uint_as_float(v[part][j * 8 + 2 * q + 1]));
                   w[q] = *reinterpret_cast<uint32_t*>(&h2);
                 }
-                const uint32_t chunk = static_cast<uint32_t>(half * 4 + j);
+                const uint32_t chunk = static_cast<uint32_t>(part * 4 + j);
                 st_shared_v4(row_addr + ((chunk ^ swz) << 4), w[0], w[1], w[2], w[3]);
               }
             }
