@@ -577,6 +577,10 @@ static int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 struct ConvWs {
   int64_t cp, cchunks, in_bytes, w_bytes;
 };
+// Shapes that run as a 1x1 conv over their im2col form (conv_im2col_kernel).
+static bool conv_small_c(int64_t c, int64_t r, int64_t s, int64_t groups) {
+  return groups == 1 && c <= 8 && r * s >= 4 && r * s * c <= 1024;  // one block pass covers a pixel's row
+}
 static ConvWs conv_ws(int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s,
                       int64_t groups) {
   ConvWs ws;
@@ -585,7 +589,79 @@ static ConvWs conv_ws(int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int
   ws.cchunks = (cg + 31) / 32;
   ws.in_bytes = round_up(n * h * w * ws.cp * 4, 1024);
   ws.w_bytes = round_up(k * r * s * ws.cchunks * 32 * 4, 1024);
+  if (conv_small_c(c, r, s, groups)) {
+    // room for the im2col form of a few-channel input (one row of taps x channels per output
+    // pixel), bounded by one output pixel per input pixel
+    const int64_t col = round_up(n * h * w * round_up(r * s * c, 32) * 4, 1024);
+    if (col > ws.in_bytes) ws.in_bytes = col;
+  }
   return ws;
+}
+
+// Few input channels under a filter with several taps: a 32-channel K block of the per-tap
+// lowering would hold mostly padding (3 real channels in 32 for an RGB stem), so such a conv is
+// run as a 1x1 conv over its im2col form instead: per output pixel one row of taps x channels,
+// padded to a multiple of 32.
+constexpr int kColSeg = 64;  // output pixels of one image row handled by one block
+
+__global__ void __launch_bounds__(256)
+conv_im2col_kernel(const float* __restrict__ in, const float* __restrict__ wgt, float* __restrict__ col,
+                   float* __restrict__ w2, int N, int C, int H, int W, int K, int R, int S, int P, int Q, int Kp,
+                   int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int segs,
+                   int col_blocks) {
+  grid_launch_dependents();
+  const int kreal = R * S * C;
+  if (static_cast<int>(blockIdx.x) < col_blocks) {
+    // A block owns a segment of one output row; a thread owns one group of 4 consecutive K indices
+    // (a 16-byte store) and walks the segment's pixels, so the (tap, channel) of its four entries is
+    // worked out once.
+    const int gpp = Kp >> 2;                    // groups per pixel
+    const int ppb = 256 / gpp;                  // pixels per pass (Kp <= 1024)
+    const int g = threadIdx.x % gpp, lane_px = threadIdx.x / gpp;
+    const int seg = blockIdx.x % segs;
+    const int oh = (blockIdx.x / segs) % P;
+    const int img = blockIdx.x / (segs * P);
+    int ch[4], dh[4], dw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = 4 * g + j;
+      const int tap = idx / C;
+      ch[j] = idx < kreal ? idx - tap * C : -1;
+      const int tr = tap / S;
+      dh[j] = tr * dil_h - pad_h;
+      dw[j] = (tap - tr * S) * dil_w - pad_w;
+    }
+    const float* src = in + static_cast<long long>(img) * C * H * W;
+    float* dst = col + (static_cast<long long>(img) * P + oh) * Q * Kp + 4 * g;
+    const int ow_end = min(Q, (seg + 1) * kColSeg);
+    if (lane_px < ppb) {
+      for (int ow = seg * kColSeg + lane_px; ow < ow_end; ow += ppb) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int ih = oh * stride_h + dh[j], iw = ow * stride_w + dw[j];
+          v[j] = (ch[j] >= 0 && ih >= 0 && ih < H && iw >= 0 && iw < W)
+                     ? __ldg(src + (static_cast<long long>(ch[j]) * H + ih) * W + iw) : 0.0f;
+        }
+        *reinterpret_cast<float4*>(dst + static_cast<long long>(ow) * Kp) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+    }
+  } else {
+    // filter [K][C][R*S] -> [K][Kp] with the same (tap, channel) order, zero tail
+    const long long total = static_cast<long long>(K) * Kp;
+    const long long nb = gridDim.x - col_blocks;
+    for (long long i = static_cast<long long>(blockIdx.x - col_blocks) * blockDim.x + threadIdx.x; i < total;
+         i += nb * blockDim.x) {
+      const int idx = static_cast<int>(i % Kp);
+      const int ko = static_cast<int>(i / Kp);
+      float x = 0.0f;
+      if (idx < kreal) {
+        const int tap = idx / C, c = idx - tap * C;
+        x = wgt[(static_cast<long long>(ko) * C + c) * R * S + tap];
+      }
+      w2[i] = x;
+    }
+  }
 }
 
 // One launch: blocks [0, in_blocks) transpose NCHW -> NHWC(Cp) through a shared-memory tile of
@@ -919,7 +995,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   const int num_sms = sm_count();
 
   const int algo = user ? user->algo : 0;
-  if (algo < 0 || algo > 3) return FTB_E_BAD_CONFIG;
+  if (algo < 0 || algo > 4) return FTB_E_BAD_CONFIG;
   // A 1x1 filter at stride 1 without padding is a batched GEMM on the NCHW tensors as they are:
   // out[b] (K x HW) = weight (K x C) * in[b] (C x HW), the pixels being the contiguous dimension
   // of both the B operand and the result.  No layout pass, no workspace traffic.
@@ -943,6 +1019,23 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
                           stream_v, nullptr, 0, &ex);
     }
   }
+  // Few input channels: continue as a 1x1, stride-1, unpadded conv over the im2col form, an
+  // [n][P][Q][Kp] channels-last image (written by conv_im2col_kernel where the layout pass would run).
+  ConvWs wsx = ws;
+  bool im2col = false;
+  struct { int64_t c, h, w, r, s; int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w; } orig =
+      {c, h, w, r, s, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w};
+  if ((algo == 0 || algo == 4) && conv_small_c(c, r, s, groups)) {
+    const int64_t kp = round_up(r * s * c, 32);
+    if (round_up(n * P * Q * kp * 4, 1024) <= ws.in_bytes && n * P * Q * kp < (1ll << 31)) {
+      im2col = true;
+      wsx.cp = kp;
+      wsx.cchunks = kp / 32;
+      h = P; w = Q; r = 1; s = 1;
+      stride_h = stride_w = 1; pad_h = pad_w = 0; dil_h = dil_w = 1;
+    }
+  }
+  if (algo == 4 && !im2col) return FTB_E_UNSUPPORTED;
   // Filters with more than one tap at stride 1 go to the slab kernel when it can take them.
   SlabPlan sp;
   sp.ok = false;
@@ -1009,7 +1102,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   if (tile_h < 1 || tile_h * tile_w > 128 || tile_h * stride_h > 256) return FTB_E_BAD_CONFIG;
   const int tiles_w = static_cast<int>((Q + tile_w - 1) / tile_w);
   const int tiles_h = static_cast<int>((P + tile_h - 1) / tile_h);
-  const int num_kb = static_cast<int>(r * s * ws.cchunks);
+  const int num_kb = static_cast<int>(r * s * wsx.cchunks);
   const long long tiles_m = static_cast<long long>(n) * tiles_h * tiles_w;
   ftb_config cfg;
   // The result leaves through bulk tensor stores when they can address it (16-byte aligned rows
@@ -1082,9 +1175,35 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   }
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v,
-                    cfg.split_k > 1 ? out : nullptr, n * k * P * Q);
-  if (rc) return rc;
+  if (im2col) {
+    if (cfg.split_k > 1) {
+      cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(n * k * P * Q) * 4, stream);
+      if (e != cudaSuccess) {
+        set_last_cuda_error(static_cast<int>(e));
+        return FTB_E_CUDA;
+      }
+    }
+    const int kp = static_cast<int>(wsx.cp);
+    const int segs = static_cast<int>((Q + kColSeg - 1) / kColSeg);
+    const long long col_blocks = n * P * segs;
+    long long w_blocks = (k * kp + 255) / 256;
+    if (w_blocks > 2ll * num_sms) w_blocks = 2ll * num_sms;
+    conv_im2col_kernel<<<static_cast<unsigned>(col_blocks + w_blocks), 256, 0, stream>>>(
+        in, weight, in_nhwc, w_packed, static_cast<int>(n), static_cast<int>(orig.c), static_cast<int>(orig.h),
+        static_cast<int>(orig.w), static_cast<int>(k), static_cast<int>(orig.r), static_cast<int>(orig.s),
+        static_cast<int>(P), static_cast<int>(Q), kp, orig.stride_h, orig.stride_w, orig.pad_h, orig.pad_w,
+        orig.dil_h, orig.dil_w, segs, static_cast<int>(col_blocks));
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      set_last_cuda_error(static_cast<int>(e));
+      return FTB_E_CUDA;
+    }
+  } else {
+    rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v,
+                      cfg.split_k > 1 ? out : nullptr, n * k * P * Q);
+    if (rc) return rc;
+  }
   for (int g = 0; g < groups; ++g) {
     UmmaParams p;
     memset(&p, 0, sizeof(p));
@@ -1122,7 +1241,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.bias = bias;
     p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);
     p.tile_h = tile_h; p.tile_w = tile_w; p.tiles_h = tiles_h; p.tiles_w = tiles_w;
-    p.R = static_cast<int>(r); p.S = static_cast<int>(s); p.cchunks = static_cast<int>(ws.cchunks);
+    p.R = static_cast<int>(r); p.S = static_cast<int>(s); p.cchunks = static_cast<int>(wsx.cchunks);
     p.stride_h = stride_h; p.stride_w = stride_w; p.pad_h = pad_h; p.pad_w = pad_w;
     p.dil_h = dil_h; p.dil_w = dil_w;
     p.status = status ? status : fallback_status();
@@ -1131,10 +1250,10 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     CUtensorMap ta, tb;
     {
       // (c, w, h, n) view of the channels-last copy; a group sees its own Cg channels.
-      uint64_t dims[4] = {static_cast<uint64_t>(groups > 1 ? cg : ws.cp), static_cast<uint64_t>(w),
+      uint64_t dims[4] = {static_cast<uint64_t>(groups > 1 ? cg : wsx.cp), static_cast<uint64_t>(w),
                           static_cast<uint64_t>(h), static_cast<uint64_t>(n)};
-      uint64_t strides[3] = {static_cast<uint64_t>(ws.cp) * 4, static_cast<uint64_t>(w) * ws.cp * 4,
-                             static_cast<uint64_t>(h) * w * ws.cp * 4};
+      uint64_t strides[3] = {static_cast<uint64_t>(wsx.cp) * 4, static_cast<uint64_t>(w) * wsx.cp * 4,
+                             static_cast<uint64_t>(h) * w * wsx.cp * 4};
       uint32_t box[4] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(tile_w * stride_w),
                          static_cast<uint32_t>(tile_h * stride_h), 1};
       uint32_t es[4] = {1, static_cast<uint32_t>(stride_w), static_cast<uint32_t>(stride_h), 1};

@@ -369,7 +369,10 @@ def generate_space_intra_op_b200(op, down_graph=None):
         # (the padding stage feeding this op is the identity when padding is 0)
         gemm_ok = (taps == 1 and one_group and unit_stride and tuple(op.attrs.get("padding", (0, 0))) == (0, 0)
                    and (out_h * out_w) % 4 == 0 and rc % 4 == 0)
-        space.add_subspace("algo", KnobSpace("algo", [1, 2] if slab_ok else ([1, 3] if gemm_ok else [1])), "inline")
+        # 4 = a 1x1 conv over the im2col form (at most 8 input channels under a filter of 4 taps or more)
+        im2col_ok = one_group and rc <= 8 and taps >= 4
+        algos = [1] + ([2] if slab_ok else []) + ([3] if gemm_ok else []) + ([4] if im2col_ok else [])
+        space.add_subspace("algo", KnobSpace("algo", algos), "inline")
     else:  # depthwise
         out_h = extents["h"]
         strips = sorted(set(_divisor_like(out_h, [1, 2, 4, 7, 8, 14, 16, 28, 32, 56, 64, 112]) + [out_h]))

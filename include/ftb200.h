@@ -57,7 +57,8 @@ typedef struct ftb_config {
   int32_t algo;      /* conv2d: 0 auto; 1 one shifted input tile per filter tap; 2 one input slab per
                         channel chunk shared by all taps, filter resident in shared memory (stride 1,
                         groups 1, <= 256 output channels, single-pass TF32); 3 batched GEMM on the
-                        NCHW tensors as they are (1x1 filter, stride 1, no padding, groups 1)        */
+                        NCHW tensors as they are (1x1 filter, stride 1, no padding, groups 1); 4 a 1x1
+                        conv over the im2col form of the input (at most 8 input channels, groups 1)    */
   int32_t reserved[5];
 } ftb_config;
 

@@ -436,13 +436,36 @@ def test_conv2d_1x1_as_batched_gemm(B, status, shape, cfg):
         run_conv(B, x, w, bias, 1, 1, 1, 1, cfg={"algo": 3}, status=status)
 
 
+@pytest.mark.parametrize("shape", [
+    # n, c, h, w, k, r, stride, pad, dil
+    (1, 3, 64, 64, 64, 7, 2, 3, 1),      # RGB stem, 7x7 stride 2
+    (2, 3, 30, 34, 24, 3, 1, 1, 1),      # 27 of 32 K entries real
+    (1, 8, 19, 23, 40, 5, 1, 2, 2),      # 8 channels, dilation, 200 K entries -> 7 blocks
+    (2, 1, 28, 28, 16, 5, 2, 0, 1),      # one channel, no padding
+])
+@pytest.mark.parametrize("cfg", [{}, {"algo": 4}, {"algo": 4, "split_k": 1, "tile_n": 32}, {"algo": 1}, {"algo": 4, "fp32_mode": 1}])
+def test_conv2d_few_channels_as_im2col(B, status, shape, cfg):
+    """Few input channels: a 1x1 conv over the im2col form (algo 4) against the oracle and the per-tap lowering."""
+    n, c, h, wd, k, r, stride, pad, dil = shape
+    x, w = O.conv2d_inputs(n, c, h, wd, k, r, r, seed=63)
+    bias = np.random.default_rng(64).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, stride, pad, dil, 1)
+    got = run_conv(B, x, w, bias, stride, pad, dil, 1, cfg=cfg, status=status)
+    assert got.shape == want.shape
+    assert O.normalised_error(got, want) <= (TOL["conv2d_3xtf32"] if cfg.get("fp32_mode") else TOL["conv2d_tf32"])
+    assert int(status.item()) == 0
+    x16, w16 = O.conv2d_inputs(1, 16, 12, 12, 8, 3, 3, seed=65)
+    with pytest.raises(B.FtbError):                        # 16 channels: not this form
+        run_conv(B, x16, w16, None, 1, 1, 1, 1, cfg={"algo": 4}, status=status)
+
+
 def test_conv2d_slab_algorithm_refuses_what_it_cannot_take(B, status):
     x, w = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, seed=59)
     for kwargs, cfg in ((dict(stride=2), {"algo": 2}),                 # stride 2
                         (dict(stride=1), {"algo": 2, "fp32_mode": 1}),  # 3xTF32
                         (dict(stride=1), {"algo": 2, "tile_n": 16}),                # not a tile width
                         (dict(stride=1), {"algo": 3}),                             # GEMM form of a 3x3
-                        (dict(stride=1), {"algo": 4})):
+                        (dict(stride=1), {"algo": 5})):
         with pytest.raises(B.FtbError):
             run_conv(B, x, w, None, kwargs["stride"], 1, 1, 1, cfg=cfg, status=status)
     xg, wg = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, groups=2, seed=59)
