@@ -153,7 +153,8 @@ static int resolve_config(const ftb_config* user, const KindInfo& ki, bool split
           best_bn = bn;
         }
         if (waves == 1) {
-          const long long ctas_used = tiles * cluster;
+          // SMs kept busy with real work: CTAs used times the share of their tiles inside the problem
+          const long long ctas_used = static_cast<long long>(tiles * cluster * (useful / (static_cast<double>(tiles) * tm * bn)));
           if (ctas_used > best_ctas) {
             best_ctas = ctas_used;
             wave_cluster = cluster;
@@ -355,7 +356,6 @@ static bool pick_small_f32(const ftb_config* user, const KindInfo& ki, bool spli
                            long long batch, long long m, long long n, int num_kb, int num_sms, ftb_config* out) {
   if (!eligible) return false;
   if (user && (user->tile_n != 0 || user->cluster != 0 || user->split_k != 0)) return false;
-  if (batch * ((m + 127) / 128) * ((n + 127) / 128) > num_sms) return false;  // more than one wave: not this regime
   double best = 1e30;
   int best_cluster = 0, best_bn = 0, best_split = 0;
   for (int cluster = 1; cluster <= (split3 ? 1 : 2); ++cluster) {
@@ -1044,6 +1044,10 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     sp = plan_slab(user, n, kg, P, Q, r, s, ws.cchunks, dil_h, dil_w, pad_h, pad_w,
                    (reinterpret_cast<uintptr_t>(out) & 15) == 0, num_sms);
   if (algo == 2 && !sp.ok) return FTB_E_UNSUPPORTED;
+  // Left to itself the slab kernel is taken when the whole filter stays resident, or when the tile
+  // list is shorter than the SM count (where a split reduction is wanted anyway); a long tile list
+  // with the taps split would add every partial sum of a large result in global memory.
+  if (sp.ok && algo == 0 && sp.p.split > 1 && sp.p.tiles >= num_sms) sp.ok = false;
   if (sp.ok) {
     if (user) {
       rc = ftb_validate(3, user, n * P * Q, k, c * r * s);
