@@ -122,7 +122,9 @@ class PeerGatheredOutput(object):
             raise RuntimeError("symmetric memory gave %d buffers for %d ranks" % (len(self.ptrs), self.world))
 
     def slice_ptrs(self, lo):
-        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        # own buffer first, then the peers starting with the next rank: at any moment the ranks'
+        # stores are spread over different receivers instead of all aiming at rank 0 first
+        order = [(self.rank + k) % self.world for k in range(self.world)]
         return [self.ptrs[r] + lo * self.item_bytes for r in order]
 
     def barrier(self):
