@@ -674,7 +674,7 @@ __global__ void __launch_bounds__(256)
 conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt, float* __restrict__ in_nhwc,
                     float* __restrict__ w_packed, int N, int C, int HW, int Cp, int K, int Cg, int RS,
                     int cchunks, int hw_tiles, int c_tiles, int in_blocks, int w_blocks, float* __restrict__ zero,
-                    long long zero_n) {
+                    long long zero_n, int plane, int sub_q, int sub_row, int sub_col) {
   __shared__ __align__(16) float tile[kPreCh][kPrePx + 1];
   // The conv kernel that follows is launched as a programmatic dependent: it may set itself up
   // (barriers, tensor memory, descriptor fetch) while this grid runs, and waits for this grid's
@@ -698,15 +698,25 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
     const int ht = (bid / c_tiles) % hw_tiles;
     const int img = bid / (c_tiles * hw_tiles);
     const int c0 = ct * kPreCh, p0 = ht * kPrePx;
-    const float* src = in + static_cast<long long>(img) * C * HW;
-    const bool vec = (HW % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+    // `HW` counts the pixels that are copied, `plane` the pixels of one source channel plane; they
+    // differ when a strided 1x1 conv keeps only every sub_row-th / sub_col-th pixel (sub_q > 0: kept
+    // pixels per row), which is all such a conv reads.
+    const float* src = in + static_cast<long long>(img) * C * plane;
+    const bool vec = sub_q == 0 && (HW % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
     // load: thread -> (channel, 4 pixels)
     for (int i = threadIdx.x; i < kPreCh * (kPrePx / 4); i += 256) {
       const int ch = i / (kPrePx / 4), q = (i % (kPrePx / 4)) * 4;
       const int c = c0 + ch, px = p0 + q;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (c < C && px < HW) {
-        const float* rp = src + static_cast<long long>(c) * HW + px;
+      if (c < C && px < HW && sub_q > 0) {
+        const float* cp_ = src + static_cast<long long>(c) * plane;
+        float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (px + j < HW) t[j] = __ldg(cp_ + ((px + j) / sub_q) * sub_row + ((px + j) % sub_q) * sub_col);
+        v = make_float4(t[0], t[1], t[2], t[3]);
+      } else if (c < C && px < HW) {
+        const float* rp = src + static_cast<long long>(c) * plane + px;
         if (vec && px + 3 < HW) {
           v = __ldg(reinterpret_cast<const float4*>(rp));
         } else {
@@ -790,9 +800,12 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
 // `zero` (may be null): `zero_n` floats of the result to clear in the same launch.
 static int conv_prepass(const float* in, const float* weight, float* in_nhwc, float* w_packed, int64_t n, int64_t c,
                         int64_t h, int64_t w, int64_t k, int64_t cg, int64_t r, int64_t s, const ConvWs& ws,
-                        int num_sms, void* stream_v, float* zero = nullptr, long long zero_n = 0) {
+                        int num_sms, void* stream_v, float* zero = nullptr, long long zero_n = 0, int sub_q = 0,
+                        int sub_p = 0, int sub_sh = 1, int sub_sw = 1) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  const int HW = static_cast<int>(h * w);
+  // sub_q > 0: keep sub_p x sub_q pixels of every plane, every sub_sh-th row and sub_sw-th column
+  const int plane = static_cast<int>(h * w);
+  const int HW = sub_q > 0 ? sub_p * sub_q : plane;
   const int hw_tiles = (HW + kPrePx - 1) / kPrePx, c_tiles = static_cast<int>((ws.cp + kPreCh - 1) / kPreCh);
   const int in_blocks = static_cast<int>(n) * hw_tiles * c_tiles;
   // one work unit of the filter packing = one output channel x one run of input channels
@@ -808,7 +821,7 @@ static int conv_prepass(const float* in, const float* weight, float* in_nhwc, fl
   conv_prepass_kernel<<<in_blocks + w_blocks + z_blocks, 256, 0, stream>>>(
       in, weight, in_nhwc, w_packed, static_cast<int>(n), static_cast<int>(c), HW, static_cast<int>(ws.cp),
       static_cast<int>(k), static_cast<int>(cg), static_cast<int>(r * s), static_cast<int>(ws.cchunks), hw_tiles,
-      c_tiles, in_blocks, w_blocks, zero, zero_n);
+      c_tiles, in_blocks, w_blocks, zero, zero_n, plane, sub_q, sub_sh * static_cast<int>(w), sub_sw);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -1036,6 +1049,18 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     }
   }
   if (algo == 4 && !im2col) return FTB_E_UNSUPPORTED;
+  // A strided 1x1 filter without padding reads only every stride-th pixel: the layout pass copies
+  // just those, and what follows is a stride-1 conv over the P x Q image of kept pixels.
+  int sub_sh = 1, sub_sw = 1;
+  const int64_t h_in = h, w_in = w;
+  if (!im2col && r == 1 && s == 1 && pad_h == 0 && pad_w == 0 && (stride_h > 1 || stride_w > 1)) {
+    sub_sh = stride_h;
+    sub_sw = stride_w;
+    h = P;
+    w = Q;
+    stride_h = stride_w = 1;
+  }
+  const bool subsample = sub_sh > 1 || sub_sw > 1;
   // Filters with more than one tap at stride 1 go to the slab kernel when it can take them.
   SlabPlan sp;
   sp.ok = false;
@@ -1204,8 +1229,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       return FTB_E_CUDA;
     }
   } else {
-    rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v,
-                      cfg.split_k > 1 ? out : nullptr, n * k * P * Q);
+    rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h_in, w_in, k, cg, r, s, ws, num_sms, stream_v,
+                      cfg.split_k > 1 ? out : nullptr, n * k * P * Q, subsample ? static_cast<int>(Q) : 0,
+                      static_cast<int>(P), sub_sh, sub_sw);
     if (rc) return rc;
   }
   for (int g = 0; g < groups; ++g) {

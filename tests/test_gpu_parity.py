@@ -459,6 +459,25 @@ def test_conv2d_few_channels_as_im2col(B, status, shape, cfg):
         run_conv(B, x16, w16, None, 1, 1, 1, 1, cfg={"algo": 4}, status=status)
 
 
+@pytest.mark.parametrize("shape", [
+    # n, c, h, w, k, stride, groups
+    (2, 64, 14, 14, 96, 2, 1),      # even extent
+    (3, 40, 15, 13, 48, 2, 1),      # odd extents: the last kept row and column are the image border
+    (1, 32, 29, 31, 64, 3, 1),      # stride 3
+    (2, 32, 12, 12, 32, 2, 2),      # two groups
+])
+@pytest.mark.parametrize("cfg", [{}, {"split_k": 1, "tile_n": 32}, {"fp32_mode": 1}])
+def test_conv2d_strided_1x1_keeps_only_the_pixels_it_reads(B, status, shape, cfg):
+    n, c, h, wd, k, stride, groups = shape
+    x, w = O.conv2d_inputs(n, c, h, wd, k, 1, 1, groups=groups, seed=66)
+    bias = np.random.default_rng(67).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, stride, 0, 1, groups)
+    got = run_conv(B, x, w, bias, stride, 0, 1, groups, cfg=cfg, status=status)
+    assert got.shape == want.shape
+    assert O.normalised_error(got, want) <= (TOL["conv2d_3xtf32"] if cfg.get("fp32_mode") else TOL["conv2d_tf32"])
+    assert int(status.item()) == 0
+
+
 def test_conv2d_slab_algorithm_refuses_what_it_cannot_take(B, status):
     x, w = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, seed=59)
     for kwargs, cfg in ((dict(stride=2), {"algo": 2}),                 # stride 2
