@@ -1132,7 +1132,15 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   const int tiles_w = static_cast<int>((Q + tile_w - 1) / tile_w);
   const int tiles_h = static_cast<int>((P + tile_h - 1) / tile_h);
   const int num_kb = static_cast<int>(r * s * wsx.cchunks);
-  const long long tiles_m = static_cast<long long>(n) * tiles_h * tiles_w;
+  // Images of at most 64 output pixels share a tile: as many whole images as fit in its 128 rows.
+  int tile_imgs = 1;
+  if (tiles_h == 1 && tiles_w == 1 && tile_h * tile_w <= 64 && !(user && user->tile_h > 0)) {
+    tile_imgs = 128 / (tile_h * tile_w);
+    if (tile_imgs > n) tile_imgs = static_cast<int>(n);
+    if (tile_imgs * tile_h * stride_h > 256) tile_imgs = 1;
+  }
+  const long long tiles_m = tile_imgs > 1 ? (n + tile_imgs - 1) / tile_imgs
+                                          : static_cast<long long>(n) * tiles_h * tiles_w;
   ftb_config cfg;
   // The result leaves through bulk tensor stores when they can address it (16-byte aligned rows
   // and boxes) and the staging buffers fit beside the chosen pipeline depth.
@@ -1256,7 +1264,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.b_bytes = static_cast<uint32_t>(p.b_rows) * 128u;
     p.a_boxes = 1;
     p.a_box_mn = kTileM;
-    p.a_box_bytes = static_cast<uint32_t>(tile_h * tile_w) * 128u;
+    p.a_box_bytes = static_cast<uint32_t>(tile_imgs * tile_h * tile_w) * 128u;
+    p.tile_imgs = tile_imgs;
+    p.n_imgs = static_cast<int>(n);
     p.a_lbo = 16; p.a_sbo = 1024; p.a_kadv = static_cast<uint32_t>(ki.umma_k * ki.esize);
     CUtensorMapSwizzle b_swz;
     operand_layout(ki, 0, p.b_rows, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv,
@@ -1285,7 +1295,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       uint64_t strides[3] = {static_cast<uint64_t>(wsx.cp) * 4, static_cast<uint64_t>(w) * wsx.cp * 4,
                              static_cast<uint64_t>(h) * w * wsx.cp * 4};
       uint32_t box[4] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(tile_w * stride_w),
-                         static_cast<uint32_t>(tile_h * stride_h), 1};
+                         static_cast<uint32_t>(tile_h * stride_h), static_cast<uint32_t>(tile_imgs)};
       uint32_t es[4] = {1, static_cast<uint32_t>(stride_w), static_cast<uint32_t>(stride_h), 1};
       rc = make_tmap(&ta, ki.dt, 4, in_nhwc + g * cg, dims, strides, box, es);
       if (rc) return rc;
@@ -1319,7 +1329,8 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
                           static_cast<uint64_t>(n)};
       uint64_t strides[3] = {static_cast<uint64_t>(Q) * 4, static_cast<uint64_t>(P) * Q * 4,
                              static_cast<uint64_t>(k) * P * Q * 4};
-      uint32_t box[4] = {static_cast<uint32_t>(tile_w), static_cast<uint32_t>(tile_h), 32, 1};
+      uint32_t box[4] = {static_cast<uint32_t>(tile_w), static_cast<uint32_t>(tile_h), 32,
+                         static_cast<uint32_t>(tile_imgs)};
       const uint32_t ones[4] = {1, 1, 1, 1};
       rc = make_tmap(&tc.dst[0], ki.dt, 4, out + static_cast<int64_t>(g) * kg * P * Q, dims, strides, box, ones,
                      CU_TENSOR_MAP_SWIZZLE_NONE);

@@ -71,6 +71,8 @@ struct UmmaParams {
   int conv, P, Q, tile_h, tile_w, tiles_h, tiles_w, R, S, cchunks;
   int conv_ktot, conv_koff;  // output channels of the whole conv / first channel of this group
   int conv_tiles;            // number of 128-pixel tiles (a CTA pair takes two consecutive ones)
+  int tile_imgs;             // whole images per tile (> 1 only when an image has at most 64 output pixels)
+  int n_imgs;                // images of the batch
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   int* status;
   int pdl;  // launched as a programmatic dependent: wait for the previous kernel before touching memory
@@ -216,7 +218,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int mt = PAIR ? tc.m * 2 + static_cast<int>(cta_rank) : tc.m;
           const int tw = mt % p.tiles_w;
           const int th = (mt / p.tiles_w) % p.tiles_h;
-          img = mt / (p.tiles_w * p.tiles_h);
+          img = mt / (p.tiles_w * p.tiles_h) * p.tile_imgs;  // first image of the tile
           h0 = th * p.tile_h * p.stride_h - p.pad_h;
           w0 = tw * p.tile_w * p.stride_w - p.pad_w;
           cc = kb0 % p.cchunks;
@@ -457,11 +459,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int mt = PAIR ? tc.m * 2 + static_cast<int>(cta_rank) : tc.m;
         const int tw = mt % p.tiles_w;
         const int th = (mt / p.tiles_w) % p.tiles_h;
-        const int img = mt / (p.tiles_w * p.tiles_h);
-        conv_mt = mt; conv_tw = tw; conv_th = th; conv_img = img;
-        const int oh = th * p.tile_h + row / p.tile_w;
-        const int ow = tw * p.tile_w + row % p.tile_w;
-        row_ok = mt < p.conv_tiles && row < p.tile_h * p.tile_w && oh < p.P && ow < p.Q;
+        // several small images per tile: rows are [image][pixel of the image]
+        const int px_per_img = p.tile_h * p.tile_w;
+        const int img_l = p.tile_imgs > 1 ? row / px_per_img : 0;
+        const int rr = p.tile_imgs > 1 ? row - img_l * px_per_img : row;
+        const int img0 = mt / (p.tiles_w * p.tiles_h) * p.tile_imgs;
+        const int img = img0 + img_l;
+        conv_mt = mt; conv_tw = tw; conv_th = th; conv_img = img0;
+        const int oh = th * p.tile_h + rr / p.tile_w;
+        const int ow = tw * p.tile_w + rr % p.tile_w;
+        row_ok = mt < p.conv_tiles && row < p.tile_imgs * px_per_img && img < p.n_imgs && oh < p.P && ow < p.Q;
         col_stride = static_cast<long long>(p.P) * p.Q;
         row_off = (static_cast<long long>(img) * p.conv_ktot + p.conv_koff) * col_stride +
                   static_cast<long long>(oh) * p.Q + ow;
@@ -478,8 +485,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // consecutive pixels, so the shared-memory writes of a channel are conflict-free and global
         // memory sees whole rows of every channel plane of the NCHW result.
         const bool leader = (warp == 2 && lane == 0);
-        const bool in_tile = row < p.tile_h * p.tile_w;
-        const uint32_t ch_stride = static_cast<uint32_t>(p.tile_h * p.tile_w) * 4u;
+        const int px_img = p.tile_h * p.tile_w;
+        const bool in_tile = row < p.tile_imgs * px_img;
+        const uint32_t ch_stride = static_cast<uint32_t>(px_img) * 4u;
+        // staging is [image of the tile][channel][pixel]: the box of the store is (w, h, 32 channels, images)
+        const uint32_t row_byte = p.tile_imgs > 1
+            ? static_cast<uint32_t>(row / px_img) * 32u * ch_stride + static_cast<uint32_t>(row % px_img) * 4u
+            : static_cast<uint32_t>(row) * 4u;
         const bool add_bias = p.bias != nullptr && tc.ks == 0;
         const bool tile_ok = has_work && conv_mt < p.conv_tiles;
         for (int c = 0; c < bn; c += 32, ++slab_seq) {
@@ -502,7 +514,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int j = 0; j < 32; ++j) {
               float x = __uint_as_float(v[j]);
               if (add_bias && n0 + c + j < N) x += p.bias[p.conv_koff + n0 + c + j];
-              st_shared_f32(buf + static_cast<uint32_t>(j) * ch_stride + static_cast<uint32_t>(row) * 4u, x);
+              st_shared_f32(buf + static_cast<uint32_t>(j) * ch_stride + row_byte, x);
             }
           }
           fence_proxy_async_smem();

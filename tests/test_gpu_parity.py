@@ -478,6 +478,30 @@ def test_conv2d_strided_1x1_keeps_only_the_pixels_it_reads(B, status, shape, cfg
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("shape", [
+    # n, c, h, w, k, r, stride, pad, groups
+    (16, 64, 7, 7, 96, 1, 1, 0, 1),      # two 49-pixel images per tile, 1x1
+    (5, 32, 7, 7, 48, 3, 1, 1, 1),       # odd image count: the last tile holds one image
+    (3, 16, 4, 4, 24, 3, 1, 1, 1),       # eight would fit, the batch has three
+    (9, 32, 5, 3, 40, 1, 1, 0, 1),       # 15-pixel images, rows that bulk stores cannot address
+    (6, 64, 14, 14, 32, 1, 2, 0, 1),     # strided 1x1 down to 7x7
+    (4, 32, 6, 6, 32, 3, 1, 1, 2),       # two groups
+])
+@pytest.mark.parametrize("cfg", [{"algo": 1}, {"algo": 1, "split_k": 2}, {"algo": 1, "cluster": 2}, {"algo": 1, "fp32_mode": 1}])
+def test_conv2d_small_images_share_a_tile(B, status, shape, cfg):
+    """Images of at most 64 output pixels are packed several to a 128-row tile."""
+    n, c, h, wd, k, r, stride, pad, groups = shape
+    if cfg.get("split_k", 1) > r * r * ((c // groups + 31) // 32):
+        pytest.skip("more splits than K blocks")
+    x, w = O.conv2d_inputs(n, c, h, wd, k, r, r, groups=groups, seed=68)
+    bias = np.random.default_rng(69).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, stride, pad, 1, groups)
+    got = run_conv(B, x, w, bias, stride, pad, 1, groups, cfg=cfg, status=status)
+    assert got.shape == want.shape
+    assert O.normalised_error(got, want) <= (TOL["conv2d_3xtf32"] if cfg.get("fp32_mode") else TOL["conv2d_tf32"])
+    assert int(status.item()) == 0
+
+
 def test_conv2d_slab_algorithm_refuses_what_it_cannot_take(B, status):
     x, w = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, seed=59)
     for kwargs, cfg in ((dict(stride=2), {"algo": 2}),                 # stride 2
