@@ -6,7 +6,7 @@ import sys
 import time
 
 from ..scheduler import schedule, schedule_with_config
-from ..task import Task
+from ..task import Task, register_task
 from ..utils import Config
 from .common import evaluate, test
 
@@ -18,6 +18,7 @@ def optimize(category, name, func, shapes, args_of, slevel=4, rlevel=3, target="
     for shape in shapes:
         print("Optimize %s shape %s [%.6f]" % (name, str(shape), time.time()), flush=True)
         task = Task(category, name, func, args_of(shape), target, dev_id)
+        register_task(task, override=True)   # as the reference's drivers do before they schedule
         kwargs = {}
         if trials_of is not None:
             kwargs["trials"] = trials_of(trials)
@@ -51,14 +52,31 @@ def optimize(category, name, func, shapes, args_of, slevel=4, rlevel=3, target="
     return ret
 
 
-def replay(path, dev_id, check):
+def _register_from_key(key, category, name, func):
+    """A log line of this driver names a task that only ``optimize`` registered: rebuild it from
+    the key, ``<category>_<name>_<args tuple>_<target>(<device>)``."""
+    import ast
+    prefix = "%s_%s_" % (category, name)
+    if not key.startswith(prefix):
+        return
+    body = key[len(prefix):]
+    args_text, _, tail = body.rpartition("_")
+    target, _, dev_text = tail.partition("(")
+    args = ast.literal_eval(args_text)
+    register_task(Task(category, name, func, tuple(args), target, int(dev_text.rstrip(")") or 0)), override=True)
+
+
+def replay(path, dev_id, check, category=None, name=None, func=None):
+    from ..task import TASK_TABLE
     with open(path, "r") as fin:
         for line in fin:
             if not line.strip():
                 continue
-            name, string = line.split(":", 1)
+            key, string = line.split(":", 1)
+            if key not in TASK_TABLE and func is not None:
+                _register_from_key(key, category, name, func)
             obj = json.loads(string)
-            test(name, Config(obj[0], obj[1]), dev_id, check_result=check)
+            test(key, Config(obj[0], obj[1]), dev_id, check_result=check)
 
 
 def main(category, name, func, shapes, args_of, trials_of=None):
@@ -74,7 +92,7 @@ def main(category, name, func, shapes, args_of, trials_of=None):
         torch.manual_seed(args.seed)
     end = len(shapes) if args.to < 0 else args.to
     if args.test != "":
-        replay(args.test, args.device, args.check)
+        replay(args.test, args.device, args.check, category, name, func)
         return
     kwargs = dict(slevel=args.slevel, rlevel=args.rlevel, target=args.target, dev_id=args.device,
                   timeout=args.timeout, trials=args.trials, parallel=args.parallel, method=args.method,

@@ -412,3 +412,27 @@ def test_saved_search_log_replays():
             assert plan.steps and name in TASK_TABLE
             count += 1
     assert count >= 5
+
+
+def test_driver_registers_the_tasks_it_creates(monkeypatch, tmp_path):
+    """The per-operator drivers build task keys that are not in the table beforehand: the search
+    leg registers them, and the --test leg rebuilds them from the keys of the log."""
+    from flextensor_b200.optimize import driver
+    from flextensor_b200.task import conv2d
+    monkeypatch.setattr(driver, "evaluate", lambda *a, **k: 0.0)
+    shape = (2, 16, 10, 12, 24, 3, 1, 1, 1, 1)
+    key = "conv2d_conv2d_%s_cuda(0)" % (shape,)
+    TASK_TABLE.pop(key, None)
+    log = tmp_path / "conv.log"
+    with open(log, "w") as flog:
+        got = driver.optimize("conv2d", "conv2d", conv2d, [shape], lambda s_: tuple(s_), trials=2, timeout=1,
+                              parallel=1, logfile=flog, trials_of=lambda t: [1, t], measurer=_fake_measurer())
+    assert key in got and key in TASK_TABLE
+    line = open(log).read().strip()
+    assert line.startswith(key + ":")
+    TASK_TABLE.pop(key)
+    driver._register_from_key(key, "conv2d", "conv2d", conv2d)
+    assert TASK_TABLE[key].args == shape and TASK_TABLE[key].target == "cuda" and TASK_TABLE[key].dev_id == 0
+    obj = json.loads(line.split(":", 1)[1])
+    plan, _ = schedule_with_config(key, Config(obj[0], obj[1]))
+    assert plan.steps
