@@ -180,6 +180,63 @@ __global__ void __launch_bounds__(256) dwconv3x3_direct_kernel(const DwParams p,
   }
 }
 
+// Square filters of 3 or 5 taps a side at stride 1 or 2 (dilation 1) that the kernel above does not take
+// (stride 2, 5x5, rows that are no multiple of 16 bytes, planes of a few pixels): still no staging
+// and no barrier.  A thread owns four adjacent outputs of one row, reads the K x ((4-1)*STRIDE + K)
+// input window they share straight from global memory (neighbouring threads hit the same lines in
+// L1; out-of-image taps read as zero) and serves every output channel of its input plane from it.
+template <int K, int STRIDE>
+__global__ void __launch_bounds__(256) dwconv_window_kernel(const DwParams p, long long items, int groups_w) {
+  const long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (item >= items) return;
+  constexpr int SPAN = 3 * STRIDE + K;
+  const int g = static_cast<int>(item % groups_w);
+  const int oh = static_cast<int>((item / groups_w) % p.P);
+  const long long plane = item / (static_cast<long long>(groups_w) * p.P);  // n * C + c
+  const int c = static_cast<int>(plane % p.C);
+  const long long n = plane / p.C;
+  const int ow = g * 4;
+  const float* src = p.in + plane * p.H * p.W;
+  const int ih0 = oh * STRIDE - p.pad_h, iw0 = ow * STRIDE - p.pad_w;
+
+  float x[K][SPAN];
+#pragma unroll
+  for (int r = 0; r < K; ++r) {
+    const int ih = ih0 + r;
+    const bool row_ok = ih >= 0 && ih < p.H;
+    const float* rp = src + static_cast<long long>(row_ok ? ih : 0) * p.W;
+#pragma unroll
+    for (int j = 0; j < SPAN; ++j) {
+      const int iw = iw0 + j;
+      x[r][j] = (row_ok && iw >= 0 && iw < p.W) ? __ldg(rp + iw) : 0.f;
+    }
+  }
+  for (int f = 0; f < p.F; ++f) {
+    const int co = c * p.F + f;
+    const float* wp = p.w + static_cast<long long>(co) * K * K;
+    float acc[4];
+    const float b = p.bias ? __ldg(p.bias + co) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = b;
+#pragma unroll
+    for (int r = 0; r < K; ++r)
+#pragma unroll
+      for (int t = 0; t < K; ++t) {
+        const float wv = __ldg(wp + r * K + t);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] = fmaf(x[r][j * STRIDE + t], wv, acc[j]);
+      }
+    float* dst = p.out + ((n * p.C * p.F + co) * p.P + oh) * p.Q + ow;
+    if (ow + 3 < p.Q && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (ow + j < p.Q) dst[j] = acc[j];
+    }
+  }
+}
+
 }  // namespace ftb
 
 extern "C" int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const float* bias, float* out,
@@ -238,6 +295,30 @@ extern "C" int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const
       dwconv3x3_direct_kernel<4><<<static_cast<unsigned>(blocks_d), threads_d, 0, stream>>>(p, items, vcols, rblocks);
     else
       dwconv3x3_direct_kernel<8><<<static_cast<unsigned>(blocks_d), threads_d, 0, stream>>>(p, items, vcols, rblocks);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      set_last_cuda_error(static_cast<int>(e));
+      return FTB_E_CUDA;
+    }
+    return FTB_OK;
+  }
+
+  // Window path (default when no strip height is asked for): 3x3 and 5x5 at stride 1 or 2, dilation 1.
+  if (want_rows == 0 && r == s && (r == 3 || r == 5) && stride_h == stride_w && (stride_h == 1 || stride_h == 2) &&
+      dil_h == 1 && dil_w == 1) {
+    int threads_w = cfg && cfg->threads > 0 ? cfg->threads : 128;
+    if (threads_w < 32 || threads_w > 256 || threads_w % 32) return FTB_E_BAD_CONFIG;
+    const int groups_w = static_cast<int>((Q + 3) / 4);
+    const long long items = static_cast<long long>(n) * c * P * groups_w;
+    const long long blocks_w = (items + threads_w - 1) / threads_w;
+    if (blocks_w > 0x7fffffffll) return FTB_E_TOO_LARGE;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const unsigned gb = static_cast<unsigned>(blocks_w);
+    if (r == 3 && stride_h == 1) dwconv_window_kernel<3, 1><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+    else if (r == 3) dwconv_window_kernel<3, 2><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+    else if (stride_h == 1) dwconv_window_kernel<5, 1><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+    else dwconv_window_kernel<5, 2><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

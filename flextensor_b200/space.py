@@ -376,7 +376,8 @@ def generate_space_intra_op_b200(op, down_graph=None):
     else:  # depthwise
         out_h = extents["h"]
         strips = sorted(set(_divisor_like(out_h, [1, 2, 4, 7, 8, 14, 16, 28, 32, 56, 64, 112]) + [out_h]))
-        space.add_subspace("tile_h", KnobSpace("tile_h", [s for s in strips if s <= out_h]), "spatial")
+        # 0 = no staging: the register-tiled 3x3 kernel or the window kernel, whichever takes the shape
+        space.add_subspace("tile_h", KnobSpace("tile_h", [0] + [s for s in strips if s <= out_h]), "spatial")
         space.add_subspace("threads", KnobSpace("threads", [64, 128, 256, 512]), "spatial")
     return space
 
