@@ -571,6 +571,21 @@ def test_depthwise_shapes(B, shape):
     assert O.normalised_error(got, want) <= TOL["depthwise_f32"]
 
 
+@pytest.mark.parametrize("shape", [(2, 12, 17, 19, 2, 5, 1, 2), (3, 9, 28, 28, 1, 5, 2, 2), (1, 7, 13, 13, 1, 3, 2, 0),
+                                   (4, 64, 14, 14, 1, 3, 2, 1), (2, 5, 6, 50, 3, 3, 1, 1)])
+@pytest.mark.parametrize("cfg", [None, {"threads": 256}, {"tile_h": 4}])
+def test_depthwise_window_kernel_and_staged_kernel_agree(B, shape, cfg):
+    """3x3 / 5x5 at stride 1 or 2: the window kernel (default) and the staged kernel (a strip height is
+    given) against the oracle."""
+    n, c, h, w_, f, r, stride, pad = shape
+    x, w = O.depthwise_inputs(n, c, h, w_, f, r, r, seed=63)
+    bias = np.random.default_rng(64).standard_normal(c * f).astype(np.float32)
+    got = run_dw(B, x, w, bias, stride, pad, 1, cfg=cfg)
+    want = O.depthwise_conv2d_nchw(x, w, bias, stride, pad, 1)
+    assert got.shape == want.shape
+    assert O.normalised_error(got, want) <= TOL["depthwise_f32"]
+
+
 def test_a_wait_that_runs_out_is_reported_not_hung(B):
     """A barrier nothing completes: the bounded wait gives up, the status word says so, and the
     device keeps working afterwards."""
