@@ -502,6 +502,44 @@ def test_conv2d_small_images_share_a_tile(B, status, shape, cfg):
     assert int(status.item()) == 0
 
 
+def _random_conv_cases(count, seed):
+    import random
+    rng = random.Random(seed)
+    cases = []
+    while len(cases) < count:
+        groups = rng.choice([1, 1, 1, 2, 4])
+        cg = rng.choice([4, 8, 16, 32]) if groups > 1 else rng.choice([1, 2, 3, 4, 5, 8, 12, 16, 24, 32, 40, 64])
+        kg = rng.choice([1, 3, 8, 16, 24, 32, 48, 64, 100, 128])
+        r = rng.choice([1, 1, 2, 3, 3, 3, 5, 7])
+        s = r if rng.random() < 0.8 else rng.choice([1, 2, 3, 5])
+        stride, dil, pad = rng.choice([1, 1, 1, 2, 2, 3]), rng.choice([1, 1, 1, 2]), rng.choice([0, 0, 1, 1, 2, 3])
+        h = rng.randint(max(1, dil * (r - 1) + 1 - 2 * pad), 24)
+        w = rng.randint(max(1, dil * (s - 1) + 1 - 2 * pad), 40)
+        if rng.random() < 0.2:
+            h = w = rng.choice([4, 7, 8, 14])
+        n = rng.choice([1, 1, 2, 3, 5, 9])
+        if O.out_size(h, r, stride, pad, dil) <= 0 or O.out_size(w, s, stride, pad, dil) <= 0:
+            continue
+        cfg = rng.choice([None, None, {"fp32_mode": 1}, {"algo": 1}, {"split_k": 1}])
+        cases.append((n, cg * groups, h, w, kg * groups, r, s, stride, pad, dil, groups, rng.random() < 0.5, cfg))
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_conv_cases(48, 7))
+def test_conv2d_random_shapes_against_the_oracle(B, status, case):
+    """Seeded random shapes through whatever algorithm the library picks for them (per-tap, slab, batched
+    GEMM, im2col form, kept-pixel copy, several images per tile), each against the numpy oracle."""
+    n, c, h, wd, k, r, s, stride, pad, dil, groups, with_bias, cfg = case
+    x, w = O.conv2d_inputs(n, c, h, wd, k, r, s, groups=groups, seed=70)
+    bias = np.random.default_rng(71).standard_normal(k).astype(np.float32) if with_bias else None
+    want = O.conv2d_nchw(x, w, bias, stride, pad, dil, groups)
+    got = run_conv(B, x, w, bias, stride, pad, dil, groups, cfg=cfg, status=status)
+    assert got.shape == want.shape
+    tol = TOL["conv2d_3xtf32"] if (cfg or {}).get("fp32_mode") else TOL["conv2d_tf32"]
+    assert O.normalised_error(got, want) <= tol, case
+    assert int(status.item()) == 0
+
+
 def test_conv2d_slab_algorithm_refuses_what_it_cannot_take(B, status):
     x, w = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, seed=59)
     for kwargs, cfg in ((dict(stride=2), {"algo": 2}),                 # stride 2
