@@ -284,8 +284,13 @@ extern "C" int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const
   if (direct_ok && (want_rows == 0 || want_rows == 4 || want_rows == 8)) {
     int threads_d = cfg && cfg->threads > 0 ? cfg->threads : 128;
     if (threads_d < 32 || threads_d > 256 || threads_d % 32) return FTB_E_BAD_CONFIG;
-    const int rh = want_rows == 4 ? 4 : 8;
     const int vcols = p.W / 4;
+    // 8 rows per thread reuse more of what they load; on a small problem 4 rows give twice the threads
+    // to hide the latency with (chosen when 8 rows would leave fewer than four CTAs per SM)
+    int rh = want_rows == 4 ? 4 : 8;
+    if (want_rows == 0 &&
+        static_cast<long long>(n) * c * vcols * ((p.P + 7) / 8) < 4ll * sm_count() * threads_d)
+      rh = 4;
     const int rblocks = (p.P + rh - 1) / rh;
     const long long items = static_cast<long long>(n) * c * vcols * rblocks;
     const long long blocks_d = (items + threads_d - 1) / threads_d;
