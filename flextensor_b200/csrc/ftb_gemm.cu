@@ -1070,9 +1070,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
                    (reinterpret_cast<uintptr_t>(out) & 15) == 0, num_sms);
   if (algo == 2 && !sp.ok) return FTB_E_UNSUPPORTED;
   // Left to itself the slab kernel is taken when the whole filter stays resident, or when the tile
-  // list is shorter than the SM count (where a split reduction is wanted anyway); a long tile list
+  // list is shorter than half the SM count (where a split reduction is wanted anyway); a long tile list
   // with the taps split would add every partial sum of a large result in global memory.
-  if (sp.ok && algo == 0 && sp.p.split > 1 && sp.p.tiles >= num_sms) sp.ok = false;
+  if (sp.ok && algo == 0 && sp.p.split > 1 && 2ll * sp.p.tiles > num_sms) sp.ok = false;
   if (sp.ok) {
     if (user) {
       rc = ftb_validate(3, user, n * P * Q, k, c * r * s);
