@@ -624,6 +624,74 @@ def test_depthwise_window_kernel_and_staged_kernel_agree(B, shape, cfg):
     assert O.normalised_error(got, want) <= TOL["depthwise_f32"]
 
 
+def _random_depthwise_cases(count, seed):
+    import random
+    rng = random.Random(seed)
+    cases = []
+    while len(cases) < count:
+        c, f = rng.choice([1, 3, 8, 17, 32, 64]), rng.choice([1, 1, 2, 3])
+        r = rng.choice([1, 3, 3, 3, 5, 5, 7])
+        stride, dil, pad = rng.choice([1, 1, 2, 3]), rng.choice([1, 1, 1, 2]), rng.choice([0, 1, 1, 2, 3])
+        h = rng.randint(max(1, dil * (r - 1) + 1 - 2 * pad), 30)
+        w = rng.choice([8, 16, 28, 56]) if rng.random() < 0.3 else rng.randint(max(1, dil * (r - 1) + 1 - 2 * pad), 50)
+        if O.out_size(h, r, stride, pad, dil) <= 0 or O.out_size(w, r, stride, pad, dil) <= 0:
+            continue
+        cfg = rng.choice([None, None, None, {"tile_h": 4}, {"tile_h": 8}, {"threads": 256}, {"tile_h": 2, "threads": 64}])
+        cases.append((rng.choice([1, 2, 5]), c, h, w, f, r, stride, pad, dil, cfg))
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_depthwise_cases(36, 11))
+def test_depthwise_random_shapes_against_the_oracle(B, case):
+    n, c, h, w_, f, r, stride, pad, dil, cfg = case
+    x, w = O.depthwise_inputs(n, c, h, w_, f, r, r, seed=72)
+    bias = np.random.default_rng(73).standard_normal(c * f).astype(np.float32)
+    got = run_dw(B, x, w, bias, stride, pad, dil, cfg=cfg)
+    want = O.depthwise_conv2d_nchw(x, w, bias, stride, pad, dil)
+    assert got.shape == want.shape
+    assert O.normalised_error(got, want) <= TOL["depthwise_f32"], case
+
+
+def _random_gemm_cases(count, seed):
+    import random
+    rng = random.Random(seed)
+    cases = []
+    for _ in range(count):
+        cfg = rng.choice([None, None, None, {"cluster": 1, "tile_n": 64}, {"cluster": 2, "tile_n": 128},
+                          {"cluster": 2, "tile_n": 512}, {"cluster": 1, "tile_n": 256, "stages": 2}])
+        cases.append((rng.choice(["tf32", "3xtf32", "bf16", "s8"]), rng.choice([1, 7, 64, 100, 128, 200, 256, 384, 520]),
+                      rng.choice([4, 8, 36, 64, 100, 128, 256, 520, 1000]), rng.choice([4, 8, 20, 32, 64, 100, 256, 520]),
+                      rng.random() < 0.3, rng.random() < 0.3, cfg))
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_gemm_cases(40, 13))
+def test_gemm_random_shapes_against_the_oracle(B, status, case):
+    """Seeded random shapes, majors and knobs over the three GEMM entry points, including operands that only
+    the CUDA-core kernel can address; a knob set the library refuses must be refused with a config error."""
+    kind, m, n, k, ta, tb, cfg = case
+    try:
+        if kind in ("tf32", "3xtf32"):
+            a, b = O.gemm_inputs(m, n, k, seed=74)
+            got = run_gemm_f32(B, a.T.copy() if ta else a, b.T.copy() if tb else b, ta, tb,
+                               cfg=dict(cfg or {}, fp32_mode=1 if kind == "3xtf32" else 0), status=status)
+            assert O.normalised_error(got, O.gemm(a, b)) <= TOL["gemm_f32_3xtf32" if kind == "3xtf32" else "gemm_f32_tf32"], case
+        elif kind == "bf16":
+            items = [O.batch_gemm_item(i, m, n, k, seed=75) for i in range(2)]
+            a, b = np.stack([i[0] for i in items]), np.stack([i[1] for i in items])
+            c = torch.full((2, m, n), float("nan"), device="cuda")
+            B.bgemm_bf16(bf16_dev(np.ascontiguousarray(np.swapaxes(a, 1, 2)) if ta else a),
+                         bf16_dev(np.ascontiguousarray(np.swapaxes(b, 1, 2)) if tb else b), c, ta, tb, cfg=cfg, status=status)
+            assert O.normalised_error(c.cpu().numpy(), O.batch_gemm(a, b)) <= TOL["bgemm_bf16_out_f32"], case
+        else:
+            a, b = O.gemm_int8_inputs(m, n, k, seed=76)
+            got = run_gemm_s8(B, a.T.copy() if ta else a, b.T.copy() if tb else b, ta, tb, cfg=cfg, status=status)
+            assert (got == O.gemm_int8(a, b)).all(), case
+    except B.FtbError as err:
+        assert cfg is not None and err.code == -3, case
+    assert int(status.item()) == 0
+
+
 def test_a_wait_that_runs_out_is_reported_not_hung(B):
     """A barrier nothing completes: the bounded wait gives up, the status word says so, and the
     device keeps working afterwards."""
