@@ -16,7 +16,9 @@
 //
 //   warp 0      TMA producer     filter once, then one slab per (tile, channel chunk)
 //   warp 1      MMA issuer       taps x 4 tcgen05.mma per slab, accumulators in TMEM
-//   warps 2-5   epilogue         tcgen05.ld -> NCHW stores (atomic adds when taps are split)
+//   warps 2-5   epilogue         tcgen05.ld -> [channel][pixel] staging -> bulk tensor stores of NCHW rows
+//                                (bulk reduce-adds when the taps are split; per-thread stores where bulk
+//                                stores cannot address the rows)
 //
 // CTAs with the same blockIdx.x % split share a subset of the taps and walk the tile list
 // with a stride of gridDim.x / split.
