@@ -10,7 +10,10 @@ import threading
 
 import torch
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libftb200.so")
+# FTB200_LIBRARY may name another build of the same library (e.g. the wait-profiling build that
+# `python -m flextensor_b200.build --profile-waits` writes next to the product one).
+_LIB_PATH = os.environ.get("FTB200_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib",
+                                                             "libftb200.so")
 _lib = None
 _lib_lock = threading.Lock()
 
@@ -41,16 +44,20 @@ class FtbConfig(ctypes.Structure):
         ("threads", ctypes.c_int32),
         ("cluster", ctypes.c_int32),
         ("algo", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 5),
+        ("epilogue", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 4),
     ]
 
     KNOBS = ("tile_n", "stages", "raster", "group_m", "split_k", "fp32_mode", "ctas", "tile_h", "threads",
-             "cluster", "algo")
+             "cluster", "algo", "epilogue")
 
     @classmethod
     def from_dict(cls, knobs):
         cfg = cls()
         for name, value in (knobs or {}).items():
+            if name == "_diag":  # diagnostic builds of the library only
+                cfg.reserved[0] = int(value)
+                continue
             if name not in cls.KNOBS:
                 raise KeyError("unknown kernel knob %r" % (name,))
             setattr(cfg, name, int(value))
@@ -107,6 +114,8 @@ def lib():
         handle.ftb_launch_count.argtypes = []
         handle.ftb_validate.restype = i32
         handle.ftb_validate.argtypes = [i32, cfgp, i64, i64, i64]
+        handle.ftb_debug_wait_profile.restype = i32
+        handle.ftb_debug_wait_profile.argtypes = [ctypes.POINTER(ctypes.c_uint64), i32]
         handle.ftb_selftest_bounded_wait.restype = i32
         handle.ftb_selftest_bounded_wait.argtypes = [vp, vp]
         handle.ftb_gemm_f32.restype = i32
@@ -129,14 +138,18 @@ def lib():
         handle.ftb_conv2d_nchw_f32_noalloc.argtypes = [vp] * 4 + [i64] * 7 + [i32] * 7 + [cfgp, vp, vp]
         handle.ftb_dwconv2d_nchw_f32.restype = i32
         handle.ftb_dwconv2d_nchw_f32.argtypes = [vp] * 4 + [i64] * 7 + [i32] * 6 + [cfgp, vp, vp]
+        handle.ftb_dwconv2d_nchw_f32_multi.restype = i32
+        handle.ftb_dwconv2d_nchw_f32_multi.argtypes = ([vp] * 3 + [ctypes.POINTER(vp), i32] + [i64] * 7 + [i32] * 6 +
+                                                       [cfgp, vp, vp])
         _lib = handle
     return _lib
 
 
 EXPORTED_SYMBOLS = (
     "ftb_version", "ftb_strerror", "ftb_last_cuda_error", "ftb_device_check", "ftb_validate",
-    "ftb_launch_count", "ftb_selftest_bounded_wait", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_bgemm_bf16_multi", "ftb_gemm_s8",
+    "ftb_launch_count", "ftb_selftest_bounded_wait", "ftb_debug_wait_profile", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_bgemm_bf16_multi", "ftb_gemm_s8",
     "ftb_conv2d_workspace_bytes", "ftb_conv2d_nchw_f32", "ftb_conv2d_nchw_f32_noalloc", "ftb_dwconv2d_nchw_f32",
+    "ftb_dwconv2d_nchw_f32_multi",
 )
 
 
@@ -190,6 +203,20 @@ def validate(op, cfg, m, n, k):
 
 def launch_count():
     return int(lib().ftb_launch_count())
+
+
+WAIT_PROFILE_SLOTS = ("producer_wait_empty", "issuer_wait_full", "issuer_wait_tmem_free", "epilogue_wait_tmem_full",
+                      "producer_loop", "issuer_loop", "epilogue_loop", "ctas")
+
+
+def wait_profile(reset=True):
+    """Cycle counters of a wait-profiling build (``FTB200_LIBRARY`` pointing at it) as a dict;
+    raises ``FtbError`` (unsupported) on the product build."""
+    arr = (ctypes.c_uint64 * 8)()
+    rc = lib().ftb_debug_wait_profile(arr, int(reset))
+    if rc:
+        raise FtbError(rc, "ftb_debug_wait_profile")
+    return dict(zip(WAIT_PROFILE_SLOTS, (int(v) for v in arr)))
 
 
 def selftest_bounded_wait(status, stream=None):
@@ -373,3 +400,30 @@ def dwconv2d_nchw_f32(x, weight, out, bias=None, stride=(1, 1), padding=(0, 0), 
             _cfg_ptr(cfg), _status_ptr(status), _stream_ptr(stream))
     if rc:
         raise FtbError(rc, "ftb_dwconv2d_nchw_f32")
+
+
+def dwconv2d_nchw_f32_multi(x, weight, dst_ptrs, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), cfg=None,
+                            status=None, stream=None):
+    """Depthwise conv whose result goes to several buffers at once.
+
+    ``dst_ptrs``: 1..8 device addresses (ints), each of an [N, C*f, P, Q] fp32 buffer on this GPU
+    or a mapped buffer of a peer GPU (e.g. a rank's slice in every rank's gathered output).
+    """
+    for t, nm in ((x, "x"), (weight, "weight")):
+        _check(t, torch.float32, nm)
+    if bias is not None:
+        _check(bias, torch.float32, "bias")
+    n, c, h, w = x.shape
+    c2, f, r, s = weight.shape
+    if c2 != c:
+        raise ValueError("depthwise: weight is [C,f,R,S] with C = input channels")
+    if not 1 <= len(dst_ptrs) <= 8:
+        raise ValueError("between 1 and 8 destinations")
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*[ctypes.c_void_p(int(p)) for p in dst_ptrs])
+    with torch.cuda.device(x.device):
+        rc = lib().ftb_dwconv2d_nchw_f32_multi(
+            x.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, arr, len(dst_ptrs),
+            n, c, h, w, f, r, s, stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
+            _cfg_ptr(cfg), _status_ptr(status), _stream_ptr(stream))
+    if rc:
+        raise FtbError(rc, "ftb_dwconv2d_nchw_f32_multi")

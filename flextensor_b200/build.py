@@ -33,6 +33,21 @@ def needs_build():
     return _newest(deps) > os.path.getmtime(LIB)
 
 
+PROFILE_LIB = os.path.join(LIB_DIR, "libftb200_prof.so")
+
+
+def build_profile_waits():
+    """The same sources with -DFTB_PROFILE_WAITS (per-role wait counters in the GEMM kernel), as a
+    second library beside the product one; load it with FTB200_LIBRARY=<path>."""
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    os.makedirs(LIB_DIR, exist_ok=True)
+    cmd = [nvcc] + NVCC_FLAGS + ["-DFTB_PROFILE_WAITS", "-o", PROFILE_LIB] + sources()
+    proc = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc failed:\n%s\n%s" % (proc.stdout, proc.stderr))
+    return PROFILE_LIB
+
+
 def build(force=False, verbose=False):
     """Compile the library if it is missing or older than its sources; returns its path."""
     if not force and not needs_build():
@@ -51,4 +66,7 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--profile-waits" in sys.argv:
+        print(build_profile_waits())
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -23,7 +23,22 @@ struct DwParams {
   int tile_rows;        // input rows staged per strip
   int tile_pitch;       // floats per staged row (multiple of 4)
   int lead;             // staged column of input column 0 (multiple of 4, >= pad_w)
+  // Further buffers that receive the same result (same layout as `out`): this GPU's memory or a
+  // peer GPU's mapped buffer.  The batch-sharded path uses them to place a rank's slice in every
+  // rank's gathered output with plain stores.
+  float* extra[7];
+  int num_extra;
 };
+
+// Byte distance from `out` to the d-th extra destination is the same for every element.
+__device__ __forceinline__ void dw_store4(const DwParams& p, float* dst, const float4& v) {
+  *reinterpret_cast<float4*>(dst) = v;
+  for (int d = 0; d < p.num_extra; ++d) *reinterpret_cast<float4*>(p.extra[d] + (dst - p.out)) = v;
+}
+__device__ __forceinline__ void dw_store1(const DwParams& p, float* dst, float v) {
+  *dst = v;
+  for (int d = 0; d < p.num_extra; ++d) p.extra[d][dst - p.out] = v;
+}
 
 // Staging tile: row i holds input row (h_in0 + i); column (lead + x) holds input column x.
 template <bool K3S1>
@@ -111,11 +126,11 @@ __global__ void dwconv_kernel(const DwParams p) {
       }
       float* dst = dst_plane + static_cast<long long>(oh0 + orow) * p.Q + ow;
       if (vec_out) {
-        *reinterpret_cast<float4*>(dst) = make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b);
+        dw_store4(p, dst, make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b));
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (ow + j < p.Q) dst[j] = acc[j] + b;
+          if (ow + j < p.Q) dw_store1(p, dst + j, acc[j] + b);
       }
     }
   }
@@ -174,8 +189,7 @@ __global__ void __launch_bounds__(256) dwconv3x3_direct_kernel(const DwParams p,
         for (int s = 0; s < 3; ++s)
 #pragma unroll
           for (int j = 0; j < 4; ++j) acc[j] = fmaf(x[i + r][j + s], wv[r * 3 + s], acc[j]);
-      *reinterpret_cast<float4*>(dst + static_cast<long long>(i) * p.Q) =
-          make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b);
+      dw_store4(p, dst + static_cast<long long>(i) * p.Q, make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b));
     }
   }
 }
@@ -228,23 +242,50 @@ __global__ void __launch_bounds__(256) dwconv_window_kernel(const DwParams p, lo
       }
     float* dst = p.out + ((n * p.C * p.F + co) * p.P + oh) * p.Q + ow;
     if (ow + 3 < p.Q && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-      *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      dw_store4(p, dst, make_float4(acc[0], acc[1], acc[2], acc[3]));
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        if (ow + j < p.Q) dst[j] = acc[j];
+        if (ow + j < p.Q) dw_store1(p, dst + j, acc[j]);
     }
   }
 }
 
 }  // namespace ftb
 
+namespace ftb {
+static int dwconv_generic(const float* in, const float* weight, const float* bias, float* out, float* const* extra,
+                          int num_extra, int64_t n, int64_t c, int64_t h, int64_t w, int64_t factor, int64_t r,
+                          int64_t s, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                          const ftb_config* cfg, int* status, void* stream_v);
+}
+
 extern "C" int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const float* bias, float* out,
                                      int64_t n, int64_t c, int64_t h, int64_t w, int64_t factor, int64_t r,
                                      int64_t s, int stride_h, int stride_w, int pad_h, int pad_w,
                                      int dil_h, int dil_w, const ftb_config* cfg, int* status,
                                      void* stream_v) {
-  using namespace ftb;
+  return ftb::dwconv_generic(in, weight, bias, out, nullptr, 0, n, c, h, w, factor, r, s, stride_h, stride_w, pad_h,
+                             pad_w, dil_h, dil_w, cfg, status, stream_v);
+}
+
+extern "C" int ftb_dwconv2d_nchw_f32_multi(const float* in, const float* weight, const float* bias,
+                                           float* const* out_dst, int num_dst, int64_t n, int64_t c, int64_t h,
+                                           int64_t w, int64_t factor, int64_t r, int64_t s, int stride_h,
+                                           int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                                           const ftb_config* cfg, int* status, void* stream_v) {
+  if (!out_dst || num_dst < 1 || num_dst > 8) return FTB_E_BAD_ARG;
+  for (int d = 0; d < num_dst; ++d)
+    if (!out_dst[d]) return FTB_E_BAD_ARG;
+  return ftb::dwconv_generic(in, weight, bias, out_dst[0], out_dst + 1, num_dst - 1, n, c, h, w, factor, r, s,
+                             stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, cfg, status, stream_v);
+}
+
+namespace ftb {
+static int dwconv_generic(const float* in, const float* weight, const float* bias, float* out, float* const* extra,
+                          int num_extra, int64_t n, int64_t c, int64_t h, int64_t w, int64_t factor, int64_t r,
+                          int64_t s, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                          const ftb_config* cfg, int* status, void* stream_v) {
   (void)status;  // no in-kernel waits: nothing to report
   if (!in || !weight || !out) return FTB_E_BAD_ARG;
   if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || factor <= 0 || r <= 0 || s <= 0) return FTB_E_BAD_ARG;
@@ -260,6 +301,12 @@ extern "C" int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const
   DwParams p;
   memset(&p, 0, sizeof(p));
   p.in = in; p.w = weight; p.bias = bias; p.out = out;
+  p.num_extra = num_extra;
+  for (int d = 0; d < num_extra; ++d) {
+    // the vector stores need every destination as aligned as the first
+    if ((reinterpret_cast<uintptr_t>(extra[d]) & 15) != (reinterpret_cast<uintptr_t>(out) & 15)) return FTB_E_BAD_ARG;
+    p.extra[d] = extra[d];
+  }
   p.N = static_cast<int>(n); p.C = static_cast<int>(c); p.H = static_cast<int>(h); p.W = static_cast<int>(w);
   p.F = static_cast<int>(factor); p.R = static_cast<int>(r); p.S = static_cast<int>(s);
   p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);
@@ -376,3 +423,4 @@ extern "C" int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const
   }
   return FTB_OK;
 }
+}  // namespace ftb

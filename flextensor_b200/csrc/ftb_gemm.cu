@@ -427,10 +427,8 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   const int out_esize = out == OUT_BF16 ? 2 : 4;
   bool store_ok = ((n * out_esize) & 15) == 0 && (reinterpret_cast<uintptr_t>(c) & 15) == 0;
   for (int d = 0; d < num_extra; ++d) store_ok = store_ok && (reinterpret_cast<uintptr_t>(extra_dst[d]) & 15) == 0;
-  {
-    const char* e = getenv("FTB_EPILOGUE");  // "direct" forces per-thread global stores (diagnostics)
-    if (e && strcmp(e, "direct") == 0) store_ok = false;
-  }
+  if (user && user->epilogue == 1) store_ok = false;  // per-thread stores asked for
+  if (user && (user->epilogue < 0 || user->epilogue > 1)) return FTB_E_BAD_CONFIG;
 
   const int num_sms = sm_count();
   const int num_kb = static_cast<int>((k + ki.kblk - 1) / ki.kblk);
@@ -485,6 +483,7 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   // split-K goes through the staged epilogue as bulk fp32 reduce-adds (one destination only)
   p.tma_store = (store_ok && p.bn % p.slab_cols == 0 &&
                  (p.split_k == 1 || (out == OUT_F32 && num_extra == 0))) ? 1 : 0;
+  p.diag = user ? user->reserved[0] : 0;
   p.num_dst = 1 + num_extra;
   if (num_extra > 0 && !p.tma_store) return FTB_E_UNSUPPORTED;  // several destinations only through bulk stores
 
@@ -570,12 +569,14 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
 }
 
 // ------------------------------------------------------------------ conv2d as implicit GEMM
-// Workspace layout: [input as N,H,W,Cp floats][weights as K, R*S*cchunks*32 floats],
-// Cp = C rounded up to 4 (TMA pitch rule), both regions 1024-byte aligned.
+// Workspace layout: [input as N,H,W,Cp floats][weights as K, R*S*cchunks*32 floats], both regions
+// 1024-byte aligned.  Cp = C rounded up to 4 (TMA pitch rule); with groups, every group's channels
+// are padded to a multiple of 4 (`cgp`) and Cp = groups * cgp, so that each group starts on a
+// 16-byte boundary whatever the number of channels per group.
 static int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
 struct ConvWs {
-  int64_t cp, cchunks, in_bytes, w_bytes;
+  int64_t cp, cgp, cchunks, in_bytes, w_bytes;
 };
 // Shapes that run as a 1x1 conv over their im2col form (conv_im2col_kernel).
 static bool conv_small_c(int64_t c, int64_t r, int64_t s, int64_t groups) {
@@ -585,7 +586,8 @@ static ConvWs conv_ws(int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int
                       int64_t groups) {
   ConvWs ws;
   const int64_t cg = c / groups;
-  ws.cp = round_up(c, 4);
+  ws.cgp = round_up(cg, 4);
+  ws.cp = groups > 1 ? groups * ws.cgp : round_up(c, 4);
   ws.cchunks = (cg + 31) / 32;
   ws.in_bytes = round_up(n * h * w * ws.cp * 4, 1024);
   ws.w_bytes = round_up(k * r * s * ws.cchunks * 32 * 4, 1024);
@@ -674,7 +676,7 @@ __global__ void __launch_bounds__(256)
 conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt, float* __restrict__ in_nhwc,
                     float* __restrict__ w_packed, int N, int C, int HW, int Cp, int K, int Cg, int RS,
                     int cchunks, int hw_tiles, int c_tiles, int in_blocks, int w_blocks, float* __restrict__ zero,
-                    long long zero_n, int plane, int sub_q, int sub_row, int sub_col) {
+                    long long zero_n, int plane, int sub_q, int sub_row, int sub_col, int cgp) {
   __shared__ __align__(16) float tile[kPreCh][kPrePx + 1];
   // The conv kernel that follows is launched as a programmatic dependent: it may set itself up
   // (barriers, tensor memory, descriptor fetch) while this grid runs, and waits for this grid's
@@ -706,7 +708,15 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
     // load: thread -> (channel, 4 pixels)
     for (int i = threadIdx.x; i < kPreCh * (kPrePx / 4); i += 256) {
       const int ch = i / (kPrePx / 4), q = (i % (kPrePx / 4)) * 4;
-      const int c = c0 + ch, px = p0 + q;
+      const int px = p0 + q;
+      // Channel of the source for channel c0 + ch of the copy.  With groups (cgp > 0) the copy pads
+      // every group to cgp channels: copy channel g * cgp + j is source channel g * Cg + j for
+      // j < Cg and zero padding otherwise.
+      int c = c0 + ch;
+      if (cgp > 0) {
+        const int g = c / cgp, j = c - g * cgp;
+        c = (j < Cg) ? g * Cg + j : C;
+      }
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (c < C && px < HW && sub_q > 0) {
         const float* cp_ = src + static_cast<long long>(c) * plane;
@@ -801,7 +811,7 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
 static int conv_prepass(const float* in, const float* weight, float* in_nhwc, float* w_packed, int64_t n, int64_t c,
                         int64_t h, int64_t w, int64_t k, int64_t cg, int64_t r, int64_t s, const ConvWs& ws,
                         int num_sms, void* stream_v, float* zero = nullptr, long long zero_n = 0, int sub_q = 0,
-                        int sub_p = 0, int sub_sh = 1, int sub_sw = 1) {
+                        int sub_p = 0, int sub_sh = 1, int sub_sw = 1, bool grouped = false) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   // sub_q > 0: keep sub_p x sub_q pixels of every plane, every sub_sh-th row and sub_sw-th column
   const int plane = static_cast<int>(h * w);
@@ -821,7 +831,8 @@ static int conv_prepass(const float* in, const float* weight, float* in_nhwc, fl
   conv_prepass_kernel<<<in_blocks + w_blocks + z_blocks, 256, 0, stream>>>(
       in, weight, in_nhwc, w_packed, static_cast<int>(n), static_cast<int>(c), HW, static_cast<int>(ws.cp),
       static_cast<int>(k), static_cast<int>(cg), static_cast<int>(r * s), static_cast<int>(ws.cchunks), hw_tiles,
-      c_tiles, in_blocks, w_blocks, zero, zero_n, plane, sub_q, sub_sh * static_cast<int>(w), sub_sw);
+      c_tiles, in_blocks, w_blocks, zero, zero_n, plane, sub_q, sub_sh * static_cast<int>(w), sub_sw,
+      grouped ? static_cast<int>(ws.cgp) : 0);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -995,7 +1006,6 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   int rc = device_ok();
   if (rc) return rc;
   const int64_t cg = c / groups, kg = k / groups;
-  if (groups > 1 && (cg % 4)) return FTB_E_UNSUPPORTED;  // group base must stay 16-byte aligned
   const ConvWs ws = conv_ws(n, c, h, w, k, r, s, groups);
   if (!workspace || workspace_bytes < static_cast<size_t>(ws.in_bytes + ws.w_bytes)) return FTB_E_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return FTB_E_WORKSPACE;
@@ -1146,22 +1156,20 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   // and boxes) and the staging buffers fit beside the chosen pipeline depth.
   bool staged = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && Q % 4 == 0 && tile_w % 4 == 0 &&
                 (P * Q * 4) % 16 == 0 && (groups == 1 || (kg * P * Q * 4) % 16 == 0);
-  {
-    const char* e = getenv("FTB_EPILOGUE");  // "direct" forces per-thread global stores (diagnostics)
-    if (e && strcmp(e, "direct") == 0) staged = false;
-  }
+  if (user && user->epilogue == 1) staged = false;  // per-thread stores asked for
+  if (user && (user->epilogue < 0 || user->epilogue > 1)) return FTB_E_BAD_CONFIG;
   // One wave of tiles or less, knobs left open: pick tile width and reduction split together by
   // what a CTA has to stage and issue (same cost model as pick_small_f32: a short tile list is
   // bound by per-CTA L2 traffic and MMA chain, not by latency).
   ftb_config tuned;
   bool conv_tuned = false;
-  if (groups == 1 && (!user || (user->tile_n == 0 && user->cluster == 0 && user->split_k == 0)) &&
-      tiles_m * ((kg + 127) / 128) <= num_sms) {
+  if ((!user || (user->tile_n == 0 && user->cluster == 0 && user->split_k == 0)) &&
+      groups * tiles_m * ((kg + 127) / 128) <= num_sms) {
     double best = 1e30;
     int best_bn = 0, best_split = 1;
     for (int bn = 32; bn <= 256; bn *= 2) {
       if (bn > 32 && bn >= 2 * kg) break;  // wider than the output channels: pure padding
-      const long long tiles = tiles_m * ((kg + bn - 1) / bn);
+      const long long tiles = groups * tiles_m * ((kg + bn - 1) / bn);
       if (tiles > num_sms) continue;
       for (int split = 1; split <= 32 && split <= num_kb; ++split) {
         if (num_kb % split) continue;
@@ -1190,19 +1198,19 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   }
   rc = FTB_E_BAD_CONFIG;
   if (staged)
-    rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg,
+    rc = resolve_config(user, ki, split3, 0, !split3, groups, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg,
                         kEpilogueStaging);
   if (rc) {
     staged = false;
-    rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg);
+    rc = resolve_config(user, ki, split3, 0, !split3, groups, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg);
   }
   if (rc) return rc;
   const bool pair = cfg.cluster == 2;
   const long long tiles_m_launch = pair ? (tiles_m + 1) / 2 : tiles_m;
-  if (!conv_tuned && (!user || user->split_k == 0) && groups == 1) {
+  if (!conv_tuned && (!user || user->split_k == 0)) {
     // A short tile list leaves SMs idle: split the reduction so that about all SMs get work (the
     // partial sums meet in global memory through bulk reduce-adds into the zeroed result).
-    const long long tiles = tiles_m_launch * ((kg + cfg.tile_n - 1) / cfg.tile_n);
+    const long long tiles = groups * tiles_m_launch * ((kg + cfg.tile_n - 1) / cfg.tile_n);
     int want = static_cast<int>((num_sms / (pair ? 2 : 1)) / (tiles > 0 ? tiles : 1));
     if (want > 32) want = 32;
     int pick = 1;
@@ -1239,16 +1247,19 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   } else {
     rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h_in, w_in, k, cg, r, s, ws, num_sms, stream_v,
                       cfg.split_k > 1 ? out : nullptr, n * k * P * Q, subsample ? static_cast<int>(Q) : 0,
-                      static_cast<int>(P), sub_sh, sub_sw);
+                      static_cast<int>(P), sub_sh, sub_sw, groups > 1);
     if (rc) return rc;
   }
-  for (int g = 0; g < groups; ++g) {
+  // One launch for all groups: a tile's batch coordinate is its group, and the tensor maps of
+  // the operands and of the result carry a group dimension.
+  {
     UmmaParams p;
     memset(&p, 0, sizeof(p));
     p.M = static_cast<int>(tiles_m) * kTileM;
     p.N = static_cast<int>(kg);
     p.K = num_kb * ki.kblk;
-    p.batch = 1;
+    p.batch = groups;
+    p.conv_groups = groups;
     p.bn = cfg.tile_n;
     p.stages = cfg.stages;
     p.num_kb = num_kb;
@@ -1274,9 +1285,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.a_layout = 2;
     p.pair_m = pair ? 2 * kTileM : kTileM;
     p.conv = 1;
-    p.pdl = (g == 0) ? 1 : 0;  // the first launch directly follows the layout pass
+    p.pdl = 1;  // directly follows the layout pass
     p.conv_ktot = static_cast<int>(k);
-    p.conv_koff = static_cast<int>(g * kg);
+    p.conv_koff = 0;
     p.C = out;
     p.bias = bias;
     p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);
@@ -1288,28 +1299,41 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     if (!p.status) return FTB_E_CUDA;
 
     CUtensorMap ta, tb;
-    {
-      // (c, w, h, n) view of the channels-last copy; a group sees its own Cg channels.
-      uint64_t dims[4] = {static_cast<uint64_t>(groups > 1 ? cg : wsx.cp), static_cast<uint64_t>(w),
+    if (groups > 1) {
+      // (c in group, group, w, h, n) view of the channels-last copy: a group's channels beyond Cg
+      // (padding of the copy, or the next group) lie outside dimension 0 and read as zeros.
+      uint64_t dims[5] = {static_cast<uint64_t>(cg), static_cast<uint64_t>(groups), static_cast<uint64_t>(w),
+                          static_cast<uint64_t>(h), static_cast<uint64_t>(n)};
+      uint64_t strides[4] = {static_cast<uint64_t>(wsx.cgp) * 4, static_cast<uint64_t>(wsx.cp) * 4,
+                             static_cast<uint64_t>(w) * wsx.cp * 4, static_cast<uint64_t>(h) * w * wsx.cp * 4};
+      uint32_t box[5] = {static_cast<uint32_t>(ki.kblk), 1, static_cast<uint32_t>(tile_w * stride_w),
+                         static_cast<uint32_t>(tile_h * stride_h), static_cast<uint32_t>(tile_imgs)};
+      uint32_t es[5] = {1, 1, static_cast<uint32_t>(stride_w), static_cast<uint32_t>(stride_h), 1};
+      rc = make_tmap(&ta, ki.dt, 5, in_nhwc, dims, strides, box, es);
+      if (rc) return rc;
+    } else {
+      // (c, w, h, n) view of the channels-last copy
+      uint64_t dims[4] = {static_cast<uint64_t>(wsx.cp), static_cast<uint64_t>(w),
                           static_cast<uint64_t>(h), static_cast<uint64_t>(n)};
       uint64_t strides[3] = {static_cast<uint64_t>(wsx.cp) * 4, static_cast<uint64_t>(w) * wsx.cp * 4,
                              static_cast<uint64_t>(h) * w * wsx.cp * 4};
       uint32_t box[4] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(tile_w * stride_w),
                          static_cast<uint32_t>(tile_h * stride_h), static_cast<uint32_t>(tile_imgs)};
       uint32_t es[4] = {1, static_cast<uint32_t>(stride_w), static_cast<uint32_t>(stride_h), 1};
-      rc = make_tmap(&ta, ki.dt, 4, in_nhwc + g * cg, dims, strides, box, es);
+      rc = make_tmap(&ta, ki.dt, 4, in_nhwc, dims, strides, box, es);
       if (rc) return rc;
     }
     {
+      // packed filter [group][k in group][taps x channel chunks x 32]
       const uint64_t kdim = static_cast<uint64_t>(num_kb) * ki.kblk;
-      uint64_t dims[3] = {kdim, static_cast<uint64_t>(kg), 1};
+      uint64_t dims[3] = {kdim, static_cast<uint64_t>(kg), static_cast<uint64_t>(groups)};
       uint64_t strides[2] = {kdim * 4, kdim * 4 * kg};
       uint32_t box[3] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(p.b_rows), 1};
       const uint32_t ones[3] = {1, 1, 1};
-      rc = make_tmap(&tb, ki.dt, 3, w_packed + static_cast<uint64_t>(g) * kg * kdim, dims, strides, box, ones);
+      rc = make_tmap(&tb, ki.dt, 3, w_packed, dims, strides, box, ones);
       if (rc) return rc;
     }
-    const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.split_k;
+    const long long total = static_cast<long long>(p.batch) * p.tiles_m * p.tiles_n * p.split_k;
     if (total > 0x7fffffffll) return FTB_E_TOO_LARGE;
     int ctas = cfg.ctas > 0 ? cfg.ctas : num_sms;
     if (pair) {
@@ -1321,19 +1345,32 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     }
     StoreMaps tc;
     memset(&tc, 0, sizeof(tc));
-    if (staged) {
-      // (w, h, channel, image) view of this group's planes of the NCHW result
+    if (staged && groups > 1) {
+      // (w, h, channel in group, group, image) view of the NCHW result: a box of 32 channels is
+      // clipped at the end of its group
       p.tma_store = 1;
       p.num_dst = 1;
-      uint64_t dims[4] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(kg),
+      uint64_t dims[5] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(kg),
+                          static_cast<uint64_t>(groups), static_cast<uint64_t>(n)};
+      uint64_t strides[4] = {static_cast<uint64_t>(Q) * 4, static_cast<uint64_t>(P) * Q * 4,
+                             static_cast<uint64_t>(kg) * P * Q * 4, static_cast<uint64_t>(k) * P * Q * 4};
+      uint32_t box[5] = {static_cast<uint32_t>(tile_w), static_cast<uint32_t>(tile_h), 32, 1,
+                         static_cast<uint32_t>(tile_imgs)};
+      const uint32_t ones[5] = {1, 1, 1, 1, 1};
+      rc = make_tmap(&tc.dst[0], ki.dt, 5, out, dims, strides, box, ones, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    } else if (staged) {
+      // (w, h, channel, image) view of the NCHW result
+      p.tma_store = 1;
+      p.num_dst = 1;
+      uint64_t dims[4] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(k),
                           static_cast<uint64_t>(n)};
       uint64_t strides[3] = {static_cast<uint64_t>(Q) * 4, static_cast<uint64_t>(P) * Q * 4,
                              static_cast<uint64_t>(k) * P * Q * 4};
       uint32_t box[4] = {static_cast<uint32_t>(tile_w), static_cast<uint32_t>(tile_h), 32,
                          static_cast<uint32_t>(tile_imgs)};
       const uint32_t ones[4] = {1, 1, 1, 1};
-      rc = make_tmap(&tc.dst[0], ki.dt, 4, out + static_cast<int64_t>(g) * kg * P * Q, dims, strides, box, ones,
-                     CU_TENSOR_MAP_SWIZZLE_NONE);
+      rc = make_tmap(&tc.dst[0], ki.dt, 4, out, dims, strides, box, ones, CU_TENSOR_MAP_SWIZZLE_NONE);
       if (rc) return rc;
     }
     rc = dispatch(KIND_TF32, OUT_F32, split3, pair, ta, tb, tc, p, ctas, stream);
@@ -1378,6 +1415,29 @@ int ftb_gemm_s8(const int8_t* a, const int8_t* b, int32_t* c, int64_t m, int64_t
                 int trans_a, int trans_b, const ftb_config* cfg, int* status, void* stream) {
   return ftb::gemm_generic(ftb::KIND_I8, ftb::OUT_S32, a, b, c, 1, m, n, k, trans_a, trans_b, cfg,
                            status, stream, nullptr, 0);
+}
+
+int ftb_debug_wait_profile(uint64_t* cycles, int reset) {
+#ifdef FTB_PROFILE_WAITS
+  if (!cycles) return FTB_E_BAD_ARG;
+  unsigned long long host[ftb::PROF_SLOTS];
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(host, ftb::g_wait_cycles, sizeof(host));
+  if (e == cudaSuccess && reset) {
+    unsigned long long zero[ftb::PROF_SLOTS] = {0};
+    e = cudaMemcpyToSymbol(ftb::g_wait_cycles, zero, sizeof(zero));
+  }
+  if (e != cudaSuccess) {
+    ftb::set_last_cuda_error(static_cast<int>(e));
+    return FTB_E_CUDA;
+  }
+  for (int i = 0; i < ftb::PROF_SLOTS; ++i) cycles[i] = host[i];
+  return FTB_OK;
+#else
+  (void)cycles;
+  (void)reset;
+  return FTB_E_UNSUPPORTED;
+#endif
 }
 
 size_t ftb_conv2d_workspace_bytes(int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r,

@@ -69,7 +69,9 @@ struct UmmaParams {
   int a_bcast;        // GEMM: every batch entry reads A of batch 0
   // implicit-GEMM conv geometry (conv != 0)
   int conv, P, Q, tile_h, tile_w, tiles_h, tiles_w, R, S, cchunks;
-  int conv_ktot, conv_koff;  // output channels of the whole conv / first channel of this group
+  int conv_ktot, conv_koff;  // output channels of the whole conv / first channel of this launch
+  int conv_groups;           // > 1: the batch coordinate of a tile is its group; operands and result are
+                             // addressed through tensor maps with a group dimension
   int conv_tiles;            // number of 128-pixel tiles (a CTA pair takes two consecutive ones)
   int tile_imgs;             // whole images per tile (> 1 only when an image has at most 64 output pixels)
   int n_imgs;                // images of the batch
@@ -79,6 +81,11 @@ struct UmmaParams {
   // TMA-store epilogue: tma_store != 0 stages 128-byte wide output slabs in shared memory and
   // writes each with one bulk tensor store per destination.
   int tma_store, num_dst, slab_cols;
+  // diagnostic builds (-DFTB_PROFILE_WAITS) only: bit 0 = the producer signals stages without
+  // loading them, bit 1 = the issuer releases stages without issuing MMAs, bit 2 = no producer at
+  // all and an issuer that neither waits for stages nor releases them: MMAs back to back (results
+  // are garbage; the timings tell whether the main loop is bound by the loads or by the tensor pipe)
+  int diag;
 };
 
 constexpr int kMaxDst = 8;
@@ -90,6 +97,31 @@ constexpr uint32_t kEpiBufBytes = kTileM * 128;  // one staged output slab: 128 
 struct StoreMaps {
   CUtensorMap dst[kMaxDst];
 };
+
+// Where the roles of a CTA wait (diagnostic builds only, -DFTB_PROFILE_WAITS): SM cycles spent inside
+// each kind of barrier wait and each role's whole loop, summed over the CTAs of every launch into
+// g_wait_cycles.  The product build compiles none of it.
+enum {
+  PROF_PRODUCER_EMPTY = 0,  // TMA producer waiting for a free stage
+  PROF_ISSUER_FULL = 1,     // MMA issuer waiting for a stage to land
+  PROF_ISSUER_TEMPTY = 2,   // MMA issuer waiting for the epilogue to hand an accumulator back
+  PROF_EPI_TFULL = 3,       // epilogue (warp 2) waiting for an accumulator to complete
+  PROF_PRODUCER_LOOP = 4,   // whole producer loop
+  PROF_ISSUER_LOOP = 5,     // whole issuer loop
+  PROF_EPI_LOOP = 6,        // whole epilogue loop of warp 2
+  PROF_CTAS = 7,            // CTAs that reported
+  PROF_SLOTS = 8
+};
+#ifdef FTB_PROFILE_WAITS
+__device__ unsigned long long g_wait_cycles[PROF_SLOTS];
+#define FTB_PROF_T0(var) const long long var = clock64()
+#define FTB_PROF_ADD(acc, var) (acc) += clock64() - (var)
+#define FTB_PROF_FLUSH(slot, acc) atomicAdd(&g_wait_cycles[slot], static_cast<unsigned long long>(acc))
+#else
+#define FTB_PROF_T0(var) do { } while (0)
+#define FTB_PROF_ADD(acc, var) do { } while (0)
+#define FTB_PROF_FLUSH(slot, acc) do { } while (0)
+#endif
 
 struct TileCoord {
   int b, m, n, ks;
@@ -199,10 +231,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t a_box_bytes = p.a_box_bytes, b_box_bytes = p.b_box_bytes;
       const uint32_t tx = a_boxes * a_box_bytes + b_boxes * b_box_bytes;
       const bool a_mn = p.a_mn != 0, b_mn = p.b_mn != 0, conv = p.conv != 0;
+      const bool grouped = conv && p.conv_groups > 1;  // grouped conv: a tile's batch coordinate is its group
       // In a pair every completion is reported to the leader's barrier.
       const uint32_t full_sig0 = PAIR ? map_to_cta(full0, 0) : full0;
       uint32_t s = 0, ph = 0, sa = smem_base;
       bool ok = true;
+      long long prof_wait = 0;
+      FTB_PROF_T0(prof_loop0);
       for (int t = unit; t < total_tiles && ok; t += units) {
         const TileCoord tc = decode_tile(p, t);
         const int kb0 = tc.ks * kb_per_split;
@@ -228,21 +263,40 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         int kc = kb0 * kblk;  // K coordinate of the block
         for (int kb = kb0; kb < kb1; ++kb, kc += kblk) {
+          FTB_PROF_T0(prof_w0);
+#ifdef FTB_PROFILE_WAITS
+          if (p.diag & 4) continue;
+#endif
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, &abort_flag)) {
             atomicOr(p.status, FTB_DEV_WAIT_EMPTY);
             abort_flag = 1;
             ok = false;
             break;
           }
+          FTB_PROF_ADD(prof_wait, prof_w0);
           const uint32_t sb = sa + kATileBytes;
           const uint32_t full = full_sig0 + 8 * s;
+#ifdef FTB_PROFILE_WAITS
+          if (p.diag & 4) continue;
+          if (p.diag & 1) {
+            if (cta_rank == 0) mbar_arrive(full0 + 8 * s);
+            sa += stage_bytes;
+            if (++s == stages) {
+              s = 0;
+              ph ^= 1u;
+              sa = smem_base;
+            }
+            continue;
+          }
+#endif
           if constexpr (PAIR) {
             // The leader arms the phase for the two equal halves.  (Bytes of the peer may be
             // reported before that; the phase still cannot complete until the leader's
             // own arrival.)
             if (cta_rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * tx);
             if (conv) {
-              tma_load_4d_pair(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
+              if (grouped) tma_load_5d_pair(sa, &tmap_a, full, cc * kblk, tc.b, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
+              else tma_load_4d_pair(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
               if (++cc == p.cchunks) {
                 cc = 0;
                 if (++ts == p.S) {
@@ -265,7 +319,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           } else {
             mbar_expect_tx(full, tx);
             if (conv) {
-              tma_load_4d(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
+              if (grouped) tma_load_5d(sa, &tmap_a, full, cc * kblk, tc.b, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
+              else tma_load_4d(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
               if (++cc == p.cchunks) {
                 cc = 0;
                 if (++ts == p.S) {
@@ -294,6 +349,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
+      long long prof_loop = 0;
+      FTB_PROF_ADD(prof_loop, prof_loop0);
+      FTB_PROF_FLUSH(PROF_PRODUCER_EMPTY, prof_wait);
+      FTB_PROF_FLUSH(PROF_PRODUCER_LOOP, prof_loop);
+      FTB_PROF_FLUSH(PROF_CTAS, 1);
+      (void)prof_wait; (void)prof_loop;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -310,13 +371,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t lo_enc = pair_bytes >> 4;  // (A_lo, B_lo) pair of a 3xTF32 stage
       const uint32_t ready0 = SPLIT3 ? split0 : full0;
       // Barriers the commits arrive on; in a pair both CTAs' copies are signalled.
-      const uint32_t empty_l = PAIR ? map_to_cta(empty0, 0) : empty0;
-      const uint32_t empty_r = PAIR ? map_to_cta(empty0, 1) : 0u;
-      const uint32_t tfull_l = PAIR ? map_to_cta(smem_u32(&bar_tfull[0]), 0) : smem_u32(&bar_tfull[0]);
-      const uint32_t tfull_r = PAIR ? map_to_cta(smem_u32(&bar_tfull[0]), 1) : 0u;
+      const uint32_t tfull0 = smem_u32(&bar_tfull[0]);
       uint32_t s = 0, ph = 0, a_lo = a_lo0;
       int local = 0;
       bool ok = true;
+      long long prof_full = 0, prof_tempty = 0;
+      FTB_PROF_T0(prof_loop0);
+      // The issuer is one in-order thread feeding a shallow MMA queue: every cycle it spends between
+      // two MMAs on something else shows up as an idle tensor pipe (measured: about 80 cycles per
+      // barrier wait, about 80 per commit).  So it asks about the NEXT stage before it issues the
+      // MMAs of the current one; the probe's latency then runs under the MMA issue.
+      uint32_t ready = 0;
       for (int t = unit; t < total_tiles && ok; t += units, ++local) {
         const int ks = (p.split_k > 1) ? (t % p.split_k) : 0;
         const int kb0 = ks * kb_per_split;
@@ -324,41 +389,65 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // Plain tiles alternate between the two accumulators; a wide tile owns both (one per half).
         const uint32_t acc = WIDE ? 0u : (local & 1);
         const uint32_t aph = WIDE ? (local & 1u) : ((local >> 1) & 1u);
+        FTB_PROF_T0(prof_t0);
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, &abort_flag)) {
           atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
           abort_flag = 1;
           break;
         }
+        FTB_PROF_ADD(prof_tempty, prof_t0);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
         uint32_t accumulate = 0;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(ready0 + 8 * s, ph, &abort_flag)) {
+          FTB_PROF_T0(prof_f0);
+#ifdef FTB_PROFILE_WAITS
+          if (!(p.diag & 4))
+#endif
+          if (!ready && !mbar_wait(ready0 + 8 * s, ph, &abort_flag)) {
             atomicOr(p.status, SPLIT3 ? FTB_DEV_WAIT_XFORM : FTB_DEV_WAIT_FULL);
             abort_flag = 1;
             ok = false;
             break;
           }
+          FTB_PROF_ADD(prof_full, prof_f0);
           tc_fence_after();
+          {
+            // has the next stage of the ring landed already?  (answer used in the next iteration)
+            const uint32_t sn = (s + 1 == stages) ? 0u : s + 1;
+            ready = mbar_test_wait(ready0 + 8 * sn, sn == 0 ? (ph ^ 1u) : ph);
+          }
           const uint32_t b_lo = a_lo + b_off + b_lbo_delta;
+#ifdef FTB_PROFILE_WAITS
+          if ((p.diag & 2) && kb > kb0 && kb + 1 < kb1) {
+            if constexpr (PAIR) tc_commit_pair_both(empty0 + 8 * s);
+            else tc_commit(empty0 + 8 * s);
+            a_lo += stage_enc;
+            if (++s == stages) {
+              s = 0;
+              ph ^= 1u;
+              a_lo = a_lo0;
+            }
+            continue;
+          }
+#endif
           if constexpr (WIDE) {
             const bool last = kb + 1 == kb1;
 #pragma unroll
             for (int k = 0; k < kMmaPerKb; ++k)
               umma<KIND, PAIR>(d_tmem, a_lo + k * a_k, a_hi, b_lo + k * b_k, b_hi, idesc, k > 0 ? 1u : accumulate);
             // the first half is complete one K block's worth of MMAs before the second
-            if (last) {
-              tc_commit_pair(tfull_l);
-              tc_commit_pair(tfull_r);
-            }
+            if (last) tc_commit_pair_both(tfull0);
             if (kb == kb0) {
               // the second half may still be draining the previous tile
+              FTB_PROF_T0(prof_t1);
               if (!mbar_wait(smem_u32(&bar_tempty[1]), aph ^ 1u, &abort_flag)) {
                 atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
                 abort_flag = 1;
                 ok = false;
                 break;
               }
+              FTB_PROF_ADD(prof_tempty, prof_t1);
               tc_fence_after();
             }
             const uint32_t b_half = b_lo + p.b_half_enc;
@@ -381,11 +470,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           // Free the stage (in both CTAs of a pair) once these MMAs have read it.
+#ifdef FTB_PROFILE_WAITS
+          if (p.diag & 4) continue;
+#endif
           if constexpr (PAIR) {
-            tc_commit_pair(empty_l + 8 * s);
-            tc_commit_pair(empty_r + 8 * s);
+            tc_commit_pair_both(empty0 + 8 * s);
           } else {
-            tc_commit(empty_l + 8 * s);
+            tc_commit(empty0 + 8 * s);
           }
           a_lo += stage_enc;
           if (++s == stages) {
@@ -396,16 +487,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         if (ok) {
           if constexpr (WIDE) {
-            tc_commit_pair(tfull_l + 8);
-            tc_commit_pair(tfull_r + 8);
+            tc_commit_pair_both(tfull0 + 8);
           } else if constexpr (PAIR) {
-            tc_commit_pair(tfull_l + 8 * acc);
-            tc_commit_pair(tfull_r + 8 * acc);
+            tc_commit_pair_both(tfull0 + 8 * acc);
           } else {
-            tc_commit(tfull_l + 8 * acc);
+            tc_commit(tfull0 + 8 * acc);
           }
         }
       }
+      long long prof_loop = 0;
+      FTB_PROF_ADD(prof_loop, prof_loop0);
+      FTB_PROF_FLUSH(PROF_ISSUER_FULL, prof_full);
+      FTB_PROF_FLUSH(PROF_ISSUER_TEMPTY, prof_tempty);
+      FTB_PROF_FLUSH(PROF_ISSUER_LOOP, prof_loop);
+      (void)prof_full; (void)prof_tempty; (void)prof_loop;
     }
     __syncwarp();
   } else if (warp < 6 || (WIDE && p.tma_store != 0)) {
@@ -424,6 +519,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t slab_seq = 0;
     int local = 0;
     bool alive = true;
+    long long prof_tfull = 0;
+    FTB_PROF_T0(prof_loop0);
     for (int t = unit; t < total_tiles && alive; t += units, ++local) {
       const TileCoord tc = decode_tile(p, t);
      // a wide tile is drained in two passes, one per accumulator half
@@ -432,7 +529,41 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t acc = WIDE ? static_cast<uint32_t>(half) : (local & 1);
       const uint32_t aph = WIDE ? (local & 1u) : ((local >> 1) & 1u);
       const bool has_work = tc.ks * kb_per_split < num_kb;  // a split past the K range adds nothing
+      FTB_PROF_T0(prof_e0);
       bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull[acc]), aph, &abort_flag));
+      FTB_PROF_ADD(prof_tfull, prof_e0);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kAccStride;
+      // A wide tile's accumulator half is wanted back by the MMA issuer as soon as possible (the
+      // next tile cannot start before it is free), so a warp first pulls all of its group's 128
+      // columns of the half into registers (every other slab: two slabs of 64 columns for a 16-bit
+      // result, four of 32 for a 32-bit one) and hands the accumulator back - before the warps
+      // agree on anything - and only then converts, stages and stores, under the next tile's main loop.
+      uint32_t wide_v[WIDE ? 4 : 1][32];
+      if constexpr (WIDE) {
+        if (p.tma_store && got) {
+          tc_fence_after();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int col = (OUT == OUT_BF16) ? grp * 64 + (q >> 1) * 128 + (q & 1) * 32 : grp * 32 + q * 64;
+            tmem_ld_32x32(taddr + col, wide_v[q]);
+          }
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_sig0 + 8 * acc);
+          if constexpr (OUT == OUT_BF16) {
+            // a 16-bit result is rounded and packed right away: half the registers to carry
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(wide_v[q][2 * j]),
+                                                          __uint_as_float(wide_v[q][2 * j + 1]));
+                wide_v[q][j] = *reinterpret_cast<uint32_t*>(&h2);
+              }
+          }
+        }
+      }
       // The staged epilogue synchronises the four warps with each other: they must agree.
       if (p.tma_store) got = named_barrier_all(bar_vote_id, 128, got);
       if (!got) {
@@ -444,7 +575,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         break;
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kAccStride;
       const int n0 = tc.n * p.bn;
       // problem column of accumulator column c (a slab of 32 or 64 columns never straddles the
       // boundary between the two CTAs' parts of a wide tile)
@@ -455,6 +585,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       long long row_off;  // element offset of (row, column 0 of the problem)
       long long col_stride = 1;
       int conv_mt = 0, conv_tw = 0, conv_th = 0, conv_img = 0;
+      // first output channel of this tile's group (grouped conv: group = batch coordinate)
+      const int koff = p.conv ? p.conv_koff + tc.b * N : 0;
       if (p.conv) {
         const int mt = PAIR ? tc.m * 2 + static_cast<int>(cta_rank) : tc.m;
         const int tw = mt % p.tiles_w;
@@ -470,7 +602,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int ow = tw * p.tile_w + rr % p.tile_w;
         row_ok = mt < p.conv_tiles && row < p.tile_imgs * px_per_img && img < p.n_imgs && oh < p.P && ow < p.Q;
         col_stride = static_cast<long long>(p.P) * p.Q;
-        row_off = (static_cast<long long>(img) * p.conv_ktot + p.conv_koff) * col_stride +
+        row_off = (static_cast<long long>(img) * p.conv_ktot + koff) * col_stride +
                   static_cast<long long>(oh) * p.Q + ow;
       } else {
         const int gm = tc.m * p.pair_m + static_cast<int>(cta_rank) * kTileM + row;
@@ -513,7 +645,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               float x = __uint_as_float(v[j]);
-              if (add_bias && n0 + c + j < N) x += p.bias[p.conv_koff + n0 + c + j];
+              if (add_bias && n0 + c + j < N) x += p.bias[koff + n0 + c + j];
               st_shared_f32(buf + static_cast<uint32_t>(j) * ch_stride + row_byte, x);
             }
           }
@@ -521,10 +653,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           named_barrier_sync(1, 128);
           if (leader) {
             if (tile_ok && n0 + c < N) {
-              if (p.split_k > 1)
+              if (p.conv_groups > 1) {
+                if (p.split_k > 1)
+                  tma_reduce_add_5d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, tc.b, conv_img);
+                else
+                  tma_store_5d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, tc.b, conv_img);
+              } else if (p.split_k > 1) {
                 tma_reduce_add_4d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, conv_img);
-              else
+              } else {
                 tma_store_4d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, conv_img);
+              }
             }
             bulk_commit_group();
           }
@@ -538,6 +676,61 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int m0 = tc.m * p.pair_m + static_cast<int>(cta_rank) * kTileM;
         const uint32_t swz = static_cast<uint32_t>(row & 7);
         const int c_step = WIDE ? 2 * slab_cols : slab_cols;
+        if constexpr (WIDE) {
+          // the accumulator columns are already in registers (wide_v) and the accumulator handed back
+          auto& v = wide_v;
+          float bias = 0.0f;
+          if constexpr (OUT == OUT_F32) {
+            if (p.bias != nullptr && tc.ks == 0 && m0 + row < p.M) bias = p.bias[m0 + row];
+          }
+          const uint32_t buf = epi_base + static_cast<uint32_t>(grp) * kEpiBufBytes;
+          const uint32_t row_addr = buf + static_cast<uint32_t>(row) * 128u;
+          constexpr int kSlabs = (OUT == OUT_BF16) ? 2 : 4;
+#pragma unroll
+          for (int i = 0; i < kSlabs; ++i) {
+            const int c = grp * slab_cols + i * c_step;
+            // the store that used this group's buffer before must have finished reading it
+            if (leader) bulk_wait_group_read<0>();
+            named_barrier_sync(bar_sync_id, 128);
+            if constexpr (OUT == OUT_BF16) {
+              // v[2 * i + part][0..15] hold 32 columns as packed pairs
+#pragma unroll
+              for (int part = 0; part < 2; ++part) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint32_t chunk = static_cast<uint32_t>(part * 4 + j);
+                  st_shared_v4(row_addr + ((chunk ^ swz) << 4), v[2 * i + part][4 * j], v[2 * i + part][4 * j + 1],
+                               v[2 * i + part][4 * j + 2], v[2 * i + part][4 * j + 3]);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  w[q] = v[i][4 * j + q];
+                  if constexpr (OUT == OUT_F32) w[q] = __float_as_uint(__uint_as_float(w[q]) + bias);
+                }
+                st_shared_v4(row_addr + ((static_cast<uint32_t>(j) ^ swz) << 4), w[0], w[1], w[2], w[3]);
+              }
+            }
+            fence_proxy_async_smem();  // the slab must be visible to the bulk-copy engine
+            named_barrier_sync(bar_sync_id, 128);
+            if (leader) {
+              if (has_work && ncol(c) < N) {
+                if (p.split_k > 1) {
+                  tma_reduce_add_3d(&tmap_c.dst[0], buf, ncol(c), m0, tc.b);
+                } else {
+                  for (int d = 0; d < p.num_dst; ++d) tma_store_3d(&tmap_c.dst[d], buf, ncol(c), m0, tc.b);
+                }
+              }
+              bulk_commit_group();
+            }
+          }
+          slab_seq += kSlabs;
+          continue;
+        }
         for (int c = grp * slab_cols; c < bn; c += c_step, ++slab_seq) {
           // plain tiles alternate between the two buffers; a group of a wide tile owns one
           const uint32_t buf = epi_base + (WIDE ? static_cast<uint32_t>(grp) : (slab_seq & 1u)) * kEpiBufBytes;
@@ -634,7 +827,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int n = nbase + j;
             if (n < N) {
               float x = __uint_as_float(v[j]);
-              if (p.bias != nullptr && tc.ks == 0) x += p.bias[p.conv_koff + n];
+              if (p.bias != nullptr && tc.ks == 0) x += p.bias[koff + n];
               float* dst = out + row_off + n * col_stride;
               if (p.split_k > 1) atomicAdd(dst, x);
               else *dst = x;
@@ -690,6 +883,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
      }
     }
+    if (warp == 2 && lane == 0) {
+      long long prof_loop = 0;
+      FTB_PROF_ADD(prof_loop, prof_loop0);
+      FTB_PROF_FLUSH(PROF_EPI_TFULL, prof_tfull);
+      FTB_PROF_FLUSH(PROF_EPI_LOOP, prof_loop);
+      (void)prof_loop;
+    }
+    (void)prof_tfull;
     // Shared memory must outlive the bulk stores' reads of it.  Their global writes are part of
     // this grid's memory operations and are complete when the grid is; only stores into a peer
     // GPU's memory (several destinations) are waited for in full before the CTA exits.

@@ -10,9 +10,11 @@ one per GPU (``GpuPoolMeasurer``), a worker that exceeds the timeout is killed a
 replaced, and its candidate scores ``inf``.  ``build_and_eval`` and ``master_routine``
 keep their reference signatures.
 """
+import importlib
 import multiprocessing as _mp
 import os
 import queue as _queue
+import sys
 import time
 
 mp = _mp.get_context("spawn")
@@ -110,38 +112,114 @@ def _evaluate(s, bufs, target, dev_id, number=1, q=None):
     return cost
 
 
+class Job(tuple):
+    """One candidate, ``(task_key, Config, op_pos)`` when unpacked, plus what a worker in
+    another process needs beside it: the fp32 ``precision`` the plan is to be built with and,
+    for a task that was registered at run time, ``task_spec`` - what rebuilds the task there.
+
+    The reference forks its measurement children, which therefore inherit ``TASK_TABLE``
+    (flextensor/scheduler.py:715-752); workers here are spawned (a forked child cannot use CUDA),
+    so a task the parent registered after import has to travel with the job.
+    """
+
+    def __new__(cls, task_key, config, op_pos, precision=None, task_spec=None):
+        self = super().__new__(cls, (task_key, config, op_pos))
+        self.precision = precision
+        self.task_spec = task_spec
+        return self
+
+    def __reduce__(self):
+        return (Job, (self[0], self[1], self[2], self.precision, self.task_spec))
+
+
+def task_spec(task):
+    """``(category, name, module, function, args, target, dev_id)`` of a task whose builder is a
+    module-level function, or None when the builder cannot be named (a lambda, a closure): such
+    a task can only be measured in the registering process."""
+    func = task.func
+    module, name = getattr(func, "__module__", None), getattr(func, "__qualname__", "")
+    if not module or not name or "<" in name or "." in name:
+        return None
+    category = task.category
+    prefix, suffix = category + "_", "_%s_%s(%d)" % (task.args, task.target, task.dev_id)
+    if not (task.key.startswith(prefix) and task.key.endswith(suffix)):
+        return None
+    task_name = task.key[len(prefix):len(task.key) - len(suffix)]
+    return (category, task_name, module, name, tuple(task.args), task.target, task.dev_id)
+
+
+def make_job(task_key, config, op_pos, precision=None):
+    """A ``Job`` for a registered task, carrying the task's spec so that any worker can resolve it."""
+    from .task import TASK_TABLE
+    task = TASK_TABLE.get(task_key)
+    return Job(task_key, config, op_pos, precision, task_spec(task) if task is not None else None)
+
+
+def resolve_task(job):
+    """The task of a job in this process: from ``TASK_TABLE``, or rebuilt from the job's spec and
+    registered (a worker's table only holds the import-time registrations)."""
+    from .task import TASK_TABLE, Task, register_task
+    task_key = job[0]
+    task = TASK_TABLE.get(task_key)
+    if task is not None:
+        return task
+    spec = getattr(job, "task_spec", None)
+    if spec is None:
+        raise KeyError("task %r is not registered in this process and the job carries no way to rebuild it "
+                       "(its builder must be a module-level function)" % (task_key,))
+    category, name, module, func_name, args, target, dev_id = spec
+    func = getattr(importlib.import_module(module), func_name)
+    task = Task(category, name, func, tuple(args), target, dev_id)
+    if task.key != task_key:
+        raise KeyError("job spec rebuilds %r, not %r" % (task.key, task_key))
+    register_task(task)
+    return task
+
+
 def _evaluate_job(job, number, dev_id):
     """One candidate: (task_key, Config, op_pos) -> milliseconds on GPU ``dev_id``."""
     from .scheduler import schedule_with_config
-    from .task import TASK_TABLE
     task_key, config, op_pos = job
-    task = TASK_TABLE[task_key]
-    s, bufs = schedule_with_config(task_key, config, op_pos=op_pos)
+    task = resolve_task(job)
+    s, bufs = schedule_with_config(task_key, config, op_pos=op_pos, precision=getattr(job, "precision", None))
     return build_and_eval(None, s, bufs, task.target, dev_id, None, number)
 
 
-def _worker_main(dev_id, jobs, results):
+def _load_evaluate(evaluate):
+    """``"module:function"`` -> the function (the evaluator a worker runs per job)."""
+    if evaluate is None:
+        return _evaluate_job
+    module, _, name = evaluate.partition(":")
+    return getattr(importlib.import_module(module), name)
+
+
+def _worker_main(dev_id, jobs, results, evaluate=None, sys_path=None):
     """Worker process: pinned to one GPU, serves jobs until it receives ``None``."""
     os.environ.setdefault("CUDA_DEVICE_ORDER", "PCI_BUS_ID")
+    for entry in reversed(sys_path or []):
+        if entry not in sys.path:
+            sys.path.insert(0, entry)
     from . import task as _task  # noqa: F401  (fills TASK_TABLE in this process)
+    run = _load_evaluate(evaluate)
     while True:
         item = jobs.get()
         if item is None:
             return
         job_id, job, number = item
         try:
-            value = _evaluate_job(job, number, dev_id)
+            value = run(job, number, dev_id)
         except Exception as exc:  # sent as text: any exception type survives the queue
             value = RuntimeError("%s: %s" % (type(exc).__name__, exc))
         results.put((job_id, value))
 
 
 class _Worker(object):
-    def __init__(self, dev_id):
+    def __init__(self, dev_id, evaluate=None):
         self.dev_id = dev_id
         self.jobs = mp.Queue()
         self.results = mp.Queue()
-        self.proc = mp.Process(target=_worker_main, args=(dev_id, self.jobs, self.results), daemon=True)
+        self.proc = mp.Process(target=_worker_main, args=(dev_id, self.jobs, self.results, evaluate, list(sys.path)),
+                               daemon=True)
         self.proc.start()
 
     def stop(self, kill=False):
@@ -165,7 +243,13 @@ class GpuPoolMeasurer(object):
     (``parallel == 1`` is the serial re-measurement of the search's leaders).
     """
 
-    def __init__(self, devices=None, startup_timeout=120.0):
+    def __init__(self, devices=None, startup_timeout=120.0, evaluate=None):
+        """``evaluate``: ``"module:function"`` naming what a worker runs per job, called as
+        ``function(job, number, dev_id) -> milliseconds`` (default: plan, build and time the
+        candidate on the worker's GPU).  Host-side tests of the pool's failure handling pass
+        evaluators that sleep, raise or exit without touching a GPU."""
+        self.evaluate = evaluate
+        self.replaced = 0  # workers killed after a timeout or found dead, and replaced
         if devices is None:
             import torch
             devices = list(range(torch.cuda.device_count()))
@@ -180,7 +264,7 @@ class GpuPoolMeasurer(object):
     def _worker(self, dev_id):
         w = self.workers.get(dev_id)
         if w is None or not w.proc.is_alive():
-            w = _Worker(dev_id)
+            w = _Worker(dev_id, self.evaluate)
             self.workers[dev_id] = w
             self.fresh.add(dev_id)
         return w
@@ -212,6 +296,7 @@ class GpuPoolMeasurer(object):
                         w.stop(kill=True)
                         del self.workers[dev]
                         del running[dev]
+                        self.replaced += 1
                         progressed = True
                     continue
                 self.fresh.discard(dev)

@@ -28,6 +28,8 @@ def optimize(category, name, func, shapes, args_of, slevel=4, rlevel=3, target="
             kwargs["measurer"] = measurer
         if precision is not None:
             kwargs["precision"] = precision
+        if use_model:
+            kwargs["use_model"] = True
         beg = time.time()
         s, bufs, configs = schedule(task.key, slevel=slevel, rlevel=rlevel, op_trial=trials, timeout=timeout,
                                     op_stop=trials // 2, method=method, parallel=parallel, number=10, **kwargs)

@@ -21,6 +21,7 @@ from collections import deque
 
 import numpy as np
 
+from .measure import make_job
 from .model import WalkerGroup
 from .space import generate_space_inter_op, generate_space_intra_op
 from .task import TASK_TABLE
@@ -98,6 +99,8 @@ class Scheduler(object):
         self.warm_up_epoch = 20
         self.warm_up_number = 20
         self.early_stop_eps = 0.02  # milliseconds, as in the reference (capped at 1 % of the best, see below)
+        self.precision = None  # fp32 mode ("tf32" | "3xtf32") the candidates are built with; None = default
+        self.seeds = []  # configs to measure and remember before the warm-up (e.g. from a saved log)
 
     def _stop_eps(self, best_value):
         """'Best did not move' threshold of the early stop: the reference's 0.02 ms, but never more than
@@ -124,7 +127,7 @@ class Scheduler(object):
                 op_pos = None
             else:
                 raise RuntimeError("Unknown mode %s" % mode)
-            jobs.append((self.task_key, full, op_pos))
+            jobs.append(make_job(self.task_key, full, op_pos, precision=self.precision))
         measurer = self.measurer
         if measurer is None:
             from .measure import default_measurer
@@ -140,6 +143,36 @@ class Scheduler(object):
         results = self.parallel_evaluate(configs, candidates, number=self.number)
         self.walker_group.add_perf_data(indices_lst, results)
         return results
+
+    # ------------------------------------------------------------ seeding
+    def _indices_of(self, config):
+        """The point of this scheduler's space that a config names, or None when an entity of the
+        config is not in its sub-space."""
+        indices = {}
+        for type_key, names in self.space.types.items():
+            entities = config.get(type_key) or []
+            if len(entities) != len(names):
+                return None
+            for name, entity in zip(names, entities):
+                sub = self.space.subspaces[name]
+                try:
+                    indices[name] = [list(e) for e in sub.static_entities].index(list(entity))
+                except ValueError:
+                    return None
+        return indices
+
+    def _measure_seeds(self, configs, use_model):
+        """Seed configs (from a saved log, or from the reference's logs through ``logcompat``) are
+        measured first and go into the heap memory like warm-up points, so that the walk can start
+        from them."""
+        points = [ind for ind in (self._indices_of(c) for c in self.seeds) if ind is not None]
+        if not points:
+            return
+        results = self._evaluate(configs, points, use_model)
+        _log("seeds [%.6f] %s" % (time.time(), _fmt(results)))
+        for indices, value in zip(points, results):
+            if value < float("inf"):
+                self.walker_group.record(indices, value)
 
     # ------------------------------------------------------------ warm-up
     def _warm_up(self, warm_up_epoches, warm_up_trials, configs, type_keys, max_repeat=20, use_model=False):
@@ -310,6 +343,8 @@ class Scheduler(object):
             # a single point: nothing to search (the reference would measure it 400 times in warm-up)
             only = {name: 0 for name in self.space.subspaces}
             return self.walker_group.to_config(only)
+        if self.seeds:
+            self._measure_seeds(configs, use_model)
         if method == "searching":
             return self._searching_schedule(configs, type_keys, use_model=use_model)
         if method == "q":
@@ -365,7 +400,9 @@ def schedule(task_key, slevel=4, rlevel=3, op_trial=50, graph_trial=10, op_stop=
     Extra keyword arguments, as in the reference: ``trials`` (per-op trial budgets),
     ``op_perf_model_path`` ([(op_pos, path)]), ``graph_perf_model_path``, ``force_inline``,
     ``rpc_info`` (ignored: no remote boards).  New ones: ``measurer`` (callable measuring
-    a batch of candidates), ``precision`` ("tf32" | "3xtf32") for fp32 contractions.
+    a batch of candidates), ``precision`` ("tf32" | "3xtf32") for fp32 contractions,
+    ``use_model`` (search on the saved performance models instead of measuring), ``seeds`` ([(op_pos, op_config)]: configs measured before the warm-up, e.g. from
+    ``logcompat.seeds_from_log``).
     """
     task = TASK_TABLE[task_key]
     ops, bufs = task.func(*task.args)
@@ -377,6 +414,9 @@ def schedule(task_key, slevel=4, rlevel=3, op_trial=50, graph_trial=10, op_stop=
     for op_pos, path in kwargs.get("op_perf_model_path", []):
         op_perf_paths[op_pos] = path
     graph_perf_path = kwargs.get("graph_perf_model_path")
+    # ``use_model=True`` (what the drivers' --use_model passes): every op's search queries its
+    # performance model, stored under the default file names, instead of measuring
+    use_model_everywhere = bool(kwargs.get("use_model", False))
     force_inline = bool(kwargs.get("force_inline", False))
     if "rewrite" in kwargs:
         raise RuntimeError("the NCHWc CPU rewrite of the reference has no counterpart on this backend")
@@ -403,16 +443,20 @@ def schedule(task_key, slevel=4, rlevel=3, op_trial=50, graph_trial=10, op_stop=
         _log("op", pos, "space size:", len(space))
         op_scheduler = OpScheduler(task_key, pos, space, parallel=parallel, timeout=timeout, trial=force_trials[pos],
                                    number=number, early_stop=op_stop, measurer=measurer)
+        op_scheduler.seeds = [cfg for seed_pos, cfg in kwargs.get("seeds", []) if seed_pos == pos]
+        op_scheduler.precision = kwargs.get("precision")
         if (force_inline and graph_space.subspaces["inline"].able_inline(pos)) or not space.subspaces:
             op_config = {}
         else:
-            op_config = op_scheduler.schedule(configs, method=method, use_model=op_perf_paths[pos] is not None,
+            op_config = op_scheduler.schedule(configs, method=method,
+                                              use_model=op_perf_paths[pos] is not None or use_model_everywhere,
                                               perf_path=op_perf_paths[pos])
         configs.op_config_lst.append(op_config)
     _log("space size", total_size)
 
     graph_scheduler = GraphScheduler(task_key, graph_space, parallel=parallel, timeout=timeout, trial=graph_trial,
                                      number=number, early_stop=graph_stop, measurer=measurer)
+    graph_scheduler.precision = kwargs.get("precision")
     graph_config = graph_scheduler.schedule(configs, method=method, use_model=graph_perf_path is not None,
                                             perf_path=graph_perf_path)
     configs = Config(configs.op_config_lst, graph_config)

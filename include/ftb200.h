@@ -10,7 +10,9 @@
  *
  * Conventions
  *   - every pointer is a device pointer owned by the caller; the library allocates no
- *     device memory (it keeps two small `__device__` words per process for status);
+ *     device memory at run time (its image holds two `__device__` status words and the fixed
+ *     FTB_NOALLOC_SCRATCH_BYTES array of ftb_conv2d_nchw_f32_noalloc, resident on every GPU
+ *     that loads it);
  *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous on it;
  *   - return value: 0 on success, a negative FTB_E_* code otherwise; nothing throws,
  *     exits or prints;
@@ -59,7 +61,9 @@ typedef struct ftb_config {
                         groups 1, <= 256 output channels, single-pass TF32); 3 batched GEMM on the
                         NCHW tensors as they are (1x1 filter, stride 1, no padding, groups 1); 4 a 1x1
                         conv over the im2col form of the input (at most 8 input channels, groups 1)    */
-  int32_t reserved[5];
+  int32_t epilogue;  /* 0 = bulk tensor stores from shared memory wherever they can address the result
+                        (default); 1 = per-thread global stores everywhere (same bits; for diagnosis)   */
+  int32_t reserved[4];
 } ftb_config;
 
 int ftb_version(void);
@@ -80,6 +84,15 @@ int64_t ftb_launch_count(void);
  * seconds the wait gives up, ORs FTB_DEV bit 1 into *status and the kernel ends normally; the
  * context stays usable.  Lets a host verify that a stuck pipeline surfaces as a status, not a hang. */
 int ftb_selftest_bounded_wait(int* status, void* stream);
+
+/* Diagnostic builds only (library compiled with -DFTB_PROFILE_WAITS; the product build returns
+ * FTB_E_UNSUPPORTED): synchronises the device and copies out eight counters of SM cycles, summed
+ * over the CTAs of every tensor-core GEMM launch since the last reset - [0] producer waiting for a
+ * free stage, [1] MMA issuer waiting for a stage to land, [2] MMA issuer waiting for a free
+ * accumulator, [3] epilogue waiting for a finished accumulator, [4] [5] [6] the whole loops of the
+ * producer, the issuer and the first epilogue warp, [7] CTAs that reported.  Tells which hand-off
+ * of the pipeline a kernel is waiting on; no counterpart in the reference. */
+int ftb_debug_wait_profile(uint64_t* cycles, int reset);
 
 /* GEMM entry points: operands whose row pitch or base address is not a multiple of 16 bytes cannot
  * be read by TMA; such calls are served by a CUDA-core kernel (correct, roughly 10x slower; plain
@@ -158,6 +171,15 @@ int ftb_dwconv2d_nchw_f32(const float* in, const float* weight, const float* bia
                           int64_t n, int64_t c, int64_t h, int64_t w, int64_t factor, int64_t r,
                           int64_t s, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h,
                           int dil_w, const ftb_config* cfg, int* status, void* stream);
+
+/* The same, with the result written to `num_dst` (1..8) buffers at once (all [N,C*f,P,Q], equally
+ * aligned): this GPU's memory or a peer GPU's mapped buffer.  The batch-sharded path places a
+ * rank's images directly in every rank's gathered output this way (plain stores over NVLink, no
+ * collective); no counterpart in the reference (it is single-device). */
+int ftb_dwconv2d_nchw_f32_multi(const float* in, const float* weight, const float* bias, float* const* out_dst,
+                                int num_dst, int64_t n, int64_t c, int64_t h, int64_t w, int64_t factor,
+                                int64_t r, int64_t s, int stride_h, int stride_w, int pad_h, int pad_w,
+                                int dil_h, int dil_w, const ftb_config* cfg, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -250,7 +250,7 @@ def test_gemm_f32_wide_pair_tile(B, status):
         run_gemm_f32(B, a, b, cfg={"cluster": 2, "tile_n": 512, "fp32_mode": 1}, status=status)
 
 
-def test_epilogues_agree(B, status, monkeypatch):
+def test_epilogues_agree(B, status):
     """The staged bulk-store epilogue and the per-thread store epilogue give the same bits."""
     items = [O.batch_gemm_item(i, 328, 264, 136, seed=34) for i in range(2)]
     a = bf16_dev(np.stack([i[0] for i in items]))
@@ -258,8 +258,7 @@ def test_epilogues_agree(B, status, monkeypatch):
     c1 = torch.full((2, 328, 264), float("nan"), device="cuda", dtype=torch.bfloat16)
     c2 = torch.full((2, 328, 264), float("nan"), device="cuda", dtype=torch.bfloat16)
     B.bgemm_bf16(a, b, c1, status=status)
-    monkeypatch.setenv("FTB_EPILOGUE", "direct")
-    B.bgemm_bf16(a, b, c2, status=status)
+    B.bgemm_bf16(a, b, c2, cfg={"epilogue": 1}, status=status)
     torch.cuda.synchronize()
     assert torch.equal(c1, c2)
 
@@ -335,11 +334,17 @@ def run_conv(B, x, w, bias=None, stride=1, padding=0, dilation=1, groups=1, cfg=
 
 
 def test_conv2d_golden(B, status):
+    # the reference's own conv2d test case (flextensor/test/test_ops.py:85-115): 6 channels in 3 groups
+    # (2 per group), 9 filters, stride 2, padding 1, dilation 2, bias
     g = _load("conv2d_grouped")
     stride, pad, dil, groups = (int(v) for v in g["params"])
-    # 2 input channels per group: the group base is not 16-byte aligned -> refused, not miscomputed
-    with pytest.raises(B.FtbError):
-        run_conv(B, g["x"], g["w"], g["b"], stride, pad, dil, groups)
+    for mode, tol in ((0, TOL["conv2d_tf32"]), (1, TOL["conv2d_3xtf32"])):
+        for extra in ({}, {"epilogue": 1}, {"split_k": 3}):
+            cfg = dict(extra, fp32_mode=mode)
+            got = run_conv(B, g["x"], g["w"], g["b"], stride, pad, dil, groups, cfg=cfg, status=status)
+            assert got.shape == g["y"].shape
+            assert O.normalised_error(got, g["y"]) <= tol, cfg
+    assert int(status.item()) == 0
     g = _load("conv2d_3x3")
     for mode, tol in ((0, TOL["conv2d_tf32"]), (1, TOL["conv2d_3xtf32"])):
         got = run_conv(B, g["x"], g["w"], None, 1, 1, 1, 1, cfg={"fp32_mode": mode}, status=status)
@@ -508,7 +513,7 @@ def _random_conv_cases(count, seed):
     cases = []
     while len(cases) < count:
         groups = rng.choice([1, 1, 1, 2, 4])
-        cg = rng.choice([4, 8, 16, 32]) if groups > 1 else rng.choice([1, 2, 3, 4, 5, 8, 12, 16, 24, 32, 40, 64])
+        cg = rng.choice([1, 2, 3, 4, 5, 6, 8, 16, 32, 40]) if groups > 1 else rng.choice([1, 2, 3, 4, 5, 8, 12, 16, 24, 32, 40, 64])
         kg = rng.choice([1, 3, 8, 16, 24, 32, 48, 64, 100, 128])
         r = rng.choice([1, 1, 2, 3, 3, 3, 5, 7])
         s = r if rng.random() < 0.8 else rng.choice([1, 2, 3, 5])
@@ -537,6 +542,27 @@ def test_conv2d_random_shapes_against_the_oracle(B, status, case):
     assert got.shape == want.shape
     tol = TOL["conv2d_3xtf32"] if (cfg or {}).get("fp32_mode") else TOL["conv2d_tf32"]
     assert O.normalised_error(got, want) <= tol, case
+    assert int(status.item()) == 0
+
+
+# the reference's grouped benchmark shapes (flextensor/configs/grouped_config.py:1-6) plus small
+# channel counts per group that are no multiple of 4
+@pytest.mark.parametrize("shape", [(1, 1024, 14, 14, 512, 1, 1, 0, 4), (1, 1024, 14, 14, 512, 1, 1, 0, 8),
+                                   (1, 1024, 14, 14, 512, 1, 1, 0, 16), (1, 1024, 14, 14, 512, 1, 1, 0, 32),
+                                   (2, 30, 13, 12, 45, 3, 1, 1, 15), (3, 21, 9, 16, 14, 3, 2, 1, 7),
+                                   (1, 10, 20, 20, 10, 3, 1, 1, 10), (2, 66, 8, 8, 33, 1, 1, 0, 11)])
+def test_conv2d_groups_run_as_one_launch(B, status, shape):
+    """Any number of channels per group, every group in the same launch: the layout pass plus one
+    tensor-core kernel, whatever the group count."""
+    n, c, h, wd, k, r, stride, pad, groups = shape
+    x, w = O.conv2d_inputs(n, c, h, wd, k, r, r, groups=groups, seed=77)
+    bias = np.random.default_rng(78).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, stride, pad, 1, groups)
+    for cfg, tol in (({"fp32_mode": 0}, TOL["conv2d_tf32"]), ({"fp32_mode": 1}, TOL["conv2d_3xtf32"])):
+        before = B.launch_count()
+        got = run_conv(B, x, w, bias, stride, pad, 1, groups, cfg=cfg, status=status)
+        assert B.launch_count() - before == 2, "layout pass + one conv kernel"
+        assert O.normalised_error(got, want) <= tol, (shape, cfg)
     assert int(status.item()) == 0
 
 

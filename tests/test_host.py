@@ -436,3 +436,98 @@ def test_driver_registers_the_tasks_it_creates(monkeypatch, tmp_path):
     obj = json.loads(line.split(":", 1)[1])
     plan, _ = schedule_with_config(key, Config(obj[0], obj[1]))
     assert plan.steps
+
+
+# ---------------------------------------------------------------- reference config logs as search seeds
+def _reference_lines():
+    # line 1 of flextensor/optimize/gemm-config.log and line 2 of
+    # flextensor/baselines/flextensor/yolo-conv2d-b32-v100.txt, verbatim
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_config_lines.txt")
+    with open(path) as fin:
+        return [ln for ln in fin.read().splitlines() if ln.strip()]
+
+
+def test_logcompat_parses_reference_lines():
+    from flextensor_b200 import logcompat as L
+    gemm_line, conv_line = _reference_lines()
+    key, cfg = L.parse_line(gemm_line)
+    assert key == "gemm_gemm_(256, 128, 128)_opencl(0)"
+    assert L.parse_key(key) == ("gemm", "gemm", (256, 128, 128), "opencl", 0)
+    assert cfg.op_config_lst[0]["spatial"] == [[64, 1, 2, 2], [1, 1, 32, 4]]
+    assert cfg.op_config_lst[0]["reduce"] == [[2, 32, 2]]
+    # one thread block covered 1*2*2 = 4 rows and 1*32*4 = 128 columns; K came in 2 refills of 64
+    assert L.block_tiles(cfg.op_config_lst[0]) == ([4, 128], [(2, 64)])
+    key, cfg = L.parse_line(conv_line)
+    category, name, args, target, dev = L.parse_key(key)
+    assert (category, name, target, dev) == ("conv2d", "conv2d_yolo_batch32", "cuda", 0)
+    assert args == (32, 64, 112, 112, 192, 3, 1, 1, 1, 1)
+    assert len(cfg.op_config_lst) == 2 and cfg.graph_config["inline"] == [[0, 0]]
+    with pytest.raises(ValueError):
+        L.parse_line("no payload here")
+
+
+def test_logcompat_maps_reference_factors_to_legal_knobs():
+    from flextensor_b200 import logcompat as L
+    from flextensor_b200.space import generate_space_intra_op
+    from flextensor_b200.task import Task, conv2d, gemm
+    from flextensor_b200.templates import config_to_knobs
+    gemm_line, conv_line = _reference_lines()
+    _, cfg = L.parse_line(gemm_line)
+    op = gemm(256, 128, 128)[0][0]
+    knobs = L.knobs_from_reference(op, cfg.op_config_lst[0])
+    assert knobs["tile_n"] == 128 and knobs["cluster"] == 1 and knobs["split_k"] == 1 and knobs["stages"] == 3
+    seed = L.seed_for(op, cfg.op_config_lst[0])
+    space = generate_space_intra_op(op, None, target="cuda")
+    for type_key, names in space.types.items():                     # every entity is a member of its sub-space
+        for name, entity in zip(names, seed[type_key]):
+            assert list(entity) in [list(e) for e in space.subspaces[name].static_entities]
+    assert config_to_knobs(seed, op)["tile_n"] == 128
+    # conv2d: the second op config of the line belongs to the convolution (the first to its padding stage)
+    key, cfg = L.parse_line(conv_line)
+    args = L.parse_key(key)[2]
+    op = conv2d(*args)[0][0]
+    knobs = L.knobs_from_reference(op, cfg.op_config_lst[1])
+    # spatial [[8,2,2,1],[2,6,2,8],[14,1,8,1],[28,1,4,1]]: 96 channels x (4 images x 8 rows x 4 columns) per block
+    assert knobs["tile_n"] == 96 and knobs["tile_h"] == 8 and knobs["cluster"] == 1
+    seed = L.seed_for(op, cfg.op_config_lst[1])
+    got = config_to_knobs(seed, op)
+    assert got["tile_n"] == 128                                       # smallest legal tile not below 96
+    assert got["tile_h"] == 1                                         # a 112-pixel row fills a 128-row tile
+    assert got["algo"] == 2                                           # 3x3 stride 1: the slab kernel
+
+
+def test_schedule_measures_seeds_first(tmp_path):
+    """Seeds from a reference log are measured before the warm-up and can win the search."""
+    from flextensor_b200 import logcompat as L
+    from flextensor_b200.scheduler import schedule
+    from flextensor_b200.templates import config_to_knobs
+    path = tmp_path / "ref.log"
+    path.write_text(_reference_lines()[0] + "\n")
+    seeds = L.seeds_from_log(str(path))
+    key = "gemm_gemm_(256, 128, 128)_cuda(0)"
+    assert list(seeds) == [key]
+    seen = []
+
+    def measurer(jobs, number=1, timeout=5.0, parallel=None):
+        out = []
+        for task_key, config, op_pos in jobs:
+            from flextensor_b200.task import TASK_TABLE
+            op = TASK_TABLE[task_key].func(*TASK_TABLE[task_key].args)[0][0]
+            knobs = config_to_knobs(config.op_config_lst[-1], op)
+            seen.append(knobs)
+            # the seed (tile 128, one CTA, 3 stages) is the optimum of this made-up cost
+            out.append(1.0 + abs(knobs["tile_n"] - 128) / 64.0 + abs(knobs["stages"] - 3) + (knobs["cluster"] - 1))
+        return out
+
+    import flextensor_b200.scheduler as S
+    old = S.VERBOSE
+    S.VERBOSE = False
+    try:
+        s, bufs, configs = schedule(key, op_trial=2, op_stop=1, graph_trial=1, parallel=2, method="searching",
+                                    measurer=measurer, seeds=seeds[key])
+    finally:
+        S.VERBOSE = old
+    assert seen[0]["tile_n"] == 128 and seen[0]["stages"] == 3 and seen[0]["cluster"] == 1   # measured first
+    op = s.steps[0].op
+    final = config_to_knobs(configs.op_config_lst[0], op)
+    assert (final["tile_n"], final["stages"], final["cluster"]) == (128, 3, 1)
