@@ -14,7 +14,10 @@ sites use on a ``tvm.runtime.Module``:
   func.export_library(path)                  writes the plan as JSON; ``load_module(path)`` reads it back
                                              (measure.py:91,107) - the kernels themselves are pre-compiled
 
-Arrays are CUDA ``torch.Tensor``s.  The padding stage of a conv graph never runs as a
+Arrays are CUDA ``torch.Tensor``s.  The output may instead be a ``sharded.PeerSlice`` - a rank's
+slice of an output that every rank of a batch-sharded run holds: the kernel then writes its
+result into every rank's copy (batched GEMM bf16 and depthwise conv2d do it themselves, store
+by store; other operators write the local copy and leave the rest to ``PeerSlice.push``).  The padding stage of a conv graph never runs as a
 kernel of its own: the conv kernels read out-of-image taps as zeros, so the graph-level
 "inline" choice of the reference is always in effect; a bias stage is folded into the conv
 epilogue.
@@ -130,6 +133,8 @@ class Module(object):
         self.imported_modules = [self]
         self._status = None
         self._workspaces = {}
+        self._peer_dst = {}
+        self.pushed_by_kernel = True  # False after a call whose PeerSlice output was written locally only
 
     # ------------------------------------------------------------ execution
     def _bind(self, arrays):
@@ -137,7 +142,13 @@ class Module(object):
         if len(arrays) != len(bufs):
             raise ValueError("expected %d arrays (bufs order, output last), got %d" % (len(bufs), len(arrays)))
         table = {}
+        self._peer_dst = {}
         for buf, arr in zip(bufs, arrays):
+            if hasattr(arr, "dst_ptrs") and hasattr(arr, "tensor"):
+                # a slice of a peer-gathered output: the local view stands for it in every check
+                # below, and kernels that can write several destinations get the whole list
+                self._peer_dst[id(buf)] = [int(p) for p in arr.dst_ptrs]
+                arr = arr.tensor
             if not isinstance(arr, torch.Tensor) or not arr.is_cuda:
                 raise TypeError("arrays must be CUDA torch tensors")
             if tuple(arr.shape) != to_tuple(buf.shape):
@@ -162,6 +173,7 @@ class Module(object):
     def __call__(self, *arrays):
         table = self._bind(arrays)
         device = arrays[-1].device
+        self.pushed_by_kernel = True
         status = self._status_word(device)
         for idx, step in enumerate(self.plan.steps):
             op = step.op
@@ -172,11 +184,17 @@ class Module(object):
                 raise RuntimeError("every tensor a kernel touches must be one of bufs (intermediates are fused)")
             bias = table[id(step.bias)] if step.bias is not None else None
             cfg = step.knobs or None
+            peers = self._peer_dst.get(id(step.out))  # every rank's copy of this step's output, own first
             if op.kind == "gemm":
                 backend.gemm_f32(ins[0], ins[1], out, op.attrs["transposeA"], op.attrs["transposeB"], cfg=cfg,
                                  status=status)
             elif op.kind == "batch_gemm":
-                if ins[0].dtype == torch.bfloat16:
+                if ins[0].dtype == torch.bfloat16 and peers and len(peers) > 1:
+                    backend.bgemm_bf16_multi(ins[0], ins[1], peers, out.shape[1], out.shape[2],
+                                             op.attrs["transposeA"], op.attrs["transposeB"],
+                                             out_f32=out.dtype == torch.float32, cfg=cfg, status=status)
+                    peers = None
+                elif ins[0].dtype == torch.bfloat16:
                     backend.bgemm_bf16(ins[0], ins[1], out, op.attrs["transposeA"], op.attrs["transposeB"],
                                        cfg=cfg, status=status)
                 else:
@@ -193,10 +211,19 @@ class Module(object):
                 backend.conv2d_nchw_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
                                         op.attrs["dilation"], groups, cfg=cfg, workspace=ws, status=status)
             elif op.kind == "depthwise_conv2d":
-                backend.dwconv2d_nchw_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
-                                          op.attrs["dilation"], cfg=cfg, status=status)
+                if peers and len(peers) > 1:
+                    backend.dwconv2d_nchw_f32_multi(ins[0], ins[1], peers, bias, op.attrs["stride"],
+                                                    op.attrs["padding"], op.attrs["dilation"], cfg=cfg, status=status)
+                    peers = None
+                else:
+                    backend.dwconv2d_nchw_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
+                                              op.attrs["dilation"], cfg=cfg, status=status)
             else:
                 raise RuntimeError("no kernel for op kind %r" % (op.kind,))
+            if peers and len(peers) > 1:
+                # this operator's kernel writes one destination: the caller still has to push the
+                # local copy to the peers (sharded.PeerSlice.push)
+                self.pushed_by_kernel = False
 
     def capture(self, *arrays):
         """Record one call on these arrays into a CUDA graph; returns an object whose ``replay()``

@@ -1,10 +1,14 @@
-"""Two or more GPUs: the batch-sharded batched GEMM with the gather fused into the epilogue
-(bulk stores into every rank's output over NVLink) and with the NCCL all-gather, each rank
-checking the whole gathered result against the oracle.  Skipped on a single-GPU box.
+"""Two or more GPUs: batch-sharded batched GEMM, conv2d and depthwise conv2d, the output returned
+to every rank by the kernels themselves (stores into every rank's buffer over NVLink), by
+device-to-device pushes, and by an NCCL all-gather - each rank checking the whole gathered result
+against the oracle.  Skipped on a single-GPU box.
 
-Ranks are child processes, one per GPU; NVLS is switched off for NCCL and the kernels use plain
-peer stores, so a rank that fails cannot leave a multicast binding behind.  A rank only leaves
-between steps, with nothing in flight.
+Ranks are child processes, one per GPU.  NVLS is switched off for NCCL and symmetric memory is
+told not to bind a multicast object (``TORCH_SYMM_MEM_DISABLE_MULTICAST=1``); the kernels use
+plain peer stores.  The ranks agree on the host (a gloo all-reduce of a flag) that every launch
+went through before any of them enters a device-side barrier, so a rank whose launch failed
+cannot leave its peers waiting; every rank drops its symmetric buffers and destroys the process
+group on every exit path, and a rank only leaves between steps, with nothing in flight.
 """
 import os
 import socket
@@ -27,46 +31,119 @@ def _free_port():
 
 
 def _rank_main(rank, world, port, results):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     import torch.distributed as dist
     from flextensor_b200 import backend as B
-    from flextensor_b200.sharded import BatchSharded, PeerGatheredOutput, shard_range
+    from flextensor_b200.sharded import BatchSharded, PeerGatheredOutput, ShardedOp, shard_range
+    from flextensor_b200.task import batch_gemm, conv2d, depthwise_conv2d
     torch.cuda.set_device(rank)
     device = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    host = dist.new_group(backend="gloo")       # host-side agreement, never touches a GPU
+    outcome = {}
+    opened = []
+
+    def all_ranks_ok(local_ok):
+        flag = torch.tensor([1 if local_ok else 0], dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=host)
+        return bool(flag.item())
+
+    def dev(x):
+        return torch.from_numpy(np.ascontiguousarray(x)).to(device)
+
+    def run_sharded(name, op, inputs, check):
+        """launch -> agree on the host -> device barrier / gather -> compare the gathered output"""
+        opened.append(op)
+        err = None
+        try:
+            op.launch(*inputs)
+            torch.cuda.synchronize()
+        except Exception as exc:  # recorded; the peers learn of it before they wait for this rank
+            err = "%s: %s" % (type(exc).__name__, exc)
+        if not all_ranks_ok(err is None):
+            outcome[name] = err or "a peer's launch failed"
+            return
+        op.finish()
+        torch.cuda.synchronize()
+        op.check()
+        outcome[name] = bool(check(op.out_full))
+
     try:
+        # ---- batched GEMM bf16: raw multi-destination entry point, then the same through the task interface
         batch, m, n, k = 2 * world, 256, 384, 192
         lo, hi = shard_range(batch, world, rank)
         items = [O.batch_gemm_item(i, m, n, k, seed=71) for i in range(batch)]
         want = O.batch_gemm(np.stack([i[0] for i in items]), np.stack([i[1] for i in items]))
-        a = torch.from_numpy(np.stack([i[0] for i in items[lo:hi]])).to(device).bfloat16()
-        b = torch.from_numpy(np.stack([i[1] for i in items[lo:hi]])).to(device).bfloat16()
+        a = dev(np.stack([i[0] for i in items[lo:hi]])).bfloat16()
+        b = dev(np.stack([i[1] for i in items[lo:hi]])).bfloat16()
         status = B.new_status(device)
-        # fused: epilogue stores into every rank's buffer, then one barrier
-        out = PeerGatheredOutput(batch, m, n, torch.bfloat16)
+        out = PeerGatheredOutput(batch, m, n, dtype=torch.bfloat16)
         out.tensor.fill_(float("nan"))
         dist.barrier()
-        B.bgemm_bf16_multi(a, b, out.slice_ptrs(lo), m, n, status=status)
-        out.barrier()
-        torch.cuda.synchronize()
-        fused_ok = O.bf16_output_ok(out.tensor.float().cpu().numpy(), want)
-        # NCCL: local compute, all-gather
+        err = None
+        try:
+            B.bgemm_bf16_multi(a, b, out.slice_ptrs(lo), m, n, status=status)
+            torch.cuda.synchronize()
+        except Exception as exc:
+            err = "%s: %s" % (type(exc).__name__, exc)
+        if all_ranks_ok(err is None):
+            out.barrier()
+            torch.cuda.synchronize()
+            outcome["bgemm_raw_fused"] = bool(O.bf16_output_ok(out.tensor.float().cpu().numpy(), want))
+        else:
+            outcome["bgemm_raw_fused"] = err or "a peer's launch failed"
+        fused_copy = out.tensor.clone()
+        out.close()
         sh = BatchSharded(batch)
         c_local = torch.empty(hi - lo, m, n, device=device, dtype=torch.bfloat16)
         c_full = torch.full((batch, m, n), float("nan"), device=device, dtype=torch.bfloat16)
         sh.run(lambda l, h: B.bgemm_bf16(a[l:h], b[l:h], c_local[l:h], status=status), c_local, c_full, chunks=2)
         torch.cuda.synchronize()
-        nccl_ok = O.bf16_output_ok(c_full.float().cpu().numpy(), want)
+        outcome["bgemm_nccl"] = bool(O.bf16_output_ok(c_full.float().cpu().numpy(), want)) and \
+            bool(torch.equal(c_full, fused_copy))
         B.check_status(status)
-        results[rank] = (bool(fused_ok), bool(nccl_ok), bool(torch.equal(c_full, out.tensor)))
-        dist.barrier()
+        for mode in ("fused", "nccl"):
+            op = ShardedOp("gemm", "batch_gemm", batch_gemm, (batch, m, k, n), gather=mode)
+            run_sharded("bgemm_module_" + mode, op, (a, b),
+                        lambda full: O.bf16_output_ok(full.float().cpu().numpy(), want))
+        # ---- conv2d (grouped, 3 channels per group) and depthwise conv2d, images sharded over the ranks
+        nimg = 2 * world
+        x, w = O.conv2d_inputs(nimg, 12, 14, 16, 24, 3, 3, groups=4, seed=72)
+        want_conv = O.conv2d_nchw(x, w, None, 1, 1, 1, 4)
+        lo, hi = shard_range(nimg, world, rank)
+        for mode in ("fused", "push", "nccl"):
+            op = ShardedOp("conv2d", "sharded", conv2d, (nimg, 12, 14, 16, 24, 3, 1, 1, 1, 4), gather=mode)
+            run_sharded("conv2d_" + mode, op, (dev(x[lo:hi]), dev(w)),
+                        lambda full: O.normalised_error(full.cpu().numpy(), want_conv) <= O.TOLERANCE["conv2d_tf32"])
+        xd, wd = O.depthwise_inputs(nimg, 16, 28, 28, 2, 3, 3, seed=73)
+        want_dw = O.depthwise_conv2d_nchw(xd, wd, None, 1, 1, 1)
+        for mode in ("fused", "push", "nccl"):
+            op = ShardedOp("conv2d", "depthwise", depthwise_conv2d, (nimg, 16, 28, 28, 2, 3, 1, 1, 1), gather=mode)
+            run_sharded("depthwise_" + mode, op, (dev(xd[lo:hi]), dev(wd)),
+                        lambda full: O.normalised_error(full.cpu().numpy(), want_dw) <= O.TOLERANCE["depthwise_f32"])
+        results[rank] = dict(outcome)
     except Exception as exc:
-        results[rank] = "error: %s: %s" % (type(exc).__name__, exc)
+        outcome["error"] = "%s: %s" % (type(exc).__name__, exc)
+        results[rank] = dict(outcome)
     finally:
-        dist.destroy_process_group()
+        try:
+            torch.cuda.synchronize()
+        except Exception:
+            pass
+        for op in opened:
+            op.close()
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
 
 
-def test_sharded_bgemm_fused_and_nccl(native_lib):
+EXPECTED = ["bgemm_raw_fused", "bgemm_nccl", "bgemm_module_fused", "bgemm_module_nccl", "conv2d_fused", "conv2d_push",
+            "conv2d_nccl", "depthwise_fused", "depthwise_push", "depthwise_nccl"]
+
+
+def test_sharded_operators_fused_push_and_nccl(native_lib):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
@@ -78,10 +155,12 @@ def test_sharded_bgemm_fused_and_nccl(native_lib):
     for p in procs:
         p.start()
     for p in procs:
-        p.join(timeout=300)
-        if p.is_alive():
-            p.terminate()
-    assert dict(results) == {r: (True, True, True) for r in range(world)}
+        p.join(timeout=600)
+    stuck = [p for p in procs if p.is_alive()]
+    for p in stuck:
+        p.terminate()
+    assert not stuck, "ranks did not finish"
+    assert dict(results) == {r: {name: True for name in EXPECTED} for r in range(world)}
 
 
 def test_measurement_pool_uses_every_gpu(native_lib):
