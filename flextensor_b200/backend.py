@@ -134,6 +134,14 @@ def lib():
         handle.ftb_conv2d_nchw_f32.restype = i32
         handle.ftb_conv2d_nchw_f32.argtypes = ([vp] * 4 + [i64] * 7 + [i32] * 7 +
                                                [cfgp, vp, ctypes.c_size_t, vp, vp])
+        handle.ftb_conv2d_pack_filter.restype = i32
+        handle.ftb_conv2d_pack_filter.argtypes = [vp] + [i64] * 7 + [i32] * 7 + [cfgp, vp, ctypes.c_size_t, vp]
+        handle.ftb_conv2d_nchw_f32_prepacked.restype = i32
+        handle.ftb_conv2d_nchw_f32_prepacked.argtypes = ([vp] * 4 + [i64] * 7 + [i32] * 7 +
+                                                         [cfgp, vp, ctypes.c_size_t, vp, vp])
+        handle.ftb_conv2d_nchw_f32_multi.restype = i32
+        handle.ftb_conv2d_nchw_f32_multi.argtypes = ([vp] * 3 + [ctypes.POINTER(vp), i32] + [i64] * 7 + [i32] * 8 +
+                                                     [cfgp, vp, ctypes.c_size_t, vp, vp])
         handle.ftb_conv2d_nchw_f32_noalloc.restype = i32
         handle.ftb_conv2d_nchw_f32_noalloc.argtypes = [vp] * 4 + [i64] * 7 + [i32] * 7 + [cfgp, vp, vp]
         handle.ftb_dwconv2d_nchw_f32.restype = i32
@@ -149,7 +157,8 @@ EXPORTED_SYMBOLS = (
     "ftb_version", "ftb_strerror", "ftb_last_cuda_error", "ftb_device_check", "ftb_validate",
     "ftb_launch_count", "ftb_selftest_bounded_wait", "ftb_debug_wait_profile", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_bgemm_bf16_multi", "ftb_gemm_s8",
     "ftb_conv2d_workspace_bytes", "ftb_conv2d_nchw_f32", "ftb_conv2d_nchw_f32_noalloc", "ftb_dwconv2d_nchw_f32",
-    "ftb_dwconv2d_nchw_f32_multi",
+    "ftb_dwconv2d_nchw_f32_multi", "ftb_conv2d_nchw_f32_multi", "ftb_conv2d_pack_filter",
+    "ftb_conv2d_nchw_f32_prepacked",
 )
 
 
@@ -327,10 +336,31 @@ def conv2d_workspace_bytes(n, c, h, w, k, r, s, groups=1):
     return int(lib().ftb_conv2d_workspace_bytes(n, c, h, w, k, r, s, groups))
 
 
+def conv2d_pack_filter(weight, x_shape, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, cfg=None,
+                       workspace=None, stream=None):
+    """Packs ``weight`` into the filter region of ``workspace`` for conv calls on inputs of
+    ``x_shape`` with the same knobs; follow with ``conv2d_nchw_f32(..., prepacked=True)``."""
+    _check(weight, torch.float32, "weight")
+    n, c, h, w = (int(v) for v in x_shape)
+    k, cg, r, s = weight.shape
+    need = conv2d_workspace_bytes(n, c, h, w, k, r, s, groups)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        raise ValueError("conv2d: workspace of at least %d bytes required" % need)
+    with torch.cuda.device(weight.device):
+        rc = lib().ftb_conv2d_pack_filter(
+            weight.data_ptr(), n, c, h, w, k, r, s, stride[0], stride[1], padding[0], padding[1], dilation[0],
+            dilation[1], groups, _cfg_ptr(cfg), workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+            _stream_ptr(stream))
+    if rc:
+        raise FtbError(rc, "ftb_conv2d_pack_filter")
+
+
 def conv2d_nchw_f32(x, weight, out, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1,
-                    cfg=None, workspace=None, status=None, stream=None):
+                    cfg=None, workspace=None, status=None, stream=None, prepacked=False):
     """out[N,K,P,Q] = conv2d(x[N,C,H,W], weight[K,C/groups,R,S]) (+ bias); the caller owns
-    ``workspace`` (a uint8 CUDA tensor of at least conv2d_workspace_bytes bytes)."""
+    ``workspace`` (a uint8 CUDA tensor of at least conv2d_workspace_bytes bytes).  ``prepacked``:
+    the workspace already holds this weight's packing (``conv2d_pack_filter`` or an earlier call
+    with the same shapes and knobs): only the input is laid out."""
     for t, nm in ((x, "x"), (weight, "weight"), (out, "out")):
         _check(t, torch.float32, nm)
     if bias is not None:
@@ -343,13 +373,43 @@ def conv2d_nchw_f32(x, weight, out, bias=None, stride=(1, 1), padding=(0, 0), di
     if workspace is None or workspace.numel() * workspace.element_size() < need:
         raise ValueError("conv2d: workspace of at least %d bytes required" % need)
     with torch.cuda.device(out.device):
-        rc = lib().ftb_conv2d_nchw_f32(
+        entry = lib().ftb_conv2d_nchw_f32_prepacked if prepacked else lib().ftb_conv2d_nchw_f32
+        rc = entry(
             x.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(),
             n, c, h, w, k, r, s, stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
             groups, _cfg_ptr(cfg), workspace.data_ptr(), workspace.numel() * workspace.element_size(),
             _status_ptr(status), _stream_ptr(stream))
     if rc:
         raise FtbError(rc, "ftb_conv2d_nchw_f32")
+
+
+def conv2d_nchw_f32_multi(x, weight, dst_ptrs, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1,
+                          cfg=None, workspace=None, status=None, stream=None, prepacked=False):
+    """conv2d whose result goes to several buffers at once (``dst_ptrs``: 1..8 device addresses of
+    [N,K,P,Q] fp32 buffers, this GPU's or a peer's mapped memory).  Raises ``FtbError`` with code
+    -2 when the kernel that serves the shape has a single destination."""
+    for t, nm in ((x, "x"), (weight, "weight")):
+        _check(t, torch.float32, nm)
+    if bias is not None:
+        _check(bias, torch.float32, "bias")
+    n, c, h, w = x.shape
+    k, cg, r, s = weight.shape
+    if cg * groups != c:
+        raise ValueError("conv2d: weight channels %d x groups %d != input channels %d" % (cg, groups, c))
+    need = conv2d_workspace_bytes(n, c, h, w, k, r, s, groups)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        raise ValueError("conv2d: workspace of at least %d bytes required" % need)
+    if not 1 <= len(dst_ptrs) <= 8:
+        raise ValueError("between 1 and 8 destinations")
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*[ctypes.c_void_p(int(p)) for p in dst_ptrs])
+    with torch.cuda.device(x.device):
+        rc = lib().ftb_conv2d_nchw_f32_multi(
+            x.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, arr, len(dst_ptrs),
+            n, c, h, w, k, r, s, stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
+            groups, int(prepacked), _cfg_ptr(cfg), workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(), _status_ptr(status), _stream_ptr(stream))
+    if rc:
+        raise FtbError(rc, "ftb_conv2d_nchw_f32_multi")
 
 
 NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024

@@ -40,6 +40,7 @@ struct ConvSlabParams {
   int a_stages;
   // staged epilogue: epi_bufs (0 = off, 1 or 2) buffers of 32 channels x tile pixels after the slabs
   int epi_bufs;
+  int num_dst;  // destinations of the staged epilogue (1..kMaxDst): the same box goes to each of them
   uint32_t epi_buf_bytes;
   uint32_t slab_bytes;   // bytes one slab load delivers
   uint32_t slab_alloc;   // bytes reserved per slab stage (covers the furthest tap's 128 rows)
@@ -52,7 +53,7 @@ struct ConvSlabParams {
 
 __global__ void __launch_bounds__(192, 1)
 conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_constant__ CUtensorMap tmap_w,
-                 const __grid_constant__ CUtensorMap tmap_out,
+                 const __grid_constant__ StoreMaps tmap_out,
                  const __grid_constant__ ConvSlabParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_afull[kSlabMaxStages];
@@ -94,7 +95,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
     fence_proxy_async_smem();
     prefetch_tmap(&tmap_in);
     prefetch_tmap(&tmap_w);
-    if (p.epi_bufs) prefetch_tmap(&tmap_out);
+    if (p.epi_bufs)
+      for (int d = 0; d < p.num_dst; ++d) prefetch_tmap(&tmap_out.dst[d]);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
@@ -282,8 +284,14 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             named_barrier_sync(1, 128);
             if (leader) {
               if (c < p.N) {
-                if (p.split > 1) tma_reduce_add_4d(&tmap_out, buf, tw * p.tile_w, th * p.tile_h, c, img);
-                else tma_store_4d(&tmap_out, buf, tw * p.tile_w, th * p.tile_h, c, img);
+                if (p.split > 1) {
+                  tma_reduce_add_4d(&tmap_out.dst[0], buf, tw * p.tile_w, th * p.tile_h, c, img);
+                } else {
+                  // every destination gets the same box: this GPU's result and, in a batch-sharded
+                  // run, the same images of every peer's gathered output (stores over NVLink)
+                  for (int d = 0; d < p.num_dst; ++d)
+                    tma_store_4d(&tmap_out.dst[d], buf, tw * p.tile_w, th * p.tile_h, c, img);
+                }
               }
               bulk_commit_group();
             }
@@ -318,8 +326,11 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       }
     }
     // Shared memory must outlive the bulk stores' reads of it; their global writes are complete
-    // when the grid is.
-    if (p.epi_bufs && warp == 2 && lane == 0) bulk_wait_group_read<0>();
+    // when the grid is - except stores into a peer GPU's memory, which are waited for in full.
+    if (p.epi_bufs && warp == 2 && lane == 0) {
+      if (p.num_dst > 1) bulk_wait_group<0>();
+      else bulk_wait_group_read<0>();
+    }
     __syncwarp();
   }
 

@@ -811,23 +811,25 @@ conv_prepass_kernel(const float* __restrict__ in, const float* __restrict__ wgt,
 static int conv_prepass(const float* in, const float* weight, float* in_nhwc, float* w_packed, int64_t n, int64_t c,
                         int64_t h, int64_t w, int64_t k, int64_t cg, int64_t r, int64_t s, const ConvWs& ws,
                         int num_sms, void* stream_v, float* zero = nullptr, long long zero_n = 0, int sub_q = 0,
-                        int sub_p = 0, int sub_sh = 1, int sub_sw = 1, bool grouped = false) {
+                        int sub_p = 0, int sub_sh = 1, int sub_sw = 1, bool grouped = false, int parts = 3) {
+  // parts: bit 0 = copy the input, bit 1 = pack the filter
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   // sub_q > 0: keep sub_p x sub_q pixels of every plane, every sub_sh-th row and sub_sw-th column
   const int plane = static_cast<int>(h * w);
   const int HW = sub_q > 0 ? sub_p * sub_q : plane;
   const int hw_tiles = (HW + kPrePx - 1) / kPrePx, c_tiles = static_cast<int>((ws.cp + kPreCh - 1) / kPreCh);
-  const int in_blocks = static_cast<int>(n) * hw_tiles * c_tiles;
+  const int in_blocks = (parts & 1) ? static_cast<int>(n) * hw_tiles * c_tiles : 0;
   // one work unit of the filter packing = one output channel x one run of input channels
   const long long wtotal = k * r * s * ws.cchunks * 32;
   long long w_units = (wtotal + 2047) / 2048;
   if (w_units < k) w_units = k;
-  int w_blocks = static_cast<int>(w_units > 8ll * num_sms ? 8ll * num_sms : w_units);
+  int w_blocks = (parts & 2) ? static_cast<int>(w_units > 8ll * num_sms ? 8ll * num_sms : w_units) : 0;
   int z_blocks = 0;
   if (zero && zero_n > 0) {
     const long long want = (zero_n / 4 + 255) / 256;
     z_blocks = static_cast<int>(want < 1 ? 1 : want > 2 * num_sms ? 2 * num_sms : want);
   }
+  if (in_blocks + w_blocks + z_blocks == 0) return FTB_OK;
   conv_prepass_kernel<<<in_blocks + w_blocks + z_blocks, 256, 0, stream>>>(
       in, weight, in_nhwc, w_packed, static_cast<int>(n), static_cast<int>(c), HW, static_cast<int>(ws.cp),
       static_cast<int>(k), static_cast<int>(cg), static_cast<int>(r * s), static_cast<int>(ws.cchunks), hw_tiles,
@@ -950,7 +952,7 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   return sp;
 }
 
-static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap& tout, const SlabPlan& sp,
+static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const StoreMaps& tout, const SlabPlan& sp,
                        cudaStream_t stream) {
   static std::mutex mu;
   static bool done[64] = {false};
@@ -994,8 +996,26 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
                    int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,
                    int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
                    const ftb_config* user, void* workspace, size_t workspace_bytes, int* status,
-                   void* stream_v) {
-  if (!in || !weight || !out) return FTB_E_BAD_ARG;
+                   void* stream_v, float* const* extra_dst, int num_extra, int filter_mode) {
+  // filter_mode: 0 = pack the filter and run; 1 = pack the filter into the workspace and return;
+  // 2 = the workspace already holds this filter's packing (same shape arguments and knobs)
+  if (filter_mode < 0 || filter_mode > 2) return FTB_E_BAD_ARG;
+  const bool pack_only = filter_mode == 1;
+  const int parts = pack_only ? 2 : filter_mode == 2 ? 1 : 3;
+  if (!weight || (!pack_only && (!in || !out))) return FTB_E_BAD_ARG;
+  if (num_extra < 0 || num_extra > kMaxDst - 1 || (num_extra > 0 && !extra_dst)) return FTB_E_BAD_ARG;
+  for (int d = 0; d < num_extra; ++d)
+    if (!extra_dst[d] || (reinterpret_cast<uintptr_t>(extra_dst[d]) & 15)) return FTB_E_BAD_ARG;
+  // Several destinations exist only in the epilogues that leave through bulk tensor stores and
+  // add nothing in global memory: the reduction is then kept inside one CTA per tile.
+  ftb_config multi_cfg;
+  if (num_extra > 0) {
+    memset(&multi_cfg, 0, sizeof(multi_cfg));
+    if (user) multi_cfg = *user;
+    if (multi_cfg.split_k > 1 || multi_cfg.epilogue == 1) return FTB_E_UNSUPPORTED;
+    multi_cfg.split_k = 1;
+    user = &multi_cfg;
+  }
   if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || k <= 0 || r <= 0 || s <= 0 || groups <= 0) return FTB_E_BAD_ARG;
   if (stride_h <= 0 || stride_w <= 0 || dil_h <= 0 || dil_w <= 0 || pad_h < 0 || pad_w < 0) return FTB_E_BAD_ARG;
   if (c % groups || k % groups) return FTB_E_BAD_ARG;
@@ -1026,8 +1046,8 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     const bool is_gemm = r == 1 && s == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 &&
                          groups == 1 && (h * w) % 4 == 0 && c % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
-    if (algo == 3 && !is_gemm) return FTB_E_UNSUPPORTED;
-    if (is_gemm && (algo == 0 || algo == 3)) {
+    if (algo == 3 && !is_gemm && !pack_only) return FTB_E_UNSUPPORTED;
+    if (is_gemm && (algo == 0 || algo == 3) && !pack_only) {
       ftb_config gcfg;
       memset(&gcfg, 0, sizeof(gcfg));
       if (user) {
@@ -1039,7 +1059,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       ex.a_broadcast = 1;
       ex.row_bias = bias;
       return gemm_generic(KIND_TF32, OUT_F32, weight, in, out, n, k, h * w, c, 0, 0, user ? &gcfg : nullptr, status,
-                          stream_v, nullptr, 0, &ex);
+                          stream_v, reinterpret_cast<void* const*>(extra_dst), num_extra, &ex);
     }
   }
   // Few input channels: continue as a 1x1, stride-1, unpadded conv over the im2col form, an
@@ -1078,6 +1098,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       !(user && user->cluster == 2))
     sp = plan_slab(user, n, kg, P, Q, r, s, ws.cchunks, dil_h, dil_w, pad_h, pad_w,
                    (reinterpret_cast<uintptr_t>(out) & 15) == 0, num_sms);
+  if (sp.ok && num_extra > 0 && (sp.p.epi_bufs == 0 || sp.p.split > 1)) sp.ok = false;
   if (algo == 2 && !sp.ok) return FTB_E_UNSUPPORTED;
   // Left to itself the slab kernel is taken when the whole filter stays resident, or when the tile
   // list is shorter than half the SM count (where a split reduction is wanted anyway); a long tile list
@@ -1089,8 +1110,8 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       if (rc) return rc;
     }
     rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v,
-                      sp.p.split > 1 ? out : nullptr, n * k * P * Q);
-    if (rc) return rc;
+                      (sp.p.split > 1 && !pack_only) ? out : nullptr, n * k * P * Q, 0, 0, 1, 1, false, parts);
+    if (rc || pack_only) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     sp.p.out = out;
     sp.p.bias = bias;
@@ -1117,8 +1138,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       rc = make_tmap(&tw, ki.dt, 3, w_packed, dims, strides, box, ones);
       if (rc) return rc;
     }
-    CUtensorMap tout;
+    StoreMaps tout;
     memset(&tout, 0, sizeof(tout));
+    sp.p.num_dst = 1 + num_extra;
     if (sp.p.epi_bufs) {
       // (w, h, channel, image) view of the NCHW result; a box is 32 channels of one output tile.
       uint64_t dims[4] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(k),
@@ -1127,8 +1149,11 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
                              static_cast<uint64_t>(k) * P * Q * 4};
       uint32_t box[4] = {static_cast<uint32_t>(sp.p.tile_w), static_cast<uint32_t>(sp.p.tile_h), 32, 1};
       const uint32_t ones[4] = {1, 1, 1, 1};
-      rc = make_tmap(&tout, ki.dt, 4, out, dims, strides, box, ones, CU_TENSOR_MAP_SWIZZLE_NONE);
-      if (rc) return rc;
+      for (int d = 0; d < sp.p.num_dst; ++d) {
+        rc = make_tmap(&tout.dst[d], ki.dt, 4, d == 0 ? out : extra_dst[d - 1], dims, strides, box, ones,
+                       CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+      }
     }
     return launch_slab(tin, tw, tout, sp, stream);
   }
@@ -1205,9 +1230,10 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     rc = resolve_config(user, ki, split3, 0, !split3, groups, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg);
   }
   if (rc) return rc;
+  if (num_extra > 0 && !staged) return FTB_E_UNSUPPORTED;
   const bool pair = cfg.cluster == 2;
   const long long tiles_m_launch = pair ? (tiles_m + 1) / 2 : tiles_m;
-  if (!conv_tuned && (!user || user->split_k == 0)) {
+  if (!conv_tuned && (!user || user->split_k == 0) && num_extra == 0) {
     // A short tile list leaves SMs idle: split the reduction so that about all SMs get work (the
     // partial sums meet in global memory through bulk reduce-adds into the zeroed result).
     const long long tiles = groups * tiles_m_launch * ((kg + cfg.tile_n - 1) / cfg.tile_n);
@@ -1221,7 +1247,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
 
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (im2col) {
-    if (cfg.split_k > 1) {
+    if (cfg.split_k > 1 && !pack_only) {
       cudaError_t e = cudaMemsetAsync(out, 0, static_cast<size_t>(n * k * P * Q) * 4, stream);
       if (e != cudaSuccess) {
         set_last_cuda_error(static_cast<int>(e));
@@ -1230,9 +1256,10 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     }
     const int kp = static_cast<int>(wsx.cp);
     const int segs = static_cast<int>((Q + kColSeg - 1) / kColSeg);
-    const long long col_blocks = n * P * segs;
+    const long long col_blocks = (parts & 1) ? n * P * segs : 0;
     long long w_blocks = (k * kp + 255) / 256;
     if (w_blocks > 2ll * num_sms) w_blocks = 2ll * num_sms;
+    if (!(parts & 2)) w_blocks = 0;
     conv_im2col_kernel<<<static_cast<unsigned>(col_blocks + w_blocks), 256, 0, stream>>>(
         in, weight, in_nhwc, w_packed, static_cast<int>(n), static_cast<int>(orig.c), static_cast<int>(orig.h),
         static_cast<int>(orig.w), static_cast<int>(k), static_cast<int>(orig.r), static_cast<int>(orig.s),
@@ -1246,10 +1273,11 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     }
   } else {
     rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h_in, w_in, k, cg, r, s, ws, num_sms, stream_v,
-                      cfg.split_k > 1 ? out : nullptr, n * k * P * Q, subsample ? static_cast<int>(Q) : 0,
-                      static_cast<int>(P), sub_sh, sub_sw, groups > 1);
+                      (cfg.split_k > 1 && !pack_only) ? out : nullptr, n * k * P * Q,
+                      subsample ? static_cast<int>(Q) : 0, static_cast<int>(P), sub_sh, sub_sw, groups > 1, parts);
     if (rc) return rc;
   }
+  if (pack_only) return FTB_OK;
   // One launch for all groups: a tile's batch coordinate is its group, and the tensor maps of
   // the operands and of the result carry a group dimension.
   {
@@ -1349,7 +1377,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       // (w, h, channel in group, group, image) view of the NCHW result: a box of 32 channels is
       // clipped at the end of its group
       p.tma_store = 1;
-      p.num_dst = 1;
+      p.num_dst = 1 + num_extra;
       uint64_t dims[5] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(kg),
                           static_cast<uint64_t>(groups), static_cast<uint64_t>(n)};
       uint64_t strides[4] = {static_cast<uint64_t>(Q) * 4, static_cast<uint64_t>(P) * Q * 4,
@@ -1357,12 +1385,15 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       uint32_t box[5] = {static_cast<uint32_t>(tile_w), static_cast<uint32_t>(tile_h), 32, 1,
                          static_cast<uint32_t>(tile_imgs)};
       const uint32_t ones[5] = {1, 1, 1, 1, 1};
-      rc = make_tmap(&tc.dst[0], ki.dt, 5, out, dims, strides, box, ones, CU_TENSOR_MAP_SWIZZLE_NONE);
-      if (rc) return rc;
+      for (int d = 0; d < p.num_dst; ++d) {
+        rc = make_tmap(&tc.dst[d], ki.dt, 5, d == 0 ? out : extra_dst[d - 1], dims, strides, box, ones,
+                       CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+      }
     } else if (staged) {
       // (w, h, channel, image) view of the NCHW result
       p.tma_store = 1;
-      p.num_dst = 1;
+      p.num_dst = 1 + num_extra;
       uint64_t dims[4] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(k),
                           static_cast<uint64_t>(n)};
       uint64_t strides[3] = {static_cast<uint64_t>(Q) * 4, static_cast<uint64_t>(P) * Q * 4,
@@ -1370,8 +1401,11 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       uint32_t box[4] = {static_cast<uint32_t>(tile_w), static_cast<uint32_t>(tile_h), 32,
                          static_cast<uint32_t>(tile_imgs)};
       const uint32_t ones[4] = {1, 1, 1, 1};
-      rc = make_tmap(&tc.dst[0], ki.dt, 4, out, dims, strides, box, ones, CU_TENSOR_MAP_SWIZZLE_NONE);
-      if (rc) return rc;
+      for (int d = 0; d < p.num_dst; ++d) {
+        rc = make_tmap(&tc.dst[d], ki.dt, 4, d == 0 ? out : extra_dst[d - 1], dims, strides, box, ones,
+                       CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+      }
     }
     rc = dispatch(KIND_TF32, OUT_F32, split3, pair, ta, tb, tc, p, ctas, stream);
     if (rc) return rc;
@@ -1454,7 +1488,35 @@ int ftb_conv2d_nchw_f32(const float* in, const float* weight, const float* bias,
                         void* stream) {
   return ftb::conv2d_generic(in, weight, bias, out, n, c, h, w, k, r, s, stride_h, stride_w, pad_h,
                              pad_w, dil_h, dil_w, groups, cfg, workspace, workspace_bytes, status,
-                             stream);
+                             stream, nullptr, 0, 0);
+}
+
+int ftb_conv2d_pack_filter(const float* weight, int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r,
+                           int64_t s, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                           int groups, const ftb_config* cfg, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  return ftb::conv2d_generic(nullptr, weight, nullptr, nullptr, n, c, h, w, k, r, s, stride_h, stride_w, pad_h, pad_w,
+                             dil_h, dil_w, groups, cfg, workspace, workspace_bytes, nullptr, stream, nullptr, 0, 1);
+}
+
+int ftb_conv2d_nchw_f32_prepacked(const float* in, const float* weight, const float* bias, float* out, int64_t n,
+                                  int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,
+                                  int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
+                                  const ftb_config* cfg, void* workspace, size_t workspace_bytes, int* status,
+                                  void* stream) {
+  return ftb::conv2d_generic(in, weight, bias, out, n, c, h, w, k, r, s, stride_h, stride_w, pad_h, pad_w, dil_h,
+                             dil_w, groups, cfg, workspace, workspace_bytes, status, stream, nullptr, 0, 2);
+}
+
+int ftb_conv2d_nchw_f32_multi(const float* in, const float* weight, const float* bias, float* const* out_dst,
+                              int num_dst, int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r,
+                              int64_t s, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                              int groups, int prepacked, const ftb_config* cfg, void* workspace,
+                              size_t workspace_bytes, int* status, void* stream) {
+  if (!out_dst || num_dst < 1 || num_dst > ftb::kMaxDst) return FTB_E_BAD_ARG;
+  return ftb::conv2d_generic(in, weight, bias, out_dst[0], n, c, h, w, k, r, s, stride_h, stride_w, pad_h,
+                             pad_w, dil_h, dil_w, groups, cfg, workspace, workspace_bytes, status, stream,
+                             out_dst + 1, num_dst - 1, prepacked ? 2 : 0);
 }
 
 }  // extern "C"

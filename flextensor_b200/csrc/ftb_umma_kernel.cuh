@@ -657,11 +657,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 if (p.split_k > 1)
                   tma_reduce_add_5d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, tc.b, conv_img);
                 else
-                  tma_store_5d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, tc.b, conv_img);
+                  for (int d = 0; d < p.num_dst; ++d)
+                    tma_store_5d(&tmap_c.dst[d], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, tc.b, conv_img);
               } else if (p.split_k > 1) {
                 tma_reduce_add_4d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, conv_img);
               } else {
-                tma_store_4d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, conv_img);
+                for (int d = 0; d < p.num_dst; ++d)
+                  tma_store_4d(&tmap_c.dst[d], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, conv_img);
               }
             }
             bulk_commit_group();

@@ -7,6 +7,9 @@ reference's ``flextensor/nn/ops.py``:
   zero_pad2d             ops.py:83-117
   conv2d_nchw            ops.py:419-479   (pad -> conv [-> bias]: a 2- or 3-op graph)
   depthwise_conv2d_nchw  ops.py:622-678   (weight layout [C, factor, kh, kw])
+  conv1d                 ops.py:293-351   (the same kernels, on a one-row image)
+  gemm_conv2d_nchw       ops.py:982-1044  (im2col -> GEMM -> col2img: the conv2d result by another route)
+  conv2d_1x1_packed      task.py:168-173  (out[b,k,i] = sum_rc A[b,rc,i] * B[k,rc])
   gemm                   ops.py:1074-1108 (four transpose variants)
   batch_gemm             ops.py:1111-1158
   gemm_int8              no ops.py symbol; contract of test/test_tvm/legacy/gemm_int8.py:15-21
@@ -72,6 +75,62 @@ def conv2d_nchw(inputs, weight, bias=None, stride=1, padding=0, dilation=1, grou
     if bias is not None:
         out = _bias_add(out, bias)
     return out
+
+
+def zero_pad1d(inputs, padding=0):
+    """Zero padding of [batch, channel, length]; padding int or (left, right)."""
+    if isinstance(padding, int):
+        padding = (padding, padding)
+    assert_print(isinstance(padding, tuple) and len(padding) == 2, "type(padding)={}".format(type(padding)))
+    b, c, l = (int(s) for s in inputs.shape)
+    op = ComputeOp("pad2d", "Padding", (b, c, l + padding[0] + padding[1]), inputs.dtype, [inputs], ("b", "c", "l"),
+                   attrs={"padding": tuple(padding)})
+    return op.output(0)
+
+
+def conv1d(inputs, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    """inputs [N,C,L], weight [K, C/groups, k] -> [N, K, out_len]: served by the conv2d kernels
+    on a one-row image (flextensor/nn/ops.py:293-351)."""
+    n, c, in_len = (int(s) for s in inputs.shape)
+    k, cg, k_len = (int(s) for s in weight.shape)
+    assert_print(cg * groups == c, "left=%d, right=%d" % (cg * groups, c))
+    assert_print(k % groups == 0)
+    stride = stride[0] if isinstance(stride, tuple) else int(stride)
+    padding = padding[0] if isinstance(padding, tuple) else int(padding)
+    dilation = int(dilation)
+    out_len = (in_len + 2 * padding - dilation * (k_len - 1) - 1) // stride + 1
+    rc = reduce_axis((0, cg), name="rc")
+    rl = reduce_axis((0, k_len), name="rl")
+    padded = zero_pad1d(inputs, padding=padding)
+    op = ComputeOp("conv2d", "compute", (n, k, out_len), _acc_dtype(inputs.dtype), [padded, weight],
+                   ("b", "c", "l"), reduce_axes=[rc, rl],
+                   attrs={"stride": (1, stride), "padding": (0, padding), "dilation": (1, dilation), "groups": groups,
+                          "form": "conv1d"})
+    out = op.output(0)
+    if bias is not None:
+        bop = ComputeOp("bias_add", "bias_add", (n, k, out_len), out.dtype, [out, bias], ("b", "c", "l"),
+                        attrs={"axis": 1})
+        out = bop.output(0)
+    return out
+
+
+def gemm_conv2d_nchw(inputs, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    """The reference builds this result as im2col -> GEMM -> col2img (flextensor/nn/ops.py:982-1044);
+    the numbers are those of ``conv2d_nchw``, and here the same implicit-GEMM kernels compute them
+    without materialising the column matrix."""
+    return conv2d_nchw(inputs, weight, bias=bias, stride=stride, padding=padding, dilation=dilation, groups=groups)
+
+
+def conv2d_1x1_packed(A, B):
+    """out[b,k,i] = sum_rc A[b,rc,i] * B[k,rc]: a 1x1 convolution on pixels packed into one axis
+    (flextensor/task.py:168-173), i.e. a batched GEMM with the same left operand for every item."""
+    n, c, hw = (int(s) for s in A.shape)
+    k, c2 = (int(s) for s in B.shape)
+    assert_print(c2 == c)
+    rc = reduce_axis((0, c), name="rc")
+    op = ComputeOp("conv2d", "compute", (n, k, hw), _acc_dtype(A.dtype), [A, B], ("b", "k", "i"), reduce_axes=[rc],
+                   attrs={"stride": (1, 1), "padding": (0, 0), "dilation": (1, 1), "groups": 1, "form": "packed_1x1"})
+    return op.output(0)
 
 
 def depthwise_conv2d_nchw(inputs, weight, bias=None, stride=1, padding=0, dilation=1):

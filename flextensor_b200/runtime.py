@@ -134,6 +134,9 @@ class Module(object):
         self._status = None
         self._workspaces = {}
         self._peer_dst = {}
+        self._conv_single_dst = {}
+        self._packed = {}      # step -> (weight tensor, its version, workspace) whose packing the workspace holds
+        self.pack_once = True  # conv2d: pack the filter on the first call only (see __call__)
         self.pushed_by_kernel = True  # False after a call whose PeerSlice output was written locally only
 
     # ------------------------------------------------------------ execution
@@ -204,12 +207,41 @@ class Module(object):
                 backend.gemm_s8(ins[0], ins[1], out, op.attrs["transposeA"], op.attrs["transposeB"], cfg=cfg,
                                 status=status)
             elif op.kind == "conv2d":
+                form = op.attrs.get("form")
+                if form == "conv1d":        # [N,C,L] is a one-row image, the filter a one-row filter
+                    ins = [ins[0].unsqueeze(2), ins[1].unsqueeze(2)]
+                    out = out.unsqueeze(2)
+                elif form == "packed_1x1":  # [N,C,HW] is a one-column image under a 1x1 filter
+                    ins = [ins[0].unsqueeze(3), ins[1].view(ins[1].shape[0], ins[1].shape[1], 1, 1)]
+                    out = out.unsqueeze(3)
                 n, c, h, w = ins[0].shape
                 k, _, r, s = ins[1].shape
                 groups = op.attrs["groups"]
                 ws = self._workspace(idx, backend.conv2d_workspace_bytes(n, c, h, w, k, r, s, groups), device)
-                backend.conv2d_nchw_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
-                                        op.attrs["dilation"], groups, cfg=cfg, workspace=ws, status=status)
+                # Weights are constant per task: the filter is packed by the first call and found in
+                # the workspace by the next ones, for as long as the same weight tensor comes back
+                # unmodified (identity and torch's version counter; `invalidate()` after changing
+                # it behind torch's back, e.g. through a raw pointer).
+                seen = self._packed.get(idx)
+                prepacked = (self.pack_once and seen is not None and seen[0] is ins[1] and
+                             seen[1] == ins[1]._version and seen[2] is ws)
+                if self.pack_once and not prepacked:
+                    self._packed[idx] = (ins[1], ins[1]._version, ws)
+                fused = False
+                if peers and len(peers) > 1 and not self._conv_single_dst.get(idx):
+                    try:
+                        backend.conv2d_nchw_f32_multi(ins[0], ins[1], peers, bias, op.attrs["stride"],
+                                                      op.attrs["padding"], op.attrs["dilation"], groups, cfg=cfg,
+                                                      workspace=ws, status=status, prepacked=prepacked)
+                        fused, peers = True, None
+                    except backend.FtbError as exc:
+                        if exc.code != -2:
+                            raise
+                        self._conv_single_dst[idx] = True  # this shape's kernel writes one destination
+                if not fused:
+                    backend.conv2d_nchw_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
+                                            op.attrs["dilation"], groups, cfg=cfg, workspace=ws, status=status,
+                                            prepacked=prepacked)
             elif op.kind == "depthwise_conv2d":
                 if peers and len(peers) > 1:
                     backend.dwconv2d_nchw_f32_multi(ins[0], ins[1], peers, bias, op.attrs["stride"],
@@ -224,6 +256,10 @@ class Module(object):
                 # this operator's kernel writes one destination: the caller still has to push the
                 # local copy to the peers (sharded.PeerSlice.push)
                 self.pushed_by_kernel = False
+
+    def invalidate(self):
+        """Forget packed filters: the next conv2d call packs its weights again."""
+        self._packed.clear()
 
     def capture(self, *arrays):
         """Record one call on these arrays into a CUDA graph; returns an object whose ``replay()``

@@ -230,11 +230,10 @@ class ShardedOp(object):
         from .utils import Config
         if gather not in GATHER_MODES:
             raise ValueError("gather must be one of %s" % (GATHER_MODES,))
-        if not dist.is_initialized():
-            raise RuntimeError("torch.distributed is not initialised")
         self.group = group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        # without a process group the operator runs on this GPU alone (world size 1)
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.batch = int(args[0])
         if self.batch % self.world:
             raise ValueError("batch %d is not a multiple of the world size %d" % (self.batch, self.world))

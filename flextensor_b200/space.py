@@ -345,8 +345,16 @@ def generate_space_intra_op_b200(op, down_graph=None):
         space.add_subspace("raster", KnobSpace("raster", [[1, 0], [2, 0], [3, 2], [3, 4], [3, 8], [3, 16]]), "reorder")
         space.add_subspace("ctas", KnobSpace("ctas", [8, 7, 6, 4]), "unroll")
     elif family == "conv2d":
-        k_out = extents["c"] // op.attrs.get("groups", 1)
-        out_h, out_w = extents["h"], extents["w"]
+        # axes (b, c, h, w); a conv1d has (b, c, l) and runs as a one-row image, the packed 1x1 form
+        # has (b, k, i) and runs as a one-column image
+        form = op.attrs.get("form")
+        k_out = extents.get("c", extents.get("k")) // op.attrs.get("groups", 1)
+        if form == "conv1d":
+            out_h, out_w = 1, extents["l"]
+        elif form == "packed_1x1":
+            out_h, out_w = extents["i"], 1
+        else:
+            out_h, out_w = extents["h"], extents["w"]
         tiles = [t for t in (32, 64, 128, 256) if t <= max(32, 2 * k_out)]
         space.add_subspace("tile_n", KnobSpace("tile_n", tiles), "spatial")
         tile_w = min(out_w, 128)
@@ -354,7 +362,9 @@ def generate_space_intra_op_b200(op, down_graph=None):
         space.add_subspace("tile_h", KnobSpace("tile_h", [h for h in range(1, max_h + 1) if h <= out_h]), "spatial")
         space.add_subspace("cluster", KnobSpace("cluster", [1, 2]), "spatial")
         rc = op.reduce_axis[0].dom.extent.value
-        taps = op.reduce_axis[1].dom.extent.value * op.reduce_axis[2].dom.extent.value
+        taps = 1
+        for axis in op.reduce_axis[1:]:
+            taps *= axis.dom.extent.value
         num_kb = taps * math.ceil(rc / 32)
         space.add_subspace("stages", KnobSpace("stages", [2, 3, 4, 5, 6, 7, 8]), "reduce")
         space.add_subspace("split_k", KnobSpace("split_k", [s for s in (1, 2, 3, 4, 6, 9) if s <= num_kb]), "reduce")

@@ -14,10 +14,12 @@ from .configs.conv2d_config import (yolo_shapes, res_shapes, res_shapes_b1, goog
                                     vgg_16_shapes, test_conv_shapes, yolo_shapes_b8, mobilev2_shapes,
                                     overfeat_shapes, b200_conv2d_shape)
 from .configs.depthwise_config import depthwise_shapes, depthwise_shapes_b8, depthwise_shapes_b16, b200_depthwise_shape
+from .configs.grouped_config import grouped_shapes, dilation_shapes
+from .configs.conv1d_config import conv1d_shapes
 from .configs.gemm_config import gemm_shapes, test_gemm_shapes, b200_batch_gemm_shapes, b200_gemm_int8_shapes
 from .ir import placeholder
 from .nn import conv2d_nchw, depthwise_conv2d_nchw, gemm as op_gemm, batch_gemm as op_batch_gemm, \
-    gemm_int8 as op_gemm_int8
+    gemm_int8 as op_gemm_int8, conv1d as op_conv1d, gemm_conv2d_nchw, conv2d_1x1_packed as op_1x1_packed
 from .space import EnumSpace
 
 TASK_TABLE = {}
@@ -56,6 +58,27 @@ def conv2d(N, C, H, W, K, kernel_size, stride=1, padding=0, dilation=1, groups=1
     Wt = placeholder((K, C // groups, kernel_size, kernel_size))
     Output = conv2d_nchw(Img, Wt, stride=stride, padding=padding, dilation=dilation, groups=groups)
     return [Output.op], [Img, Wt, Output]
+
+
+def conv1d(N, C, L, K, kernel, stride=1, padding=0, dilation=1, groups=1):
+    Seq = placeholder((N, C, L))
+    Wt = placeholder((K, C // groups, kernel))
+    Output = op_conv1d(Seq, Wt, stride=stride, padding=padding, dilation=dilation, groups=groups)
+    return [Output.op], [Seq, Wt, Output]
+
+
+def gemm_conv2d(N, C, H, W, K, kernel_size, stride=1, padding=0, dilation=1, groups=1):
+    Img = placeholder((N, C, H, W))
+    Wt = placeholder((K, C // groups, kernel_size, kernel_size))
+    Output = gemm_conv2d_nchw(Img, Wt, stride=stride, padding=padding, dilation=dilation, groups=groups)
+    return [Output.op], [Img, Wt, Output]
+
+
+def conv2d_1x1_packed(N, C, H, W, K, kernel_size):
+    A = placeholder((N, C, H * W))
+    B = placeholder((K, C))
+    Output = op_1x1_packed(A, B)
+    return [Output.op], [A, B, Output]
 
 
 def depthwise_conv2d(N, C, H, W, factor, kernel_size, stride=1, padding=0, dilation=1):
@@ -112,6 +135,28 @@ for _name, _shapes in conv2d_shape_dict.items():
     for _i, _shape in enumerate(_shapes):
         _b, _c, _h, _w, _k, _, _kh, _kw, _, _st, _pad, _dil, _grp = _shape
         _register_all("conv2d", _name + str(_i), conv2d, (_b, _c, _h, _w, _k, _kh, _st, _pad, _dil, _grp))
+
+# the same layer lists through the im2col -> GEMM -> col2img definition (task.py:346-363 registers them
+# for every conv2d table; the batch-1 YOLO and ResNet lists are kept here)
+for _name in ("yolo", "res_b1"):
+    for _i, _shape in enumerate(conv2d_shape_dict[_name]):
+        _b, _c, _h, _w, _k, _, _kh, _kw, _, _st, _pad, _dil, _grp = _shape
+        _register_all("gemm_conv2d", _name + str(_i), gemm_conv2d, (_b, _c, _h, _w, _k, _kh, _st, _pad, _dil, _grp))
+
+for _shape in grouped_shapes:
+    _b, _c, _h, _w, _k, _kh, _, _st, _pad, _dil, _grp = _shape
+    _register_all("conv2d", "grouped", conv2d, (_b, _c, _h, _w, _k, _kh, _st, _pad, _dil, _grp))
+
+for _shape in dilation_shapes:
+    _b, _c, _h, _w, _k, _kh, _, _st, _pad, _dil, _grp = _shape
+    _register_all("conv2d", "dilation", conv2d, (_b, _c, _h, _w, _k, _kh, _st, _pad, _dil, _grp))
+
+for _shape in conv1d_shapes:
+    _b, _c, _l, _k, _, _kl, _, _st, _pad, _dil, _grp = _shape
+    _register_all("conv1d", "conv1d", conv1d, (_b, _c, _l, _k, _kl, _st, _pad, _dil, _grp))
+
+# the packed 1x1 convolution (task.py:218 registers this one shape)
+_register_all("conv2d", "1x1-packed", conv2d_1x1_packed, (256, 256, 14, 14, 512, 1))
 
 for _shape in list(depthwise_shapes) + list(depthwise_shapes_b8) + list(depthwise_shapes_b16) + [b200_depthwise_shape]:
     _b, _c, _h, _w, _f, _k, _, _st, _pad, _dil = _shape

@@ -9,8 +9,22 @@ search produces to a ``{knob: value}`` dict.  The positional layout is
 """
 from .space import B200_LAYOUT, op_family
 
-# number of SMs the 'ctas' knob is a fraction of is resolved at launch (0 = all SMs)
-_NUM_SMS_B200 = 148
+_SM_COUNT = {}
+
+
+def sm_count(device=None):
+    """SMs of the device the 'ctas' knob is a fraction of (the current CUDA device by default);
+    148, a B200, where no GPU is visible (planning on a CPU-only host)."""
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return 148
+        index = torch.cuda.current_device() if device is None else int(device)
+        if index not in _SM_COUNT:
+            _SM_COUNT[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+        return _SM_COUNT[index]
+    except Exception:
+        return 148
 
 
 def config_to_knobs(config, op):
@@ -34,7 +48,7 @@ def config_to_knobs(config, op):
             elif name == "ctas":
                 eighths = int(entity[0])
                 if 0 < eighths < 8:
-                    knobs["ctas"] = max(2, (_NUM_SMS_B200 * eighths // 8) & ~1)
+                    knobs["ctas"] = max(2, (sm_count() * eighths // 8) & ~1)
             else:
                 knobs[name] = int(entity[0])
     return knobs
@@ -55,7 +69,7 @@ def knobs_to_config(knobs, op):
                 config[type_key].append([int(knobs.get("raster", 0)), int(knobs.get("group_m", 0))])
             elif name == "ctas":
                 ctas = int(knobs.get("ctas", 0))
-                config[type_key].append([8 if ctas <= 0 else max(1, min(8, round(ctas * 8 / _NUM_SMS_B200)))])
+                config[type_key].append([8 if ctas <= 0 else max(1, min(8, round(ctas * 8 / sm_count())))])
             else:
                 config[type_key].append([int(knobs.get(name, defaults.get(name, 0)))])
     return config

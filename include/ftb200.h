@@ -142,6 +142,36 @@ int ftb_conv2d_nchw_f32(const float* in, const float* weight, const float* bias,
                         int groups, const ftb_config* cfg, void* workspace, size_t workspace_bytes,
                         int* status, void* stream);
 
+/* Filter packing taken off the per-call path (weights are constant per task: the reference
+ * binds them as a placeholder of the task, flextensor/task.py:74-78).  ftb_conv2d_pack_filter writes the
+ * packed form of `weight` into the filter region of `workspace` and returns; after it,
+ * ftb_conv2d_nchw_f32_prepacked runs the conv with the SAME shape arguments, knobs and workspace
+ * and only lays out the input.  `weight` is still passed (1x1 filters that run as a GEMM on the
+ * NCHW tensors read it as it is).  The caller re-packs when the weights change. */
+int ftb_conv2d_pack_filter(const float* weight, int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r,
+                           int64_t s, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                           int groups, const ftb_config* cfg, void* workspace, size_t workspace_bytes,
+                           void* stream);
+int ftb_conv2d_nchw_f32_prepacked(const float* in, const float* weight, const float* bias, float* out, int64_t n,
+                                  int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,
+                                  int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
+                                  const ftb_config* cfg, void* workspace, size_t workspace_bytes, int* status,
+                                  void* stream);
+
+/* The same, with the result written to `num_dst` (1..8) buffers at once: c_dst-style host array of
+ * device pointers to [N,K,P,Q] buffers, this GPU's or a peer GPU's mapped memory (16-byte
+ * aligned).  The batch-sharded path places a rank's images in every rank's gathered output this
+ * way (bulk tensor stores over NVLink from the conv epilogue).  Only the epilogues that leave
+ * through bulk stores can do it: output rows of a multiple of 16 bytes, no reduction split over
+ * CTAs; anything else returns FTB_E_UNSUPPORTED and the caller copies the result itself.
+ * `prepacked` != 0: the workspace already holds the filter's packing (see above).  No
+ * counterpart in the reference (it is single-device). */
+int ftb_conv2d_nchw_f32_multi(const float* in, const float* weight, const float* bias, float* const* out_dst,
+                              int num_dst, int64_t n, int64_t c, int64_t h, int64_t w, int64_t k, int64_t r,
+                              int64_t s, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                              int groups, int prepacked, const ftb_config* cfg, void* workspace,
+                              size_t workspace_bytes, int* status, void* stream);
+
 /* conv2d without a caller workspace - no counterpart in the reference.
  *
  * For callers that cannot allocate device memory: code that receives its input and output

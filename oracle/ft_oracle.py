@@ -76,6 +76,22 @@ def conv2d_nchw(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1,
     return out.astype(out_dtype)
 
 
+def conv1d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, acc="f64", out_dtype=np.float32):
+    """out[b,c,l] = sum_{rc,rl} padded[b, c//Kg*Cg + rc, l*stride + rl*dilation] * weight[c,rc,rl]
+    (flextensor/nn/ops.py:339-347): the 2-d expression with one image row."""
+    n, c, length = x.shape
+    k, cg, k_len = weight.shape
+    out = conv2d_nchw(x.reshape(n, c, 1, length), weight.reshape(k, cg, 1, k_len), bias, (1, stride), (0, padding),
+                      (1, dilation), groups, acc=acc, out_dtype=out_dtype)
+    return out.reshape(n, k, -1)
+
+
+def conv2d_1x1_packed(a, b, acc="f64", out_dtype=np.float32):
+    """out[b,k,i] = sum_rc A[b,rc,i] * B[k,rc] (flextensor/task.py:168-173)."""
+    at = _acc_dtype(acc)
+    return np.einsum("bci,kc->bki", a.astype(at), b.astype(at), optimize=True).astype(out_dtype)
+
+
 def depthwise_conv2d_nchw(x, weight, bias=None, stride=1, padding=0, dilation=1, acc="f64", out_dtype=np.float32):
     stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
     n, c, h, w = x.shape

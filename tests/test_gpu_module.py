@@ -141,3 +141,103 @@ def test_gpu_pool_measurer_and_failures(native_lib):
     finally:
         pool.close()
     assert 0 < res[0] < 100 and res[1] == float("inf") and 0 < res[2] < 100
+
+
+def test_conv_filter_is_packed_once_per_weight_tensor(native_lib):
+    """The second call with the same weight tensor finds the packed filter in the workspace (the
+    layout pass then only copies the input) and gives the same bits; a modified or another weight
+    tensor is packed again; every algorithm's filter layout goes through the same path."""
+    from flextensor_b200 import backend as B
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config
+    from flextensor_b200.task import Task, conv2d, register_task
+    from flextensor_b200.templates import knobs_to_config
+    from flextensor_b200.utils import Config
+    for args, knobs in (((2, 32, 28, 28, 48, 3, 1, 1, 1, 1), {"algo": 2}),        # slab kernel
+                        ((2, 40, 20, 24, 48, 3, 2, 1, 1, 1), {"algo": 1}),        # per-tap lowering
+                        ((1, 3, 64, 64, 16, 7, 2, 3, 1, 1), {"algo": 4}),         # im2col rows
+                        ((2, 64, 14, 14, 32, 1, 1, 0, 1, 1), {"algo": 3}),        # GEMM on the NCHW tensors: no packing
+                        ((2, 18, 15, 16, 12, 3, 1, 1, 1, 6), {"algo": 1})):       # groups of 3 channels
+        task = Task("conv2d", "packonce", conv2d, args, "cuda", 0)
+        register_task(task)
+        op = task.func(*task.args)[0][0]
+        s, bufs = schedule_with_config(task.key, Config([{}, knobs_to_config(knobs, op)], None))
+        func = build(s, bufs)
+        n, c, h, w, k, r, stride, pad, dil, groups = args
+        x, wt = O.conv2d_inputs(n, c, h, w, k, r, r, groups=groups, seed=81)
+        want = O.conv2d_nchw(x, wt, None, stride, pad, dil, groups)
+        xd, wd = dev(x), dev(wt)
+        out1 = torch.full(want.shape, float("nan"), device="cuda")
+        out2 = torch.full(want.shape, float("nan"), device="cuda")
+        func(xd, wd, out1)
+        assert func._packed, "first call records the packed weight"
+        func(xd, wd, out2)                       # packed filter reused
+        func.check()
+        assert torch.equal(out1, out2)
+        assert O.normalised_error(out2.cpu().numpy(), want) <= O.TOLERANCE["conv2d_tf32"], args
+        wd.mul_(2.0)                             # in-place change bumps the version: packed again
+        func(xd, wd, out2)
+        func.check()
+        assert O.normalised_error(out2.cpu().numpy(), 2.0 * want) <= O.TOLERANCE["conv2d_tf32"], args
+        wd2 = dev(-wt)                           # another tensor: packed again
+        func(xd, wd2, out2)
+        func(xd, wd2, out1)
+        func.check()
+        assert torch.equal(out1, out2)
+        assert O.normalised_error(out1.cpu().numpy(), -want) <= O.TOLERANCE["conv2d_tf32"], args
+
+
+@pytest.mark.parametrize("args", [(2, 24, 200, 36, 9, 1, 4, 1, 3), (1, 16, 333, 8, 3, 2, 1, 2, 1),
+                                  (3, 64, 196, 128, 1, 1, 0, 1, 1)])
+def test_conv1d_task_runs_on_the_conv2d_kernels(native_lib, args):
+    """conv1d (flextensor/nn/ops.py:293-351) through Task -> schedule_with_config -> build."""
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config
+    from flextensor_b200.task import Task, conv1d, register_task
+    from flextensor_b200.utils import Config
+    n, c, length, k, k_len, stride, pad, dil, groups = args
+    task = Task("conv1d", "conv1d", conv1d, args, "cuda", 0)
+    register_task(task)
+    s, bufs = schedule_with_config(task.key, Config([{}, {}], None))
+    func = build(s, bufs)
+    rng = np.random.default_rng(83)
+    x = rng.standard_normal((n, c, length)).astype(np.float32)
+    w = rng.standard_normal((k, c // groups, k_len)).astype(np.float32)
+    want = O.conv1d(x, w, None, stride, pad, dil, groups)
+    out = torch.full(want.shape, float("nan"), device="cuda")
+    assert tuple(bufs[-1].shape) == want.shape
+    func(dev(x), dev(w), out)
+    func.check()
+    assert O.normalised_error(out.cpu().numpy(), want) <= O.TOLERANCE["conv2d_tf32"]
+
+
+def test_packed_1x1_and_gemm_conv2d_tasks(native_lib):
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config
+    from flextensor_b200.task import Task, conv2d_1x1_packed, gemm_conv2d, register_task
+    from flextensor_b200.utils import Config
+    # out[b,k,i] = sum_rc A[b,rc,i] * B[k,rc]  (flextensor/task.py:168-173)
+    task = Task("conv2d", "1x1-packed", conv2d_1x1_packed, (5, 48, 14, 14, 72, 1), "cuda", 0)
+    register_task(task)
+    s, bufs = schedule_with_config(task.key, Config([{}], None))
+    func = build(s, bufs)
+    rng = np.random.default_rng(84)
+    a = rng.standard_normal((5, 48, 196)).astype(np.float32)
+    b = rng.standard_normal((72, 48)).astype(np.float32)
+    want = O.conv2d_1x1_packed(a, b)
+    out = torch.full(want.shape, float("nan"), device="cuda")
+    func(dev(a), dev(b), out)
+    func.check()
+    assert O.normalised_error(out.cpu().numpy(), want) <= O.TOLERANCE["conv2d_tf32"]
+    # the im2col -> GEMM -> col2img definition gives the conv2d numbers (flextensor/nn/ops.py:982-1044)
+    args = (2, 12, 13, 16, 18, 3, 2, 1, 1, 3)
+    task = Task("gemm_conv2d", "t", gemm_conv2d, args, "cuda", 0)
+    register_task(task)
+    s, bufs = schedule_with_config(task.key, Config([{}, {}], None))
+    func = build(s, bufs)
+    x, w = O.conv2d_inputs(2, 12, 13, 16, 18, 3, 3, groups=3, seed=85)
+    want = O.conv2d_nchw(x, w, None, 2, 1, 1, 3)
+    out = torch.full(want.shape, float("nan"), device="cuda")
+    func(dev(x), dev(w), out)
+    func.check()
+    assert O.normalised_error(out.cpu().numpy(), want) <= O.TOLERANCE["conv2d_tf32"]

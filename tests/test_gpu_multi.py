@@ -68,6 +68,8 @@ def _rank_main(rank, world, port, results):
         torch.cuda.synchronize()
         op.check()
         outcome[name] = bool(check(op.out_full))
+        if op.gather == "fused":
+            outcome[name + "_by_kernel"] = bool(op.func.pushed_by_kernel)
 
     try:
         # ---- batched GEMM bf16: raw multi-destination entry point, then the same through the task interface
@@ -116,6 +118,18 @@ def _rank_main(rank, world, port, results):
             op = ShardedOp("conv2d", "sharded", conv2d, (nimg, 12, 14, 16, 24, 3, 1, 1, 1, 4), gather=mode)
             run_sharded("conv2d_" + mode, op, (dev(x[lo:hi]), dev(w)),
                         lambda full: O.normalised_error(full.cpu().numpy(), want_conv) <= O.TOLERANCE["conv2d_tf32"])
+        # one group, stride 1: the slab kernel, whose epilogue also stores into every rank's buffer
+        xs, ws_ = O.conv2d_inputs(nimg, 32, 14, 16, 40, 3, 3, seed=74)
+        want_slab = O.conv2d_nchw(xs, ws_, None, 1, 1, 1, 1)
+        op = ShardedOp("conv2d", "sharded_slab", conv2d, (nimg, 32, 14, 16, 40, 3, 1, 1, 1, 1), gather="fused")
+        run_sharded("conv2d_slab_fused", op, (dev(xs[lo:hi]), dev(ws_)),
+                    lambda full: O.normalised_error(full.cpu().numpy(), want_slab) <= O.TOLERANCE["conv2d_tf32"])
+        # output rows of 15 floats cannot leave through bulk stores: one destination, pushed afterwards
+        xo, wo = O.conv2d_inputs(nimg, 8, 9, 15, 8, 3, 3, seed=75)
+        want_odd = O.conv2d_nchw(xo, wo, None, 1, 1, 1, 1)
+        op = ShardedOp("conv2d", "sharded_odd", conv2d, (nimg, 8, 9, 15, 8, 3, 1, 1, 1, 1), gather="fused")
+        run_sharded("conv2d_odd_fused", op, (dev(xo[lo:hi]), dev(wo)),
+                    lambda full: O.normalised_error(full.cpu().numpy(), want_odd) <= O.TOLERANCE["conv2d_tf32"])
         xd, wd = O.depthwise_inputs(nimg, 16, 28, 28, 2, 3, 3, seed=73)
         want_dw = O.depthwise_conv2d_nchw(xd, wd, None, 1, 1, 1)
         for mode in ("fused", "push", "nccl"):
@@ -139,8 +153,12 @@ def _rank_main(rank, world, port, results):
             pass
 
 
-EXPECTED = ["bgemm_raw_fused", "bgemm_nccl", "bgemm_module_fused", "bgemm_module_nccl", "conv2d_fused", "conv2d_push",
-            "conv2d_nccl", "depthwise_fused", "depthwise_push", "depthwise_nccl"]
+EXPECTED = {"bgemm_raw_fused": True, "bgemm_nccl": True, "bgemm_module_fused": True, "bgemm_module_fused_by_kernel": True,
+            "bgemm_module_nccl": True, "conv2d_fused": True, "conv2d_fused_by_kernel": True, "conv2d_push": True,
+            "conv2d_nccl": True, "conv2d_slab_fused": True, "conv2d_slab_fused_by_kernel": True,
+            "conv2d_odd_fused": True, "conv2d_odd_fused_by_kernel": False,
+            "depthwise_fused": True, "depthwise_fused_by_kernel": True, "depthwise_push": True,
+            "depthwise_nccl": True}
 
 
 def test_sharded_operators_fused_push_and_nccl(native_lib):
@@ -160,7 +178,7 @@ def test_sharded_operators_fused_push_and_nccl(native_lib):
     for p in stuck:
         p.terminate()
     assert not stuck, "ranks did not finish"
-    assert dict(results) == {r: {name: True for name in EXPECTED} for r in range(world)}
+    assert dict(results) == {r: EXPECTED for r in range(world)}
 
 
 def test_measurement_pool_uses_every_gpu(native_lib):

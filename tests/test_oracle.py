@@ -131,3 +131,25 @@ def test_batch_items_do_not_depend_on_shard_count():
     a1, _ = O.batch_gemm_item(5, 8, 8, 8)
     a2, _ = O.batch_gemm_item(6, 8, 8, 8)
     assert (a0 == a1).all() and not (a0 == a2).all()
+
+
+def test_conv1d_and_packed_1x1_restatements_against_torch():
+    """conv1d with groups, stride and dilation against torch CPU (the comparator the reference's op
+    tests use); the packed 1x1 form against a literal loop nest."""
+    import torch
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((2, 6, 31)).astype(np.float32)
+    w = rng.standard_normal((9, 2, 4)).astype(np.float32)
+    b = rng.standard_normal(9).astype(np.float32)
+    got = O.conv1d(x, w, b, stride=2, padding=3, dilation=2, groups=3)
+    want = torch.nn.functional.conv1d(torch.tensor(x), torch.tensor(w), torch.tensor(b), stride=2, padding=3,
+                                      dilation=2, groups=3).numpy()
+    assert got.shape == want.shape and O.normalised_error(got, want) < 1e-5
+    a = rng.standard_normal((2, 5, 7)).astype(np.float32)
+    m = rng.standard_normal((3, 5)).astype(np.float32)
+    loops = np.zeros((2, 3, 7))
+    for bi in range(2):
+        for k in range(3):
+            for i in range(7):
+                loops[bi, k, i] = sum(float(a[bi, rc, i]) * float(m[k, rc]) for rc in range(5))
+    assert O.normalised_error(O.conv2d_1x1_packed(a, m), loops) < 1e-6

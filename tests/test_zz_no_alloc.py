@@ -19,7 +19,8 @@ from oracle import ft_oracle as O
 pytestmark = pytest.mark.gpu
 
 
-def _both(B, x, w, bias, stride, pad, dil, groups, status):
+def _both(B, x, w, bias, stride, pad, dil, groups, status, cfg=None):
+    cfg = {"fp32_mode": 1, "split_k": 1} if cfg is None else cfg
     n, c, h, wd = x.shape
     k, _, r, s = w.shape
     p = O.out_size(h, r, stride, pad, dil)
@@ -29,11 +30,11 @@ def _both(B, x, w, bias, stride, pad, dil, groups, status):
     args = (bd, (stride, stride), (pad, pad), (dil, dil), groups)
     ref = torch.full((n, k, p, q), float("nan"), device="cuda")
     ws = torch.empty(B.conv2d_workspace_bytes(n, c, h, wd, k, r, s, groups), dtype=torch.uint8, device="cuda")
-    B.conv2d_nchw_f32(xd, wdv, ref, *args, cfg={"fp32_mode": 1, "split_k": 1}, workspace=ws, status=status)
+    B.conv2d_nchw_f32(xd, wdv, ref, *args, cfg=cfg, workspace=ws, status=status)
     got = torch.full((n, k, p, q), float("nan"), device="cuda")
     torch.cuda.synchronize()
     allocated = torch.cuda.memory_allocated()
-    B.conv2d_nchw_f32_noalloc(xd, wdv, got, *args, cfg={"fp32_mode": 1, "split_k": 1}, status=status)
+    B.conv2d_nchw_f32_noalloc(xd, wdv, got, *args, cfg=cfg, status=status)
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == allocated     # torch's allocator was not touched either
     return got.cpu().numpy(), ref.cpu().numpy()
@@ -54,6 +55,35 @@ def test_noalloc_conv_matches_regular_entry_point_twice(native_lib):
     got, ref = _both(B, x, w, bias, 2, 2, 2, 3, status)
     assert np.array_equal(got, ref)
     assert O.normalised_error(got, O.conv2d_nchw(x, w, bias, 2, 2, 2, 3)) <= O.TOLERANCE["conv2d_3xtf32"]
+    B.check_status(status)
+
+
+def test_noalloc_conv_every_workspace_layout_back_to_back(native_lib):
+    """The shared array is laid out differently by each lowering of the conv: a channels-last copy
+    (per-tap and slab kernels), one row of taps x channels per output pixel (few input channels),
+    only the pixels a strided 1x1 filter reads, groups padded to four channels.  Each case runs
+    straight after one that left another layout behind and must still agree with the regular
+    entry point: bit for bit where the kernels add nothing in global memory, within the conv
+    tolerance where the library's default splits the reduction over CTAs."""
+    from flextensor_b200 import backend as B
+    status = B.new_status()
+    cases = [
+        # (n, c, h, w, k, r, stride, pad, groups, cfg, exact)
+        (1, 3, 64, 64, 16, 7, 2, 3, 1, {"algo": 4, "split_k": 1}, True),      # im2col rows
+        (2, 32, 28, 28, 48, 3, 1, 1, 1, {"algo": 2, "split_k": 1}, True),     # slab kernel, default TF32
+        (2, 64, 28, 28, 32, 1, 2, 0, 1, {"algo": 1, "split_k": 1}, True),     # strided 1x1: kept pixels only
+        (1, 64, 56, 56, 64, 3, 1, 1, 1, {}, False),                           # library defaults: split reduction
+        (2, 18, 15, 13, 12, 3, 1, 1, 6, {"split_k": 1}, True),                # 3 channels per group, padded to 4
+        (1, 3, 64, 64, 16, 7, 2, 3, 1, {"algo": 4, "split_k": 1}, True),      # and the first layout again
+    ]
+    for n, c, h, w, k, r, stride, pad, groups, cfg, exact in cases:
+        x, wt = O.conv2d_inputs(n, c, h, w, k, r, r, groups=groups, seed=5)
+        got, ref = _both(B, x, wt, None, stride, pad, 1, groups, status, cfg=cfg)
+        if exact:
+            assert np.array_equal(got, ref), (n, c, h, w, k, r, stride, pad, groups, cfg)
+        else:
+            assert O.normalised_error(got, ref) <= O.TOLERANCE["conv2d_tf32"]
+        assert O.normalised_error(got, O.conv2d_nchw(x, wt, None, stride, pad, 1, groups)) <= O.TOLERANCE["conv2d_tf32"]
     B.check_status(status)
 
 
