@@ -41,7 +41,7 @@ KNOBS = {"cluster": 2, "tile_n": 512, "raster": 3, "group_m": 8}
 # N > 1 with the fused gather: the epilogue's bulk stores cross NVLink and take longer, and the
 # 256 x 512 tile overlaps its epilogue with the next main loop only half by half; the 256 x 256
 # tile (whole-tile overlap) is the faster one there (measured at N = 2: 0.48 ms against 0.66 ms).
-KNOBS_FUSED = {"cluster": 2, "tile_n": 256, "raster": 3, "group_m": 4}
+KNOBS_FUSED = {"cluster": 2, "tile_n": 256, "raster": 3, "group_m": 4, "stages": 6, "release": 2}
 # Receive bandwidth per GPU (GB/s) when every rank pushes its slice into all the others at the same
 # time, by world size; 770 is the one-pair peer copy measured on this pool.
 ALL_TO_ALL_GBS = {2: 770.0, 4: 770.0, 8: 770.0}

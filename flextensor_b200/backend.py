@@ -45,11 +45,13 @@ class FtbConfig(ctypes.Structure):
         ("cluster", ctypes.c_int32),
         ("algo", ctypes.c_int32),
         ("epilogue", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 4),
+        ("release", ctypes.c_int32),
+        ("relu", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 2),
     ]
 
     KNOBS = ("tile_n", "stages", "raster", "group_m", "split_k", "fp32_mode", "ctas", "tile_h", "threads",
-             "cluster", "algo", "epilogue")
+             "cluster", "algo", "epilogue", "release", "relu")
 
     @classmethod
     def from_dict(cls, knobs):
@@ -215,13 +217,14 @@ def launch_count():
 
 
 WAIT_PROFILE_SLOTS = ("producer_wait_empty", "issuer_wait_full", "issuer_wait_tmem_free", "epilogue_wait_tmem_full",
-                      "producer_loop", "issuer_loop", "epilogue_loop", "ctas")
+                      "producer_loop", "issuer_loop", "epilogue_loop", "ctas", "epilogue_tmem_ld",
+                      "epilogue_bulk_wait", "epilogue_stage", "unused")
 
 
 def wait_profile(reset=True):
     """Cycle counters of a wait-profiling build (``FTB200_LIBRARY`` pointing at it) as a dict;
     raises ``FtbError`` (unsupported) on the product build."""
-    arr = (ctypes.c_uint64 * 8)()
+    arr = (ctypes.c_uint64 * 12)()
     rc = lib().ftb_debug_wait_profile(arr, int(reset))
     if rc:
         raise FtbError(rc, "ftb_debug_wait_profile")

@@ -40,6 +40,7 @@ struct ConvSlabParams {
   int a_stages;
   // staged epilogue: epi_bufs (0 = off, 1 or 2) buffers of 32 channels x tile pixels after the slabs
   int epi_bufs;
+  int relu;     // clamp the result at zero after the bias (never with split taps)
   int num_dst;  // destinations of the staged epilogue (1..kMaxDst): the same box goes to each of them
   uint32_t epi_buf_bytes;
   uint32_t slab_bytes;   // bytes one slab load delivers
@@ -277,6 +278,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
               for (int j = 0; j < 32; ++j) {
                 float x = __uint_as_float(v[j]);
                 if (add_bias && c + j < p.N) x += p.bias[c + j];
+                if (p.relu) x = fmaxf(x, 0.0f);
                 st_shared_f32(buf + static_cast<uint32_t>(j) * ch_stride + px_off, x);
               }
             }
@@ -317,6 +319,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             if (n < p.N) {
               float x = __uint_as_float(v[j]);
               if (p.bias != nullptr && ks == 0) x += p.bias[n];
+              if (p.relu) x = fmaxf(x, 0.0f);
               float* dst = dst0 + n * plane;
               if (p.split > 1) atomicAdd(dst, x);
               else *dst = x;

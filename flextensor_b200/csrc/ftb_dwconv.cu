@@ -28,14 +28,17 @@ struct DwParams {
   // rank's gathered output with plain stores.
   float* extra[7];
   int num_extra;
+  int relu;  // clamp the result at zero after the bias
 };
 
 // Byte distance from `out` to the d-th extra destination is the same for every element.
-__device__ __forceinline__ void dw_store4(const DwParams& p, float* dst, const float4& v) {
+__device__ __forceinline__ void dw_store4(const DwParams& p, float* dst, float4 v) {
+  if (p.relu) v = make_float4(fmaxf(v.x, 0.f), fmaxf(v.y, 0.f), fmaxf(v.z, 0.f), fmaxf(v.w, 0.f));
   *reinterpret_cast<float4*>(dst) = v;
   for (int d = 0; d < p.num_extra; ++d) *reinterpret_cast<float4*>(p.extra[d] + (dst - p.out)) = v;
 }
 __device__ __forceinline__ void dw_store1(const DwParams& p, float* dst, float v) {
+  if (p.relu) v = fmaxf(v, 0.f);
   *dst = v;
   for (int d = 0; d < p.num_extra; ++d) p.extra[d][dst - p.out] = v;
 }
@@ -301,6 +304,8 @@ static int dwconv_generic(const float* in, const float* weight, const float* bia
   DwParams p;
   memset(&p, 0, sizeof(p));
   p.in = in; p.w = weight; p.bias = bias; p.out = out;
+  if (cfg && (cfg->relu < 0 || cfg->relu > 1)) return FTB_E_BAD_CONFIG;
+  p.relu = cfg ? cfg->relu : 0;
   p.num_extra = num_extra;
   for (int d = 0; d < num_extra; ++d) {
     // the vector stores need every destination as aligned as the first

@@ -484,6 +484,10 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   p.tma_store = (store_ok && p.bn % p.slab_cols == 0 &&
                  (p.split_k == 1 || (out == OUT_F32 && num_extra == 0))) ? 1 : 0;
   p.diag = user ? user->reserved[0] : 0;
+  if (user && (user->release < 0 || user->release > 2)) return FTB_E_BAD_CONFIG;
+  // (the 256 x 512 tile keeps the per-stage hand-back: its four stages are too few to give one up)
+  p.release_pairs = (user && user->release == 2 && !split3 && cfg.tile_n != 512 && cfg.stages % 2 == 0 &&
+                     cfg.stages >= 4) ? 1 : 0;
   p.num_dst = 1 + num_extra;
   if (num_extra > 0 && !p.tma_store) return FTB_E_UNSUPPORTED;  // several destinations only through bulk stores
 
@@ -1009,11 +1013,14 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   // Several destinations exist only in the epilogues that leave through bulk tensor stores and
   // add nothing in global memory: the reduction is then kept inside one CTA per tile.
   ftb_config multi_cfg;
-  if (num_extra > 0) {
+  if (user && (user->relu < 0 || user->relu > 1)) return FTB_E_BAD_CONFIG;
+  const int relu = user ? user->relu : 0;
+  if (num_extra > 0 || relu) {
     memset(&multi_cfg, 0, sizeof(multi_cfg));
     if (user) multi_cfg = *user;
-    if (multi_cfg.split_k > 1 || multi_cfg.epilogue == 1) return FTB_E_UNSUPPORTED;
-    multi_cfg.split_k = 1;
+    if (multi_cfg.split_k > 1) return num_extra > 0 ? FTB_E_UNSUPPORTED : FTB_E_BAD_CONFIG;
+    if (num_extra > 0 && multi_cfg.epilogue == 1) return FTB_E_UNSUPPORTED;
+    multi_cfg.split_k = 1;  // partial sums cannot be clamped, nor added into a peer's memory
     user = &multi_cfg;
   }
   if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || k <= 0 || r <= 0 || s <= 0 || groups <= 0) return FTB_E_BAD_ARG;
@@ -1047,7 +1054,8 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
                          groups == 1 && (h * w) % 4 == 0 && c % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
     if (algo == 3 && !is_gemm && !pack_only) return FTB_E_UNSUPPORTED;
-    if (is_gemm && (algo == 0 || algo == 3) && !pack_only) {
+    if (algo == 3 && relu) return FTB_E_UNSUPPORTED;  // the GEMM epilogue has no clamp
+    if (is_gemm && (algo == 0 || algo == 3) && !pack_only && !relu) {
       ftb_config gcfg;
       memset(&gcfg, 0, sizeof(gcfg));
       if (user) {
@@ -1115,6 +1123,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     sp.p.out = out;
     sp.p.bias = bias;
+    sp.p.relu = relu;
     sp.p.conv_ktot = static_cast<int>(k);
     sp.p.status = status ? status : fallback_status();
     if (!sp.p.status) return FTB_E_CUDA;
@@ -1233,7 +1242,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   if (num_extra > 0 && !staged) return FTB_E_UNSUPPORTED;
   const bool pair = cfg.cluster == 2;
   const long long tiles_m_launch = pair ? (tiles_m + 1) / 2 : tiles_m;
-  if (!conv_tuned && (!user || user->split_k == 0) && num_extra == 0) {
+  if (!conv_tuned && (!user || user->split_k == 0) && num_extra == 0 && !relu) {
     // A short tile list leaves SMs idle: split the reduction so that about all SMs get work (the
     // partial sums meet in global memory through bulk reduce-adds into the zeroed result).
     const long long tiles = groups * tiles_m_launch * ((kg + cfg.tile_n - 1) / cfg.tile_n);
@@ -1316,6 +1325,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.pdl = 1;  // directly follows the layout pass
     p.conv_ktot = static_cast<int>(k);
     p.conv_koff = 0;
+    p.relu = relu;
     p.C = out;
     p.bias = bias;
     p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);

@@ -81,6 +81,11 @@ struct UmmaParams {
   // TMA-store epilogue: tma_store != 0 stages 128-byte wide output slabs in shared memory and
   // writes each with one bulk tensor store per destination.
   int tma_store, num_dst, slab_cols;
+  // 1: stages are handed back to the producer two at a time (one commit per two K blocks; needs an
+  // even number of stages).  A commit costs the tensor pipe about 80 cycles, so on tiles whose K block
+  // is a few hundred cycles of math the saving outweighs the slightly shorter prefetch.
+  int release_pairs;
+  int relu;  // conv: clamp the result at zero after the bias (never with a reduction split over CTAs)
   // diagnostic builds (-DFTB_PROFILE_WAITS) only: bit 0 = the producer signals stages without
   // loading them, bit 1 = the issuer releases stages without issuing MMAs, bit 2 = no producer at
   // all and an issuer that neither waits for stages nor releases them: MMAs back to back (results
@@ -110,7 +115,10 @@ enum {
   PROF_ISSUER_LOOP = 5,     // whole issuer loop
   PROF_EPI_LOOP = 6,        // whole epilogue loop of warp 2
   PROF_CTAS = 7,            // CTAs that reported
-  PROF_SLOTS = 8
+  PROF_EPI_TMEM_LD = 8,     // epilogue warp 2 (wide tiles, staged): inside the tcgen05.ld of its columns + wait
+  PROF_EPI_BULK_WAIT = 9,   // same warp's leader thread waiting for a bulk store to have read its staging buffer
+  PROF_EPI_STAGE = 10,      // same warp: conversion, shared-memory writes and the barriers around them
+  PROF_SLOTS = 12
 };
 #ifdef FTB_PROFILE_WAITS
 __device__ unsigned long long g_wait_cycles[PROF_SLOTS];
@@ -232,6 +240,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t tx = a_boxes * a_box_bytes + b_boxes * b_box_bytes;
       const bool a_mn = p.a_mn != 0, b_mn = p.b_mn != 0, conv = p.conv != 0;
       const bool grouped = conv && p.conv_groups > 1;  // grouped conv: a tile's batch coordinate is its group
+      const bool release_pairs = p.release_pairs != 0;
       // In a pair every completion is reported to the leader's barrier.
       const uint32_t full_sig0 = PAIR ? map_to_cta(full0, 0) : full0;
       uint32_t s = 0, ph = 0, sa = smem_base;
@@ -267,7 +276,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #ifdef FTB_PROFILE_WAITS
           if (p.diag & 4) continue;
 #endif
-          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, &abort_flag)) {
+          if ((!release_pairs || (s & 1u) == 0) &&
+              !mbar_wait(empty0 + 8 * (release_pairs ? (s >> 1) : s), ph ^ 1u, &abort_flag)) {
             atomicOr(p.status, FTB_DEV_WAIT_EMPTY);
             abort_flag = 1;
             ok = false;
@@ -382,6 +392,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // barrier wait, about 80 per commit).  So it asks about the NEXT stage before it issues the
       // MMAs of the current one; the probe's latency then runs under the MMA issue.
       uint32_t ready = 0;
+      uint32_t pend_a = 0, pend_s = 0, pend_acc = 0;  // wide tiles: a K block whose second half is still to be issued
+      const bool release_pairs = p.release_pairs != 0;
       for (int t = unit; t < total_tiles && ok; t += units, ++local) {
         const int ks = (p.split_k > 1) ? (t % p.split_k) : 0;
         const int kb0 = ks * kb_per_split;
@@ -419,7 +431,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           const uint32_t b_lo = a_lo + b_off + b_lbo_delta;
 #ifdef FTB_PROFILE_WAITS
-          if ((p.diag & 2) && kb > kb0 && kb + 1 < kb1) {
+          if (!WIDE && (p.diag & 2) && kb > kb0 && kb + 1 < kb1) {
             if constexpr (PAIR) tc_commit_pair_both(empty0 + 8 * s);
             else tc_commit(empty0 + 8 * s);
             a_lo += stage_enc;
@@ -432,30 +444,62 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
 #endif
           if constexpr (WIDE) {
+            // Order of the two halves.  In the middle of a tile a K block feeds the first half, then
+            // the second.  At both ends of a tile two K blocks are taken together, first half twice,
+            // then second half twice: the first half then completes two K blocks' worth of MMAs
+            // (about a thousand cycles) before the second instead of one, and at the start of the
+            // next tile the second half is wanted that much later - time in which the epilogue warps,
+            // which serve both halves one after the other, drain them without the tensor pipe waiting.
+            const int j = kb - kb0, nkb = kb1 - kb0;
+            const bool skew = nkb >= 4;
             const bool last = kb + 1 == kb1;
 #pragma unroll
             for (int k = 0; k < kMmaPerKb; ++k)
               umma<KIND, PAIR>(d_tmem, a_lo + k * a_k, a_hi, b_lo + k * b_k, b_hi, idesc, k > 0 ? 1u : accumulate);
-            // the first half is complete one K block's worth of MMAs before the second
-            if (last) tc_commit_pair_both(tfull0);
-            if (kb == kb0) {
-              // the second half may still be draining the previous tile
-              FTB_PROF_T0(prof_t1);
-              if (!mbar_wait(smem_u32(&bar_tempty[1]), aph ^ 1u, &abort_flag)) {
-                atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
-                abort_flag = 1;
-                ok = false;
-                break;
+            if (last) tc_commit_pair_both(tfull0);  // the first half is complete
+            if (skew && (j == 0 || j == nkb - 2)) {
+              // this K block's second half is issued together with the next one's
+              pend_a = a_lo;
+              pend_s = s;
+              pend_acc = accumulate;
+            } else {
+              const bool with_pending = skew && (j == 1 || last);
+              if (j == (skew ? 1 : 0)) {
+                // the second half may still be draining the previous tile
+                FTB_PROF_T0(prof_t1);
+                if (!mbar_wait(smem_u32(&bar_tempty[1]), aph ^ 1u, &abort_flag)) {
+                  atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
+                  abort_flag = 1;
+                  ok = false;
+                  break;
+                }
+                FTB_PROF_ADD(prof_tempty, prof_t1);
+                tc_fence_after();
               }
-              FTB_PROF_ADD(prof_tempty, prof_t1);
-              tc_fence_after();
-            }
-            const uint32_t b_half = b_lo + p.b_half_enc;
+              if (with_pending) {
+                const uint32_t pb = pend_a + b_off + b_lbo_delta + p.b_half_enc;
 #pragma unroll
-            for (int k = 0; k < kMmaPerKb; ++k)
-              umma<KIND, PAIR>(d_tmem + kAccStride, a_lo + k * a_k, a_hi, b_half + k * b_k, b_hi, idesc,
-                               k > 0 ? 1u : accumulate);
+                for (int k = 0; k < kMmaPerKb; ++k)
+                  umma<KIND, PAIR>(d_tmem + kAccStride, pend_a + k * a_k, a_hi, pb + k * b_k, b_hi, idesc,
+                                   k > 0 ? 1u : pend_acc);
+                tc_commit_pair_both(empty0 + 8 * pend_s);
+              }
+              const uint32_t b_half = b_lo + p.b_half_enc;
+              const uint32_t acc1 = with_pending ? 1u : accumulate;
+#pragma unroll
+              for (int k = 0; k < kMmaPerKb; ++k)
+                umma<KIND, PAIR>(d_tmem + kAccStride, a_lo + k * a_k, a_hi, b_half + k * b_k, b_hi, idesc,
+                                 k > 0 ? 1u : acc1);
+              tc_commit_pair_both(empty0 + 8 * s);
+            }
             accumulate = 1;
+            a_lo += stage_enc;
+            if (++s == stages) {
+              s = 0;
+              ph ^= 1u;
+              a_lo = a_lo0;
+            }
+            continue;
           } else {
 #pragma unroll
             for (int k = 0; k < kMmaPerKb; ++k) {
@@ -473,10 +517,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #ifdef FTB_PROFILE_WAITS
           if (p.diag & 4) continue;
 #endif
-          if constexpr (PAIR) {
-            tc_commit_pair_both(empty0 + 8 * s);
-          } else {
-            tc_commit(empty0 + 8 * s);
+          if (!release_pairs) {
+            if constexpr (PAIR) tc_commit_pair_both(empty0 + 8 * s);
+            else tc_commit(empty0 + 8 * s);
+          } else if (s & 1u) {
+            // stages s - 1 and s go back together
+            if constexpr (PAIR) tc_commit_pair_both(empty0 + 8 * (s >> 1));
+            else tc_commit(empty0 + 8 * (s >> 1));
           }
           a_lo += stage_enc;
           if (++s == stages) {
@@ -519,7 +566,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t slab_seq = 0;
     int local = 0;
     bool alive = true;
-    long long prof_tfull = 0;
+    long long prof_tfull = 0, prof_ld = 0, prof_bulk = 0, prof_stage = 0;
     FTB_PROF_T0(prof_loop0);
     for (int t = unit; t < total_tiles && alive; t += units, ++local) {
       const TileCoord tc = decode_tile(p, t);
@@ -542,12 +589,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if constexpr (WIDE) {
         if (p.tma_store && got) {
           tc_fence_after();
+          FTB_PROF_T0(prof_l0);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int col = (OUT == OUT_BF16) ? grp * 64 + (q >> 1) * 128 + (q & 1) * 32 : grp * 32 + q * 64;
             tmem_ld_32x32(taddr + col, wide_v[q]);
           }
           tmem_ld_wait();
+          FTB_PROF_ADD(prof_ld, prof_l0);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(tempty_sig0 + 8 * acc);
@@ -646,6 +695,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int j = 0; j < 32; ++j) {
               float x = __uint_as_float(v[j]);
               if (add_bias && n0 + c + j < N) x += p.bias[koff + n0 + c + j];
+              if (p.relu) x = fmaxf(x, 0.0f);
               st_shared_f32(buf + static_cast<uint32_t>(j) * ch_stride + row_byte, x);
             }
           }
@@ -692,7 +742,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int i = 0; i < kSlabs; ++i) {
             const int c = grp * slab_cols + i * c_step;
             // the store that used this group's buffer before must have finished reading it
+            FTB_PROF_T0(prof_b0);
             if (leader) bulk_wait_group_read<0>();
+            FTB_PROF_ADD(prof_bulk, prof_b0);
+            FTB_PROF_T0(prof_s0);
             named_barrier_sync(bar_sync_id, 128);
             if constexpr (OUT == OUT_BF16) {
               // v[2 * i + part][0..15] hold 32 columns as packed pairs
@@ -719,6 +772,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             fence_proxy_async_smem();  // the slab must be visible to the bulk-copy engine
             named_barrier_sync(bar_sync_id, 128);
+            FTB_PROF_ADD(prof_stage, prof_s0);
             if (leader) {
               if (has_work && ncol(c) < N) {
                 if (p.split_k > 1) {
@@ -731,8 +785,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           slab_seq += kSlabs;
-          continue;
-        }
+        } else
         for (int c = grp * slab_cols; c < bn; c += c_step, ++slab_seq) {
           // plain tiles alternate between the two buffers; a group of a wide tile owns one
           const uint32_t buf = epi_base + (WIDE ? static_cast<uint32_t>(grp) : (slab_seq & 1u)) * kEpiBufBytes;
@@ -830,6 +883,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (n < N) {
               float x = __uint_as_float(v[j]);
               if (p.bias != nullptr && tc.ks == 0) x += p.bias[koff + n];
+              if (p.relu) x = fmaxf(x, 0.0f);
               float* dst = out + row_off + n * col_stride;
               if (p.split_k > 1) atomicAdd(dst, x);
               else *dst = x;
@@ -890,9 +944,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       FTB_PROF_ADD(prof_loop, prof_loop0);
       FTB_PROF_FLUSH(PROF_EPI_TFULL, prof_tfull);
       FTB_PROF_FLUSH(PROF_EPI_LOOP, prof_loop);
+      FTB_PROF_FLUSH(PROF_EPI_TMEM_LD, prof_ld);
+      FTB_PROF_FLUSH(PROF_EPI_BULK_WAIT, prof_bulk);
+      FTB_PROF_FLUSH(PROF_EPI_STAGE, prof_stage);
       (void)prof_loop;
     }
-    (void)prof_tfull;
+    (void)prof_tfull; (void)prof_ld; (void)prof_bulk; (void)prof_stage;
     // Shared memory must outlive the bulk stores' reads of it.  Their global writes are part of
     // this grid's memory operations and are complete when the grid is; only stores into a peer
     // GPU's memory (several destinations) are waited for in full before the CTA exits.

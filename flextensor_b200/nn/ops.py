@@ -54,6 +54,14 @@ def _bias_add(output, bias):
     return op.output(0)
 
 
+def relu(inputs):
+    """max(x, 0) elementwise; following a convolution (or its bias) it is folded into the conv kernel's
+    epilogue, as the bias is - the conv + bias + ReLU chain of a network runs as one kernel."""
+    names = ("b", "c", "h", "w")[:len(inputs.shape)] if len(inputs.shape) != 3 else ("b", "c", "l")
+    op = ComputeOp("relu", "relu", tuple(int(s) for s in inputs.shape), inputs.dtype, [inputs], names)
+    return op.output(0)
+
+
 def conv2d_nchw(inputs, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
     """inputs [N,C,H,W], weight [K, C/groups, kh, kw] -> [N, K, out_h, out_w]."""
     n, c, in_h, in_w = (int(s) for s in inputs.shape)

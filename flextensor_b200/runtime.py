@@ -77,10 +77,10 @@ class KernelPlan(object):
         for i, op in enumerate(self.op_lst):
             if op.kind == "pad2d":
                 continue  # read as zeros by the consuming conv kernel
-            if op.kind == "bias_add":
+            if op.kind in ("bias_add", "relu"):
                 if id(op) in consumed_bias:
                     continue
-                raise RuntimeError("a bias stage must follow a convolution")
+                raise RuntimeError("a %s stage must follow a convolution" % op.kind)
             knobs = config_to_knobs(self._config_of(i), op)
             inputs = list(op.input_tensors)
             bias = None
@@ -89,10 +89,14 @@ class KernelPlan(object):
                 padded = inputs[0]
                 if getattr(padded.op, "kind", None) == "pad2d":
                     inputs[0] = padded.op.input_tensors[0]
-                # a bias stage consuming this conv is folded into the epilogue
+                # a bias stage consuming this conv, and a ReLU consuming either, are folded into the epilogue
                 for later in self.op_lst[i + 1:]:
-                    if later.kind == "bias_add" and later.input_tensors[0] is op.output(0):
+                    if later.kind == "bias_add" and later.input_tensors[0] is out and bias is None:
                         bias = later.input_tensors[1]
+                        out = later.output(0)
+                        consumed_bias.add(id(later))
+                    elif later.kind == "relu" and later.input_tensors[0] is out and not knobs.get("relu"):
+                        knobs["relu"] = 1
                         out = later.output(0)
                         consumed_bias.add(id(later))
             if op.kind in DEFAULT_PRECISION and op.input_tensors[0].dtype == "float32":

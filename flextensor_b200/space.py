@@ -290,7 +290,7 @@ def generate_space_intra_op_llvm(op, down_graph, slevel=4, rlevel=3, groups=3, s
 # Positional layout of a CUDA-target op config (what ``to_config`` emits and the kernel
 # template in ``templates.py`` reads back).
 B200_LAYOUT = {
-    "contraction": {"spatial": ["tile_n", "cluster"], "reduce": ["stages", "split_k"], "reorder": ["raster"],
+    "contraction": {"spatial": ["tile_n", "cluster"], "reduce": ["stages", "split_k", "release"], "reorder": ["raster"],
                     "unroll": ["ctas"]},
     "conv2d": {"spatial": ["tile_n", "tile_h", "cluster"], "reduce": ["stages", "split_k"], "reorder": ["raster"],
                "unroll": ["ctas"], "inline": ["algo"]},
@@ -342,6 +342,8 @@ def generate_space_intra_op_b200(op, down_graph=None):
         f32_out = op.output(0).dtype == "float32"
         splits = [s for s in (1, 2, 4, 8) if s <= num_kb] if f32_out else [1]
         space.add_subspace("split_k", KnobSpace("split_k", splits), "reduce")
+        # stages handed back to the loader one by one, or two at a time (half the commits)
+        space.add_subspace("release", KnobSpace("release", [1, 2]), "reduce")
         space.add_subspace("raster", KnobSpace("raster", [[1, 0], [2, 0], [3, 2], [3, 4], [3, 8], [3, 16]]), "reorder")
         space.add_subspace("ctas", KnobSpace("ctas", [8, 7, 6, 4]), "unroll")
     elif family == "conv2d":

@@ -62,7 +62,7 @@ def knobs_to_config(knobs, op):
         return {}
     config = {"fuse": [], "spatial": [], "reduce": [], "reorder": [], "inline": [], "unroll": [], "merge": [],
               "special": []}
-    defaults = {"tile_n": 0, "cluster": 0, "tile_h": 0, "threads": 0, "stages": 0, "split_k": 1}
+    defaults = {"tile_n": 0, "cluster": 0, "tile_h": 0, "threads": 0, "stages": 0, "split_k": 1, "release": 1}
     for type_key, names in B200_LAYOUT[family].items():
         for name in names:
             if name == "raster":

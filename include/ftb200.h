@@ -63,7 +63,12 @@ typedef struct ftb_config {
                         conv over the im2col form of the input (at most 8 input channels, groups 1)    */
   int32_t epilogue;  /* 0 = bulk tensor stores from shared memory wherever they can address the result
                         (default); 1 = per-thread global stores everywhere (same bits; for diagnosis)   */
-  int32_t reserved[4];
+  int32_t release;   /* GEMMs: 0 or 1 = a pipeline stage goes back to the loader after every K block;
+                        2 = stages go back two at a time (half the tcgen05.commit count; needs an even
+                        number of stages >= 4, ignored otherwise, for 3xTF32 and for tile_n = 512)      */
+  int32_t relu;      /* conv2d and depthwise: 1 = clamp the result at zero after the bias (the conv + bias +
+                        ReLU chain of a network as one kernel); not a search knob                       */
+  int32_t reserved[2];
 } ftb_config;
 
 int ftb_version(void);
@@ -86,11 +91,13 @@ int64_t ftb_launch_count(void);
 int ftb_selftest_bounded_wait(int* status, void* stream);
 
 /* Diagnostic builds only (library compiled with -DFTB_PROFILE_WAITS; the product build returns
- * FTB_E_UNSUPPORTED): synchronises the device and copies out eight counters of SM cycles, summed
+ * FTB_E_UNSUPPORTED): synchronises the device and copies out twelve counters of SM cycles, summed
  * over the CTAs of every tensor-core GEMM launch since the last reset - [0] producer waiting for a
  * free stage, [1] MMA issuer waiting for a stage to land, [2] MMA issuer waiting for a free
  * accumulator, [3] epilogue waiting for a finished accumulator, [4] [5] [6] the whole loops of the
- * producer, the issuer and the first epilogue warp, [7] CTAs that reported.  Tells which hand-off
+ * producer, the issuer and the first epilogue warp, [7] CTAs that reported, [8] [9] [10] first
+ * epilogue warp of a 256 x 512 tile: inside its tcgen05.ld, waiting for a bulk store to release
+ * its staging buffer, converting and staging ([11] unused).  Tells which hand-off
  * of the pipeline a kernel is waiting on; no counterpart in the reference. */
 int ftb_debug_wait_profile(uint64_t* cycles, int reset);
 

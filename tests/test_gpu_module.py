@@ -241,3 +241,55 @@ def test_packed_1x1_and_gemm_conv2d_tasks(native_lib):
     func(dev(x), dev(w), out)
     func.check()
     assert O.normalised_error(out.cpu().numpy(), want) <= O.TOLERANCE["conv2d_tf32"]
+
+
+@pytest.mark.parametrize("case", [dict(n=2, c=32, h=20, w=24, k=48, r=3, stride=1, pad=1, groups=1),      # slab kernel
+                                  dict(n=2, c=24, h=15, w=16, k=36, r=3, stride=2, pad=1, groups=3),      # per-tap, groups
+                                  dict(n=1, c=16, h=9, w=7, k=8, r=3, stride=1, pad=0, groups=1)])        # per-thread stores
+def test_conv_bias_relu_chain_is_one_kernel(native_lib, case):
+    """pad -> conv2d -> bias -> ReLU planned from the op graph: one layout pass and one conv kernel whose
+    epilogue adds the bias and clamps at zero (flextensor/nn/ops.py:474-478 is the bias stage)."""
+    from flextensor_b200 import backend as B
+    from flextensor_b200.ir import placeholder
+    from flextensor_b200.nn import conv2d_nchw, relu
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config_ops
+    from flextensor_b200.utils import Config
+    n, c, h, w, k, r = case["n"], case["c"], case["h"], case["w"], case["k"], case["r"]
+    img = placeholder((n, c, h, w))
+    wt = placeholder((k, c // case["groups"], r, r))
+    bias = placeholder((k,))
+    out = relu(conv2d_nchw(img, wt, bias, stride=case["stride"], padding=case["pad"], groups=case["groups"]))
+    s, bufs = schedule_with_config_ops([out.op], [img, wt, bias, out], Config([{}, {}, {}, {}], None))
+    assert [st.op.kind for st in s.steps] == ["conv2d"] and s.steps[0].knobs["relu"] == 1
+    func = build(s, bufs)
+    x, wv = O.conv2d_inputs(n, c, h, w, k, r, r, groups=case["groups"], seed=86)
+    bv = np.random.default_rng(87).standard_normal(k).astype(np.float32)
+    want = np.maximum(O.conv2d_nchw(x, wv, bv, case["stride"], case["pad"], 1, case["groups"]), 0.0)
+    got = torch.full(want.shape, float("nan"), device="cuda")
+    before = B.launch_count()
+    func(dev(x), dev(wv), dev(bv), got)
+    func.check()
+    assert B.launch_count() - before == 2
+    got = got.cpu().numpy()
+    assert (got >= 0).all() and (got == 0).any()
+    assert O.normalised_error(got, want) <= O.TOLERANCE["conv2d_tf32"]
+
+
+def test_depthwise_bias_relu_chain(native_lib):
+    from flextensor_b200.ir import placeholder
+    from flextensor_b200.nn import depthwise_conv2d_nchw, relu
+    from flextensor_b200.runtime import build
+    from flextensor_b200.scheduler import schedule_with_config_ops
+    from flextensor_b200.utils import Config
+    img, wt, bias = placeholder((2, 16, 28, 28)), placeholder((16, 2, 3, 3)), placeholder((32,))
+    out = relu(depthwise_conv2d_nchw(img, wt, bias, stride=1, padding=1))
+    s, bufs = schedule_with_config_ops([out.op], [img, wt, bias, out], Config([{}, {}, {}, {}], None))
+    func = build(s, bufs)
+    x, wv = O.depthwise_inputs(2, 16, 28, 28, 2, 3, 3, seed=88)
+    bv = np.random.default_rng(89).standard_normal(32).astype(np.float32)
+    want = np.maximum(O.depthwise_conv2d_nchw(x, wv, bv, 1, 1, 1), 0.0)
+    got = torch.full(want.shape, float("nan"), device="cuda")
+    func(dev(x), dev(wv), dev(bv), got)
+    func.check()
+    assert O.normalised_error(got.cpu().numpy(), want) <= O.TOLERANCE["depthwise_f32"]

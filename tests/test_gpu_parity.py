@@ -250,6 +250,31 @@ def test_gemm_f32_wide_pair_tile(B, status):
         run_gemm_f32(B, a, b, cfg={"cluster": 2, "tile_n": 512, "fp32_mode": 1}, status=status)
 
 
+@pytest.mark.parametrize("tile_n,cluster", [(512, 2), (256, 2), (128, 2), (256, 1), (64, 1)])
+@pytest.mark.parametrize("stages", [2, 3, 4, 6])
+@pytest.mark.parametrize("release", [1, 2])
+def test_bgemm_bf16_pipeline_knobs_give_the_same_bits(B, status, tile_n, cluster, stages, release):
+    """Every combination of tile, pipeline depth and stage hand-back (one by one, or two at a time)
+    computes the same bf16 result as the library defaults, on a K long enough for several tiles'
+    worth of ring wrap-arounds (K = 1184: 19 K blocks, an odd count)."""
+    items = [O.batch_gemm_item(i, 520, 1040, 1184, seed=37) for i in range(3)]
+    a = bf16_dev(np.stack([i[0] for i in items]))
+    b = bf16_dev(np.stack([i[1] for i in items]))
+    ref = torch.full((3, 520, 1040), float("nan"), device="cuda", dtype=torch.bfloat16)
+    B.bgemm_bf16(a, b, ref, status=status)
+    got = torch.full((3, 520, 1040), float("nan"), device="cuda", dtype=torch.bfloat16)
+    cfg = {"tile_n": tile_n, "cluster": cluster, "stages": stages, "release": release}
+    if B.validate(B.OP_BGEMM_BF16, cfg, 520, 1040, 1184) != 0:
+        pytest.skip("this depth does not fit in shared memory with this tile")
+    B.bgemm_bf16(a, b, got, cfg=cfg, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(got, ref)
+    if (tile_n, stages, release) == (512, 4, 1):
+        want = O.batch_gemm(np.stack([i[0] for i in items]), np.stack([i[1] for i in items]))
+        assert O.bf16_output_ok(ref.float().cpu().numpy(), want)
+
+
 def test_epilogues_agree(B, status):
     """The staged bulk-store epilogue and the per-thread store epilogue give the same bits."""
     items = [O.batch_gemm_item(i, 328, 264, 136, seed=34) for i in range(2)]

@@ -136,8 +136,8 @@ def test_reference_style_space_sizes():
 def test_b200_space_per_family():
     ops_, _ = gemm(1024, 1024, 1024)
     space = SP.generate_space_intra_op(ops_[0], {}, target="cuda")
-    assert list(space.subspaces) == ["tile_n", "cluster", "stages", "split_k", "raster", "ctas"]
-    assert space.types["spatial"] == ["tile_n", "cluster"] and space.types["reduce"] == ["stages", "split_k"]
+    assert list(space.subspaces) == ["tile_n", "cluster", "stages", "split_k", "release", "raster", "ctas"]
+    assert space.types["spatial"] == ["tile_n", "cluster"] and space.types["reduce"] == ["stages", "split_k", "release"]
     assert [e[0] for e in space.subspaces["tile_n"].static_entities] == [32, 64, 128, 256, 512]
     for sub in space.subspaces.values():          # every sub-space speaks the walker protocol
         assert sub.num_direction == len(sub.directions) == 2 and len(sub) == len(sub.static_entities) > 0
@@ -173,9 +173,9 @@ def test_b200_space_per_family():
 def test_config_knob_round_trip():
     ops_, _ = gemm(1024, 1024, 1024)
     op = ops_[0]
-    knobs = {"tile_n": 128, "cluster": 2, "stages": 6, "split_k": 1, "raster": 3, "group_m": 8}
+    knobs = {"tile_n": 128, "cluster": 2, "stages": 6, "split_k": 1, "release": 2, "raster": 3, "group_m": 8}
     cfg = knobs_to_config(knobs, op)
-    assert cfg["spatial"] == [[128], [2]] and cfg["reduce"] == [[6], [1]] and cfg["reorder"] == [[3, 8]]
+    assert cfg["spatial"] == [[128], [2]] and cfg["reduce"] == [[6], [1], [2]] and cfg["reorder"] == [[3, 8]]
     assert config_to_knobs(cfg, op) == knobs
     assert config_to_knobs({}, op) == {}
     assert config_to_knobs({"spatial": [[64]]}, op) == {"tile_n": 64}
