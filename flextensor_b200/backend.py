@@ -218,13 +218,14 @@ def launch_count():
 
 WAIT_PROFILE_SLOTS = ("producer_wait_empty", "issuer_wait_full", "issuer_wait_tmem_free", "epilogue_wait_tmem_full",
                       "producer_loop", "issuer_loop", "epilogue_loop", "ctas", "epilogue_tmem_ld",
-                      "epilogue_bulk_wait", "epilogue_stage", "unused")
+                      "epilogue_bulk_wait", "epilogue_stage", "epilogue_store_issue", "epilogue_vote", "unused13",
+                      "unused14", "unused15")
 
 
 def wait_profile(reset=True):
     """Cycle counters of a wait-profiling build (``FTB200_LIBRARY`` pointing at it) as a dict;
     raises ``FtbError`` (unsupported) on the product build."""
-    arr = (ctypes.c_uint64 * 12)()
+    arr = (ctypes.c_uint64 * 16)()
     rc = lib().ftb_debug_wait_profile(arr, int(reset))
     if rc:
         raise FtbError(rc, "ftb_debug_wait_profile")

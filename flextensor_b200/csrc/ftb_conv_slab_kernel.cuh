@@ -22,6 +22,12 @@
 //
 // CTAs with the same blockIdx.x % split share a subset of the taps and walk the tile list
 // with a stride of gridDim.x / split.
+//
+// PAIR = true runs two CTAs of a cluster as one tcgen05 `cta_group::2` unit on two consecutive
+// tiles (M = 256): each CTA stages the slab of its own tile and HALF of the filter's output
+// channels, the leader issues one MMA for both.  A 128 x 64 TF32 MMA is 32 cycles of math but
+// reads 6 KB of operands from shared memory and costs the single issuing thread about as long to
+// issue; the 256 x 64 form does twice the math per instruction and reads 5 KB per SM.
 #pragma once
 #include "ftb_umma_kernel.cuh"
 
@@ -41,6 +47,10 @@ struct ConvSlabParams {
   // staged epilogue: epi_bufs (0 = off, 1 or 2) buffers of 32 channels x tile pixels after the slabs
   int epi_bufs;
   int relu;     // clamp the result at zero after the bias (never with split taps)
+  int diag;     // diagnostic builds (-DFTB_PROFILE_WAITS) only, results are garbage: 1 = every tap reads the
+                // slab from offset 0, 2 = tap offsets rounded down to a multiple of eight pixel rows (the
+                // 1024-byte period of the swizzle); timing either against the real kernel shows what the
+                // taps' odd start addresses cost
   int num_dst;  // destinations of the staged epilogue (1..kMaxDst): the same box goes to each of them
   uint32_t epi_buf_bytes;
   uint32_t slab_bytes;   // bytes one slab load delivers
@@ -52,6 +62,7 @@ struct ConvSlabParams {
   int* status;
 };
 
+template <bool PAIR>
 __global__ void __launch_bounds__(192, 1)
 conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ StoreMaps tmap_out,
@@ -70,9 +81,14 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_stages = p.a_stages;
 
-  const int ks = static_cast<int>(blockIdx.x) % p.split;
-  const int walker = static_cast<int>(blockIdx.x) / p.split;
-  const int walkers = static_cast<int>(gridDim.x) / p.split;
+  // a tile-walking unit is a CTA, or a CTA pair that takes two consecutive tiles at a time
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const int unit = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int units = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int ks = unit % p.split;
+  const int walker = unit / p.split;
+  const int walkers = units / p.split;
+  const int steps = PAIR ? (p.tiles + 1) / 2 : p.tiles;  // positions of the tile list a unit walks over
   const int taps = p.R * p.S;
   const int tap0 = ks * p.taps_per_split;
   const int tap1 = min(taps, tap0 + p.taps_per_split);
@@ -90,7 +106,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
     mbar_init(smem_u32(&bar_bfull), 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
-      mbar_init(smem_u32(&bar_tempty[a]), 4);
+      mbar_init(smem_u32(&bar_tempty[a]), PAIR ? 8 : 4);  // the leader's copy counts both CTAs' epilogue warps
     }
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -100,11 +116,17 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       for (int d = 0; d < p.num_dst; ++d) prefetch_tmap(&tmap_out.dst[d]);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(&tmem_base_slot), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   // Launched as a programmatic dependent of the layout pass: everything above overlapped its tail.
@@ -117,16 +139,27 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0 && ntaps > 0) {
-      mbar_expect_tx(bfull, static_cast<uint32_t>(ntaps * p.cchunks) * p.b_tile_bytes);
+      // In a pair every completion is reported to the leader's barriers, which the leader arms for
+      // the bytes of both CTAs; each CTA stages its own tile's slab and its own half of the filter rows.
+      const uint32_t bfull_sig = PAIR ? map_to_cta(bfull, 0) : bfull;
+      const uint32_t afull_sig0 = PAIR ? map_to_cta(afull0, 0) : afull0;
+      const uint32_t b_bytes_all = static_cast<uint32_t>(ntaps * p.cchunks) * p.b_tile_bytes;
+      if (cta_rank == 0) mbar_expect_tx(bfull, PAIR ? 2u * b_bytes_all : b_bytes_all);
       {
         uint32_t dst = b_base;
         int kc = tap0 * p.cchunks * 32;  // the packed filter is [k_out][tap][chunk][32]
-        for (int i = 0; i < ntaps * p.cchunks; ++i, dst += p.b_tile_bytes, kc += 32)
-          tma_load_3d(dst, &tmap_w, bfull, kc, 0, 0);
+        const int n0 = static_cast<int>(cta_rank) * (p.bn / 2);
+        for (int i = 0; i < ntaps * p.cchunks; ++i, dst += p.b_tile_bytes, kc += 32) {
+          if constexpr (PAIR) tma_load_3d_pair(dst, &tmap_w, bfull_sig, kc, n0, 0);
+          else tma_load_3d(dst, &tmap_w, bfull, kc, 0, 0);
+        }
       }
       uint32_t s = 0, ph = 0, sa = a_base;
       bool ok = true;
-      for (int t = walker; t < p.tiles && ok; t += walkers) {
+      for (int tp = walker; tp < steps && ok; tp += walkers) {
+        // a tile index past the end (odd tile count in a pair) addresses an image outside the
+        // tensor: its loads deliver zeros and its result is never stored
+        const int t = PAIR ? 2 * tp + static_cast<int>(cta_rank) : tp;
         const int img = t / tiles_per_img;
         const int rem = t - img * tiles_per_img;
         const int th = rem / p.tiles_w, tw = rem - th * p.tiles_w;
@@ -138,8 +171,13 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             ok = false;
             break;
           }
-          mbar_expect_tx(afull0 + 8 * s, p.slab_bytes);
-          tma_load_4d(sa, &tmap_in, afull0 + 8 * s, cc * 32, w0, h0, img);
+          if constexpr (PAIR) {
+            if (cta_rank == 0) mbar_expect_tx(afull0 + 8 * s, 2u * p.slab_bytes);
+            tma_load_4d_pair(sa, &tmap_in, afull_sig0 + 8 * s, cc * 32, w0, h0, img);
+          } else {
+            mbar_expect_tx(afull0 + 8 * s, p.slab_bytes);
+            tma_load_4d(sa, &tmap_in, afull0 + 8 * s, cc * 32, w0, h0, img);
+          }
           sa += p.slab_alloc;
           if (++s == a_stages) {
             s = 0;
@@ -152,7 +190,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && ntaps > 0) {
+    if (lane == 0 && ntaps > 0 && cta_rank == 0) {
       const uint32_t idesc = p.idesc;
       const uint32_t hi = smem_desc_hi(16, 1024, 2);
       const uint32_t b_tile_enc = p.b_tile_bytes >> 4;
@@ -168,7 +206,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         atomicOr(p.status, FTB_DEV_WAIT_FULL);
         abort_flag = 1;
       }
-      for (int t = walker; t < p.tiles && ok; t += walkers, ++local) {
+      for (int tp = walker; tp < steps && ok; tp += walkers, ++local) {
         const uint32_t acc = local & 1;
         const uint32_t aph = (local >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, &abort_flag)) {
@@ -195,11 +233,15 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             // wrote the slab, so a start address that is not a multiple of the 1024-byte swizzle
             // period needs nothing else in the descriptor (its base-offset field stays 0; measured:
             // setting it to the row phase gives wrong sums).
-            const uint32_t off = static_cast<uint32_t>(tr * p.dil_h * p.slab_w + ts * p.dil_w);
+            uint32_t off = static_cast<uint32_t>(tr * p.dil_h * p.slab_w + ts * p.dil_w);
+#ifdef FTB_PROFILE_WAITS
+            if (p.diag & 1) off = 0;
+            if (p.diag & 2) off &= ~7u;
+#endif
             const uint32_t ta_lo = a_lo + off * 8u;
 #pragma unroll
             for (int k = 0; k < kMmaPerKb; ++k) {
-              umma<KIND_TF32, false>(d_tmem, ta_lo + 2u * k, hi, b_lo + 2u * k, hi, idesc, accumulate);
+              umma<KIND_TF32, PAIR>(d_tmem, ta_lo + 2u * k, hi, b_lo + 2u * k, hi, idesc, accumulate);
               accumulate = 1;
             }
             b_lo += static_cast<uint32_t>(p.cchunks) * b_tile_enc;
@@ -208,7 +250,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
               ++tr;
             }
           }
-          tc_commit(aempty0 + 8 * s);
+          if constexpr (PAIR) tc_commit_pair_both(aempty0 + 8 * s);
+          else tc_commit(aempty0 + 8 * s);
           a_lo += slab_enc;
           if (++s == a_stages) {
             s = 0;
@@ -216,7 +259,10 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             a_lo = a_lo0;
           }
         }
-        if (ok) tc_commit(smem_u32(&bar_tfull[acc]));
+        if (ok) {
+          if constexpr (PAIR) tc_commit_pair_both(smem_u32(&bar_tfull[acc]));
+          else tc_commit(smem_u32(&bar_tfull[acc]));
+        }
       }
     }
     __syncwarp();
@@ -230,8 +276,11 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
     int local = 0;
     uint32_t epi_seq = 0;
     const uint32_t epi_base = a_base + a_stages * p.slab_alloc;
+    const uint32_t tempty_sig0 = PAIR ? map_to_cta(smem_u32(&bar_tempty[0]), 0) : smem_u32(&bar_tempty[0]);
     if (ntaps > 0) {
-      for (int t = walker; t < p.tiles; t += walkers, ++local) {
+      for (int tp = walker; tp < steps; tp += walkers, ++local) {
+        const int t = PAIR ? 2 * tp + static_cast<int>(cta_rank) : tp;
+        const bool tile_valid = t < p.tiles;
         const uint32_t acc = local & 1;
         const uint32_t aph = (local >> 1) & 1u;
         bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull[acc]), aph, &abort_flag));
@@ -270,7 +319,10 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             if (c + 32 >= p.bn) {
               tc_fence_before();
               __syncwarp();
-              if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+              if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(tempty_sig0 + 8 * acc);
+                else mbar_arrive(tempty_sig0 + 8 * acc);
+              }
             }
             if (in_tile) {
               const bool add_bias = p.bias != nullptr && ks == 0;
@@ -285,7 +337,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             fence_proxy_async_smem();
             named_barrier_sync(1, 128);
             if (leader) {
-              if (c < p.N) {
+              if (c < p.N && tile_valid) {
                 if (p.split > 1) {
                   tma_reduce_add_4d(&tmap_out.dst[0], buf, tw * p.tile_w, th * p.tile_h, c, img);
                 } else {
@@ -301,7 +353,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
           continue;
         }
         const int oh = th * p.tile_h + prow, ow = tw * p.tile_w + pcol;
-        const bool row_ok = in_tile && oh < p.P && ow < p.Q;
+        const bool row_ok = in_tile && oh < p.P && ow < p.Q && tile_valid;
         float* dst0 = p.out + static_cast<long long>(img) * p.conv_ktot * plane + static_cast<long long>(oh) * p.Q + ow;
         for (int c = 0; c < p.bn; c += 32) {
           uint32_t v[32];
@@ -310,7 +362,10 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
           if (c + 32 >= p.bn) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+            if (lane == 0) {
+              if constexpr (PAIR) mbar_arrive_cluster(tempty_sig0 + 8 * acc);
+              else mbar_arrive(tempty_sig0 + 8 * acc);
+            }
           }
           if (!row_ok) continue;
 #pragma unroll
@@ -344,9 +399,11 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's shared memory and TMEM stay alive until both are done
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 

@@ -852,6 +852,7 @@ static int conv_prepass(const float* in, const float* weight, float* in_nhwc, fl
 // shape or the knobs do not fit it.
 struct SlabPlan {
   bool ok;
+  bool pair;  // two CTAs of a cluster on two consecutive tiles (cta_group::2)
   ConvSlabParams p;
   int ctas;
   size_t smem;
@@ -895,7 +896,14 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   const int tiles_h = static_cast<int>((P + tile_h - 1) / tile_h);
   const long long tiles = n * tiles_h * tiles_w;
   if (tiles > 0x7fffffffll) return sp;
-  const uint32_t b_tile = static_cast<uint32_t>(bn) * 128u;
+  // A CTA pair shares one MMA over two consecutive tiles and splits the filter rows between its CTAs.
+  // Taken when asked for (cluster = 2) or, left open, when there are enough tiles to keep every pair
+  // busy; it needs halves of the filter rows that are whole 8-row groups.
+  const int want_cluster = user ? user->cluster : 0;
+  const bool pair = bn % 16 == 0 && num_sms >= 2 && want_cluster != 1 &&
+                    (want_cluster == 2 || tiles >= 2ll * num_sms);
+  sp.pair = pair;
+  const uint32_t b_tile = static_cast<uint32_t>(pair ? bn / 2 : bn) * 128u;
   const size_t after_min = tail > epi_buf ? tail : epi_buf;
   auto fits = [&](int split, int* a_stages, int* epi_bufs) {
     const int tps = (taps + split - 1) / split;
@@ -916,7 +924,7 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
     // Splitting the taps over CTAs fills idle SMs when the tile list is short (at the price of
     // adding partial sums in global memory) and shrinks the resident filter when it would not
     // fit otherwise.
-    long long want = num_sms / (tiles > 0 ? tiles : 1);
+    long long want = (pair ? num_sms / 2 : num_sms) / (tiles > 0 ? (pair ? (tiles + 1) / 2 : tiles) : 1);
     if (want > 4) want = 4;
     for (int d = 1; d <= taps; ++d) {
       if ((d - 1) * ((taps + d - 1) / d) >= taps) continue;  // would leave a split without taps
@@ -942,12 +950,14 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   p.slab_bytes = static_cast<uint32_t>(slab_rows * 128);
   p.slab_alloc = slab_stride;
   p.b_tile_bytes = b_tile;
-  p.idesc = make_idesc(kind_info(KIND_TF32), bn, 0, 0, kTileM);
-  long long walkers = num_sms / split;
-  if (user && user->ctas > 0) walkers = user->ctas / split;
-  if (walkers > tiles) walkers = tiles;
+  p.idesc = make_idesc(kind_info(KIND_TF32), bn, 0, 0, pair ? 2 * kTileM : kTileM);
+  const long long units_avail = pair ? num_sms / 2 : num_sms;
+  const long long steps = pair ? (tiles + 1) / 2 : tiles;
+  long long walkers = units_avail / split;
+  if (user && user->ctas > 0) walkers = (pair ? user->ctas / 2 : user->ctas) / split;
+  if (walkers > steps) walkers = steps;
   if (walkers < 1) walkers = 1;
-  sp.ctas = static_cast<int>(walkers) * split;
+  sp.ctas = static_cast<int>(walkers) * split * (pair ? 2 : 1);
   const size_t after = static_cast<size_t>(epi_bufs) * epi_buf > tail ? static_cast<size_t>(epi_bufs) * epi_buf : tail;
   sp.smem = static_cast<size_t>(tps) * cchunks * b_tile + static_cast<size_t>(a_stages) * slab_stride + after + 1024;
   sp.box_w = static_cast<uint32_t>(slab_w);
@@ -965,8 +975,11 @@ static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const Stor
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !done[dev]) {
-      cudaError_t attr_err = cudaFuncSetAttribute(conv_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t attr_err = cudaFuncSetAttribute(conv_slab_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   static_cast<int>(kSmemLimit));
+      if (attr_err == cudaSuccess)
+        attr_err = cudaFuncSetAttribute(conv_slab_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemLimit));
       if (attr_err != cudaSuccess) {
         set_last_cuda_error(static_cast<int>(attr_err));
         return FTB_E_CUDA;
@@ -981,12 +994,21 @@ static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const Stor
   lc.blockDim = dim3(192, 1, 1);
   lc.dynamicSmemBytes = sp.smem;
   lc.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = attr;
   lc.numAttrs = 1;
-  cudaLaunchKernelEx(&lc, conv_slab_kernel, tin, tw, tout, sp.p);
+  if (sp.pair) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    lc.numAttrs = 2;
+    cudaLaunchKernelEx(&lc, conv_slab_kernel<true>, tin, tw, tout, sp.p);
+  } else {
+    cudaLaunchKernelEx(&lc, conv_slab_kernel<false>, tin, tw, tout, sp.p);
+  }
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -1102,8 +1124,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   // Filters with more than one tap at stride 1 go to the slab kernel when it can take them.
   SlabPlan sp;
   sp.ok = false;
+  // (cluster = 2 without algo = 2 keeps meaning the per-tap lowering on CTA pairs)
   if (algo != 1 && groups == 1 && stride_h == 1 && stride_w == 1 && !split3 && (r * s > 1 || algo == 2) &&
-      !(user && user->cluster == 2))
+      !(user && user->cluster == 2 && algo != 2))
     sp = plan_slab(user, n, kg, P, Q, r, s, ws.cchunks, dil_h, dil_w, pad_h, pad_w,
                    (reinterpret_cast<uintptr_t>(out) & 15) == 0, num_sms);
   if (sp.ok && num_extra > 0 && (sp.p.epi_bufs == 0 || sp.p.split > 1)) sp.ok = false;
@@ -1124,6 +1147,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     sp.p.out = out;
     sp.p.bias = bias;
     sp.p.relu = relu;
+    sp.p.diag = user ? user->reserved[0] : 0;
     sp.p.conv_ktot = static_cast<int>(k);
     sp.p.status = status ? status : fallback_status();
     if (!sp.p.status) return FTB_E_CUDA;
@@ -1142,7 +1166,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       const uint64_t kdim = static_cast<uint64_t>(r * s * ws.cchunks) * 32;
       uint64_t dims[3] = {kdim, static_cast<uint64_t>(kg), 1};
       uint64_t strides[2] = {kdim * 4, kdim * 4 * kg};
-      uint32_t box[3] = {32, static_cast<uint32_t>(sp.p.bn), 1};
+      uint32_t box[3] = {32, static_cast<uint32_t>(sp.pair ? sp.p.bn / 2 : sp.p.bn), 1};
       const uint32_t ones[3] = {1, 1, 1};
       rc = make_tmap(&tw, ki.dt, 3, w_packed, dims, strides, box, ones);
       if (rc) return rc;

@@ -118,7 +118,9 @@ enum {
   PROF_EPI_TMEM_LD = 8,     // epilogue warp 2 (wide tiles, staged): inside the tcgen05.ld of its columns + wait
   PROF_EPI_BULK_WAIT = 9,   // same warp's leader thread waiting for a bulk store to have read its staging buffer
   PROF_EPI_STAGE = 10,      // same warp: conversion, shared-memory writes and the barriers around them
-  PROF_SLOTS = 12
+  PROF_EPI_STORE_ISSUE = 11,  // same warp's leader thread inside the bulk tensor store instructions and their commit
+  PROF_EPI_VOTE = 12,       // same warp: hand-back of the accumulator, packing, and the vote of the four warps
+  PROF_SLOTS = 16
 };
 #ifdef FTB_PROFILE_WAITS
 __device__ unsigned long long g_wait_cycles[PROF_SLOTS];
@@ -566,7 +568,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t slab_seq = 0;
     int local = 0;
     bool alive = true;
-    long long prof_tfull = 0, prof_ld = 0, prof_bulk = 0, prof_stage = 0;
+    long long prof_tfull = 0, prof_ld = 0, prof_bulk = 0, prof_stage = 0, prof_issue = 0, prof_vote = 0;
     FTB_PROF_T0(prof_loop0);
     for (int t = unit; t < total_tiles && alive; t += units, ++local) {
       const TileCoord tc = decode_tile(p, t);
@@ -597,6 +599,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           tmem_ld_wait();
           FTB_PROF_ADD(prof_ld, prof_l0);
+          prof_vote -= clock64();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(tempty_sig0 + 8 * acc);
@@ -615,6 +618,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       // The staged epilogue synchronises the four warps with each other: they must agree.
       if (p.tma_store) got = named_barrier_all(bar_vote_id, 128, got);
+#ifdef FTB_PROFILE_WAITS
+      if (WIDE && p.tma_store && prof_vote < 0) prof_vote += clock64();
+#endif
       if (!got) {
         if (lane == 0) {
           atomicOr(p.status, FTB_DEV_WAIT_TMEMFULL);
@@ -773,6 +779,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             fence_proxy_async_smem();  // the slab must be visible to the bulk-copy engine
             named_barrier_sync(bar_sync_id, 128);
             FTB_PROF_ADD(prof_stage, prof_s0);
+            FTB_PROF_T0(prof_i0);
             if (leader) {
               if (has_work && ncol(c) < N) {
                 if (p.split_k > 1) {
@@ -783,6 +790,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
               bulk_commit_group();
             }
+            FTB_PROF_ADD(prof_issue, prof_i0);
           }
           slab_seq += kSlabs;
         } else
@@ -947,9 +955,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       FTB_PROF_FLUSH(PROF_EPI_TMEM_LD, prof_ld);
       FTB_PROF_FLUSH(PROF_EPI_BULK_WAIT, prof_bulk);
       FTB_PROF_FLUSH(PROF_EPI_STAGE, prof_stage);
+      FTB_PROF_FLUSH(PROF_EPI_STORE_ISSUE, prof_issue);
+      FTB_PROF_FLUSH(PROF_EPI_VOTE, prof_vote);
       (void)prof_loop;
     }
-    (void)prof_tfull; (void)prof_ld; (void)prof_bulk; (void)prof_stage;
+    (void)prof_tfull; (void)prof_ld; (void)prof_bulk; (void)prof_stage; (void)prof_issue; (void)prof_vote;
     // Shared memory must outlive the bulk stores' reads of it.  Their global writes are part of
     // this grid's memory operations and are complete when the grid is; only stores into a peer
     // GPU's memory (several destinations) are waited for in full before the CTA exits.

@@ -75,7 +75,7 @@ def main():
                 "knobs": cfg, "ms": round(ms, 4), "tflops": round(args.batch * 2.0 * n ** 3 / ms / 1e9, 1),
                 "status": int(status.item()),
                 "sm_mhz_from_cycles": round(per_cta["epilogue_loop"] / (ms * 1e3), 0),
-                "cycles_per_k_block": round(per_cta["producer_loop"] / kb_per_unit, 1),
+                "cycles_per_k_block": round(per_cta["epilogue_loop"] / kb_per_unit, 1),
                 "per_k_block": {
                     "producer_wait_empty": round(per_cta["producer_wait_empty"] / kb_per_unit, 1),
                     "issuer_wait_full": round(per_cta["issuer_wait_full"] / issuers / kb_per_unit, 1),
@@ -86,6 +86,8 @@ def main():
                     "tmem_ld": round(per_cta["epilogue_tmem_ld"] / (tiles / units), 0),
                     "bulk_wait": round(per_cta["epilogue_bulk_wait"] / (tiles / units), 0),
                     "convert_and_stage": round(per_cta["epilogue_stage"] / (tiles / units), 0),
+                    "store_issue": round(per_cta["epilogue_store_issue"] / (tiles / units), 0),
+                    "hand_back_pack_vote": round(per_cta["epilogue_vote"] / (tiles / units), 0),
                     "busy_total": round((per_cta["epilogue_loop"] - per_cta["epilogue_wait_tmem_full"]) / (tiles / units), 0),
                 },
             }

@@ -91,13 +91,14 @@ int64_t ftb_launch_count(void);
 int ftb_selftest_bounded_wait(int* status, void* stream);
 
 /* Diagnostic builds only (library compiled with -DFTB_PROFILE_WAITS; the product build returns
- * FTB_E_UNSUPPORTED): synchronises the device and copies out twelve counters of SM cycles, summed
+ * FTB_E_UNSUPPORTED): synchronises the device and copies out sixteen counters of SM cycles, summed
  * over the CTAs of every tensor-core GEMM launch since the last reset - [0] producer waiting for a
  * free stage, [1] MMA issuer waiting for a stage to land, [2] MMA issuer waiting for a free
  * accumulator, [3] epilogue waiting for a finished accumulator, [4] [5] [6] the whole loops of the
  * producer, the issuer and the first epilogue warp, [7] CTAs that reported, [8] [9] [10] first
  * epilogue warp of a 256 x 512 tile: inside its tcgen05.ld, waiting for a bulk store to release
- * its staging buffer, converting and staging ([11] unused).  Tells which hand-off
+ * its staging buffer, converting and staging, [11] issuing bulk stores, [12] handing the
+ * accumulator back, packing and voting ([13]-[15] unused).  Tells which hand-off
  * of the pipeline a kernel is waiting on; no counterpart in the reference. */
 int ftb_debug_wait_profile(uint64_t* cycles, int reset);
 

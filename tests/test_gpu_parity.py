@@ -591,6 +591,35 @@ def test_conv2d_groups_run_as_one_launch(B, status, shape):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("shape", [(5, 32, 20, 24, 48, 3, 1), (3, 64, 56, 56, 64, 3, 1), (1, 40, 9, 11, 20, 3, 1),
+                                   (7, 16, 30, 130, 100, 5, 2), (2, 96, 14, 14, 256, 3, 1)])
+@pytest.mark.parametrize("extra", [{}, {"split_k": 3}, {"epilogue": 1}])
+def test_conv2d_slab_kernel_as_cta_pairs(B, status, shape, extra):
+    """The slab kernel with two CTAs of a cluster on two consecutive tiles (cluster = 2): odd tile
+    counts, split taps, both epilogues, against the oracle and against the single-CTA form."""
+    n, c, h, wd, k, r, pad = shape
+    x, w = O.conv2d_inputs(n, c, h, wd, k, r, r, seed=92)
+    bias = np.random.default_rng(93).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, 1, pad, 1, 1)
+    cfg = dict(extra, algo=2, cluster=2)
+    try:
+        got = run_conv(B, x, w, bias, 1, pad, 1, 1, cfg=cfg, status=status)
+    except B.FtbError as exc:
+        assert exc.code == -2 and extra.get("split_k")   # a split the resident filter cannot be cut into
+        pytest.skip("this split does not fit the slab kernel")
+    assert O.normalised_error(got, want) <= TOL["conv2d_tf32"]
+    # with the taps split the same way both forms issue the same MMAs per output in the same order
+    if "split_k" not in extra:
+        try:
+            single = run_conv(B, x, w, bias, 1, pad, 1, 1, cfg=dict(extra, algo=2, cluster=1, split_k=1), status=status)
+            paired = run_conv(B, x, w, bias, 1, pad, 1, 1, cfg=dict(extra, algo=2, cluster=2, split_k=1), status=status)
+        except B.FtbError as exc:
+            assert exc.code == -2                    # the whole filter does not fit in one CTA's shared memory
+        else:
+            assert np.array_equal(paired, single)
+    assert int(status.item()) == 0
+
+
 def test_conv2d_slab_algorithm_refuses_what_it_cannot_take(B, status):
     x, w = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, seed=59)
     for kwargs, cfg in ((dict(stride=2), {"algo": 2}),                 # stride 2
