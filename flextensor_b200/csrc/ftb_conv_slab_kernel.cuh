@@ -156,6 +156,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       }
       uint32_t s = 0, ph = 0, sa = a_base;
       bool ok = true;
+      long long prof_wait = 0;
+      FTB_PROF_T0(prof_loop0);
       for (int tp = walker; tp < steps && ok; tp += walkers) {
         // a tile index past the end (odd tile count in a pair) addresses an image outside the
         // tensor: its loads deliver zeros and its result is never stored
@@ -165,12 +167,14 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         const int th = rem / p.tiles_w, tw = rem - th * p.tiles_w;
         const int h0 = th * p.tile_h - p.pad_h, w0 = tw * p.tile_w - p.pad_w;
         for (int cc = 0; cc < p.cchunks; ++cc) {
+          FTB_PROF_T0(prof_w0);
           if (!mbar_wait(aempty0 + 8 * s, ph ^ 1u, &abort_flag)) {
             atomicOr(p.status, FTB_DEV_WAIT_EMPTY);
             abort_flag = 1;
             ok = false;
             break;
           }
+          FTB_PROF_ADD(prof_wait, prof_w0);
           if constexpr (PAIR) {
             if (cta_rank == 0) mbar_expect_tx(afull0 + 8 * s, 2u * p.slab_bytes);
             tma_load_4d_pair(sa, &tmap_in, afull_sig0 + 8 * s, cc * 32, w0, h0, img);
@@ -186,6 +190,12 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
           }
         }
       }
+      long long prof_loop = 0;
+      FTB_PROF_ADD(prof_loop, prof_loop0);
+      FTB_PROF_FLUSH(PROF_PRODUCER_EMPTY, prof_wait);
+      FTB_PROF_FLUSH(PROF_PRODUCER_LOOP, prof_loop);
+      FTB_PROF_FLUSH(PROF_CTAS, 1);
+      (void)prof_wait; (void)prof_loop;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -206,24 +216,30 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         atomicOr(p.status, FTB_DEV_WAIT_FULL);
         abort_flag = 1;
       }
+      long long prof_full = 0, prof_tempty = 0;
+      FTB_PROF_T0(prof_iloop0);
       for (int tp = walker; tp < steps && ok; tp += walkers, ++local) {
         const uint32_t acc = local & 1;
         const uint32_t aph = (local >> 1) & 1u;
+        FTB_PROF_T0(prof_t0);
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, &abort_flag)) {
           atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
           abort_flag = 1;
           break;
         }
+        FTB_PROF_ADD(prof_tempty, prof_t0);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
         uint32_t accumulate = 0;
         for (int cc = 0; cc < p.cchunks; ++cc) {
+          FTB_PROF_T0(prof_f0);
           if (!mbar_wait(afull0 + 8 * s, ph, &abort_flag)) {
             atomicOr(p.status, FTB_DEV_WAIT_FULL);
             abort_flag = 1;
             ok = false;
             break;
           }
+          FTB_PROF_ADD(prof_full, prof_f0);
           tc_fence_after();
           int tr = tr0, ts = ts0;
           uint32_t b_lo = b_lo0 + static_cast<uint32_t>(cc) * b_tile_enc;
@@ -264,6 +280,12 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
           else tc_commit(smem_u32(&bar_tfull[acc]));
         }
       }
+      long long prof_iloop = 0;
+      FTB_PROF_ADD(prof_iloop, prof_iloop0);
+      FTB_PROF_FLUSH(PROF_ISSUER_FULL, prof_full);
+      FTB_PROF_FLUSH(PROF_ISSUER_TEMPTY, prof_tempty);
+      FTB_PROF_FLUSH(PROF_ISSUER_LOOP, prof_iloop);
+      (void)prof_full; (void)prof_tempty; (void)prof_iloop;
     }
     __syncwarp();
   } else {
@@ -277,13 +299,17 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
     uint32_t epi_seq = 0;
     const uint32_t epi_base = a_base + a_stages * p.slab_alloc;
     const uint32_t tempty_sig0 = PAIR ? map_to_cta(smem_u32(&bar_tempty[0]), 0) : smem_u32(&bar_tempty[0]);
+    long long prof_tfull = 0;
+    FTB_PROF_T0(prof_eloop0);
     if (ntaps > 0) {
       for (int tp = walker; tp < steps; tp += walkers, ++local) {
         const int t = PAIR ? 2 * tp + static_cast<int>(cta_rank) : tp;
         const bool tile_valid = t < p.tiles;
         const uint32_t acc = local & 1;
         const uint32_t aph = (local >> 1) & 1u;
+        FTB_PROF_T0(prof_e0);
         bool got = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tfull[acc]), aph, &abort_flag));
+        FTB_PROF_ADD(prof_tfull, prof_e0);
         // The staged epilogue synchronises the four warps with each other: they must agree.
         if (p.epi_bufs) got = named_barrier_all(2, 128, got);
         if (!got) {
@@ -383,6 +409,14 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         }
       }
     }
+    if (warp == 2 && lane == 0) {
+      long long prof_eloop = 0;
+      FTB_PROF_ADD(prof_eloop, prof_eloop0);
+      FTB_PROF_FLUSH(PROF_EPI_TFULL, prof_tfull);
+      FTB_PROF_FLUSH(PROF_EPI_LOOP, prof_eloop);
+      (void)prof_eloop;
+    }
+    (void)prof_tfull;
     // Shared memory must outlive the bulk stores' reads of it; their global writes are complete
     // when the grid is - except stores into a peer GPU's memory, which are waited for in full.
     if (p.epi_bufs && warp == 2 && lane == 0) {
