@@ -32,19 +32,33 @@ struct DwParams {
 };
 
 // Byte distance from `out` to the d-th extra destination is the same for every element.
+// MULTI = false is the common case (one destination, no clamp): its kernels carry none of the
+// extra code or registers.
+template <bool MULTI>
 __device__ __forceinline__ void dw_store4(const DwParams& p, float* dst, float4 v) {
+  if constexpr (!MULTI) {
+    *reinterpret_cast<float4*>(dst) = v;
+    return;
+  }
   if (p.relu) v = make_float4(fmaxf(v.x, 0.f), fmaxf(v.y, 0.f), fmaxf(v.z, 0.f), fmaxf(v.w, 0.f));
   *reinterpret_cast<float4*>(dst) = v;
-  for (int d = 0; d < p.num_extra; ++d) *reinterpret_cast<float4*>(p.extra[d] + (dst - p.out)) = v;
+  const long long off = dst - p.out;
+  for (int d = 0; d < p.num_extra; ++d) *reinterpret_cast<float4*>(p.extra[d] + off) = v;
 }
+template <bool MULTI>
 __device__ __forceinline__ void dw_store1(const DwParams& p, float* dst, float v) {
+  if constexpr (!MULTI) {
+    *dst = v;
+    return;
+  }
   if (p.relu) v = fmaxf(v, 0.f);
   *dst = v;
-  for (int d = 0; d < p.num_extra; ++d) p.extra[d][dst - p.out] = v;
+  const long long off = dst - p.out;
+  for (int d = 0; d < p.num_extra; ++d) p.extra[d][off] = v;
 }
 
 // Staging tile: row i holds input row (h_in0 + i); column (lead + x) holds input column x.
-template <bool K3S1>
+template <bool K3S1, bool MULTI>
 __global__ void dwconv_kernel(const DwParams p) {
   extern __shared__ __align__(16) float tile[];
   __shared__ float wsm[kMaxTaps];
@@ -129,11 +143,11 @@ __global__ void dwconv_kernel(const DwParams p) {
       }
       float* dst = dst_plane + static_cast<long long>(oh0 + orow) * p.Q + ow;
       if (vec_out) {
-        dw_store4(p, dst, make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b));
+        dw_store4<MULTI>(p, dst, make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b));
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          if (ow + j < p.Q) dw_store1(p, dst + j, acc[j] + b);
+          if (ow + j < p.Q) dw_store1<MULTI>(p, dst + j, acc[j] + b);
       }
     }
   }
@@ -145,7 +159,7 @@ __global__ void dwconv_kernel(const DwParams p) {
 // threads load those lines as vectors), keeps them in registers and writes RH vectors.  Every
 // load of a thread is issued before the first use, so a CTA keeps (RH + 2) * 16 B per thread in
 // flight - what a bandwidth-bound kernel needs - and there is no barrier anywhere.
-template <int RH>
+template <int RH, bool MULTI>
 __global__ void __launch_bounds__(256) dwconv3x3_direct_kernel(const DwParams p, long long items, int vcols,
                                                                int rblocks) {
   const long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -192,7 +206,7 @@ __global__ void __launch_bounds__(256) dwconv3x3_direct_kernel(const DwParams p,
         for (int s = 0; s < 3; ++s)
 #pragma unroll
           for (int j = 0; j < 4; ++j) acc[j] = fmaf(x[i + r][j + s], wv[r * 3 + s], acc[j]);
-      dw_store4(p, dst + static_cast<long long>(i) * p.Q, make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b));
+      dw_store4<MULTI>(p, dst + static_cast<long long>(i) * p.Q, make_float4(acc[0] + b, acc[1] + b, acc[2] + b, acc[3] + b));
     }
   }
 }
@@ -202,7 +216,7 @@ __global__ void __launch_bounds__(256) dwconv3x3_direct_kernel(const DwParams p,
 // and no barrier.  A thread owns four adjacent outputs of one row, reads the K x ((4-1)*STRIDE + K)
 // input window they share straight from global memory (neighbouring threads hit the same lines in
 // L1; out-of-image taps read as zero) and serves every output channel of its input plane from it.
-template <int K, int STRIDE>
+template <int K, int STRIDE, bool MULTI>
 __global__ void __launch_bounds__(256) dwconv_window_kernel(const DwParams p, long long items, int groups_w) {
   const long long item = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (item >= items) return;
@@ -245,11 +259,11 @@ __global__ void __launch_bounds__(256) dwconv_window_kernel(const DwParams p, lo
       }
     float* dst = p.out + ((n * p.C * p.F + co) * p.P + oh) * p.Q + ow;
     if (ow + 3 < p.Q && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-      dw_store4(p, dst, make_float4(acc[0], acc[1], acc[2], acc[3]));
+      dw_store4<MULTI>(p, dst, make_float4(acc[0], acc[1], acc[2], acc[3]));
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        if (ow + j < p.Q) dw_store1(p, dst + j, acc[j]);
+        if (ow + j < p.Q) dw_store1<MULTI>(p, dst + j, acc[j]);
     }
   }
 }
@@ -307,6 +321,7 @@ static int dwconv_generic(const float* in, const float* weight, const float* bia
   if (cfg && (cfg->relu < 0 || cfg->relu > 1)) return FTB_E_BAD_CONFIG;
   p.relu = cfg ? cfg->relu : 0;
   p.num_extra = num_extra;
+  const bool multi = p.relu != 0 || num_extra > 0;  // selects the kernels that clamp and write several destinations
   for (int d = 0; d < num_extra; ++d) {
     // the vector stores need every destination as aligned as the first
     if ((reinterpret_cast<uintptr_t>(extra[d]) & 15) != (reinterpret_cast<uintptr_t>(out) & 15)) return FTB_E_BAD_ARG;
@@ -348,10 +363,11 @@ static int dwconv_generic(const float* in, const float* weight, const float* bia
     const long long blocks_d = (items + threads_d - 1) / threads_d;
     if (blocks_d > 0x7fffffffll) return FTB_E_TOO_LARGE;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    if (rh == 4)
-      dwconv3x3_direct_kernel<4><<<static_cast<unsigned>(blocks_d), threads_d, 0, stream>>>(p, items, vcols, rblocks);
-    else
-      dwconv3x3_direct_kernel<8><<<static_cast<unsigned>(blocks_d), threads_d, 0, stream>>>(p, items, vcols, rblocks);
+    const unsigned gd = static_cast<unsigned>(blocks_d);
+    if (rh == 4 && !multi) dwconv3x3_direct_kernel<4, false><<<gd, threads_d, 0, stream>>>(p, items, vcols, rblocks);
+    else if (rh == 4) dwconv3x3_direct_kernel<4, true><<<gd, threads_d, 0, stream>>>(p, items, vcols, rblocks);
+    else if (!multi) dwconv3x3_direct_kernel<8, false><<<gd, threads_d, 0, stream>>>(p, items, vcols, rblocks);
+    else dwconv3x3_direct_kernel<8, true><<<gd, threads_d, 0, stream>>>(p, items, vcols, rblocks);
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -372,10 +388,17 @@ static int dwconv_generic(const float* in, const float* weight, const float* bia
     if (blocks_w > 0x7fffffffll) return FTB_E_TOO_LARGE;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const unsigned gb = static_cast<unsigned>(blocks_w);
-    if (r == 3 && stride_h == 1) dwconv_window_kernel<3, 1><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
-    else if (r == 3) dwconv_window_kernel<3, 2><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
-    else if (stride_h == 1) dwconv_window_kernel<5, 1><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
-    else dwconv_window_kernel<5, 2><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+    if (!multi) {
+      if (r == 3 && stride_h == 1) dwconv_window_kernel<3, 1, false><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+      else if (r == 3) dwconv_window_kernel<3, 2, false><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+      else if (stride_h == 1) dwconv_window_kernel<5, 1, false><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+      else dwconv_window_kernel<5, 2, false><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+    } else {
+      if (r == 3 && stride_h == 1) dwconv_window_kernel<3, 1, true><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+      else if (r == 3) dwconv_window_kernel<3, 2, true><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+      else if (stride_h == 1) dwconv_window_kernel<5, 1, true><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+      else dwconv_window_kernel<5, 2, true><<<gb, threads_w, 0, stream>>>(p, items, groups_w);
+    }
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -408,7 +431,8 @@ static int dwconv_generic(const float* in, const float* weight, const float* bia
   if (smem > kDynLimit) return FTB_E_UNSUPPORTED;
 
   const bool k3s1 = (r == 3 && s == 3 && stride_h == 1 && stride_w == 1 && dil_h == 1 && dil_w == 1);
-  auto kern = k3s1 ? dwconv_kernel<true> : dwconv_kernel<false>;
+  auto kern = k3s1 ? (multi ? dwconv_kernel<true, true> : dwconv_kernel<true, false>)
+                   : (multi ? dwconv_kernel<false, true> : dwconv_kernel<false, false>);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(kDynLimit));
