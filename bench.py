@@ -523,6 +523,8 @@ def run_ours(args, rank, world, local_rank):
     # GEMM epilogue stores into all of them (fused gather), else one NCCL all-gather follows the call.
     fused_why = None
     knobs = KNOBS if world == 1 else KNOBS_FUSED
+    if args.knobs:
+        knobs = json.loads(args.knobs)
     op = None
     if world > 1 and not args.nccl_gather:
         try:
@@ -849,6 +851,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the per-operator lines of the other four configs")
     ap.add_argument("--nccl-gather", action="store_true", help="N > 1: return the output with an NCCL all-gather "
                     "instead of the fused epilogue stores")
+    ap.add_argument("--knobs", default="", help="JSON knob set for the headline kernel instead of the built-in one")
     ap.add_argument("--link-ceiling", action="store_true", help="N > 1: measure the all-to-all push rate of the "
                     "NVLink fabric instead of running the benchmark")
     ap.add_argument("--link-mib", type=int, default=64, help="MiB pushed to each peer by --link-ceiling")
