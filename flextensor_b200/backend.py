@@ -144,6 +144,11 @@ def lib():
         handle.ftb_conv2d_nchw_f32_multi.restype = i32
         handle.ftb_conv2d_nchw_f32_multi.argtypes = ([vp] * 3 + [ctypes.POINTER(vp), i32] + [i64] * 7 + [i32] * 8 +
                                                      [cfgp, vp, ctypes.c_size_t, vp, vp])
+        handle.ftb_conv3d_workspace_bytes.restype = ctypes.c_size_t
+        handle.ftb_conv3d_workspace_bytes.argtypes = [i64] * 10
+        handle.ftb_conv3d_ncdhw_f32.restype = i32
+        handle.ftb_conv3d_ncdhw_f32.argtypes = ([vp] * 4 + [i64] * 9 + [ctypes.POINTER(i32)] * 3 + [i32] +
+                                                [cfgp, vp, ctypes.c_size_t, vp, vp])
         handle.ftb_conv2d_nchw_f32_noalloc.restype = i32
         handle.ftb_conv2d_nchw_f32_noalloc.argtypes = [vp] * 4 + [i64] * 7 + [i32] * 7 + [cfgp, vp, vp]
         handle.ftb_dwconv2d_nchw_f32.restype = i32
@@ -160,7 +165,7 @@ EXPORTED_SYMBOLS = (
     "ftb_launch_count", "ftb_selftest_bounded_wait", "ftb_debug_wait_profile", "ftb_gemm_f32", "ftb_bgemm_f32", "ftb_bgemm_bf16", "ftb_bgemm_bf16_multi", "ftb_gemm_s8",
     "ftb_conv2d_workspace_bytes", "ftb_conv2d_nchw_f32", "ftb_conv2d_nchw_f32_noalloc", "ftb_dwconv2d_nchw_f32",
     "ftb_dwconv2d_nchw_f32_multi", "ftb_conv2d_nchw_f32_multi", "ftb_conv2d_pack_filter",
-    "ftb_conv2d_nchw_f32_prepacked",
+    "ftb_conv2d_nchw_f32_prepacked", "ftb_conv3d_workspace_bytes", "ftb_conv3d_ncdhw_f32",
 )
 
 
@@ -414,6 +419,46 @@ def conv2d_nchw_f32_multi(x, weight, dst_ptrs, bias=None, stride=(1, 1), padding
             workspace.numel() * workspace.element_size(), _status_ptr(status), _stream_ptr(stream))
     if rc:
         raise FtbError(rc, "ftb_conv2d_nchw_f32_multi")
+
+
+def _triple(value, what):
+    if isinstance(value, int):
+        return (value,) * 3
+    value = tuple(int(v) for v in value)
+    if len(value) != 3:
+        raise ValueError("%s must be an int or three ints (depth, height, width)" % what)
+    return value
+
+
+def conv3d_workspace_bytes(n, c, d, h, w, k, t, r, s, groups=1):
+    return int(lib().ftb_conv3d_workspace_bytes(n, c, d, h, w, k, t, r, s, groups))
+
+
+def conv3d_ncdhw_f32(x, weight, out, bias=None, stride=1, padding=0, dilation=1, groups=1, cfg=None,
+                     workspace=None, status=None, stream=None):
+    """out[N,K,OD,P,Q] = conv3d(x[N,C,D,H,W], weight[K,C/groups,T,R,S]) (+ bias); stride, padding and
+    dilation are ints or (depth, height, width) triples.  The caller owns ``workspace`` (a uint8 CUDA
+    tensor of at least conv3d_workspace_bytes bytes)."""
+    for t_, nm in ((x, "x"), (weight, "weight"), (out, "out")):
+        _check(t_, torch.float32, nm)
+    if bias is not None:
+        _check(bias, torch.float32, "bias")
+    n, c, d, h, w = x.shape
+    k, cg, t, r, s = weight.shape
+    if cg * groups != c:
+        raise ValueError("conv3d: weight channels %d x groups %d != input channels %d" % (cg, groups, c))
+    need = conv3d_workspace_bytes(n, c, d, h, w, k, t, r, s, groups)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        raise ValueError("conv3d: workspace of at least %d bytes required" % need)
+    triple = ctypes.c_int32 * 3
+    with torch.cuda.device(out.device):
+        rc = lib().ftb_conv3d_ncdhw_f32(
+            x.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(),
+            n, c, d, h, w, k, t, r, s, triple(*_triple(stride, "stride")), triple(*_triple(padding, "padding")),
+            triple(*_triple(dilation, "dilation")), groups, _cfg_ptr(cfg), workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(), _status_ptr(status), _stream_ptr(stream))
+    if rc:
+        raise FtbError(rc, "ftb_conv3d_ncdhw_f32")
 
 
 NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024

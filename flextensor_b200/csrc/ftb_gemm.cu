@@ -1447,6 +1447,211 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   return FTB_OK;
 }
 
+
+// ------------------------------------------------------------------ conv3d (NCDHW)
+// The same implicit GEMM as the per-tap conv2d path with one more tap loop: the layout pass
+// writes an [N][D][H][W][Cp] copy (its "pixels" are the D*H*W voxels) and packs the filter as
+// [K][T*R*S][cchunks*32]; the tile list walks (image, output depth) pairs as its images, and the
+// depth of a tap is the second coordinate of a 5-D tensor map, so that depth padding is the map's
+// out-of-range fill like the padding of rows and columns.  Groups run as one launch each, on maps
+// based at the group's channels.
+ConvWs conv3d_ws(int64_t n, int64_t c, int64_t d, int64_t h, int64_t w, int64_t k, int64_t t, int64_t r,
+                 int64_t s, int64_t groups) {
+  ConvWs ws;
+  const int64_t cg = c / groups;
+  ws.cgp = round_up(cg, 4);
+  ws.cp = groups > 1 ? groups * ws.cgp : round_up(c, 4);
+  ws.cchunks = (cg + 31) / 32;
+  ws.in_bytes = round_up(n * d * h * w * ws.cp * 4, 1024);
+  ws.w_bytes = round_up(k * t * r * s * ws.cchunks * 32 * 4, 1024);
+  return ws;
+}
+
+int conv3d_generic(const float* in, const float* weight, const float* bias, float* out, int64_t n, int64_t c,
+                   int64_t d, int64_t h, int64_t w, int64_t k, int64_t t, int64_t r, int64_t s, const int* stride,
+                   const int* pad, const int* dil, int groups, const ftb_config* user, void* workspace,
+                   size_t workspace_bytes, int* status, void* stream_v) {
+  if (!in || !weight || !out || !stride || !pad || !dil) return FTB_E_BAD_ARG;
+  if (n <= 0 || c <= 0 || d <= 0 || h <= 0 || w <= 0 || k <= 0 || t <= 0 || r <= 0 || s <= 0 || groups <= 0)
+    return FTB_E_BAD_ARG;
+  for (int i = 0; i < 3; ++i)
+    if (stride[i] <= 0 || dil[i] <= 0 || pad[i] < 0) return FTB_E_BAD_ARG;
+  if (c % groups || k % groups) return FTB_E_BAD_ARG;
+  const int64_t OD = (d + 2 * pad[0] - dil[0] * (t - 1) - 1) / stride[0] + 1;
+  const int64_t P = (h + 2 * pad[1] - dil[1] * (r - 1) - 1) / stride[1] + 1;
+  const int64_t Q = (w + 2 * pad[2] - dil[2] * (s - 1) - 1) / stride[2] + 1;
+  if (OD <= 0 || P <= 0 || Q <= 0) return FTB_E_BAD_ARG;
+  if (n * c * d * h * w > (1ll << 31) || n * k * OD * P * Q > (1ll << 31)) return FTB_E_TOO_LARGE;
+  // A filter of one tap at stride 1 without padding is the conv2d 1x1 case on [N, C, D*H, W]
+  // (a batched GEMM on the tensors as they are); same workspace size.
+  if (t * r * s == 1 && stride[0] * stride[1] * stride[2] == 1 && pad[0] + pad[1] + pad[2] == 0)
+    return conv2d_generic(in, weight, bias, out, n, c, d * h, w, k, 1, 1, 1, 1, 0, 0, 1, 1, groups, user, workspace,
+                          workspace_bytes, status, stream_v, nullptr, 0, 0);
+  if (user && (user->relu < 0 || user->relu > 1)) return FTB_E_BAD_CONFIG;
+  if (user && (user->fp32_mode < 0 || user->fp32_mode > 1)) return FTB_E_BAD_CONFIG;
+  if (user && (user->epilogue < 0 || user->epilogue > 1)) return FTB_E_BAD_CONFIG;
+  if (user && (user->algo < 0 || user->algo > 1)) return FTB_E_UNSUPPORTED;  // only the per-tap lowering
+  const int relu = user ? user->relu : 0;
+  if (relu && user->split_k > 1) return FTB_E_BAD_CONFIG;
+  int rc = device_ok();
+  if (rc) return rc;
+  const int64_t cg = c / groups, kg = k / groups;
+  const ConvWs ws = conv3d_ws(n, c, d, h, w, k, t, r, s, groups);
+  if (!workspace || workspace_bytes < static_cast<size_t>(ws.in_bytes + ws.w_bytes)) return FTB_E_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return FTB_E_WORKSPACE;
+  float* in_cl = static_cast<float*>(workspace);
+  float* w_packed = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ws.in_bytes);
+  const KindInfo ki = kind_info(KIND_TF32);
+  const bool split3 = user && user->fp32_mode == 1;
+  const int num_sms = sm_count();
+  const int stride_h = stride[1], stride_w = stride[2];
+
+  int tile_w = static_cast<int>(Q < 128 ? Q : 128);
+  if (tile_w * stride_w > 256) tile_w = 256 / stride_w;
+  int tile_h = user && user->tile_h > 0 ? user->tile_h : 128 / tile_w;
+  if (tile_h > P) tile_h = static_cast<int>(P);
+  if (tile_h < 1 || tile_h * tile_w > 128 || tile_h * stride_h > 256) return FTB_E_BAD_CONFIG;
+  const int tiles_w = static_cast<int>((Q + tile_w - 1) / tile_w);
+  const int tiles_h = static_cast<int>((P + tile_h - 1) / tile_h);
+  const int num_kb = static_cast<int>(t * r * s * ws.cchunks);
+  const long long tiles_m = n * OD * tiles_h * tiles_w;
+  bool staged = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && Q % 4 == 0 && tile_w % 4 == 0 &&
+                (P * Q * 4) % 16 == 0 && (groups == 1 || (kg * OD * P * Q * 4) % 16 == 0);
+  if (user && user->epilogue == 1) staged = false;
+  ftb_config cfg;
+  rc = FTB_E_BAD_CONFIG;
+  if (staged)
+    rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg,
+                        kEpilogueStaging);
+  if (rc) {
+    staged = false;
+    rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg);
+  }
+  if (rc) return rc;
+  const bool pair = cfg.cluster == 2;
+  const long long tiles_m_launch = pair ? (tiles_m + 1) / 2 : tiles_m;
+  if ((!user || user->split_k == 0) && !relu) {
+    // a short tile list leaves SMs idle: split the reduction over CTAs (bulk reduce-adds into the
+    // zeroed result)
+    const long long tiles = tiles_m_launch * ((kg + cfg.tile_n - 1) / cfg.tile_n);
+    int want = static_cast<int>((num_sms / (pair ? 2 : 1)) / (tiles > 0 ? tiles : 1));
+    if (want > 32) want = 32;
+    int pick = 1;
+    for (int dv = 2; dv <= want; ++dv)
+      if (num_kb % dv == 0) pick = dv;
+    cfg.split_k = pick;
+  }
+  if (relu) cfg.split_k = 1;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  rc = conv_prepass(in, weight, in_cl, w_packed, n, c, d * h, w, k, cg, t * r, s, ws, num_sms, stream_v,
+                    cfg.split_k > 1 ? out : nullptr, n * k * OD * P * Q, 0, 0, 1, 1, groups > 1, 3);
+  if (rc) return rc;
+
+  UmmaParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = static_cast<int>(tiles_m) * kTileM;
+  p.N = static_cast<int>(kg);
+  p.K = num_kb * ki.kblk;
+  p.batch = 1;
+  p.conv_groups = 1;
+  p.bn = cfg.tile_n;
+  p.stages = cfg.stages;
+  p.num_kb = num_kb;
+  p.tiles_m = static_cast<int>(tiles_m_launch);
+  p.conv_tiles = static_cast<int>(tiles_m);
+  p.tiles_n = static_cast<int>((kg + p.bn - 1) / p.bn);
+  p.raster = cfg.raster - 1;
+  p.group_m = cfg.group_m;
+  p.split_k = cfg.split_k;
+  p.kblk = ki.kblk;
+  p.idesc = make_idesc(ki, p.bn, 0, 0, pair ? 2 * kTileM : kTileM);
+  p.b_rows = pair ? p.bn / 2 : p.bn;
+  p.b_bytes = static_cast<uint32_t>(p.b_rows) * 128u;
+  p.a_boxes = 1;
+  p.a_box_mn = kTileM;
+  p.a_box_bytes = static_cast<uint32_t>(tile_h * tile_w) * 128u;
+  p.tile_imgs = 1;
+  p.n_imgs = static_cast<int>(n * OD);
+  p.a_lbo = 16; p.a_sbo = 1024; p.a_kadv = static_cast<uint32_t>(ki.umma_k * ki.esize);
+  CUtensorMapSwizzle b_swz;
+  operand_layout(ki, 0, p.b_rows, &p.b_boxes, &p.b_box_mn, &p.b_box_bytes, &p.b_lbo, &p.b_sbo, &p.b_kadv,
+                 &p.b_layout, &b_swz);
+  p.a_layout = 2;
+  p.pair_m = pair ? 2 * kTileM : kTileM;
+  p.conv = 1;
+  p.pdl = 1;
+  p.conv_ktot = static_cast<int>(k);
+  p.relu = relu;
+  p.C = out;
+  p.bias = bias;
+  p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);
+  p.tile_h = tile_h; p.tile_w = tile_w; p.tiles_h = tiles_h; p.tiles_w = tiles_w;
+  p.T = static_cast<int>(t); p.R = static_cast<int>(r); p.S = static_cast<int>(s);
+  p.cchunks = static_cast<int>(ws.cchunks);
+  p.conv_od = static_cast<int>(OD);
+  p.stride_d = stride[0]; p.stride_h = stride_h; p.stride_w = stride_w;
+  p.pad_d = pad[0]; p.pad_h = pad[1]; p.pad_w = pad[2];
+  p.dil_d = dil[0]; p.dil_h = dil[1]; p.dil_w = dil[2];
+  p.status = status ? status : fallback_status();
+  if (!p.status) return FTB_E_CUDA;
+  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.split_k;
+  if (total > 0x7fffffffll) return FTB_E_TOO_LARGE;
+  int ctas = cfg.ctas > 0 ? cfg.ctas : num_sms;
+  if (pair) {
+    if (ctas / 2 > total) ctas = static_cast<int>(total) * 2;
+    ctas &= ~1;
+    if (ctas < 2) ctas = 2;
+  } else if (ctas > total) {
+    ctas = static_cast<int>(total);
+  }
+  const uint64_t kdim = static_cast<uint64_t>(num_kb) * ki.kblk;
+  for (int g = 0; g < groups; ++g) {
+    p.conv_koff = static_cast<int>(g * kg);
+    CUtensorMap ta, tb;
+    {
+      // (c of this group, w, h, d, n) view of the channels-last copy; channels beyond the group's
+      // lie outside dimension 0 and read as zeros
+      uint64_t dims[5] = {static_cast<uint64_t>(groups > 1 ? cg : ws.cp), static_cast<uint64_t>(w),
+                          static_cast<uint64_t>(h), static_cast<uint64_t>(d), static_cast<uint64_t>(n)};
+      uint64_t strides[4] = {static_cast<uint64_t>(ws.cp) * 4, static_cast<uint64_t>(w) * ws.cp * 4,
+                             static_cast<uint64_t>(h) * w * ws.cp * 4, static_cast<uint64_t>(d) * h * w * ws.cp * 4};
+      uint32_t box[5] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(tile_w * stride_w),
+                         static_cast<uint32_t>(tile_h * stride_h), 1, 1};
+      uint32_t es[5] = {1, static_cast<uint32_t>(stride_w), static_cast<uint32_t>(stride_h), 1, 1};
+      rc = make_tmap(&ta, ki.dt, 5, in_cl + g * ws.cgp, dims, strides, box, es);
+      if (rc) return rc;
+    }
+    {
+      uint64_t dims[3] = {kdim, static_cast<uint64_t>(kg), 1};
+      uint64_t strides[2] = {kdim * 4, kdim * 4 * kg};
+      uint32_t box[3] = {static_cast<uint32_t>(ki.kblk), static_cast<uint32_t>(p.b_rows), 1};
+      const uint32_t ones[3] = {1, 1, 1};
+      rc = make_tmap(&tb, ki.dt, 3, w_packed + static_cast<uint64_t>(g) * kg * kdim, dims, strides, box, ones);
+      if (rc) return rc;
+    }
+    StoreMaps tc;
+    memset(&tc, 0, sizeof(tc));
+    if (staged) {
+      // (w, h, depth, channel of this group, image) view of the NCDHW result: a box of 32 channels is
+      // clipped at the end of the group
+      p.tma_store = 1;
+      p.num_dst = 1;
+      uint64_t dims[5] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(OD),
+                          static_cast<uint64_t>(kg), static_cast<uint64_t>(n)};
+      uint64_t strides[4] = {static_cast<uint64_t>(Q) * 4, static_cast<uint64_t>(P) * Q * 4,
+                             static_cast<uint64_t>(OD) * P * Q * 4, static_cast<uint64_t>(k) * OD * P * Q * 4};
+      uint32_t box[5] = {static_cast<uint32_t>(tile_w), static_cast<uint32_t>(tile_h), 1, 32, 1};
+      const uint32_t ones[5] = {1, 1, 1, 1, 1};
+      rc = make_tmap(&tc.dst[0], ki.dt, 5, out + static_cast<uint64_t>(g) * kg * OD * P * Q, dims, strides, box,
+                     ones, CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    }
+    rc = dispatch(KIND_TF32, OUT_F32, split3, pair, ta, tb, tc, p, ctas, stream);
+    if (rc) return rc;
+  }
+  return FTB_OK;
+}
+
 }  // namespace ftb
 
 // ------------------------------------------------------------------ C ABI
@@ -1551,6 +1756,23 @@ int ftb_conv2d_nchw_f32_multi(const float* in, const float* weight, const float*
   return ftb::conv2d_generic(in, weight, bias, out_dst[0], n, c, h, w, k, r, s, stride_h, stride_w, pad_h,
                              pad_w, dil_h, dil_w, groups, cfg, workspace, workspace_bytes, status, stream,
                              out_dst + 1, num_dst - 1, prepacked ? 2 : 0);
+}
+
+
+size_t ftb_conv3d_workspace_bytes(int64_t n, int64_t c, int64_t d, int64_t h, int64_t w, int64_t k, int64_t t,
+                                  int64_t r, int64_t s, int64_t groups) {
+  if (n <= 0 || c <= 0 || d <= 0 || h <= 0 || w <= 0 || k <= 0 || t <= 0 || r <= 0 || s <= 0 || groups <= 0) return 0;
+  if (c % groups) return 0;
+  const ftb::ConvWs ws = ftb::conv3d_ws(n, c, d, h, w, k, t, r, s, groups);
+  return static_cast<size_t>(ws.in_bytes + ws.w_bytes);
+}
+
+int ftb_conv3d_ncdhw_f32(const float* in, const float* weight, const float* bias, float* out, int64_t n, int64_t c,
+                         int64_t d, int64_t h, int64_t w, int64_t k, int64_t t, int64_t r, int64_t s,
+                         const int32_t* stride_dhw, const int32_t* pad_dhw, const int32_t* dil_dhw, int groups,
+                         const ftb_config* cfg, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+  return ftb::conv3d_generic(in, weight, bias, out, n, c, d, h, w, k, t, r, s, stride_dhw, pad_dhw, dil_dhw, groups,
+                             cfg, workspace, workspace_bytes, status, stream);
 }
 
 }  // extern "C"

@@ -76,6 +76,10 @@ struct UmmaParams {
   int tile_imgs;             // whole images per tile (> 1 only when an image has at most 64 output pixels)
   int n_imgs;                // images of the batch
   int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  // conv3d (conv_od > 0): the "images" of the tile list are (image, output depth) pairs, the filter
+  // has T depth taps in front of its R x S taps, and both tensors are addressed through 5-D maps:
+  // (c, w, h, d, n) for the input copy, (w, h, d, k, n) for the result.  One launch covers one group.
+  int conv_od, T, stride_d, pad_d, dil_d;
   int* status;
   int pdl;  // launched as a programmatic dependent: wait for the previous kernel before touching memory
   // TMA-store epilogue: tma_store != 0 stages 128-byte wide output slabs in shared memory and
@@ -242,6 +246,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t tx = a_boxes * a_box_bytes + b_boxes * b_box_bytes;
       const bool a_mn = p.a_mn != 0, b_mn = p.b_mn != 0, conv = p.conv != 0;
       const bool grouped = conv && p.conv_groups > 1;  // grouped conv: a tile's batch coordinate is its group
+      const bool conv3d = conv && p.conv_od > 0;       // (c, w, h, d, n) input map
       const bool release_pairs = p.release_pairs != 0;
       // In a pair every completion is reported to the leader's barrier.
       const uint32_t full_sig0 = PAIR ? map_to_cta(full0, 0) : full0;
@@ -257,7 +262,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int n0 = tc.n * p.bn + static_cast<int>(cta_rank) * p.b_rows;
         const int ab = p.a_bcast ? 0 : tc.b;  // batch coordinate of A
         // conv: walking (r, s, channel chunk) with counters instead of div/mod per block
-        int img = 0, h0 = 0, w0 = 0, cc = 0, ts = 0, tr = 0;
+        int img = 0, h0 = 0, w0 = 0, cc = 0, ts = 0, tr = 0, td = 0, d0 = 0;
         if (conv) {
           // this CTA's 128-pixel tile; one past the end (odd tile count in a pair) lands outside
           // the tensor and loads zeros
@@ -271,6 +276,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int rs = kb0 / p.cchunks;
           ts = rs % p.S;
           tr = rs / p.S;
+          if (conv3d) {
+            td = tr / p.R;
+            tr -= td * p.R;
+            const int n_img = img / p.conv_od;
+            d0 = (img - n_img * p.conv_od) * p.stride_d - p.pad_d;
+            img = n_img;
+          }
         }
         int kc = kb0 * kblk;  // K coordinate of the block
         for (int kb = kb0; kb < kb1; ++kb, kc += kblk) {
@@ -307,13 +319,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // own arrival.)
             if (cta_rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * tx);
             if (conv) {
-              if (grouped) tma_load_5d_pair(sa, &tmap_a, full, cc * kblk, tc.b, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
+              if (conv3d)
+                tma_load_5d_pair(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h,
+                                 d0 + td * p.dil_d, img);
+              else if (grouped)
+                tma_load_5d_pair(sa, &tmap_a, full, cc * kblk, tc.b, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
               else tma_load_4d_pair(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
               if (++cc == p.cchunks) {
                 cc = 0;
                 if (++ts == p.S) {
                   ts = 0;
-                  ++tr;
+                  if (++tr == p.R) {
+                    tr = 0;
+                    ++td;
+                  }
                 }
               }
             } else if (a_mn) {
@@ -331,13 +350,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           } else {
             mbar_expect_tx(full, tx);
             if (conv) {
-              if (grouped) tma_load_5d(sa, &tmap_a, full, cc * kblk, tc.b, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
+              if (conv3d)
+                tma_load_5d(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h, d0 + td * p.dil_d, img);
+              else if (grouped)
+                tma_load_5d(sa, &tmap_a, full, cc * kblk, tc.b, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
               else tma_load_4d(sa, &tmap_a, full, cc * kblk, w0 + ts * p.dil_w, h0 + tr * p.dil_h, img);
               if (++cc == p.cchunks) {
                 cc = 0;
                 if (++ts == p.S) {
                   ts = 0;
-                  ++tr;
+                  if (++tr == p.R) {
+                    tr = 0;
+                    ++td;
+                  }
                 }
               }
             } else if (a_mn) {
@@ -639,7 +664,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool row_ok;
       long long row_off;  // element offset of (row, column 0 of the problem)
       long long col_stride = 1;
-      int conv_mt = 0, conv_tw = 0, conv_th = 0, conv_img = 0;
+      int conv_mt = 0, conv_tw = 0, conv_th = 0, conv_img = 0, conv_dep = 0;
       // first output channel of this tile's group (grouped conv: group = batch coordinate)
       const int koff = p.conv ? p.conv_koff + tc.b * N : 0;
       if (p.conv) {
@@ -657,8 +682,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int ow = tw * p.tile_w + rr % p.tile_w;
         row_ok = mt < p.conv_tiles && row < p.tile_imgs * px_per_img && img < p.n_imgs && oh < p.P && ow < p.Q;
         col_stride = static_cast<long long>(p.P) * p.Q;
-        row_off = (static_cast<long long>(img) * p.conv_ktot + koff) * col_stride +
-                  static_cast<long long>(oh) * p.Q + ow;
+        if (p.conv_od > 0) {
+          // conv3d: image index = (image, output depth); a channel of the result is od planes
+          conv_img = img0 / p.conv_od;
+          conv_dep = img0 - conv_img * p.conv_od;
+          row_off = static_cast<long long>(conv_dep) * col_stride + static_cast<long long>(oh) * p.Q + ow;
+          col_stride *= p.conv_od;
+          row_off += (static_cast<long long>(conv_img) * p.conv_ktot + koff) * col_stride;
+        } else {
+          row_off = (static_cast<long long>(img) * p.conv_ktot + koff) * col_stride +
+                    static_cast<long long>(oh) * p.Q + ow;
+        }
       } else {
         const int gm = tc.m * p.pair_m + static_cast<int>(cta_rank) * kTileM + row;
         row_ok = gm < p.M;
@@ -709,7 +743,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           named_barrier_sync(1, 128);
           if (leader) {
             if (tile_ok && n0 + c < N) {
-              if (p.conv_groups > 1) {
+              if (p.conv_od > 0) {
+                // conv3d: (w, h, depth, channel, image)
+                if (p.split_k > 1)
+                  tma_reduce_add_5d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, conv_dep, n0 + c, conv_img);
+                else
+                  for (int d = 0; d < p.num_dst; ++d)
+                    tma_store_5d(&tmap_c.dst[d], buf, conv_tw * p.tile_w, conv_th * p.tile_h, conv_dep, n0 + c, conv_img);
+              } else if (p.conv_groups > 1) {
                 if (p.split_k > 1)
                   tma_reduce_add_5d(&tmap_c.dst[0], buf, conv_tw * p.tile_w, conv_th * p.tile_h, n0 + c, tc.b, conv_img);
                 else

@@ -8,6 +8,8 @@ reference's ``flextensor/nn/ops.py``:
   conv2d_nchw            ops.py:419-479   (pad -> conv [-> bias]: a 2- or 3-op graph)
   depthwise_conv2d_nchw  ops.py:622-678   (weight layout [C, factor, kh, kw])
   conv1d                 ops.py:293-351   (the same kernels, on a one-row image)
+  zero_pad3d             ops.py:157-189
+  conv3d_ncdhw           ops.py:689-751   (the per-tap conv kernel with a depth-tap loop)
   gemm_conv2d_nchw       ops.py:982-1044  (im2col -> GEMM -> col2img: the conv2d result by another route)
   conv2d_1x1_packed      task.py:168-173  (out[b,k,i] = sum_rc A[b,rc,i] * B[k,rc])
   gemm                   ops.py:1074-1108 (four transpose variants)
@@ -57,7 +59,7 @@ def _bias_add(output, bias):
 def relu(inputs):
     """max(x, 0) elementwise; following a convolution (or its bias) it is folded into the conv kernel's
     epilogue, as the bias is - the conv + bias + ReLU chain of a network runs as one kernel."""
-    names = ("b", "c", "h", "w")[:len(inputs.shape)] if len(inputs.shape) != 3 else ("b", "c", "l")
+    names = {3: ("b", "c", "l"), 5: ("b", "c", "d", "h", "w")}.get(len(inputs.shape), ("b", "c", "h", "w")[:len(inputs.shape)])
     op = ComputeOp("relu", "relu", tuple(int(s) for s in inputs.shape), inputs.dtype, [inputs], names)
     return op.output(0)
 
@@ -118,6 +120,59 @@ def conv1d(inputs, weight, bias=None, stride=1, padding=0, dilation=1, groups=1)
     if bias is not None:
         bop = ComputeOp("bias_add", "bias_add", (n, k, out_len), out.dtype, [out, bias], ("b", "c", "l"),
                         attrs={"axis": 1})
+        out = bop.output(0)
+    return out
+
+
+def _triple(value, what):
+    if isinstance(value, int):
+        return (value, value, value)
+    value = tuple(int(v) for v in value)
+    assert_print(len(value) == 3, "%s must be an int or a triple" % what)
+    return value
+
+
+def zero_pad3d(inputs, padding=0):
+    """Zero padding of [batch, channel, depth, height, width]; padding int, (d, h, w) or
+    (d_up, d_down, h_up, h_down, w_up, w_down)."""
+    if isinstance(padding, int):
+        padding = (padding,) * 6
+    assert_print(isinstance(padding, tuple), "type(padding)={}".format(type(padding)))
+    if len(padding) == 3:
+        padding = (padding[0], padding[0], padding[1], padding[1], padding[2], padding[2])
+    assert_print(len(padding) == 6)
+    b, c, d, h, w = (int(s) for s in inputs.shape)
+    shape = (b, c, d + padding[0] + padding[1], h + padding[2] + padding[3], w + padding[4] + padding[5])
+    op = ComputeOp("pad2d", "Padding", shape, inputs.dtype, [inputs], ("b", "c", "d", "h", "w"),
+                   attrs={"padding": tuple(padding)})
+    return op.output(0)
+
+
+def conv3d_ncdhw(inputs, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    """inputs [N,C,D,H,W], weight [K, C/groups, kd, kh, kw] -> [N, K, out_d, out_h, out_w]
+    (flextensor/nn/ops.py:689-751)."""
+    n, c, in_d, in_h, in_w = (int(s) for s in inputs.shape)
+    k, cg, k_d, k_h, k_w = (int(s) for s in weight.shape)
+    assert_print(cg * groups == c)
+    kg = k // groups
+    assert_print(kg * groups == k)
+    stride, padding, dilation = _triple(stride, "stride"), _triple(padding, "padding"), _triple(dilation, "dilation")
+    out_d = (in_d + 2 * padding[0] - dilation[0] * (k_d - 1) - 1) // stride[0] + 1
+    out_h = (in_h + 2 * padding[1] - dilation[1] * (k_h - 1) - 1) // stride[1] + 1
+    out_w = (in_w + 2 * padding[2] - dilation[2] * (k_w - 1) - 1) // stride[2] + 1
+    rc = reduce_axis((0, cg), name="rc")
+    rd = reduce_axis((0, k_d), name="rd")
+    rh = reduce_axis((0, k_h), name="rh")
+    rw = reduce_axis((0, k_w), name="rw")
+    padded = zero_pad3d(inputs, padding=padding)
+    op = ComputeOp("conv2d", "compute", (n, k, out_d, out_h, out_w), _acc_dtype(inputs.dtype), [padded, weight],
+                   ("b", "c", "d", "h", "w"), reduce_axes=[rc, rd, rw, rh],
+                   attrs={"stride": stride, "padding": padding, "dilation": dilation, "groups": groups,
+                          "form": "conv3d"})
+    out = op.output(0)
+    if bias is not None:
+        bop = ComputeOp("bias_add", "bias_add", (n, k, out_d, out_h, out_w), out.dtype, [out, bias],
+                        ("b", "c", "d", "h", "w"), attrs={"axis": 1})
         out = bop.output(0)
     return out
 

@@ -33,18 +33,31 @@ def host_result(ops, bufs, arrays):
     for op in op_lst:
         ins = op.input_tensors
         if op.kind == "pad2d":
-            p = op.attrs["padding"]
-            values[id(op.output(0))] = F.pad(val(ins[0]).double(), (p[2], p[3], p[0], p[1]))
+            p = op.attrs["padding"]  # (first axis before, after, ..., last axis before, after)
+            last_first = [v for i in range(len(p) - 2, -2, -2) for v in (p[i], p[i + 1])]
+            values[id(op.output(0))] = F.pad(val(ins[0]).double(), last_first)
         elif op.kind == "conv2d":
-            values[id(op.output(0))] = F.conv2d(val(ins[0]).double(), val(ins[1]).double(), None, op.attrs["stride"],
-                                                0, op.attrs["dilation"], op.attrs["groups"])
+            x, w = val(ins[0]).double(), val(ins[1]).double()
+            form = op.attrs.get("form")
+            if form == "conv1d":
+                res = F.conv1d(x, w, None, op.attrs["stride"][1], 0, op.attrs["dilation"][1], op.attrs["groups"])
+            elif form == "packed_1x1":
+                res = torch.einsum("bci,kc->bki", x, w)
+            elif form == "conv3d":
+                res = F.conv3d(x, w, None, op.attrs["stride"], 0, op.attrs["dilation"], op.attrs["groups"])
+            else:
+                res = F.conv2d(x, w, None, op.attrs["stride"], 0, op.attrs["dilation"], op.attrs["groups"])
+            values[id(op.output(0))] = res
         elif op.kind == "depthwise_conv2d":
             x, w = val(ins[0]).double(), val(ins[1]).double()
             c, f, r, s = w.shape
             values[id(op.output(0))] = F.conv2d(x, w.reshape(c * f, 1, r, s), None, op.attrs["stride"], 0,
                                                 op.attrs["dilation"], c)
         elif op.kind == "bias_add":
-            values[id(op.output(0))] = val(ins[0]) + val(ins[1]).double().reshape(1, -1, 1, 1)
+            x = val(ins[0])
+            values[id(op.output(0))] = x + val(ins[1]).double().reshape([1, -1] + [1] * (x.dim() - 2))
+        elif op.kind == "relu":
+            values[id(op.output(0))] = val(ins[0]).clamp(min=0)
         elif op.kind in ("gemm", "batch_gemm", "gemm_int8"):
             a, b = val(ins[0]).double(), val(ins[1]).double()
             if op.attrs["transposeA"]:

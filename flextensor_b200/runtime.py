@@ -210,6 +210,13 @@ class Module(object):
             elif op.kind == "gemm_int8":
                 backend.gemm_s8(ins[0], ins[1], out, op.attrs["transposeA"], op.attrs["transposeB"], cfg=cfg,
                                 status=status)
+            elif op.kind == "conv2d" and op.attrs.get("form") == "conv3d":
+                n, c, d, h, w = ins[0].shape
+                k, _, t, r, s = ins[1].shape
+                groups = op.attrs["groups"]
+                ws = self._workspace(idx, backend.conv3d_workspace_bytes(n, c, d, h, w, k, t, r, s, groups), device)
+                backend.conv3d_ncdhw_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
+                                         op.attrs["dilation"], groups, cfg=cfg, workspace=ws, status=status)
             elif op.kind == "conv2d":
                 form = op.attrs.get("form")
                 if form == "conv1d":        # [N,C,L] is a one-row image, the filter a one-row filter

@@ -348,7 +348,8 @@ def generate_space_intra_op_b200(op, down_graph=None):
         space.add_subspace("ctas", KnobSpace("ctas", [8, 7, 6, 4]), "unroll")
     elif family == "conv2d":
         # axes (b, c, h, w); a conv1d has (b, c, l) and runs as a one-row image, the packed 1x1 form
-        # has (b, k, i) and runs as a one-column image
+        # has (b, k, i) and runs as a one-column image, a conv3d has (b, c, d, h, w) and tiles the
+        # (h, w) plane of every output depth
         form = op.attrs.get("form")
         k_out = extents.get("c", extents.get("k")) // op.attrs.get("groups", 1)
         if form == "conv1d":
@@ -384,6 +385,8 @@ def generate_space_intra_op_b200(op, down_graph=None):
         # 4 = a 1x1 conv over the im2col form (at most 8 input channels under a filter of 4 taps or more)
         im2col_ok = one_group and rc <= 8 and taps >= 4
         algos = [1] + ([2] if slab_ok else []) + ([3] if gemm_ok else []) + ([4] if im2col_ok else [])
+        if form == "conv3d":
+            algos = [1]  # the per-tap lowering with its depth-tap loop
         space.add_subspace("algo", KnobSpace("algo", algos), "inline")
     else:  # depthwise
         out_h = extents["h"]

@@ -16,10 +16,11 @@ from .configs.conv2d_config import (yolo_shapes, res_shapes, res_shapes_b1, goog
 from .configs.depthwise_config import depthwise_shapes, depthwise_shapes_b8, depthwise_shapes_b16, b200_depthwise_shape
 from .configs.grouped_config import grouped_shapes, dilation_shapes
 from .configs.conv1d_config import conv1d_shapes
+from .configs.conv3d_config import conv3d_shapes
 from .configs.gemm_config import gemm_shapes, test_gemm_shapes, b200_batch_gemm_shapes, b200_gemm_int8_shapes
 from .ir import placeholder
 from .nn import conv2d_nchw, depthwise_conv2d_nchw, gemm as op_gemm, batch_gemm as op_batch_gemm, \
-    gemm_int8 as op_gemm_int8, conv1d as op_conv1d, gemm_conv2d_nchw, conv2d_1x1_packed as op_1x1_packed
+    gemm_int8 as op_gemm_int8, conv1d as op_conv1d, gemm_conv2d_nchw, conv2d_1x1_packed as op_1x1_packed, conv3d_ncdhw
 from .space import EnumSpace
 
 TASK_TABLE = {}
@@ -65,6 +66,13 @@ def conv1d(N, C, L, K, kernel, stride=1, padding=0, dilation=1, groups=1):
     Wt = placeholder((K, C // groups, kernel))
     Output = op_conv1d(Seq, Wt, stride=stride, padding=padding, dilation=dilation, groups=groups)
     return [Output.op], [Seq, Wt, Output]
+
+
+def conv3d(N, C, D, H, W, K, kernel_size, stride=1, padding=0, dilation=1, groups=1):
+    Img = placeholder((N, C, D, H, W))
+    Wt = placeholder((K, C // groups, kernel_size, kernel_size, kernel_size))
+    Output = conv3d_ncdhw(Img, Wt, stride=stride, padding=padding, dilation=dilation, groups=groups)
+    return [Output.op], [Img, Wt, Output]
 
 
 def gemm_conv2d(N, C, H, W, K, kernel_size, stride=1, padding=0, dilation=1, groups=1):
@@ -154,6 +162,10 @@ for _shape in dilation_shapes:
 for _shape in conv1d_shapes:
     _b, _c, _l, _k, _, _kl, _, _st, _pad, _dil, _grp = _shape
     _register_all("conv1d", "conv1d", conv1d, (_b, _c, _l, _k, _kl, _st, _pad, _dil, _grp))
+
+for _shape in conv3d_shapes:
+    _b, _c, _d, _h, _w, _k, _, _ks, _, _st, _pad, _dil, _grp = _shape
+    _register_all("conv3d", "conv3d", conv3d, (_b, _c, _d, _h, _w, _k, _ks, _st, _pad, _dil, _grp))
 
 # the packed 1x1 convolution (task.py:218 registers this one shape)
 _register_all("conv2d", "1x1-packed", conv2d_1x1_packed, (256, 256, 14, 14, 512, 1))

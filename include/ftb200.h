@@ -180,6 +180,19 @@ int ftb_conv2d_nchw_f32_multi(const float* in, const float* weight, const float*
                               int groups, int prepacked, const ftb_config* cfg, void* workspace,
                               size_t workspace_bytes, int* status, void* stream);
 
+/* out[N,K,OD,P,Q] = conv3d(in[N,C,D,H,W], w[K,C/groups,T,R,S]) (+ bias[K]), cross-correlation with
+ * zero padding folded into the loads (flextensor/nn/ops.py:157-189 zero_pad3d + :689-751
+ * conv3d_ncdhw).  stride_dhw / pad_dhw / dil_dhw point at three host ints each (depth, height,
+ * width).  The same implicit-GEMM kernel as conv2d with a third tap loop; groups run as one launch
+ * each.  Knobs as for conv2d, `algo` 0 or 1 only.  `workspace` as for conv2d, sized by
+ * ftb_conv3d_workspace_bytes. */
+size_t ftb_conv3d_workspace_bytes(int64_t n, int64_t c, int64_t d, int64_t h, int64_t w, int64_t k, int64_t t,
+                                  int64_t r, int64_t s, int64_t groups);
+int ftb_conv3d_ncdhw_f32(const float* in, const float* weight, const float* bias, float* out, int64_t n, int64_t c,
+                         int64_t d, int64_t h, int64_t w, int64_t k, int64_t t, int64_t r, int64_t s,
+                         const int32_t* stride_dhw, const int32_t* pad_dhw, const int32_t* dil_dhw, int groups,
+                         const ftb_config* cfg, void* workspace, size_t workspace_bytes, int* status, void* stream);
+
 /* conv2d without a caller workspace - no counterpart in the reference.
  *
  * For callers that cannot allocate device memory: code that receives its input and output

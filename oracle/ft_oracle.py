@@ -86,6 +86,38 @@ def conv1d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, acc=
     return out.reshape(n, k, -1)
 
 
+def conv3d_ncdhw(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, acc="f64", out_dtype=np.float32):
+    """out[b,c,d,h,w] = sum_{rc,rd,rh,rw} padded[b, c//Kg*Cg + rc, d*sd + rd*dd, h*sh + rh*dh, w*sw + rw*dw]
+    * weight[c,rc,rd,rh,rw] (+ bias[c]) (flextensor/nn/ops.py:157-189 zero_pad3d, :689-751 conv3d_ncdhw)."""
+    def triple(v):
+        return (v, v, v) if isinstance(v, int) else tuple(int(i) for i in v)
+    stride, padding, dilation = triple(stride), triple(padding), triple(dilation)
+    n, c, d, h, w = x.shape
+    k, cg, kd, kh, kw = weight.shape
+    assert cg * groups == c and k % groups == 0
+    kg = k // groups
+    od = out_size(d, kd, stride[0], padding[0], dilation[0])
+    oh = out_size(h, kh, stride[1], padding[1], dilation[1])
+    ow = out_size(w, kw, stride[2], padding[2], dilation[2])
+    at = _acc_dtype(acc)
+    padded = np.pad(x.astype(at), ((0, 0), (0, 0), (padding[0],) * 2, (padding[1],) * 2, (padding[2],) * 2))
+    wt = weight.astype(at)
+    out = np.zeros((n, k, od, oh, ow), dtype=at)
+    for g in range(groups):
+        pg = padded[:, g * cg:(g + 1) * cg]
+        wg = wt[g * kg:(g + 1) * kg]
+        for rd in range(kd):
+            for rh in range(kh):
+                for rw in range(kw):
+                    d0, h0, w0 = rd * dilation[0], rh * dilation[1], rw * dilation[2]
+                    win = pg[:, :, d0:d0 + (od - 1) * stride[0] + 1:stride[0],
+                             h0:h0 + (oh - 1) * stride[1] + 1:stride[1], w0:w0 + (ow - 1) * stride[2] + 1:stride[2]]
+                    out[:, g * kg:(g + 1) * kg] += np.einsum("bcdhw,kc->bkdhw", win, wg[:, :, rd, rh, rw], optimize=True)
+    if bias is not None:
+        out += bias.astype(at).reshape(1, k, 1, 1, 1)
+    return out.astype(out_dtype)
+
+
 def conv2d_1x1_packed(a, b, acc="f64", out_dtype=np.float32):
     """out[b,k,i] = sum_rc A[b,rc,i] * B[k,rc] (flextensor/task.py:168-173)."""
     at = _acc_dtype(acc)

@@ -41,6 +41,18 @@ def main():
     assert O.normalised_error(CO.conv2d_naive(x, w, b, (2, 2), (1, 1), (2, 2), 3), y) < 1e-6
     save("conv2d_grouped", x=x, w=w, b=b, y=y, params=np.array([2, 1, 2, 3]))
 
+    # conv3d: the reference's test case shape (flextensor/test/test_ops.py:187-214): 6 channels in 3 groups,
+    # 9 filters of 3x3x3, stride 2, padding 1, dilation 2, bias
+    rng = np.random.Generator(np.random.PCG64(106))
+    x = rng.uniform(-1, 1, (4, 6, 7, 7, 7)).astype(np.float32)
+    w = rng.uniform(-1, 1, (9, 2, 3, 3, 3)).astype(np.float32)
+    b = rng.uniform(-1, 1, 9).astype(np.float32)
+    y = O.conv3d_ncdhw(x, w, b, stride=2, padding=1, dilation=2, groups=3)
+    t = torch.nn.functional.conv3d(torch.tensor(x), torch.tensor(w), torch.tensor(b), stride=2, padding=1,
+                                   dilation=2, groups=3).numpy()
+    assert O.normalised_error(t, y) < 1e-5
+    save("conv3d_grouped", x=x, w=w, b=b, y=y, params=np.array([2, 1, 2, 3]))
+
     # conv2d: a 3x3 stride-1 pad-1 layer with a channel count that is not a multiple of 32
     x, w = O.conv2d_inputs(2, 20, 12, 14, 24, 3, 3, seed=101)
     y = O.conv2d_nchw(x, w, None, 1, 1, 1, 1)

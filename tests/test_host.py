@@ -63,6 +63,20 @@ def test_op_definitions_shapes_and_axes():
     dw = ops.depthwise_conv2d_nchw(placeholder((4, 6, 7, 7)), placeholder((6, 3, 3, 3)), stride=2, padding=1,
                                    dilation=2)
     assert to_tuple(dw.shape) == (4, 18, 3, 3)
+    # conv3d: the reference's test case shape (flextensor/test/test_ops.py:187-214) and per-axis parameters
+    c3 = ops.conv3d_ncdhw(placeholder((4, 6, 7, 7, 7)), placeholder((9, 2, 3, 3, 3)), placeholder((9,)), stride=2,
+                          padding=1, dilation=2, groups=3)
+    assert to_tuple(c3.shape) == (4, 9, 3, 3, 3) and c3.op.kind == "bias_add"
+    conv = c3.op.input_tensors[0].op
+    assert [a.var.name for a in conv.axis] == ["b", "c", "d", "h", "w"]
+    assert [(a.var.name, a.dom.extent.value) for a in conv.reduce_axis] == [("rc", 2), ("rd", 3), ("rw", 3), ("rh", 3)]
+    assert to_tuple(conv.input_tensors[0].shape) == (4, 6, 9, 9, 9)
+    c3 = ops.conv3d_ncdhw(placeholder((1, 8, 5, 9, 6)), placeholder((4, 8, 2, 3, 1)), stride=(1, 2, 3), padding=(1, 0, 2),
+                          dilation=(2, 1, 1))
+    assert to_tuple(c3.shape) == (1, 4, 5, 4, 4)
+    assert to_tuple(ops.zero_pad3d(placeholder((1, 2, 3, 4, 5)), (1, 2, 0, 1, 3, 0)).shape) == (1, 2, 6, 5, 8)
+    with pytest.raises(AssertionError):
+        ops.conv3d_ncdhw(placeholder((1, 6, 7, 7, 7)), placeholder((9, 4, 3, 3, 3)), groups=3)
     a, b = placeholder((8, 16)), placeholder((16, 4))
     assert to_tuple(ops.gemm(a, b).shape) == (8, 4)
     assert to_tuple(ops.gemm(placeholder((16, 8)), b, transposeA=True).shape) == (8, 4)
@@ -97,6 +111,7 @@ def test_task_keys_and_registry():
     assert "conv2d_depthwise_(1, 256, 56, 56, 1, 3, 1, 1, 1)_cuda(0)" in TASK_TABLE
     assert "gemm_batch_gemm_(64, 2048, 2048, 2048)_cuda(7)" in TASK_TABLE
     assert "gemm_gemm_int8_(8192, 8192, 8192)_cuda(0)" in TASK_TABLE
+    assert "conv3d_conv3d_(1, 64, 8, 28, 28, 128, 3, 2, 1, 1, 1)_cuda(0)" in TASK_TABLE
     marker = Task("gemm", "gemm", "replaced", (32, 32, 32), "cuda", 0)
     old = TASK_TABLE[marker.key]
     register_task(marker)                          # silent overwrite, as in the reference
@@ -161,6 +176,13 @@ def test_b200_space_per_family():
             .subspaces["algo"].static_entities] == [1]                    # the slab kernel is stride 1 only
     knobs = config_to_knobs({"spatial": [[64], [2], [1]], "inline": [[2]]}, op_lst[1])
     assert knobs == {"tile_n": 64, "tile_h": 2, "cluster": 1, "algo": 2}
+    from flextensor_b200.task import conv3d
+    c3 = flatten_graph(conv3d(1, 64, 8, 28, 28, 64, 3, 1, 1, 1, 1)[0])
+    assert [op.kind for op in c3[0]] == ["pad2d", "conv2d"]
+    c3s = SP.generate_space_intra_op(c3[0][1], c3[1], target="cuda")
+    assert [e[0] for e in c3s.subspaces["algo"].static_entities] == [1]      # per-tap lowering with a depth-tap loop
+    assert [e[0] for e in c3s.subspaces["tile_h"].static_entities] == [1, 2, 3, 4]   # rows of the 28 x 28 plane
+    assert 9 in [e[0] for e in c3s.subspaces["split_k"].static_entities]      # 27 taps x 2 channel chunks
     dw = SP.generate_space_intra_op(flatten_graph(depthwise_conv2d(1, 256, 56, 56, 1, 3, 1, 1, 1)[0])[0][1], {},
                                     target="cuda")
     assert list(dw.subspaces) == ["tile_h", "threads"]

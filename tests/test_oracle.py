@@ -55,6 +55,33 @@ def test_conv2d_as_reference_test_does():
     np.testing.assert_allclose(got, want, rtol=1e-5 * 1000)
 
 
+def test_golden_conv3d_grouped():
+    g = _load("conv3d_grouped")
+    stride, pad, dil, groups = (int(v) for v in g["params"])
+    y = O.conv3d_ncdhw(g["x"], g["w"], g["b"], stride, pad, dil, groups)
+    assert O.normalised_error(y, g["y"]) < 1e-6
+
+
+def test_conv3d_as_reference_test_does():
+    """flextensor/test/test_ops.py:187-214: [4,6,7,7,7] input x100, [9,2,3,3,3] filter x100, bias x100, stride 2,
+    padding 1, dilation 2, groups 3, compared with torch at rtol 1e-5; then per-axis parameters."""
+    rng = np.random.default_rng(9)
+    x = (rng.random((4, 6, 7, 7, 7)) * 100).astype(np.float32)
+    w = (rng.random((9, 2, 3, 3, 3)) * 100).astype(np.float32)
+    b = (rng.random(9) * 100).astype(np.float32)
+    want = torch.nn.functional.conv3d(torch.tensor(x).double(), torch.tensor(w).double(), torch.tensor(b).double(),
+                                      stride=2, padding=1, dilation=2, groups=3).numpy()
+    got = O.conv3d_ncdhw(x, w, b, stride=2, padding=1, dilation=2, groups=3)
+    np.testing.assert_allclose(got, want, rtol=1e-5)
+    x = rng.standard_normal((2, 8, 5, 9, 6)).astype(np.float32)
+    w = rng.standard_normal((6, 4, 2, 3, 1)).astype(np.float32)
+    want = torch.nn.functional.conv3d(torch.tensor(x).double(), torch.tensor(w).double(), None, stride=(1, 2, 3),
+                                      padding=(1, 0, 2), dilation=(2, 1, 1), groups=2).numpy()
+    got = O.conv3d_ncdhw(x, w, None, stride=(1, 2, 3), padding=(1, 0, 2), dilation=(2, 1, 1), groups=2)
+    assert got.shape == want.shape
+    assert O.normalised_error(got, want) < 1e-6
+
+
 def test_depthwise_as_reference_test_does():
     """flextensor/test/test_ops.py:152-184: weight [18,1,3,3] for torch is [6,3,3,3] for the op; rtol 1e-5."""
     rng = np.random.default_rng(8)
