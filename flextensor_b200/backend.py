@@ -144,6 +144,10 @@ def lib():
         handle.ftb_conv2d_nchw_f32_multi.restype = i32
         handle.ftb_conv2d_nchw_f32_multi.argtypes = ([vp] * 3 + [ctypes.POINTER(vp), i32] + [i64] * 7 + [i32] * 8 +
                                                      [cfgp, vp, ctypes.c_size_t, vp, vp])
+        handle.ftb_conv2d_nhwc_workspace_bytes.restype = ctypes.c_size_t
+        handle.ftb_conv2d_nhwc_workspace_bytes.argtypes = [i64] * 5
+        handle.ftb_conv2d_nhwc_f32.restype = i32
+        handle.ftb_conv2d_nhwc_f32.argtypes = ([vp] * 4 + [i64] * 7 + [i32] * 8 + [cfgp, vp, ctypes.c_size_t, vp, vp])
         handle.ftb_conv3d_workspace_bytes.restype = ctypes.c_size_t
         handle.ftb_conv3d_workspace_bytes.argtypes = [i64] * 10
         handle.ftb_conv3d_ncdhw_f32.restype = i32
@@ -166,6 +170,7 @@ EXPORTED_SYMBOLS = (
     "ftb_conv2d_workspace_bytes", "ftb_conv2d_nchw_f32", "ftb_conv2d_nchw_f32_noalloc", "ftb_dwconv2d_nchw_f32",
     "ftb_dwconv2d_nchw_f32_multi", "ftb_conv2d_nchw_f32_multi", "ftb_conv2d_pack_filter",
     "ftb_conv2d_nchw_f32_prepacked", "ftb_conv3d_workspace_bytes", "ftb_conv3d_ncdhw_f32",
+    "ftb_conv2d_nhwc_f32", "ftb_conv2d_nhwc_workspace_bytes",
 )
 
 
@@ -419,6 +424,36 @@ def conv2d_nchw_f32_multi(x, weight, dst_ptrs, bias=None, stride=(1, 1), padding
             workspace.numel() * workspace.element_size(), _status_ptr(status), _stream_ptr(stream))
     if rc:
         raise FtbError(rc, "ftb_conv2d_nchw_f32_multi")
+
+
+def conv2d_nhwc_workspace_bytes(c, k, r, s, groups=1):
+    return int(lib().ftb_conv2d_nhwc_workspace_bytes(c, k, r, s, groups))
+
+
+def conv2d_nhwc_f32(x, weight, out, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1,
+                    cfg=None, workspace=None, status=None, stream=None, prepacked=False):
+    """Channels-last conv2d: out[N,P,Q,K] = conv2d(x[N,H,W,C], weight[K,C/groups,R,S]) (+ bias), read and
+    written where the tensors lie (no layout pass).  ``workspace``: a uint8 CUDA tensor of at least
+    ``conv2d_nhwc_workspace_bytes`` bytes for the packed filter; ``prepacked``: it holds this weight's packing from an earlier call with the same shapes and knobs."""
+    for t, nm in ((x, "x"), (weight, "weight"), (out, "out")):
+        _check(t, torch.float32, nm)
+    if bias is not None:
+        _check(bias, torch.float32, "bias")
+    n, h, w, c = x.shape
+    k, cg, r, s = weight.shape
+    if cg * groups != c:
+        raise ValueError("conv2d: weight channels %d x groups %d != input channels %d" % (cg, groups, c))
+    need = conv2d_nhwc_workspace_bytes(c, k, r, s, groups)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        raise ValueError("conv2d: workspace of at least %d bytes required" % need)
+    with torch.cuda.device(out.device):
+        rc = lib().ftb_conv2d_nhwc_f32(
+            x.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(),
+            n, c, h, w, k, r, s, stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
+            groups, int(prepacked), _cfg_ptr(cfg), workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(), _status_ptr(status), _stream_ptr(stream))
+    if rc:
+        raise FtbError(rc, "ftb_conv2d_nhwc_f32")
 
 
 def _triple(value, what):

@@ -52,6 +52,8 @@ struct ConvSlabParams {
                 // 1024-byte period of the swizzle); timing either against the real kernel shows what the
                 // taps' odd start addresses cost
   int num_dst;  // destinations of the staged epilogue (1..kMaxDst): the same box goes to each of them
+  int cl_out;   // the result is channels-last [N][P][Q][K]: staged as [pixel][32 channels], stored through a
+                // (k, q, p, n) map
   uint32_t epi_buf_bytes;
   uint32_t slab_bytes;   // bytes one slab load delivers
   uint32_t slab_alloc;   // bytes reserved per slab stage (covers the furthest tap's 128 rows)
@@ -324,6 +326,61 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         const int img = t / tiles_per_img;
         const int rem = t - img * tiles_per_img;
         const int th = rem / p.tiles_w, tw = rem - th * p.tiles_w;
+        if (p.epi_bufs && p.cl_out) {
+          // ---- channels-last result: TMEM -> registers -> [tile_h][tile_w][32 channels] in shared memory
+          // (a lane writes its pixel's 128 bytes) -> one bulk tensor store per 32 output channels
+          const bool leader = (warp == 2 && lane == 0);
+          const uint32_t px_row = static_cast<uint32_t>(prow * p.tile_w + pcol) * 128u;
+          for (int c = 0; c < p.bn; c += 32, ++epi_seq) {
+            const uint32_t buf = epi_base + (p.epi_bufs == 2 ? (epi_seq & 1u) : 0u) * p.epi_buf_bytes;
+            if (leader) {
+              if (p.epi_bufs == 2) bulk_wait_group_read<1>();
+              else bulk_wait_group_read<0>();
+            }
+            named_barrier_sync(1, 128);
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c, v);
+            tmem_ld_wait();
+            if (c + 32 >= p.bn) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(tempty_sig0 + 8 * acc);
+                else mbar_arrive(tempty_sig0 + 8 * acc);
+              }
+            }
+            if (in_tile) {
+              const bool add_bias = p.bias != nullptr && ks == 0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float x = __uint_as_float(v[j]);
+                if (add_bias && c + j < p.N) x += p.bias[c + j];
+                if (p.relu) x = fmaxf(x, 0.0f);
+                v[j] = __float_as_uint(x);
+              }
+              // (the lanes' 128-byte pitch makes these stores collide on their banks; they run beside
+              // the next tile's main loop and are a small part of a tile's time)
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                st_shared_v4(buf + px_row + (static_cast<uint32_t>(j) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2],
+                             v[4 * j + 3]);
+            }
+            fence_proxy_async_smem();
+            named_barrier_sync(1, 128);
+            if (leader) {
+              if (c < p.N && tile_valid) {
+                if (p.split > 1) {
+                  tma_reduce_add_4d(&tmap_out.dst[0], buf, c, tw * p.tile_w, th * p.tile_h, img);
+                } else {
+                  for (int d = 0; d < p.num_dst; ++d)
+                    tma_store_4d(&tmap_out.dst[d], buf, c, tw * p.tile_w, th * p.tile_h, img);
+                }
+              }
+              bulk_commit_group();
+            }
+          }
+          continue;
+        }
         if (p.epi_bufs) {
           // ---- TMEM -> registers -> [channel][tile_h][tile_w] in shared memory -> one bulk tensor
           // store (or fp32 reduce-add when the taps are split) per 32 output channels.  Lanes hold
@@ -380,7 +437,9 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         }
         const int oh = th * p.tile_h + prow, ow = tw * p.tile_w + pcol;
         const bool row_ok = in_tile && oh < p.P && ow < p.Q && tile_valid;
-        float* dst0 = p.out + static_cast<long long>(img) * p.conv_ktot * plane + static_cast<long long>(oh) * p.Q + ow;
+        const long long ch_stride = p.cl_out ? 1 : plane;
+        float* dst0 = p.cl_out ? p.out + (static_cast<long long>(img) * plane + static_cast<long long>(oh) * p.Q + ow) * p.conv_ktot
+                               : p.out + static_cast<long long>(img) * p.conv_ktot * plane + static_cast<long long>(oh) * p.Q + ow;
         for (int c = 0; c < p.bn; c += 32) {
           uint32_t v[32];
           tmem_ld_32x32(taddr + c, v);
@@ -401,7 +460,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
               float x = __uint_as_float(v[j]);
               if (p.bias != nullptr && ks == 0) x += p.bias[n];
               if (p.relu) x = fmaxf(x, 0.0f);
-              float* dst = dst0 + n * plane;
+              float* dst = dst0 + n * ch_stride;
               if (p.split > 1) atomicAdd(dst, x);
               else *dst = x;
             }

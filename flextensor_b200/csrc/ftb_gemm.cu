@@ -861,16 +861,17 @@ struct SlabPlan {
 
 static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t P, int64_t Q, int64_t r, int64_t s,
                           int64_t cchunks, int dil_h, int dil_w, int pad_h, int pad_w, bool out_aligned,
-                          int num_sms) {
+                          int num_sms, bool cl_out = false) {
   SlabPlan sp;
   memset(&sp, 0, sizeof(sp));
   if (kg > 256) return sp;
   const int halo_w = static_cast<int>(s - 1) * dil_w, halo_h = static_cast<int>(r - 1) * dil_h;
   if (halo_w >= 64 || halo_h >= 128) return sp;
   // Bulk tensor stores of the result need 16-byte aligned rows and boxes.
-  const bool staged_ok = out_aligned && Q % 4 == 0;
+  // (a channels-last result has its channels innermost: the caller has checked their pitch)
+  const bool staged_ok = out_aligned && (cl_out || Q % 4 == 0);
   int tile_w = static_cast<int>(Q < 128 - halo_w ? Q : 128 - halo_w);
-  if (tile_w < Q && staged_ok) tile_w &= ~3;
+  if (tile_w < Q && staged_ok && !cl_out) tile_w &= ~3;
   const int slab_w = tile_w + halo_w;
   int tile_h = 128 / slab_w;
   if (tile_h > P) tile_h = static_cast<int>(P);
@@ -898,10 +899,12 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   if (tiles > 0x7fffffffll) return sp;
   // A CTA pair shares one MMA over two consecutive tiles and splits the filter rows between its CTAs.
   // Taken when asked for (cluster = 2) or, left open, when there are enough tiles to keep every pair
-  // busy; it needs halves of the filter rows that are whole 8-row groups.
+  // busy and more than 64 output channels (halving a 64-row filter tile saves little: 56.5 us single
+  // against 60.3 us paired on 64 -> 64 channels at 56 x 56, batch 64; 99 against 60 us on 128 -> 128
+  // at 28 x 28); it needs halves of the filter rows that are whole 8-row groups.
   const int want_cluster = user ? user->cluster : 0;
   const bool pair = bn % 16 == 0 && num_sms >= 2 && want_cluster != 1 &&
-                    (want_cluster == 2 || tiles >= 2ll * num_sms);
+                    (want_cluster == 2 || (tiles >= 2ll * num_sms && bn > 64));
   sp.pair = pair;
   const uint32_t b_tile = static_cast<uint32_t>(pair ? bn / 2 : bn) * 128u;
   const size_t after_min = tail > epi_buf ? tail : epi_buf;
@@ -946,6 +949,7 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);
   p.a_stages = a_stages;
   p.epi_bufs = epi_bufs;
+  p.cl_out = cl_out ? 1 : 0;
   p.epi_buf_bytes = epi_buf;
   p.slab_bytes = static_cast<uint32_t>(slab_rows * 128);
   p.slab_alloc = slab_stride;
@@ -1022,12 +1026,16 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
                    int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,
                    int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
                    const ftb_config* user, void* workspace, size_t workspace_bytes, int* status,
-                   void* stream_v, float* const* extra_dst, int num_extra, int filter_mode) {
+                   void* stream_v, float* const* extra_dst, int num_extra, int filter_mode, int layout) {
   // filter_mode: 0 = pack the filter and run; 1 = pack the filter into the workspace and return;
   // 2 = the workspace already holds this filter's packing (same shape arguments and knobs)
-  if (filter_mode < 0 || filter_mode > 2) return FTB_E_BAD_ARG;
+  // layout: 0 = NCHW input and result; 1 = channels-last input [N][H][W][C] and result [N][P][Q][K]:
+  // the kernels read the input where it lies (it already has the layout their tensor maps want) and
+  // the layout pass only packs the filter
+  if (filter_mode < 0 || filter_mode > 2 || layout < 0 || layout > 1) return FTB_E_BAD_ARG;
   const bool pack_only = filter_mode == 1;
-  const int parts = pack_only ? 2 : filter_mode == 2 ? 1 : 3;
+  const bool cl = layout == 1;
+  const int parts = (pack_only ? 2 : filter_mode == 2 ? 1 : 3) & (cl ? 2 : 3);
   if (!weight || (!pack_only && (!in || !out))) return FTB_E_BAD_ARG;
   if (num_extra < 0 || num_extra > kMaxDst - 1 || (num_extra > 0 && !extra_dst)) return FTB_E_BAD_ARG;
   for (int d = 0; d < num_extra; ++d)
@@ -1055,10 +1063,18 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   int rc = device_ok();
   if (rc) return rc;
   const int64_t cg = c / groups, kg = k / groups;
-  const ConvWs ws = conv_ws(n, c, h, w, k, r, s, groups);
+  ConvWs ws = conv_ws(n, c, h, w, k, r, s, groups);
+  if (cl) {
+    // Tensor maps on the caller's tensors: 16-byte aligned bases and pitches.
+    if (cg % 4 || kg % 4) return FTB_E_UNSUPPORTED;
+    if (!pack_only && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15)) return FTB_E_UNSUPPORTED;
+    ws.cgp = cg;
+    ws.cp = c;
+    ws.in_bytes = 0;  // the workspace holds the packed filter only
+  }
   if (!workspace || workspace_bytes < static_cast<size_t>(ws.in_bytes + ws.w_bytes)) return FTB_E_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return FTB_E_WORKSPACE;
-  float* in_nhwc = static_cast<float*>(workspace);
+  float* in_nhwc = cl ? const_cast<float*>(in) : static_cast<float*>(workspace);
   float* w_packed = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ws.in_bytes);
 
   const KindInfo ki = kind_info(KIND_TF32);
@@ -1072,7 +1088,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   // out[b] (K x HW) = weight (K x C) * in[b] (C x HW), the pixels being the contiguous dimension
   // of both the B operand and the result.  No layout pass, no workspace traffic.
   {
-    const bool is_gemm = r == 1 && s == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 &&
+    const bool is_gemm = !cl && r == 1 && s == 1 && stride_h == 1 && stride_w == 1 && pad_h == 0 && pad_w == 0 &&
                          groups == 1 && (h * w) % 4 == 0 && c % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
     if (algo == 3 && !is_gemm && !pack_only) return FTB_E_UNSUPPORTED;
@@ -1098,7 +1114,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   bool im2col = false;
   struct { int64_t c, h, w, r, s; int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w; } orig =
       {c, h, w, r, s, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w};
-  if ((algo == 0 || algo == 4) && conv_small_c(c, r, s, groups)) {
+  if (!cl && (algo == 0 || algo == 4) && conv_small_c(c, r, s, groups)) {
     const int64_t kp = round_up(r * s * c, 32);
     if (round_up(n * P * Q * kp * 4, 1024) <= ws.in_bytes && n * P * Q * kp < (1ll << 31)) {
       im2col = true;
@@ -1113,7 +1129,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   // just those, and what follows is a stride-1 conv over the P x Q image of kept pixels.
   int sub_sh = 1, sub_sw = 1;
   const int64_t h_in = h, w_in = w;
-  if (!im2col && r == 1 && s == 1 && pad_h == 0 && pad_w == 0 && (stride_h > 1 || stride_w > 1)) {
+  if (!cl && !im2col && r == 1 && s == 1 && pad_h == 0 && pad_w == 0 && (stride_h > 1 || stride_w > 1)) {
     sub_sh = stride_h;
     sub_sw = stride_w;
     h = P;
@@ -1128,7 +1144,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   if (algo != 1 && groups == 1 && stride_h == 1 && stride_w == 1 && !split3 && (r * s > 1 || algo == 2) &&
       !(user && user->cluster == 2 && algo != 2))
     sp = plan_slab(user, n, kg, P, Q, r, s, ws.cchunks, dil_h, dil_w, pad_h, pad_w,
-                   (reinterpret_cast<uintptr_t>(out) & 15) == 0, num_sms);
+                   (reinterpret_cast<uintptr_t>(out) & 15) == 0, num_sms, cl);
   if (sp.ok && num_extra > 0 && (sp.p.epi_bufs == 0 || sp.p.split > 1)) sp.ok = false;
   if (algo == 2 && !sp.ok) return FTB_E_UNSUPPORTED;
   // Left to itself the slab kernel is taken when the whole filter stays resident, or when the tile
@@ -1174,7 +1190,20 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     StoreMaps tout;
     memset(&tout, 0, sizeof(tout));
     sp.p.num_dst = 1 + num_extra;
-    if (sp.p.epi_bufs) {
+    if (sp.p.epi_bufs && cl) {
+      // (channel, w, h, image) view of the channels-last result; a box is 32 channels of one output tile
+      uint64_t dims[4] = {static_cast<uint64_t>(k), static_cast<uint64_t>(Q), static_cast<uint64_t>(P),
+                          static_cast<uint64_t>(n)};
+      uint64_t strides[3] = {static_cast<uint64_t>(k) * 4, static_cast<uint64_t>(Q) * k * 4,
+                             static_cast<uint64_t>(P) * Q * k * 4};
+      uint32_t box[4] = {32, static_cast<uint32_t>(sp.p.tile_w), static_cast<uint32_t>(sp.p.tile_h), 1};
+      const uint32_t ones[4] = {1, 1, 1, 1};
+      for (int d = 0; d < sp.p.num_dst; ++d) {
+        rc = make_tmap(&tout.dst[d], ki.dt, 4, d == 0 ? out : extra_dst[d - 1], dims, strides, box, ones,
+                       CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+      }
+    } else if (sp.p.epi_bufs) {
       // (w, h, channel, image) view of the NCHW result; a box is 32 channels of one output tile.
       uint64_t dims[4] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(k),
                           static_cast<uint64_t>(n)};
@@ -1214,6 +1243,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   // and boxes) and the staging buffers fit beside the chosen pipeline depth.
   bool staged = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && Q % 4 == 0 && tile_w % 4 == 0 &&
                 (P * Q * 4) % 16 == 0 && (groups == 1 || (kg * P * Q * 4) % 16 == 0);
+  if (cl) staged = true;  // channels innermost: base and pitches were checked above
   if (user && user->epilogue == 1) staged = false;  // per-thread stores asked for
   if (user && (user->epilogue < 0 || user->epilogue > 1)) return FTB_E_BAD_CONFIG;
   // One wave of tiles or less, knobs left open: pick tile width and reduction split together by
@@ -1346,6 +1376,8 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.a_layout = 2;
     p.pair_m = pair ? 2 * kTileM : kTileM;
     p.conv = 1;
+    p.conv_cl = cl ? 1 : 0;
+    p.slab_cols = 32;
     p.pdl = 1;  // directly follows the layout pass
     p.conv_ktot = static_cast<int>(k);
     p.conv_koff = 0;
@@ -1407,7 +1439,33 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     }
     StoreMaps tc;
     memset(&tc, 0, sizeof(tc));
-    if (staged && groups > 1) {
+    if (staged && cl) {
+      // channels-last result: (k, q, p, n), or (k in group, group, q, p, n) where a box of 32
+      // channels is clipped at the end of its group; the staged slab is 128-byte swizzled
+      p.tma_store = 1;
+      p.num_dst = 1 + num_extra;
+      const int rank = groups > 1 ? 5 : 4;
+      uint64_t dims[5], strides[4];
+      uint32_t box[5];
+      const uint32_t ones[5] = {1, 1, 1, 1, 1};
+      int i = 0;
+      dims[i] = static_cast<uint64_t>(kg); box[i] = 32; ++i;
+      if (groups > 1) {
+        strides[i - 1] = static_cast<uint64_t>(kg) * 4;
+        dims[i] = static_cast<uint64_t>(groups); box[i] = 1; ++i;
+      }
+      strides[i - 1] = static_cast<uint64_t>(k) * 4;
+      dims[i] = static_cast<uint64_t>(Q); box[i] = static_cast<uint32_t>(tile_w); ++i;
+      strides[i - 1] = static_cast<uint64_t>(Q) * k * 4;
+      dims[i] = static_cast<uint64_t>(P); box[i] = static_cast<uint32_t>(tile_h); ++i;
+      strides[i - 1] = static_cast<uint64_t>(P) * Q * k * 4;
+      dims[i] = static_cast<uint64_t>(n); box[i] = static_cast<uint32_t>(tile_imgs); ++i;
+      for (int d = 0; d < p.num_dst; ++d) {
+        rc = make_tmap(&tc.dst[d], ki.dt, rank, d == 0 ? out : extra_dst[d - 1], dims, strides, box, ones,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+      }
+    } else if (staged && groups > 1) {
       // (w, h, channel in group, group, image) view of the NCHW result: a box of 32 channels is
       // clipped at the end of its group
       p.tma_store = 1;
@@ -1758,6 +1816,20 @@ int ftb_conv2d_nchw_f32_multi(const float* in, const float* weight, const float*
                              out_dst + 1, num_dst - 1, prepacked ? 2 : 0);
 }
 
+
+size_t ftb_conv2d_nhwc_workspace_bytes(int64_t c, int64_t k, int64_t r, int64_t s, int64_t groups) {
+  if (c <= 0 || k <= 0 || r <= 0 || s <= 0 || groups <= 0 || c % groups) return 0;
+  return static_cast<size_t>(ftb::conv_ws(1, c, 1, 1, k, r, s, groups).w_bytes);
+}
+
+int ftb_conv2d_nhwc_f32(const float* in, const float* weight, const float* bias, float* out, int64_t n, int64_t c,
+                        int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h, int stride_w, int pad_h,
+                        int pad_w, int dil_h, int dil_w, int groups, int prepacked, const ftb_config* cfg,
+                        void* workspace, size_t workspace_bytes, int* status, void* stream) {
+  return ftb::conv2d_generic(in, weight, bias, out, n, c, h, w, k, r, s, stride_h, stride_w, pad_h, pad_w, dil_h,
+                             dil_w, groups, cfg, workspace, workspace_bytes, status, stream, nullptr, 0,
+                             prepacked ? 2 : 0, 1);
+}
 
 size_t ftb_conv3d_workspace_bytes(int64_t n, int64_t c, int64_t d, int64_t h, int64_t w, int64_t k, int64_t t,
                                   int64_t r, int64_t s, int64_t groups) {

@@ -35,6 +35,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
                    int64_t c, int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h,
                    int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int groups,
                    const ftb_config* user, void* workspace, size_t workspace_bytes, int* status,
-                   void* stream, float* const* extra_dst = nullptr, int num_extra = 0, int filter_mode = 0);
+                   void* stream, float* const* extra_dst = nullptr, int num_extra = 0, int filter_mode = 0,
+                   int layout = 0);
 
 }  // namespace ftb

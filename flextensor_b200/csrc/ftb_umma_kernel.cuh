@@ -80,6 +80,10 @@ struct UmmaParams {
   // has T depth taps in front of its R x S taps, and both tensors are addressed through 5-D maps:
   // (c, w, h, d, n) for the input copy, (w, h, d, k, n) for the result.  One launch covers one group.
   int conv_od, T, stride_d, pad_d, dil_d;
+  // conv_cl != 0: the result is channels-last ([N][P][Q][K]; the input then is [N][H][W][C] as the
+  // caller gave it): the staged epilogue writes [pixel][32 channels] slabs like the GEMM's and stores
+  // them through a (k, q, p, n) map, or (k in group, group, q, p, n) with groups.
+  int conv_cl;
   int* status;
   int pdl;  // launched as a programmatic dependent: wait for the previous kernel before touching memory
   // TMA-store epilogue: tma_store != 0 stages 128-byte wide output slabs in shared memory and
@@ -689,6 +693,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           row_off = static_cast<long long>(conv_dep) * col_stride + static_cast<long long>(oh) * p.Q + ow;
           col_stride *= p.conv_od;
           row_off += (static_cast<long long>(conv_img) * p.conv_ktot + koff) * col_stride;
+        } else if (p.conv_cl) {
+          row_off = ((static_cast<long long>(img) * p.P + oh) * p.Q + ow) * p.conv_ktot + koff;
+          col_stride = 1;
         } else {
           row_off = (static_cast<long long>(img) * p.conv_ktot + koff) * col_stride +
                     static_cast<long long>(oh) * p.Q + ow;
@@ -700,7 +707,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       row_ok = row_ok && has_work;
 
-      if (p.conv && p.tma_store) {
+      if (p.conv && !p.conv_cl && p.tma_store) {
         // ---- conv, staged: TMEM -> registers -> [channel][tile_h][tile_w] in shared memory -> one
         // bulk tensor store (fp32 reduce-add under split-K) per 32 output channels.  Lanes hold
         // consecutive pixels, so the shared-memory writes of a channel are conflict-free and global
@@ -871,7 +878,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tmem_ld_32x32(taddr + c, v);
             tmem_ld_wait();
             if constexpr (OUT == OUT_F32) {
-              if (p.bias != nullptr && tc.ks == 0 && m0 + row < p.M) {
+              if (p.conv_cl) {
+                // channels-last conv: the bias belongs to the column (output channel)
+                if (p.bias != nullptr && tc.ks == 0) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (n0 + c + j < N) v[j] = __float_as_uint(__uint_as_float(v[j]) + p.bias[koff + n0 + c + j]);
+                }
+                if (p.relu) {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.0f));
+                }
+              } else if (p.bias != nullptr && tc.ks == 0 && m0 + row < p.M) {
                 const float bias = p.bias[m0 + row];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + bias);
@@ -894,7 +912,22 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           fence_proxy_async_smem();  // the slab must be visible to the bulk-copy engine
           named_barrier_sync(bar_sync_id, 128);
           if (leader) {
-            if (has_work && ncol(c) < N) {
+            if (p.conv_cl) {
+              // the slab's rows are the tile's pixels in (image, row, column) order: the box of the store
+              if (has_work && conv_mt < p.conv_tiles && n0 + c < N) {
+                const int x = conv_tw * p.tile_w, y = conv_th * p.tile_h;
+                if (p.conv_groups > 1) {
+                  if (p.split_k > 1)
+                    tma_reduce_add_5d(&tmap_c.dst[0], buf, n0 + c, tc.b, x, y, conv_img);
+                  else
+                    for (int d = 0; d < p.num_dst; ++d) tma_store_5d(&tmap_c.dst[d], buf, n0 + c, tc.b, x, y, conv_img);
+                } else if (p.split_k > 1) {
+                  tma_reduce_add_4d(&tmap_c.dst[0], buf, n0 + c, x, y, conv_img);
+                } else {
+                  for (int d = 0; d < p.num_dst; ++d) tma_store_4d(&tmap_c.dst[d], buf, n0 + c, x, y, conv_img);
+                }
+              }
+            } else if (has_work && ncol(c) < N) {
               if (p.split_k > 1) {
                 // partial sums of the K splits meet in global memory (fp32 result, one destination)
                 tma_reduce_add_3d(&tmap_c.dst[0], buf, ncol(c), m0, tc.b);

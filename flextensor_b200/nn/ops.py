@@ -7,6 +7,7 @@ reference's ``flextensor/nn/ops.py``:
   zero_pad2d             ops.py:83-117
   conv2d_nchw            ops.py:419-479   (pad -> conv [-> bias]: a 2- or 3-op graph)
   depthwise_conv2d_nchw  ops.py:622-678   (weight layout [C, factor, kh, kw])
+  conv2d_nhwc            ops.py:482-560   (conv2d_nchwc with one channel block: channels-last tensors)
   conv1d                 ops.py:293-351   (the same kernels, on a one-row image)
   zero_pad3d             ops.py:157-189
   conv3d_ncdhw           ops.py:689-751   (the per-tap conv kernel with a depth-tap loop)
@@ -84,6 +85,36 @@ def conv2d_nchw(inputs, weight, bias=None, stride=1, padding=0, dilation=1, grou
     out = op.output(0)
     if bias is not None:
         out = _bias_add(out, bias)
+    return out
+
+
+def conv2d_nhwc(inputs, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    """inputs [N,H,W,C], weight [K, C/groups, kh, kw] -> [N, out_h, out_w, K]: the conv2d of ``conv2d_nchw`` on
+    channels-last tensors.  The reference rewrites conv2d tasks to the blocked NCHWc layout for its CPU target
+    (flextensor/nn/ops.py:482-560 conv2d_nchwc: [N, C/v, H, W, v]); with one block holding all channels that is
+    this layout, which is the one the tensor-core kernels read without a layout pass."""
+    n, in_h, in_w, c = (int(s) for s in inputs.shape)
+    k, cg, k_h, k_w = (int(s) for s in weight.shape)
+    assert_print(cg * groups == c)
+    kg = k // groups
+    assert_print(kg * groups == k)
+    stride, padding, dilation = _pair(stride, "stride"), _pair(padding, "padding"), _pair(dilation, "dilation")
+    out_h = (in_h + 2 * padding[0] - dilation[0] * (k_h - 1) - 1) // stride[0] + 1
+    out_w = (in_w + 2 * padding[1] - dilation[1] * (k_w - 1) - 1) // stride[1] + 1
+    rc = reduce_axis((0, cg), name="rc")
+    rh = reduce_axis((0, k_h), name="rh")
+    rw = reduce_axis((0, k_w), name="rw")
+    pad_op = ComputeOp("pad2d", "Padding", (n, in_h + 2 * padding[0], in_w + 2 * padding[1], c), inputs.dtype, [inputs],
+                       ("b", "h", "w", "c"), attrs={"padding": (padding[0], padding[0], padding[1], padding[1]),
+                                                    "layout": "nhwc"})
+    op = ComputeOp("conv2d", "compute", (n, out_h, out_w, k), _acc_dtype(inputs.dtype), [pad_op.output(0), weight],
+                   ("b", "h", "w", "c"), reduce_axes=[rc, rw, rh],
+                   attrs={"stride": stride, "padding": padding, "dilation": dilation, "groups": groups, "form": "nhwc"})
+    out = op.output(0)
+    if bias is not None:
+        bop = ComputeOp("bias_add", "bias_add", (n, out_h, out_w, k), out.dtype, [out, bias], ("b", "h", "w", "c"),
+                        attrs={"axis": 3})
+        out = bop.output(0)
     return out
 
 

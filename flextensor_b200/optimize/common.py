@@ -35,6 +35,8 @@ def host_result(ops, bufs, arrays):
         if op.kind == "pad2d":
             p = op.attrs["padding"]  # (first axis before, after, ..., last axis before, after)
             last_first = [v for i in range(len(p) - 2, -2, -2) for v in (p[i], p[i + 1])]
+            if op.attrs.get("layout") == "nhwc":
+                last_first = [0, 0] + last_first   # (h, w) padding of [N, H, W, C]
             values[id(op.output(0))] = F.pad(val(ins[0]).double(), last_first)
         elif op.kind == "conv2d":
             x, w = val(ins[0]).double(), val(ins[1]).double()
@@ -43,6 +45,9 @@ def host_result(ops, bufs, arrays):
                 res = F.conv1d(x, w, None, op.attrs["stride"][1], 0, op.attrs["dilation"][1], op.attrs["groups"])
             elif form == "packed_1x1":
                 res = torch.einsum("bci,kc->bki", x, w)
+            elif form == "nhwc":
+                res = F.conv2d(x.permute(0, 3, 1, 2), w, None, op.attrs["stride"], 0, op.attrs["dilation"],
+                               op.attrs["groups"]).permute(0, 2, 3, 1).contiguous()
             elif form == "conv3d":
                 res = F.conv3d(x, w, None, op.attrs["stride"], 0, op.attrs["dilation"], op.attrs["groups"])
             else:
@@ -55,7 +60,8 @@ def host_result(ops, bufs, arrays):
                                                 op.attrs["dilation"], c)
         elif op.kind == "bias_add":
             x = val(ins[0])
-            values[id(op.output(0))] = x + val(ins[1]).double().reshape([1, -1] + [1] * (x.dim() - 2))
+            axis = op.attrs.get("axis", 1)
+            values[id(op.output(0))] = x + val(ins[1]).double().reshape([1] * axis + [-1] + [1] * (x.dim() - axis - 1))
         elif op.kind == "relu":
             values[id(op.output(0))] = val(ins[0]).clamp(min=0)
         elif op.kind in ("gemm", "batch_gemm", "gemm_int8"):

@@ -217,6 +217,19 @@ class Module(object):
                 ws = self._workspace(idx, backend.conv3d_workspace_bytes(n, c, d, h, w, k, t, r, s, groups), device)
                 backend.conv3d_ncdhw_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
                                          op.attrs["dilation"], groups, cfg=cfg, workspace=ws, status=status)
+            elif op.kind == "conv2d" and op.attrs.get("form") == "nhwc":
+                n, h, w, c = ins[0].shape
+                k, _, r, s = ins[1].shape
+                groups = op.attrs["groups"]
+                ws = self._workspace(idx, backend.conv2d_nhwc_workspace_bytes(c, k, r, s, groups), device)
+                seen = self._packed.get(idx)   # the filter is packed by the first call (see below)
+                prepacked = (self.pack_once and seen is not None and seen[0] is ins[1] and
+                             seen[1] == ins[1]._version and seen[2] is ws)
+                if self.pack_once and not prepacked:
+                    self._packed[idx] = (ins[1], ins[1]._version, ws)
+                backend.conv2d_nhwc_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
+                                        op.attrs["dilation"], groups, cfg=cfg, workspace=ws, status=status,
+                                        prepacked=prepacked)
             elif op.kind == "conv2d":
                 form = op.attrs.get("form")
                 if form == "conv1d":        # [N,C,L] is a one-row image, the filter a one-row filter

@@ -418,8 +418,14 @@ def schedule(task_key, slevel=4, rlevel=3, op_trial=50, graph_trial=10, op_stop=
     # performance model, stored under the default file names, instead of measuring
     use_model_everywhere = bool(kwargs.get("use_model", False))
     force_inline = bool(kwargs.get("force_inline", False))
-    if "rewrite" in kwargs:
-        raise RuntimeError("the NCHWc CPU rewrite of the reference has no counterpart on this backend")
+    if kwargs.get("rewrite"):
+        # search the channels-last form of the task: its twin is registered and searched in its place
+        # (the reference evaluates the rewritten layout during the search too, scheduler.py:1055,1085)
+        twin = Rewriter.rewritten_task(task)
+        passed = {k: v for k, v in kwargs.items() if k != "rewrite"}
+        return schedule(twin.key, slevel=slevel, rlevel=rlevel, op_trial=op_trial, graph_trial=graph_trial,
+                        op_stop=op_stop, graph_stop=graph_stop, number=number, timeout=timeout, parallel=parallel,
+                        method=method, **passed)
 
     graph_space = generate_space_inter_op(op_lst, down_graph, force_inline=force_inline,
                                           special_space=task.special_space)
@@ -464,12 +470,52 @@ def schedule(task_key, slevel=4, rlevel=3, op_trial=50, graph_trial=10, op_stop=
     return s, bufs, configs
 
 
+class Rewriter(object):
+    """Layout rewrite of a conv2d task, the counterpart of the reference's ``Rewriter``
+    (scheduler.py:825-862).  There it turns an NCHW conv2d into the blocked NCHWc form its CPU
+    kernels vectorise over; here it turns it into the channels-last form the tensor-core kernels
+    read in place (``task.conv2d_nhwc_layout``: NCHWc with one block holding all channels), which
+    removes the layout pass from every call.  ``bufs`` change shape, as in the reference:
+    [N,H,W,C] input, [K,C/groups,R,S] filter, [N,P,Q,K] result.  The knobs carry over; an
+    ``algo`` choice that only exists for NCHW tensors (3: batched GEMM on the tensors as they
+    are, 4: im2col form) is left to the library."""
+
+    def __init__(self, configs):
+        if not isinstance(configs, Config):
+            configs = Config(configs[0], configs[1])
+        self.graph_config = configs.graph_config
+        self.op_config_lst = configs.op_config_lst
+
+    @staticmethod
+    def rewritten_task(task):
+        from .task import Task, register_task, conv2d, conv2d_nhwc_layout
+        assert_print(task.target == "cuda", "the channels-last rewrite is for the sm_100a kernels")
+        assert_print(task.category == "conv2d" and task.func is conv2d, "only conv2d tasks are rewritten")
+        twin = Task(task.category, task.name + "-nhwc", conv2d_nhwc_layout, task.args, task.target, task.dev_id)
+        register_task(twin)
+        return twin
+
+    def rewrite(self, task):
+        import copy
+        twin = self.rewritten_task(task)
+        new_graph_config = copy.deepcopy(self.graph_config)
+        new_op_config_lst = copy.deepcopy(self.op_config_lst)
+        for cfg in new_op_config_lst:
+            if cfg and cfg.get("inline") and cfg["inline"][0] and cfg["inline"][0][0] in (3, 4):
+                cfg["inline"] = []
+        ops, bufs = twin.func(*twin.args)
+        return ops, bufs, new_graph_config, new_op_config_lst
+
+
 def schedule_with_config(task_key, configs, op_pos=None, rewrite=False, precision=None):
-    """Plan a registered task with the given configs; returns ``(plan, bufs)``."""
-    if rewrite:
-        raise RuntimeError("the NCHWc CPU rewrite of the reference has no counterpart on this backend")
+    """Plan a registered task with the given configs; returns ``(plan, bufs)``.  ``rewrite``: plan
+    the channels-last form of a conv2d task instead (see ``Rewriter``)."""
     task = TASK_TABLE[task_key]
-    ops, bufs = task.func(*task.args)
+    if rewrite:
+        ops, bufs, graph_config, op_config_lst = Rewriter(configs).rewrite(task)
+        configs = Config(op_config_lst, graph_config)
+    else:
+        ops, bufs = task.func(*task.args)
     return schedule_with_config_ops(ops, bufs, configs, op_pos=op_pos, target=task.target, precision=precision,
                                     dev_id=task.dev_id)
 

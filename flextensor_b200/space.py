@@ -387,6 +387,8 @@ def generate_space_intra_op_b200(op, down_graph=None):
         algos = [1] + ([2] if slab_ok else []) + ([3] if gemm_ok else []) + ([4] if im2col_ok else [])
         if form == "conv3d":
             algos = [1]  # the per-tap lowering with its depth-tap loop
+        elif form == "nhwc":
+            algos = [1] + ([2] if slab_ok else [])  # read in place: no NCHW batched GEMM, no im2col form
         space.add_subspace("algo", KnobSpace("algo", algos), "inline")
     else:  # depthwise
         out_h = extents["h"]

@@ -20,7 +20,8 @@ from .configs.conv3d_config import conv3d_shapes
 from .configs.gemm_config import gemm_shapes, test_gemm_shapes, b200_batch_gemm_shapes, b200_gemm_int8_shapes
 from .ir import placeholder
 from .nn import conv2d_nchw, depthwise_conv2d_nchw, gemm as op_gemm, batch_gemm as op_batch_gemm, \
-    gemm_int8 as op_gemm_int8, conv1d as op_conv1d, gemm_conv2d_nchw, conv2d_1x1_packed as op_1x1_packed, conv3d_ncdhw
+    gemm_int8 as op_gemm_int8, conv1d as op_conv1d, gemm_conv2d_nchw, conv2d_1x1_packed as op_1x1_packed, conv3d_ncdhw, \
+    conv2d_nhwc
 from .space import EnumSpace
 
 TASK_TABLE = {}
@@ -30,6 +31,7 @@ NUM_DEVICES = 8
 class Task(object):
     def __init__(self, category, name, func, args, target, dev_id=0):
         self.key = "{}_{}_{}_{}({})".format(category, name, args, target, dev_id)
+        self.name = name
         self.func = func
         self.args = args
         self.target = target
@@ -58,6 +60,15 @@ def conv2d(N, C, H, W, K, kernel_size, stride=1, padding=0, dilation=1, groups=1
     Img = placeholder((N, C, H, W))
     Wt = placeholder((K, C // groups, kernel_size, kernel_size))
     Output = conv2d_nchw(Img, Wt, stride=stride, padding=padding, dilation=dilation, groups=groups)
+    return [Output.op], [Img, Wt, Output]
+
+
+def conv2d_nhwc_layout(N, C, H, W, K, kernel_size, stride=1, padding=0, dilation=1, groups=1):
+    """The conv2d task on channels-last tensors, same arguments as ``conv2d`` (what the reference's
+    conv2d_nchwc_layout, task.py:81-93, is to its CPU target: the layout its kernels want)."""
+    Img = placeholder((N, H, W, C))
+    Wt = placeholder((K, C // groups, kernel_size, kernel_size))
+    Output = conv2d_nhwc(Img, Wt, stride=stride, padding=padding, dilation=dilation, groups=groups)
     return [Output.op], [Img, Wt, Output]
 
 

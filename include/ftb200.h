@@ -180,6 +180,21 @@ int ftb_conv2d_nchw_f32_multi(const float* in, const float* weight, const float*
                               int groups, int prepacked, const ftb_config* cfg, void* workspace,
                               size_t workspace_bytes, int* status, void* stream);
 
+/* The same convolution on channels-last tensors: in[N,H,W,C], out[N,P,Q,K] (+ bias[K]); the filter keeps the
+ * reference's [K,C/groups,R,S] layout.  This is the B200 form of the layout rewrite the reference applies to
+ * conv2d tasks (flextensor/scheduler.py:825-862 Rewriter, NCHW -> NCHWc for the CPU): the tensor-core kernels
+ * want the channels innermost, so a caller that keeps its activations channels-last skips the layout pass of
+ * ftb_conv2d_nchw_f32 altogether - the tensor maps sit on `in` and `out` themselves.  Needs channels per group
+ * (in and out) that are multiples of 4 and 16-byte aligned tensors, else FTB_E_UNSUPPORTED.  `workspace`
+ * (256-byte aligned, ftb_conv2d_nhwc_workspace_bytes) holds the packed filter only; `prepacked` != 0: it
+ * already holds this filter's packing from an earlier call with the same shape arguments and knobs.  Knobs
+ * as for conv2d; `algo` 3 and 4 do not apply. */
+size_t ftb_conv2d_nhwc_workspace_bytes(int64_t c, int64_t k, int64_t r, int64_t s, int64_t groups);
+int ftb_conv2d_nhwc_f32(const float* in, const float* weight, const float* bias, float* out, int64_t n, int64_t c,
+                        int64_t h, int64_t w, int64_t k, int64_t r, int64_t s, int stride_h, int stride_w, int pad_h,
+                        int pad_w, int dil_h, int dil_w, int groups, int prepacked, const ftb_config* cfg,
+                        void* workspace, size_t workspace_bytes, int* status, void* stream);
+
 /* out[N,K,OD,P,Q] = conv3d(in[N,C,D,H,W], w[K,C/groups,T,R,S]) (+ bias[K]), cross-correlation with
  * zero padding folded into the loads (flextensor/nn/ops.py:157-189 zero_pad3d + :689-751
  * conv3d_ncdhw).  stride_dhw / pad_dhw / dil_dhw point at three host ints each (depth, height,

@@ -362,8 +362,30 @@ def test_bias_is_folded_and_unsupported_targets_refused():
     llvm_plan, _ = schedule_with_config("gemm_gemm_(32, 32, 32)_llvm(0)", Config([{}], None))
     with pytest.raises(RuntimeError):
         llvm_plan.build()
-    with pytest.raises(RuntimeError):
+    with pytest.raises(AssertionError):        # only conv2d tasks have a layout rewrite
         schedule_with_config(GEMM_KEY, Config([{}], None), rewrite=True)
+
+
+def test_layout_rewrite_of_a_conv2d_task():
+    """schedule_with_config(..., rewrite=True) plans the channels-last twin of a conv2d task (the reference's
+    Rewriter, scheduler.py:825-862, produces NCHWc buffers for its CPU target)."""
+    key = "conv2d_res_b13_(1, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)"
+    cfg = Config([{}, {"spatial": [[64], [2], [1]], "inline": [[3]]}], None)
+    plan, bufs = schedule_with_config(key, cfg, rewrite=True)
+    assert [to_tuple(b.shape) for b in bufs] == [(1, 56, 56, 64), (64, 64, 3, 3), (1, 56, 56, 64)]
+    assert [s.op.kind for s in plan.steps] == ["conv2d"] and plan.steps[0].op.attrs["form"] == "nhwc"
+    assert plan.steps[0].knobs == {"tile_n": 64, "tile_h": 2, "cluster": 1, "fp32_mode": 0}   # algo 3 is NCHW-only
+    assert cfg.op_config_lst[1]["inline"] == [[3]]                                           # the caller's config is untouched
+    assert "conv2d_res_b13-nhwc_(1, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)" in TASK_TABLE
+    ops_, _ = S.Rewriter(cfg).rewrite(TASK_TABLE[key])[:2]
+    op_lst, down = flatten_graph(ops_)
+    space = SP.generate_space_intra_op(op_lst[1], down, target="cuda")
+    assert [e[0] for e in space.subspaces["algo"].static_entities] == [1, 2]
+    out = ops.conv2d_nhwc(placeholder((4, 7, 7, 8)), placeholder((12, 4, 3, 3)), placeholder((12,)), stride=2, padding=1,
+                          dilation=2, groups=2)
+    assert to_tuple(out.shape) == (4, 3, 3, 12) and out.op.attrs["axis"] == 3
+    with pytest.raises(AssertionError):
+        schedule_with_config("conv2d_depthwise_(1, 256, 56, 56, 1, 3, 1, 1, 1)_cuda(0)", Config([], None), rewrite=True)
 
 
 # ---------------------------------------------------------------- measurement plumbing (host-side failures)
