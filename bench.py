@@ -357,18 +357,44 @@ def per_op_lines(peak_bf16, hbm_gbs):
     out["depthwise_c256_56_batch64"] = {"us": t * 1e6, "gbs": 64 * 6422528 / t / 1e9,
                                         "frac": 64 * 6422528 / t / 1e9 / hbm_gbs, "peak_source": hbm_src,
                                         "note": "411 MB of input+output per launch, larger than L2"}
+    from flextensor_b200.task import TASK_TABLE
     x64 = torch.randn(64, 64, 56, 56, device="cuda")
     w64 = torch.randn(64, 64, 3, 3, device="cuda")
     arrays = [x64, w64, torch.empty(64, 64, 56, 56, device="cuda")]
     t = timed("conv2d_res3_(64, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)", arrays, 2)
     out["conv2d_c64_56_k64_batch64_tf32"] = {"us": t * 1e6, "tflops": 64 * 231211008 / t / 1e12,
                                              "frac": 64 * 231211008 / t / 1e12 / tf32_peak, "peak_source": tf32_src}
-    del arrays, x64, w64
+    # the same layer after the layout rewrite (channels-last tensors read in place: no layout pass)
+    s_cl, bufs_cl = schedule_with_config("conv2d_res3_(64, 64, 56, 56, 64, 3, 1, 1, 1, 1)_cuda(0)", Config([], None),
+                                         rewrite=True)
+    func_cl = build(s_cl, bufs_cl)
+    arrays = [x64.permute(0, 2, 3, 1).contiguous(), w64, torch.empty(64, 56, 56, 64, device="cuda")]
+    t = func_cl.time_evaluator(func_cl.entry_name, None, number=20, repeat=5)(*arrays).median
+    out["conv2d_c64_56_k64_batch64_tf32_channels_last"] = {
+        "us": t * 1e6, "tflops": 64 * 231211008 / t / 1e12, "frac": 64 * 231211008 / t / 1e12 / tf32_peak,
+        "peak_source": tf32_src, "note": "schedule_with_config(..., rewrite=True): [N,H,W,C] in, [N,P,Q,K] out"}
+    del arrays, x64, w64, func_cl
+    # The reference's conv3d table (flextensor/configs/conv3d_config.py: 3-D ResNet-18 after the stem, batch 1),
+    # library-default knobs, single-pass TF32
+    layers3 = []
+    flop3 = 0.0
+    for key in [k for k in TASK_TABLE if k.startswith("conv3d_conv3d_") and k.endswith("_cuda(0)")]:
+        n_, c_, d_, h_, w_, k_, ks_, st_, pad_ = TASK_TABLE[key].args[:9]
+        od, oh = (d_ + 2 * pad_ - ks_) // st_ + 1, (h_ + 2 * pad_ - ks_) // st_ + 1
+        arrays = [torch.randn(n_, c_, d_, h_, w_, device="cuda"), torch.randn(k_, c_, ks_, ks_, ks_, device="cuda"),
+                  torch.empty(n_, k_, od, oh, oh, device="cuda")]
+        t = timed(key, arrays, 2)
+        flop = 2.0 * n_ * k_ * od * oh * oh * c_ * ks_ ** 3
+        flop3 += flop
+        layers3.append({"args": list(TASK_TABLE[key].args), "us": t * 1e6, "tflops": flop / t / 1e12})
+        del arrays
+    sum3 = sum(l["us"] for l in layers3)
+    out["conv3d_resnet18_b1_tf32"] = {"layers": layers3, "sum_us": sum3, "frac": flop3 / (sum3 * 1e-6) / 1e12 / tf32_peak,
+                                      "peak_source": tf32_src, "note": "batch 1: latency-sized"}
     # The reference's own conv2d benchmark: the 15 YOLO-v1 layers at batch 1
     # (flextensor/configs/conv2d_config.py:18-45), library-default knobs, single-pass TF32.  Beside
     # them the kernel times the reference published for its tuned fp32 CUDA kernels
     # (testing/others/profile/compute_flops.py:17-33; GPU not named there, sibling files are V100).
-    from flextensor_b200.task import TASK_TABLE
     published_ms = [0.1007, 0.2825, 0.0252, 0.2062, 0.0571, 0.7426, 0.0373, 0.2107, 0.0541, 0.7973, 0.0653,
                     0.2498, 0.5610, 0.3801, 0.2718]
     layers = []

@@ -151,7 +151,7 @@ def lib():
         handle.ftb_conv3d_workspace_bytes.restype = ctypes.c_size_t
         handle.ftb_conv3d_workspace_bytes.argtypes = [i64] * 10
         handle.ftb_conv3d_ncdhw_f32.restype = i32
-        handle.ftb_conv3d_ncdhw_f32.argtypes = ([vp] * 4 + [i64] * 9 + [ctypes.POINTER(i32)] * 3 + [i32] +
+        handle.ftb_conv3d_ncdhw_f32.argtypes = ([vp] * 4 + [i64] * 9 + [ctypes.POINTER(i32)] * 3 + [i32, i32] +
                                                 [cfgp, vp, ctypes.c_size_t, vp, vp])
         handle.ftb_conv2d_nchw_f32_noalloc.restype = i32
         handle.ftb_conv2d_nchw_f32_noalloc.argtypes = [vp] * 4 + [i64] * 7 + [i32] * 7 + [cfgp, vp, vp]
@@ -470,10 +470,11 @@ def conv3d_workspace_bytes(n, c, d, h, w, k, t, r, s, groups=1):
 
 
 def conv3d_ncdhw_f32(x, weight, out, bias=None, stride=1, padding=0, dilation=1, groups=1, cfg=None,
-                     workspace=None, status=None, stream=None):
+                     workspace=None, status=None, stream=None, prepacked=False):
     """out[N,K,OD,P,Q] = conv3d(x[N,C,D,H,W], weight[K,C/groups,T,R,S]) (+ bias); stride, padding and
     dilation are ints or (depth, height, width) triples.  The caller owns ``workspace`` (a uint8 CUDA
-    tensor of at least conv3d_workspace_bytes bytes)."""
+    tensor of at least conv3d_workspace_bytes bytes); ``prepacked``: it holds this weight's packing from an
+    earlier call with the same shapes and knobs."""
     for t_, nm in ((x, "x"), (weight, "weight"), (out, "out")):
         _check(t_, torch.float32, nm)
     if bias is not None:
@@ -490,7 +491,7 @@ def conv3d_ncdhw_f32(x, weight, out, bias=None, stride=1, padding=0, dilation=1,
         rc = lib().ftb_conv3d_ncdhw_f32(
             x.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(),
             n, c, d, h, w, k, t, r, s, triple(*_triple(stride, "stride")), triple(*_triple(padding, "padding")),
-            triple(*_triple(dilation, "dilation")), groups, _cfg_ptr(cfg), workspace.data_ptr(),
+            triple(*_triple(dilation, "dilation")), groups, int(prepacked), _cfg_ptr(cfg), workspace.data_ptr(),
             workspace.numel() * workspace.element_size(), _status_ptr(status), _stream_ptr(stream))
     if rc:
         raise FtbError(rc, "ftb_conv3d_ncdhw_f32")

@@ -34,6 +34,7 @@
 namespace ftb {
 
 constexpr int kSlabMaxStages = 4;
+constexpr int kSlabMaxBStages = 8;
 
 struct ConvSlabParams {
   int N;        // output channels of this launch
@@ -52,6 +53,11 @@ struct ConvSlabParams {
                 // 1024-byte period of the swizzle); timing either against the real kernel shows what the
                 // taps' odd start addresses cost
   int num_dst;  // destinations of the staged epilogue (1..kMaxDst): the same box goes to each of them
+  // Streamed filter (b_stages > 0): a filter too large to stay resident is not split over CTAs (whose
+  // partial sums would meet in global memory) but passed through a ring of b_stages stages, each
+  // holding the b_group consecutive taps' tiles of one channel chunk; a CTA then re-reads the filter
+  // from L2 for every tile, which is far less than re-reading the input once per tap.
+  int b_stages, b_group;
   int cl_out;   // the result is channels-last [N][P][Q][K]: staged as [pixel][32 channels], stored through a
                 // (k, q, p, n) map
   uint32_t epi_buf_bytes;
@@ -64,7 +70,7 @@ struct ConvSlabParams {
   int* status;
 };
 
-template <bool PAIR>
+template <bool PAIR, bool STREAM>
 __global__ void __launch_bounds__(192, 1)
 conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ StoreMaps tmap_out,
@@ -73,6 +79,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
   __shared__ __align__(8) uint64_t bar_afull[kSlabMaxStages];
   __shared__ __align__(8) uint64_t bar_aempty[kSlabMaxStages];
   __shared__ __align__(8) uint64_t bar_bfull;
+  __shared__ __align__(8) uint64_t bar_bsfull[kSlabMaxBStages];
+  __shared__ __align__(8) uint64_t bar_bsempty[kSlabMaxBStages];
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_base_slot;
@@ -95,9 +103,12 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
   const int tap0 = ks * p.taps_per_split;
   const int tap1 = min(taps, tap0 + p.taps_per_split);
   const int ntaps = tap1 - tap0;
-  // filter first, slabs after it
+  // filter (or the ring its tiles stream through) first, slabs after it
+  constexpr bool streamed = STREAM;  // p.b_stages > 0
+  const uint32_t b_stage_bytes = static_cast<uint32_t>(p.b_group) * p.b_tile_bytes;
   const uint32_t b_base = smem_base;
-  const uint32_t a_base = smem_base + static_cast<uint32_t>(p.taps_per_split * p.cchunks) * p.b_tile_bytes;
+  const uint32_t a_base = smem_base + (streamed ? static_cast<uint32_t>(p.b_stages) * b_stage_bytes
+                                                : static_cast<uint32_t>(p.taps_per_split * p.cchunks) * p.b_tile_bytes);
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -106,6 +117,10 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       mbar_init(smem_u32(&bar_aempty[s]), 1);
     }
     mbar_init(smem_u32(&bar_bfull), 1);
+    for (int s = 0; s < p.b_stages; ++s) {
+      mbar_init(smem_u32(&bar_bsfull[s]), 1);
+      mbar_init(smem_u32(&bar_bsempty[s]), 1);
+    }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bar_tfull[a]), 1);
       mbar_init(smem_u32(&bar_tempty[a]), PAIR ? 8 : 4);  // the leader's copy counts both CTAs' epilogue warps
@@ -136,6 +151,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
   const uint32_t afull0 = smem_u32(&bar_afull[0]);
   const uint32_t aempty0 = smem_u32(&bar_aempty[0]);
   const uint32_t bfull = smem_u32(&bar_bfull);
+  const uint32_t bsfull0 = smem_u32(&bar_bsfull[0]);
+  const uint32_t bsempty0 = smem_u32(&bar_bsempty[0]);
   const int tiles_per_img = p.tiles_h * p.tiles_w;
 
   if (warp == 0) {
@@ -146,8 +163,11 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       const uint32_t bfull_sig = PAIR ? map_to_cta(bfull, 0) : bfull;
       const uint32_t afull_sig0 = PAIR ? map_to_cta(afull0, 0) : afull0;
       const uint32_t b_bytes_all = static_cast<uint32_t>(ntaps * p.cchunks) * p.b_tile_bytes;
-      if (cta_rank == 0) mbar_expect_tx(bfull, PAIR ? 2u * b_bytes_all : b_bytes_all);
-      {
+      const uint32_t bsfull_sig0 = PAIR ? map_to_cta(bsfull0, 0) : bsfull0;
+      const int n0_half = static_cast<int>(cta_rank) * (p.bn / 2);
+      uint32_t bs = 0, bph = 0;
+      if (!streamed) {
+        if (cta_rank == 0) mbar_expect_tx(bfull, PAIR ? 2u * b_bytes_all : b_bytes_all);
         uint32_t dst = b_base;
         int kc = tap0 * p.cchunks * 32;  // the packed filter is [k_out][tap][chunk][32]
         const int n0 = static_cast<int>(cta_rank) * (p.bn / 2);
@@ -168,7 +188,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         const int rem = t - img * tiles_per_img;
         const int th = rem / p.tiles_w, tw = rem - th * p.tiles_w;
         const int h0 = th * p.tile_h - p.pad_h, w0 = tw * p.tile_w - p.pad_w;
-        for (int cc = 0; cc < p.cchunks; ++cc) {
+        for (int cc = 0; cc < p.cchunks && ok; ++cc) {
           FTB_PROF_T0(prof_w0);
           if (!mbar_wait(aempty0 + 8 * s, ph ^ 1u, &abort_flag)) {
             atomicOr(p.status, FTB_DEV_WAIT_EMPTY);
@@ -189,6 +209,34 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             s = 0;
             ph ^= 1u;
             sa = a_base;
+          }
+          if (streamed) {
+            // this chunk's filter tiles, b_group taps per stage, in the order the issuer takes them
+            for (int g0 = 0; g0 < ntaps && ok; g0 += p.b_group) {
+              const int nt = min(p.b_group, ntaps - g0);
+              if (!mbar_wait(bsempty0 + 8 * bs, bph ^ 1u, &abort_flag)) {
+                atomicOr(p.status, FTB_DEV_WAIT_EMPTY);
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+              const uint32_t bytes = static_cast<uint32_t>(nt) * p.b_tile_bytes;
+              uint32_t dst = b_base + bs * b_stage_bytes;
+              int kc = ((tap0 + g0) * p.cchunks + cc) * 32;  // the packed filter is [k_out][tap][chunk][32]
+              if constexpr (PAIR) {
+                if (cta_rank == 0) mbar_expect_tx(bsfull0 + 8 * bs, 2u * bytes);
+                for (int j = 0; j < nt; ++j, dst += p.b_tile_bytes, kc += p.cchunks * 32)
+                  tma_load_3d_pair(dst, &tmap_w, bsfull_sig0 + 8 * bs, kc, n0_half, 0);
+              } else {
+                mbar_expect_tx(bsfull0 + 8 * bs, bytes);
+                for (int j = 0; j < nt; ++j, dst += p.b_tile_bytes, kc += p.cchunks * 32)
+                  tma_load_3d(dst, &tmap_w, bsfull0 + 8 * bs, kc, 0, 0);
+              }
+              if (++bs == static_cast<uint32_t>(p.b_stages)) {
+                bs = 0;
+                bph ^= 1u;
+              }
+            }
           }
         }
       }
@@ -212,8 +260,10 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       // first tap of this CTA as (row, column) of the filter
       const int tr0 = tap0 / p.S, ts0 = tap0 - tr0 * p.S;
       uint32_t s = 0, ph = 0, a_lo = a_lo0;
+      uint32_t bs = 0, bph = 0;
+      const uint32_t b_stage_enc = b_stage_bytes >> 4;
       int local = 0;
-      bool ok = mbar_wait(bfull, 0, &abort_flag);
+      bool ok = streamed || mbar_wait(bfull, 0, &abort_flag);
       if (!ok) {
         atomicOr(p.status, FTB_DEV_WAIT_FULL);
         abort_flag = 1;
@@ -244,6 +294,41 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
           FTB_PROF_ADD(prof_full, prof_f0);
           tc_fence_after();
           int tr = tr0, ts = ts0;
+          if constexpr (STREAM) {
+            for (int g0 = 0; g0 < ntaps && ok; g0 += p.b_group) {
+              // the next stage of the filter ring: b_group taps' tiles of this channel chunk
+              if (!mbar_wait(bsfull0 + 8 * bs, bph, &abort_flag)) {
+                atomicOr(p.status, FTB_DEV_WAIT_FULL);
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              uint32_t b_lo = b_lo0 + bs * b_stage_enc;
+              const int nt = min(p.b_group, ntaps - g0);
+              for (int j = 0; j < nt; ++j) {
+                const uint32_t ta_lo = a_lo + static_cast<uint32_t>(tr * p.dil_h * p.slab_w + ts * p.dil_w) * 8u;
+#pragma unroll
+                for (int k = 0; k < kMmaPerKb; ++k) {
+                  umma<KIND_TF32, PAIR>(d_tmem, ta_lo + 2u * k, hi, b_lo + 2u * k, hi, idesc, accumulate);
+                  accumulate = 1;
+                }
+                b_lo += b_tile_enc;
+                if (++ts == p.S) {
+                  ts = 0;
+                  ++tr;
+                }
+              }
+              // hand the ring stage back once these MMAs have read it
+              if constexpr (PAIR) tc_commit_pair_both(bsempty0 + 8 * bs);
+              else tc_commit(bsempty0 + 8 * bs);
+              if (++bs == static_cast<uint32_t>(p.b_stages)) {
+                bs = 0;
+                bph ^= 1u;
+              }
+            }
+            if (!ok) break;
+          } else {
           uint32_t b_lo = b_lo0 + static_cast<uint32_t>(cc) * b_tile_enc;
           for (int tap = 0; tap < ntaps; ++tap) {
             // The slab is read from `off` pixel rows in.  The tensor core applies the 128-byte
@@ -267,6 +352,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
               ts = 0;
               ++tr;
             }
+          }
           }
           if constexpr (PAIR) tc_commit_pair_both(aempty0 + 8 * s);
           else tc_commit(aempty0 + 8 * s);

@@ -848,6 +848,58 @@ static int conv_prepass(const float* in, const float* weight, float* in_nhwc, fl
   return FTB_OK;
 }
 
+// Conv tiles of at most 128 output channels hand pipeline stages back two at a time unless told
+// otherwise: their K block is so short (four MMAs of about a hundred cycles) that the ~80 cycles of a
+// tcgen05.commit show (3-6 % on batched 64- and 128-channel layers; nothing at 256).  A stage count
+// the library chose itself is made even for it.
+static int conv_release_pairs(const ftb_config* user, bool split3, ftb_config* cfg) {
+  const int release = user ? user->release : 0;
+  if (split3 || release == 1) return 0;
+  if (release == 0) {
+    if (cfg->tile_n > 128) return 0;
+    if ((!user || user->stages == 0) && cfg->stages >= 5 && (cfg->stages & 1)) --cfg->stages;
+  }
+  return (cfg->stages % 2 == 0 && cfg->stages >= 4) ? 1 : 0;
+}
+
+// One wave of conv tiles or less, knobs left open: pick tile width and reduction split together by
+// what a CTA has to stage and issue (same cost model as pick_small_f32: a short tile list is
+// bound by per-CTA L2 traffic and MMA chain, not by latency).  An MMA costs about the same
+// whatever its width up to 128 columns, so narrow tiles only pay when they put idle SMs to work.
+static bool pick_small_conv(const ftb_config* user, long long groups, long long tiles_m, int64_t kg, int num_kb,
+                            bool split3, int num_sms, ftb_config* tuned) {
+  if (user && (user->tile_n != 0 || user->cluster != 0 || user->split_k != 0)) return false;
+  if (groups * tiles_m * ((kg + 127) / 128) > num_sms) return false;
+  double best = 1e30;
+  int best_bn = 0, best_split = 1;
+  for (int bn = 32; bn <= 256; bn *= 2) {
+    if (bn > 32 && bn >= 2 * kg) break;  // wider than the output channels: pure padding
+    const long long tiles = groups * tiles_m * ((kg + bn - 1) / bn);
+    if (tiles > num_sms) continue;
+    for (int split = 1; split <= 32 && split <= num_kb; ++split) {
+      if (num_kb % split) continue;
+      if (tiles * split > num_sms) break;
+      const int kb = num_kb / split;
+      const double mma_us = (bn >= 256 ? 0.140 : bn >= 128 ? 0.090 : bn >= 64 ? 0.061 : 0.050) * (split3 ? 3.0 : 1.0);
+      const double load = kb * (16384.0 + bn * 128.0) / 60e3;
+      const double math = kb * 4.0 * mma_us;
+      const double cost = (load > math ? load : math) + 128.0 * bn * 4.0 / 35e3 + (split > 1 ? 0.5 : 0.0);
+      if (cost < best) {
+        best = cost;
+        best_bn = bn;
+        best_split = split;
+      }
+    }
+  }
+  if (!best_bn) return false;
+  memset(tuned, 0, sizeof(*tuned));
+  if (user) *tuned = *user;
+  tuned->cluster = 1;
+  tuned->tile_n = best_bn;
+  tuned->split_k = best_split;
+  return true;
+}
+
 // Plan of the slab kernel (ftb_conv_slab_kernel.cuh) for one conv2d; `ok` is false when the
 // shape or the knobs do not fit it.
 struct SlabPlan {
@@ -892,7 +944,6 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   const uint32_t slab_stride = static_cast<uint32_t>((slab_rows * 128 + 1023) / 1024 * 1024);
   const size_t tail = static_cast<size_t>(reach_rows * 128 > slab_stride ? reach_rows * 128 - slab_stride : 0);
   const uint32_t epi_buf = staged_ok ? static_cast<uint32_t>((32ll * tile_h * tile_w * 4 + 127) / 128 * 128) : 0u;
-  const int taps = static_cast<int>(r * s);
   const int tiles_w = static_cast<int>((Q + tile_w - 1) / tile_w);
   const int tiles_h = static_cast<int>((P + tile_h - 1) / tile_h);
   const long long tiles = n * tiles_h * tiles_w;
@@ -903,11 +954,18 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   // against 60.3 us paired on 64 -> 64 channels at 56 x 56, batch 64; 99 against 60 us on 128 -> 128
   // at 28 x 28); it needs halves of the filter rows that are whole 8-row groups.
   const int want_cluster = user ? user->cluster : 0;
-  const bool pair = bn % 16 == 0 && num_sms >= 2 && want_cluster != 1 &&
-                    (want_cluster == 2 || (tiles >= 2ll * num_sms && bn > 64));
+  bool pair = bn % 16 == 0 && num_sms >= 2 && want_cluster != 1 &&
+              (want_cluster == 2 || (tiles >= 2ll * num_sms && bn > 64));
+  const int taps = static_cast<int>(r * s);
+  const size_t after_min = tail > epi_buf ? tail : epi_buf;
+  if (!pair && want_cluster == 0 && bn % 16 == 0 && bn > 64 && num_sms >= 2 && tiles >= num_sms / 2 &&
+      static_cast<size_t>(taps) * cchunks * bn * 128 + 2 * static_cast<size_t>(slab_stride) + after_min + 1024 > kSmemLimit) {
+    // A filter that will be streamed: a pair halves the ring and the filter bytes each SM pulls from
+    // L2 per tile (256 -> 256 channels at 14 x 14, batch 64: 48 us paired against 60 us single).
+    pair = true;
+  }
   sp.pair = pair;
   const uint32_t b_tile = static_cast<uint32_t>(pair ? bn / 2 : bn) * 128u;
-  const size_t after_min = tail > epi_buf ? tail : epi_buf;
   auto fits = [&](int split, int* a_stages, int* epi_bufs) {
     const int tps = (taps + split - 1) / split;
     const size_t b_bytes = static_cast<size_t>(tps) * cchunks * b_tile;
@@ -919,8 +977,39 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
     *epi_bufs = epi_buf == 0 ? 0 : (rest - st * slab_stride >= 2 * static_cast<size_t>(epi_buf) ? 2 : 1);
     return true;
   };
-  int split = 0, a_stages = 0, epi_bufs = 0;
-  if (user && user->split_k > 0) {
+  // The filter streamed through a ring instead of resident: stages of `group` taps' tiles (a filter
+  // row where that fits, else single taps), at least two of them and two slabs.
+  auto fits_streamed = [&](int* a_stages, int* epi_bufs, int* b_stages, int* b_group) {
+    const int cand[][2] = {{static_cast<int>(s), 4}, {static_cast<int>(s), 3}, {1, 8}, {1, 6}, {1, 4},
+                           {static_cast<int>(s), 2}, {1, 3}, {1, 2}};
+    for (const auto& c : cand) {
+      const int group = c[0] > taps ? taps : c[0];
+      const size_t ring = static_cast<size_t>(c[1]) * group * b_tile;
+      if (ring + 2 * static_cast<size_t>(slab_stride) + after_min + 1024 > kSmemLimit) continue;
+      const size_t rest = kSmemLimit - 1024 - ring;
+      size_t st = (rest - after_min) / slab_stride;
+      if (st > static_cast<size_t>(kSlabMaxStages)) st = kSlabMaxStages;
+      *a_stages = static_cast<int>(st);
+      *epi_bufs = epi_buf == 0 ? 0 : (rest - st * slab_stride >= 2 * static_cast<size_t>(epi_buf) ? 2 : 1);
+      *b_stages = c[1];
+      *b_group = group;
+      return true;
+    }
+    return false;
+  };
+  int split = 0, a_stages = 0, epi_bufs = 0, b_stages = 0, b_group = 0;
+  const int algo = user ? user->algo : 0;
+  const long long units_for_tiles = pair ? num_sms / 2 : num_sms;
+  const long long steps_all = pair ? (tiles + 1) / 2 : tiles;
+  if (algo == 5) {
+    // asked for: streamed filter, every tap in one CTA
+    if ((user && user->split_k > 1) || !fits_streamed(&a_stages, &epi_bufs, &b_stages, &b_group)) return sp;
+    split = 1;
+  } else if ((!user || user->split_k == 0) && !fits(1, &a_stages, &epi_bufs) && 2 * steps_all >= units_for_tiles &&
+             fits_streamed(&a_stages, &epi_bufs, &b_stages, &b_group)) {
+    // a filter that cannot stay resident, enough tiles to keep the SMs busy without splitting the taps
+    split = 1;
+  } else if (user && user->split_k > 0) {
     split = user->split_k;
     if (split > taps || !fits(split, &a_stages, &epi_bufs)) return sp;
   } else {
@@ -948,6 +1037,8 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   p.dil_h = dil_h; p.dil_w = dil_w; p.pad_h = pad_h; p.pad_w = pad_w;
   p.P = static_cast<int>(P); p.Q = static_cast<int>(Q);
   p.a_stages = a_stages;
+  p.b_stages = b_stages;
+  p.b_group = b_group > 0 ? b_group : 1;
   p.epi_bufs = epi_bufs;
   p.cl_out = cl_out ? 1 : 0;
   p.epi_buf_bytes = epi_buf;
@@ -963,7 +1054,9 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   if (walkers < 1) walkers = 1;
   sp.ctas = static_cast<int>(walkers) * split * (pair ? 2 : 1);
   const size_t after = static_cast<size_t>(epi_bufs) * epi_buf > tail ? static_cast<size_t>(epi_bufs) * epi_buf : tail;
-  sp.smem = static_cast<size_t>(tps) * cchunks * b_tile + static_cast<size_t>(a_stages) * slab_stride + after + 1024;
+  const size_t filter_bytes = b_stages > 0 ? static_cast<size_t>(b_stages) * p.b_group * b_tile
+                                           : static_cast<size_t>(tps) * cchunks * b_tile;
+  sp.smem = filter_bytes + static_cast<size_t>(a_stages) * slab_stride + after + 1024;
   sp.box_w = static_cast<uint32_t>(slab_w);
   sp.box_h = static_cast<uint32_t>(slab_h);
   sp.ok = true;
@@ -979,10 +1072,13 @@ static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const Stor
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !done[dev]) {
-      cudaError_t attr_err = cudaFuncSetAttribute(conv_slab_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  static_cast<int>(kSmemLimit));
-      if (attr_err == cudaSuccess)
-        attr_err = cudaFuncSetAttribute(conv_slab_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t attr_err = cudaSuccess;
+      const void* kernels[4] = {reinterpret_cast<const void*>(conv_slab_kernel<false, false>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<false, true>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<true, false>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<true, true>)};
+      for (int i = 0; i < 4 && attr_err == cudaSuccess; ++i)
+        attr_err = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemLimit));
       if (attr_err != cudaSuccess) {
         set_last_cuda_error(static_cast<int>(attr_err));
@@ -1009,9 +1105,11 @@ static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const Stor
     attr[1].val.clusterDim.y = 1;
     attr[1].val.clusterDim.z = 1;
     lc.numAttrs = 2;
-    cudaLaunchKernelEx(&lc, conv_slab_kernel<true>, tin, tw, tout, sp.p);
+    if (sp.p.b_stages > 0) cudaLaunchKernelEx(&lc, conv_slab_kernel<true, true>, tin, tw, tout, sp.p);
+    else cudaLaunchKernelEx(&lc, conv_slab_kernel<true, false>, tin, tw, tout, sp.p);
   } else {
-    cudaLaunchKernelEx(&lc, conv_slab_kernel<false>, tin, tw, tout, sp.p);
+    if (sp.p.b_stages > 0) cudaLaunchKernelEx(&lc, conv_slab_kernel<false, true>, tin, tw, tout, sp.p);
+    else cudaLaunchKernelEx(&lc, conv_slab_kernel<false, false>, tin, tw, tout, sp.p);
   }
   count_launch();
   cudaError_t e = cudaGetLastError();
@@ -1083,7 +1181,8 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   const int num_sms = sm_count();
 
   const int algo = user ? user->algo : 0;
-  if (algo < 0 || algo > 4) return FTB_E_BAD_CONFIG;
+  if (algo < 0 || algo > 5) return FTB_E_BAD_CONFIG;
+  const bool slab_asked = algo == 2 || algo == 5;  // 5: the slab kernel with its filter streamed
   // A 1x1 filter at stride 1 without padding is a batched GEMM on the NCHW tensors as they are:
   // out[b] (K x HW) = weight (K x C) * in[b] (C x HW), the pixels being the contiguous dimension
   // of both the B operand and the result.  No layout pass, no workspace traffic.
@@ -1141,12 +1240,12 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   SlabPlan sp;
   sp.ok = false;
   // (cluster = 2 without algo = 2 keeps meaning the per-tap lowering on CTA pairs)
-  if (algo != 1 && groups == 1 && stride_h == 1 && stride_w == 1 && !split3 && (r * s > 1 || algo == 2) &&
-      !(user && user->cluster == 2 && algo != 2))
+  if (algo != 1 && groups == 1 && stride_h == 1 && stride_w == 1 && !split3 && (r * s > 1 || slab_asked) &&
+      !(user && user->cluster == 2 && !slab_asked))
     sp = plan_slab(user, n, kg, P, Q, r, s, ws.cchunks, dil_h, dil_w, pad_h, pad_w,
                    (reinterpret_cast<uintptr_t>(out) & 15) == 0, num_sms, cl);
   if (sp.ok && num_extra > 0 && (sp.p.epi_bufs == 0 || sp.p.split > 1)) sp.ok = false;
-  if (algo == 2 && !sp.ok) return FTB_E_UNSUPPORTED;
+  if (slab_asked && !sp.ok) return FTB_E_UNSUPPORTED;
   // Left to itself the slab kernel is taken when the whole filter stays resident, or when the tile
   // list is shorter than half the SM count (where a split reduction is wanted anyway); a long tile list
   // with the taps split would add every partial sum of a large result in global memory.
@@ -1246,44 +1345,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   if (cl) staged = true;  // channels innermost: base and pitches were checked above
   if (user && user->epilogue == 1) staged = false;  // per-thread stores asked for
   if (user && (user->epilogue < 0 || user->epilogue > 1)) return FTB_E_BAD_CONFIG;
-  // One wave of tiles or less, knobs left open: pick tile width and reduction split together by
-  // what a CTA has to stage and issue (same cost model as pick_small_f32: a short tile list is
-  // bound by per-CTA L2 traffic and MMA chain, not by latency).
   ftb_config tuned;
-  bool conv_tuned = false;
-  if ((!user || (user->tile_n == 0 && user->cluster == 0 && user->split_k == 0)) &&
-      groups * tiles_m * ((kg + 127) / 128) <= num_sms) {
-    double best = 1e30;
-    int best_bn = 0, best_split = 1;
-    for (int bn = 32; bn <= 256; bn *= 2) {
-      if (bn > 32 && bn >= 2 * kg) break;  // wider than the output channels: pure padding
-      const long long tiles = groups * tiles_m * ((kg + bn - 1) / bn);
-      if (tiles > num_sms) continue;
-      for (int split = 1; split <= 32 && split <= num_kb; ++split) {
-        if (num_kb % split) continue;
-        if (tiles * split > num_sms) break;
-        const int kb = num_kb / split;
-        const double mma_us = (bn >= 256 ? 0.140 : bn >= 128 ? 0.090 : bn >= 64 ? 0.061 : 0.050) * (split3 ? 3.0 : 1.0);
-        const double load = kb * (16384.0 + bn * 128.0) / 60e3;
-        const double math = kb * 4.0 * mma_us;
-        const double cost = (load > math ? load : math) + 128.0 * bn * 4.0 / 35e3 + (split > 1 ? 0.5 : 0.0);
-        if (cost < best) {
-          best = cost;
-          best_bn = bn;
-          best_split = split;
-        }
-      }
-    }
-    if (best_bn) {
-      memset(&tuned, 0, sizeof(tuned));
-      if (user) tuned = *user;
-      tuned.cluster = 1;
-      tuned.tile_n = best_bn;
-      tuned.split_k = best_split;
-      user = &tuned;
-      conv_tuned = true;
-    }
-  }
+  const bool conv_tuned = pick_small_conv(user, groups, tiles_m, kg, num_kb, split3, num_sms, &tuned);
+  if (conv_tuned) user = &tuned;
   rc = FTB_E_BAD_CONFIG;
   if (staged)
     rc = resolve_config(user, ki, split3, 0, !split3, groups, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg,
@@ -1378,6 +1442,9 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     p.conv = 1;
     p.conv_cl = cl ? 1 : 0;
     p.slab_cols = 32;
+    if (user && (user->release < 0 || user->release > 2)) return FTB_E_BAD_CONFIG;
+    p.release_pairs = conv_release_pairs(user, split3, &cfg);
+    p.stages = cfg.stages;
     p.pdl = 1;  // directly follows the layout pass
     p.conv_ktot = static_cast<int>(k);
     p.conv_koff = 0;
@@ -1528,7 +1595,9 @@ ConvWs conv3d_ws(int64_t n, int64_t c, int64_t d, int64_t h, int64_t w, int64_t 
 int conv3d_generic(const float* in, const float* weight, const float* bias, float* out, int64_t n, int64_t c,
                    int64_t d, int64_t h, int64_t w, int64_t k, int64_t t, int64_t r, int64_t s, const int* stride,
                    const int* pad, const int* dil, int groups, const ftb_config* user, void* workspace,
-                   size_t workspace_bytes, int* status, void* stream_v) {
+                   size_t workspace_bytes, int* status, void* stream_v, bool prepacked) {
+  // prepacked: the workspace already holds this filter's packing (an earlier call with the same
+  // shape arguments and knobs): the layout pass copies the input only
   if (!in || !weight || !out || !stride || !pad || !dil) return FTB_E_BAD_ARG;
   if (n <= 0 || c <= 0 || d <= 0 || h <= 0 || w <= 0 || k <= 0 || t <= 0 || r <= 0 || s <= 0 || groups <= 0)
     return FTB_E_BAD_ARG;
@@ -1544,7 +1613,7 @@ int conv3d_generic(const float* in, const float* weight, const float* bias, floa
   // (a batched GEMM on the tensors as they are); same workspace size.
   if (t * r * s == 1 && stride[0] * stride[1] * stride[2] == 1 && pad[0] + pad[1] + pad[2] == 0)
     return conv2d_generic(in, weight, bias, out, n, c, d * h, w, k, 1, 1, 1, 1, 0, 0, 1, 1, groups, user, workspace,
-                          workspace_bytes, status, stream_v, nullptr, 0, 0);
+                          workspace_bytes, status, stream_v, nullptr, 0, prepacked ? 2 : 0);
   if (user && (user->relu < 0 || user->relu > 1)) return FTB_E_BAD_CONFIG;
   if (user && (user->fp32_mode < 0 || user->fp32_mode > 1)) return FTB_E_BAD_CONFIG;
   if (user && (user->epilogue < 0 || user->epilogue > 1)) return FTB_E_BAD_CONFIG;
@@ -1576,7 +1645,9 @@ int conv3d_generic(const float* in, const float* weight, const float* bias, floa
   bool staged = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && Q % 4 == 0 && tile_w % 4 == 0 &&
                 (P * Q * 4) % 16 == 0 && (groups == 1 || (kg * OD * P * Q * 4) % 16 == 0);
   if (user && user->epilogue == 1) staged = false;
-  ftb_config cfg;
+  ftb_config cfg, tuned;
+  const bool conv_tuned = !relu && pick_small_conv(user, 1, tiles_m, kg, num_kb, split3, num_sms, &tuned);
+  if (conv_tuned) user = &tuned;
   rc = FTB_E_BAD_CONFIG;
   if (staged)
     rc = resolve_config(user, ki, split3, 0, !split3, 1, tiles_m * kTileM, kg, num_kb, true, num_sms, &cfg,
@@ -1588,7 +1659,7 @@ int conv3d_generic(const float* in, const float* weight, const float* bias, floa
   if (rc) return rc;
   const bool pair = cfg.cluster == 2;
   const long long tiles_m_launch = pair ? (tiles_m + 1) / 2 : tiles_m;
-  if ((!user || user->split_k == 0) && !relu) {
+  if (!conv_tuned && (!user || user->split_k == 0) && !relu) {
     // a short tile list leaves SMs idle: split the reduction over CTAs (bulk reduce-adds into the
     // zeroed result)
     const long long tiles = tiles_m_launch * ((kg + cfg.tile_n - 1) / cfg.tile_n);
@@ -1602,7 +1673,7 @@ int conv3d_generic(const float* in, const float* weight, const float* bias, floa
   if (relu) cfg.split_k = 1;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   rc = conv_prepass(in, weight, in_cl, w_packed, n, c, d * h, w, k, cg, t * r, s, ws, num_sms, stream_v,
-                    cfg.split_k > 1 ? out : nullptr, n * k * OD * P * Q, 0, 0, 1, 1, groups > 1, 3);
+                    cfg.split_k > 1 ? out : nullptr, n * k * OD * P * Q, 0, 0, 1, 1, groups > 1, prepacked ? 1 : 3);
   if (rc) return rc;
 
   UmmaParams p;
@@ -1638,6 +1709,9 @@ int conv3d_generic(const float* in, const float* weight, const float* bias, floa
   p.pair_m = pair ? 2 * kTileM : kTileM;
   p.conv = 1;
   p.pdl = 1;
+  if (user && (user->release < 0 || user->release > 2)) return FTB_E_BAD_CONFIG;
+  p.release_pairs = conv_release_pairs(user, split3, &cfg);
+  p.stages = cfg.stages;
   p.conv_ktot = static_cast<int>(k);
   p.relu = relu;
   p.C = out;
@@ -1842,9 +1916,10 @@ size_t ftb_conv3d_workspace_bytes(int64_t n, int64_t c, int64_t d, int64_t h, in
 int ftb_conv3d_ncdhw_f32(const float* in, const float* weight, const float* bias, float* out, int64_t n, int64_t c,
                          int64_t d, int64_t h, int64_t w, int64_t k, int64_t t, int64_t r, int64_t s,
                          const int32_t* stride_dhw, const int32_t* pad_dhw, const int32_t* dil_dhw, int groups,
-                         const ftb_config* cfg, void* workspace, size_t workspace_bytes, int* status, void* stream) {
+                         int prepacked, const ftb_config* cfg, void* workspace, size_t workspace_bytes, int* status,
+                         void* stream) {
   return ftb::conv3d_generic(in, weight, bias, out, n, c, d, h, w, k, t, r, s, stride_dhw, pad_dhw, dil_dhw, groups,
-                             cfg, workspace, workspace_bytes, status, stream);
+                             cfg, workspace, workspace_bytes, status, stream, prepacked != 0);
 }
 
 }  // extern "C"

@@ -177,6 +177,18 @@ class Module(object):
             self._workspaces[key] = ws
         return ws
 
+    def _filter_is_packed(self, idx, weight, ws):
+        """Weights are constant per task: the filter is packed by the first call and found in the
+        workspace by the next ones, for as long as the same weight tensor comes back unmodified
+        (identity and torch's version counter; `invalidate()` after changing it behind torch's back,
+        e.g. through a raw pointer).  Returns whether step ``idx`` may skip the packing."""
+        seen = self._packed.get(idx)
+        packed = (self.pack_once and seen is not None and seen[0] is weight and seen[1] == weight._version and
+                  seen[2] is ws)
+        if self.pack_once and not packed:
+            self._packed[idx] = (weight, weight._version, ws)
+        return packed
+
     def __call__(self, *arrays):
         table = self._bind(arrays)
         device = arrays[-1].device
@@ -215,18 +227,16 @@ class Module(object):
                 k, _, t, r, s = ins[1].shape
                 groups = op.attrs["groups"]
                 ws = self._workspace(idx, backend.conv3d_workspace_bytes(n, c, d, h, w, k, t, r, s, groups), device)
+                prepacked = self._filter_is_packed(idx, ins[1], ws)
                 backend.conv3d_ncdhw_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
-                                         op.attrs["dilation"], groups, cfg=cfg, workspace=ws, status=status)
+                                         op.attrs["dilation"], groups, cfg=cfg, workspace=ws, status=status,
+                                         prepacked=prepacked)
             elif op.kind == "conv2d" and op.attrs.get("form") == "nhwc":
                 n, h, w, c = ins[0].shape
                 k, _, r, s = ins[1].shape
                 groups = op.attrs["groups"]
                 ws = self._workspace(idx, backend.conv2d_nhwc_workspace_bytes(c, k, r, s, groups), device)
-                seen = self._packed.get(idx)   # the filter is packed by the first call (see below)
-                prepacked = (self.pack_once and seen is not None and seen[0] is ins[1] and
-                             seen[1] == ins[1]._version and seen[2] is ws)
-                if self.pack_once and not prepacked:
-                    self._packed[idx] = (ins[1], ins[1]._version, ws)
+                prepacked = self._filter_is_packed(idx, ins[1], ws)
                 backend.conv2d_nhwc_f32(ins[0], ins[1], out, bias, op.attrs["stride"], op.attrs["padding"],
                                         op.attrs["dilation"], groups, cfg=cfg, workspace=ws, status=status,
                                         prepacked=prepacked)
@@ -242,15 +252,7 @@ class Module(object):
                 k, _, r, s = ins[1].shape
                 groups = op.attrs["groups"]
                 ws = self._workspace(idx, backend.conv2d_workspace_bytes(n, c, h, w, k, r, s, groups), device)
-                # Weights are constant per task: the filter is packed by the first call and found in
-                # the workspace by the next ones, for as long as the same weight tensor comes back
-                # unmodified (identity and torch's version counter; `invalidate()` after changing
-                # it behind torch's back, e.g. through a raw pointer).
-                seen = self._packed.get(idx)
-                prepacked = (self.pack_once and seen is not None and seen[0] is ins[1] and
-                             seen[1] == ins[1]._version and seen[2] is ws)
-                if self.pack_once and not prepacked:
-                    self._packed[idx] = (ins[1], ins[1]._version, ws)
+                prepacked = self._filter_is_packed(idx, ins[1], ws)
                 fused = False
                 if peers and len(peers) > 1 and not self._conv_single_dst.get(idx):
                     try:

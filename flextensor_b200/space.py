@@ -375,7 +375,9 @@ def generate_space_intra_op_b200(op, down_graph=None):
         space.add_subspace("ctas", KnobSpace("ctas", [8, 6, 4]), "unroll")
         # 1 = one shifted input tile per filter tap; 2 = one input slab per channel chunk shared by
         # all taps with the filter resident in shared memory (stride 1, one group, <= 256 channels
-        # out); 3 = batched GEMM on the NCHW tensors as they are (1x1, stride 1, no padding)
+        # out) or, when it does not fit, streamed through a ring of stages; 5 = the same kernel with
+        # the filter streamed whatever its size; 3 = batched GEMM on the NCHW tensors as they are (1x1,
+        # stride 1, no padding)
         unit_stride = tuple(op.attrs.get("stride", (1, 1))) == (1, 1)
         one_group = op.attrs.get("groups", 1) == 1
         slab_ok = taps > 1 and one_group and k_out <= 256 and unit_stride
@@ -384,11 +386,11 @@ def generate_space_intra_op_b200(op, down_graph=None):
                    and (out_h * out_w) % 4 == 0 and rc % 4 == 0)
         # 4 = a 1x1 conv over the im2col form (at most 8 input channels under a filter of 4 taps or more)
         im2col_ok = one_group and rc <= 8 and taps >= 4
-        algos = [1] + ([2] if slab_ok else []) + ([3] if gemm_ok else []) + ([4] if im2col_ok else [])
+        algos = [1] + ([2, 5] if slab_ok else []) + ([3] if gemm_ok else []) + ([4] if im2col_ok else [])
         if form == "conv3d":
             algos = [1]  # the per-tap lowering with its depth-tap loop
         elif form == "nhwc":
-            algos = [1] + ([2] if slab_ok else [])  # read in place: no NCHW batched GEMM, no im2col form
+            algos = [1] + ([2, 5] if slab_ok else [])  # read in place: no NCHW batched GEMM, no im2col form
         space.add_subspace("algo", KnobSpace("algo", algos), "inline")
     else:  # depthwise
         out_h = extents["h"]

@@ -60,12 +60,16 @@ typedef struct ftb_config {
                         channel chunk shared by all taps, filter resident in shared memory (stride 1,
                         groups 1, <= 256 output channels, single-pass TF32); 3 batched GEMM on the
                         NCHW tensors as they are (1x1 filter, stride 1, no padding, groups 1); 4 a 1x1
-                        conv over the im2col form of the input (at most 8 input channels, groups 1)    */
+                        conv over the im2col form of the input (at most 8 input channels, groups 1); 5 the
+                        slab kernel of 2 with the filter streamed through a ring of shared-memory stages
+                        instead of resident (what 0 and 2 pick by themselves for a filter that does not
+                        fit and a tile list long enough to keep the SMs busy)                            */
   int32_t epilogue;  /* 0 = bulk tensor stores from shared memory wherever they can address the result
                         (default); 1 = per-thread global stores everywhere (same bits; for diagnosis)   */
-  int32_t release;   /* GEMMs: 0 or 1 = a pipeline stage goes back to the loader after every K block;
-                        2 = stages go back two at a time (half the tcgen05.commit count; needs an even
-                        number of stages >= 4, ignored otherwise, for 3xTF32 and for tile_n = 512)      */
+  int32_t release;   /* 1 = a pipeline stage goes back to the loader after every K block; 2 = stages go back
+                        two at a time (half the tcgen05.commit count; needs an even number of stages >= 4,
+                        ignored otherwise, for 3xTF32 and for tile_n = 512); 0 = 1 for GEMMs, and for the
+                        per-tap conv kernels 2 on tiles of at most 128 output channels, else 1           */
   int32_t relu;      /* conv2d and depthwise: 1 = clamp the result at zero after the bias (the conv + bias +
                         ReLU chain of a network as one kernel); not a search knob                       */
   int32_t reserved[2];
@@ -200,13 +204,15 @@ int ftb_conv2d_nhwc_f32(const float* in, const float* weight, const float* bias,
  * conv3d_ncdhw).  stride_dhw / pad_dhw / dil_dhw point at three host ints each (depth, height,
  * width).  The same implicit-GEMM kernel as conv2d with a third tap loop; groups run as one launch
  * each.  Knobs as for conv2d, `algo` 0 or 1 only.  `workspace` as for conv2d, sized by
- * ftb_conv3d_workspace_bytes. */
+ * ftb_conv3d_workspace_bytes; `prepacked` != 0: it already holds this filter's packing from an earlier call
+ * with the same shape arguments and knobs (weights are constant per task), only the input is laid out. */
 size_t ftb_conv3d_workspace_bytes(int64_t n, int64_t c, int64_t d, int64_t h, int64_t w, int64_t k, int64_t t,
                                   int64_t r, int64_t s, int64_t groups);
 int ftb_conv3d_ncdhw_f32(const float* in, const float* weight, const float* bias, float* out, int64_t n, int64_t c,
                          int64_t d, int64_t h, int64_t w, int64_t k, int64_t t, int64_t r, int64_t s,
                          const int32_t* stride_dhw, const int32_t* pad_dhw, const int32_t* dil_dhw, int groups,
-                         const ftb_config* cfg, void* workspace, size_t workspace_bytes, int* status, void* stream);
+                         int prepacked, const ftb_config* cfg, void* workspace, size_t workspace_bytes, int* status,
+                         void* stream);
 
 /* conv2d without a caller workspace - no counterpart in the reference.
  *

@@ -445,6 +445,37 @@ def test_conv2d_slab_algorithm(B, status, shape, cfg):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("shape", [
+    # n, c, h, w, k, r, pad, dil
+    (3, 128, 28, 28, 128, 3, 1, 1),    # 36 filter tiles of 16 KB: cannot stay resident
+    (2, 256, 14, 14, 256, 3, 1, 1),    # 72 tiles of 32 KB
+    (5, 64, 56, 56, 64, 3, 1, 1),      # would fit resident: streamed because asked for; ring and slabs wrap
+    (2, 40, 20, 24, 200, 3, 1, 2),     # channel counts that are no multiples of 32, dilation 2
+    (1, 96, 17, 19, 144, 5, 2, 1),     # 25 taps: stages of 5 taps (a filter row), rows bulk stores cannot address
+    (2, 32, 30, 30, 72, 2, 0, 1),      # 2x2 filter, no padding
+])
+@pytest.mark.parametrize("cfg", [{"algo": 5}, {"algo": 5, "cluster": 1}, {"algo": 5, "cluster": 2}, {"algo": 5, "tile_h": 1},
+                                 {"algo": 5, "epilogue": 1}, {"algo": 5, "relu": 1}])
+def test_conv2d_slab_kernel_with_streamed_filter(B, status, shape, cfg):
+    """The slab kernel with its filter passed through a ring of shared-memory stages (algo 5) instead of
+    resident: against the oracle, on single CTAs and CTA pairs."""
+    n, c, h, wd, k, r, pad, dil = shape
+    x, w = O.conv2d_inputs(n, c, h, wd, k, r, r, seed=59)
+    bias = np.random.default_rng(60).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, 1, pad, dil, 1)
+    if cfg.get("relu"):
+        want = np.maximum(want, 0)
+    try:
+        got = run_conv(B, x, w, bias, 1, pad, dil, 1, cfg=dict(cfg, fp32_mode=0), status=status)
+    except B.FtbError as exc:
+        assert exc.code in (-2, -3), exc
+        pytest.skip("refused: %s" % exc)
+    assert got.shape == want.shape
+    assert not np.isnan(got).any()
+    assert O.normalised_error(got, want) <= TOL["conv2d_tf32"], (shape, cfg)
+    assert int(status.item()) == 0
+
+
 @pytest.mark.parametrize("shape", [(2, 64, 8, 8, 48), (3, 32, 14, 14, 256), (1, 256, 56, 56, 64), (2, 20, 6, 6, 130)])
 @pytest.mark.parametrize("cfg", [{}, {"algo": 3, "cluster": 1, "tile_n": 64, "split_k": 1}, {"algo": 3, "split_k": 2}, {"algo": 1},
                                  {"fp32_mode": 1}])
@@ -626,7 +657,8 @@ def test_conv2d_slab_algorithm_refuses_what_it_cannot_take(B, status):
                         (dict(stride=1), {"algo": 2, "fp32_mode": 1}),  # 3xTF32
                         (dict(stride=1), {"algo": 2, "tile_n": 16}),                # not a tile width
                         (dict(stride=1), {"algo": 3}),                             # GEMM form of a 3x3
-                        (dict(stride=1), {"algo": 5})):
+                        (dict(stride=1), {"algo": 5, "split_k": 3}),               # a streamed filter is never split
+                        (dict(stride=1), {"algo": 6})):
         with pytest.raises(B.FtbError):
             run_conv(B, x, w, None, kwargs["stride"], 1, 1, 1, cfg=cfg, status=status)
     xg, wg = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, groups=2, seed=59)

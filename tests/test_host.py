@@ -170,7 +170,7 @@ def test_b200_space_per_family():
     cv = SP.generate_space_intra_op(op_lst[1], down, target="cuda")
     assert [e[0] for e in cv.subspaces["tile_h"].static_entities] == [1, 2]
     assert 9 in [e[0] for e in cv.subspaces["split_k"].static_entities]
-    assert [e[0] for e in cv.subspaces["algo"].static_entities] == [1, 2] and cv.types["inline"] == ["algo"]
+    assert [e[0] for e in cv.subspaces["algo"].static_entities] == [1, 2, 5] and cv.types["inline"] == ["algo"]
     strided = flatten_graph(conv2d(1, 64, 56, 56, 64, 3, 2, 1, 1, 1)[0])
     assert [e[0] for e in SP.generate_space_intra_op(strided[0][1], strided[1], target="cuda")
             .subspaces["algo"].static_entities] == [1]                    # the slab kernel is stride 1 only
@@ -380,7 +380,7 @@ def test_layout_rewrite_of_a_conv2d_task():
     ops_, _ = S.Rewriter(cfg).rewrite(TASK_TABLE[key])[:2]
     op_lst, down = flatten_graph(ops_)
     space = SP.generate_space_intra_op(op_lst[1], down, target="cuda")
-    assert [e[0] for e in space.subspaces["algo"].static_entities] == [1, 2]
+    assert [e[0] for e in space.subspaces["algo"].static_entities] == [1, 2, 5]
     out = ops.conv2d_nhwc(placeholder((4, 7, 7, 8)), placeholder((12, 4, 3, 3)), placeholder((12,)), stride=2, padding=1,
                           dilation=2, groups=2)
     assert to_tuple(out.shape) == (4, 3, 3, 12) and out.op.attrs["axis"] == 3
