@@ -238,8 +238,13 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t by
                "r"(bytes)
                : "memory");
 }
+// Arrival on a barrier that may live in the peer CTA.  Used to hand an accumulator back to the MMA
+// issuer: what has to be ordered before it are this warp's tensor-memory reads, which
+// tcgen05.wait::ld and tcgen05.fence::before_thread_sync take care of, so the arrival carries the
+// default (CTA-scope) release and not a cluster-scope one, whose fence would sit in front of every
+// hand-back.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // TMA load issued by one CTA of a pair: data lands in this CTA, completion bytes are
 // reported to `bar`, which may live in the peer CTA.

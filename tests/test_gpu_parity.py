@@ -211,6 +211,28 @@ def test_bgemm_bf16_several_destinations(B, status):
     assert torch.equal(full[0][0:2], full[1][1:3]) and torch.equal(full[0][0:2], full[2][3:5])
 
 
+def test_bgemm_bf16_eight_destinations_with_the_fused_gather_knobs(B, status):
+    """What a rank of an 8-GPU job launches: its slice of the batch written to eight buffers at once (the
+    maximum), with the knob set the multi-GPU path uses."""
+    items = [O.batch_gemm_item(i, 512, 512, 256, seed=34) for i in range(3)]
+    a = np.stack([i[0] for i in items])
+    b = np.stack([i[1] for i in items])
+    want = O.batch_gemm(a, b)
+    full = [torch.full((4, 512, 512), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(8)]
+    ptrs = [f[d % 2:].data_ptr() for d, f in enumerate(full)]
+    cfg = {"cluster": 2, "tile_n": 256, "raster": 3, "group_m": 4, "stages": 6, "release": 2}
+    B.bgemm_bf16_multi(bf16_dev(a), bf16_dev(b), ptrs, 512, 512, cfg=cfg, status=status)
+    torch.cuda.synchronize()
+    for d, f in enumerate(full):
+        got = f[d % 2:d % 2 + 3]
+        assert O.bf16_output_ok(got.float().cpu().numpy(), want)
+        assert torch.equal(got, full[0][0:3])
+        rest = f[3:] if d % 2 == 0 else f[:1]
+        assert bool(torch.isnan(rest.float()).all())
+    with pytest.raises(ValueError):
+        B.bgemm_bf16_multi(bf16_dev(a), bf16_dev(b), ptrs + ptrs[:1], 512, 512, cfg=cfg, status=status)
+
+
 @pytest.mark.parametrize("shape", [(2, 512, 1024, 256), (3, 300, 1000, 200), (1, 1000, 776, 96), (2, 256, 520, 128)])
 def test_bgemm_bf16_wide_pair_tile(B, status, shape):
     """The 256 x 512 pair tile (two accumulator halves per tile) gives the bits of the 256 x 256 tile,
