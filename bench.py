@@ -38,10 +38,12 @@ FALLBACK_BF16_TFLOPS = 1590.0
 # algorithmic figure is 1.61e9.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = (104.52e6 + 24.33e6) * 64 / 6
 KNOBS = {"cluster": 2, "tile_n": 512, "raster": 3, "group_m": 8}
-# N > 1 with the fused gather: the epilogue's bulk stores cross NVLink and take longer, and the
-# 256 x 512 tile overlaps its epilogue with the next main loop only half by half; the 256 x 256
-# tile (whole-tile overlap) is the faster one there (measured at N = 2: 0.48 ms against 0.66 ms).
-KNOBS_FUSED = {"cluster": 2, "tile_n": 256, "raster": 3, "group_m": 4, "stages": 6, "release": 2}
+# N > 1 with the fused gather: the epilogue's bulk stores cross NVLink and take longer.  The 256 x 512
+# tile overlaps its epilogue with the next main loop only half by half, and for as long as handing an
+# accumulator half back was slow the 256 x 256 tile (whole-tile overlap) was the faster one there; with
+# that fixed the wide tile leads again (20 steps: N = 2 0.483 ms against 0.492 ms, N = 4 0.657 against
+# 0.664 ms), with a shorter grouped-M walk because a rank owns fewer items.
+KNOBS_FUSED = {"cluster": 2, "tile_n": 512, "raster": 3, "group_m": 4}
 # Receive bandwidth per GPU (GB/s) when every rank pushes its slice into all the others at the same
 # time, by world size; 770 is the one-pair peer copy measured on this pool.
 ALL_TO_ALL_GBS = {2: 737.0, 4: 730.0, 8: 730.0}
