@@ -232,12 +232,6 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// The two forms below take a cluster-window barrier address (possibly the peer CTA's).
-__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar),
-               "r"(bytes)
-               : "memory");
-}
 // Arrival on a barrier that may live in the peer CTA.  Used to hand an accumulator back to the MMA
 // issuer: what has to be ordered before it are this warp's tensor-memory reads, which
 // tcgen05.wait::ld and tcgen05.fence::before_thread_sync take care of, so the arrival carries the
