@@ -58,6 +58,11 @@ struct ConvSlabParams {
   // holding the b_group consecutive taps' tiles of one channel chunk; a CTA then re-reads the filter
   // from L2 for every tile, which is far less than re-reading the input once per tap.
   int b_stages, b_group;
+  // conv3d at stride 1 (od > 0, streamed filter only): the tile list walks (image, output depth) pairs,
+  // the filter has T depth taps in front of its R x S taps, and every (depth tap, channel chunk) pair
+  // gets a slab of its own, from input plane `output depth - pad_d + depth tap * dil_d` (planes outside
+  // the input read as zeros); input map (c, w, h, d, n), result map (w, h, d, k, n).
+  int od, T, pad_d, dil_d, depth;
   int cl_out;   // the result is channels-last [N][P][Q][K]: staged as [pixel][32 channels], stored through a
                 // (k, q, p, n) map
   uint32_t epi_buf_bytes;
@@ -188,6 +193,22 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         const int rem = t - img * tiles_per_img;
         const int th = rem / p.tiles_w, tw = rem - th * p.tiles_w;
         const int h0 = th * p.tile_h - p.pad_h, w0 = tw * p.tile_w - p.pad_w;
+        // conv3d: `img` counts (image, output depth) pairs
+        const int img_n = p.od > 0 ? img / p.od : img;
+        const int d0 = p.od > 0 ? (img - img_n * p.od) - p.pad_d : 0;
+        const int depth_taps = STREAM && p.od > 0 ? p.T : 1;
+        bool any_plane = false;
+        for (int td = 0; td < depth_taps && ok; ++td) {
+        const int dz = d0 + td * p.dil_d;
+        if (depth_taps > 1) {
+          // a single CTA skips depth taps that fall into the padding (a pair shares its MMAs between
+          // two tiles that may lie in different planes, so it loads zeros instead); the last tap is
+          // taken if nothing else was, so that the accumulator is always written
+          const bool inside = dz >= 0 && dz < p.depth;
+          if (!PAIR && !inside && !(td + 1 == depth_taps && !any_plane)) continue;
+          any_plane = true;
+        }
+        const int tap_base = tap0 + td * (p.R * p.S);
         for (int cc = 0; cc < p.cchunks && ok; ++cc) {
           FTB_PROF_T0(prof_w0);
           if (!mbar_wait(aempty0 + 8 * s, ph ^ 1u, &abort_flag)) {
@@ -199,10 +220,12 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
           FTB_PROF_ADD(prof_wait, prof_w0);
           if constexpr (PAIR) {
             if (cta_rank == 0) mbar_expect_tx(afull0 + 8 * s, 2u * p.slab_bytes);
-            tma_load_4d_pair(sa, &tmap_in, afull_sig0 + 8 * s, cc * 32, w0, h0, img);
+            if (p.od > 0) tma_load_5d_pair(sa, &tmap_in, afull_sig0 + 8 * s, cc * 32, w0, h0, dz, img_n);
+            else tma_load_4d_pair(sa, &tmap_in, afull_sig0 + 8 * s, cc * 32, w0, h0, img);
           } else {
             mbar_expect_tx(afull0 + 8 * s, p.slab_bytes);
-            tma_load_4d(sa, &tmap_in, afull0 + 8 * s, cc * 32, w0, h0, img);
+            if (p.od > 0) tma_load_5d(sa, &tmap_in, afull0 + 8 * s, cc * 32, w0, h0, dz, img_n);
+            else tma_load_4d(sa, &tmap_in, afull0 + 8 * s, cc * 32, w0, h0, img);
           }
           sa += p.slab_alloc;
           if (++s == a_stages) {
@@ -222,7 +245,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
               }
               const uint32_t bytes = static_cast<uint32_t>(nt) * p.b_tile_bytes;
               uint32_t dst = b_base + bs * b_stage_bytes;
-              int kc = ((tap0 + g0) * p.cchunks + cc) * 32;  // the packed filter is [k_out][tap][chunk][32]
+              int kc = ((tap_base + g0) * p.cchunks + cc) * 32;  // the packed filter is [k_out][tap][chunk][32]
               if constexpr (PAIR) {
                 if (cta_rank == 0) mbar_expect_tx(bsfull0 + 8 * bs, 2u * bytes);
                 for (int j = 0; j < nt; ++j, dst += p.b_tile_bytes, kc += p.cchunks * 32)
@@ -238,6 +261,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
               }
             }
           }
+        }
         }
       }
       long long prof_loop = 0;
@@ -283,6 +307,21 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
         uint32_t accumulate = 0;
+        // conv3d: the same walk over depth taps as the producer's (skips included)
+        const int depth_taps = STREAM && p.od > 0 ? p.T : 1;
+        int d0 = 0;
+        if (depth_taps > 1 && !PAIR) {
+          const int img = tp / tiles_per_img;
+          d0 = img % p.od - p.pad_d;
+        }
+        bool any_plane = false;
+        for (int td = 0; td < depth_taps && ok; ++td) {
+        if (depth_taps > 1) {
+          const int dz = d0 + td * p.dil_d;
+          const bool inside = dz >= 0 && dz < p.depth;
+          if (!PAIR && !inside && !(td + 1 == depth_taps && !any_plane)) continue;
+          any_plane = true;
+        }
         for (int cc = 0; cc < p.cchunks; ++cc) {
           FTB_PROF_T0(prof_f0);
           if (!mbar_wait(afull0 + 8 * s, ph, &abort_flag)) {
@@ -363,6 +402,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             a_lo = a_lo0;
           }
         }
+        }
         if (ok) {
           if constexpr (PAIR) tc_commit_pair_both(smem_u32(&bar_tfull[acc]));
           else tc_commit(smem_u32(&bar_tfull[acc]));
@@ -412,6 +452,9 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         const int img = t / tiles_per_img;
         const int rem = t - img * tiles_per_img;
         const int th = rem / p.tiles_w, tw = rem - th * p.tiles_w;
+        // conv3d: `img` counts (image, output depth) pairs
+        const int img_n = p.od > 0 ? img / p.od : img;
+        const int img_d = p.od > 0 ? img - img_n * p.od : 0;
         if (p.epi_bufs && p.cl_out) {
           // ---- channels-last result: TMEM -> registers -> [tile_h][tile_w][32 channels] in shared memory
           // (a lane writes its pixel's 128 bytes) -> one bulk tensor store per 32 output channels
@@ -507,7 +550,11 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             named_barrier_sync(1, 128);
             if (leader) {
               if (c < p.N && tile_valid) {
-                if (p.split > 1) {
+                if (p.od > 0) {
+                  // conv3d: (w, h, depth, channel, image)
+                  for (int d = 0; d < p.num_dst; ++d)
+                    tma_store_5d(&tmap_out.dst[d], buf, tw * p.tile_w, th * p.tile_h, img_d, c, img_n);
+                } else if (p.split > 1) {
                   tma_reduce_add_4d(&tmap_out.dst[0], buf, tw * p.tile_w, th * p.tile_h, c, img);
                 } else {
                   // every destination gets the same box: this GPU's result and, in a batch-sharded
@@ -523,9 +570,11 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         }
         const int oh = th * p.tile_h + prow, ow = tw * p.tile_w + pcol;
         const bool row_ok = in_tile && oh < p.P && ow < p.Q && tile_valid;
-        const long long ch_stride = p.cl_out ? 1 : plane;
+        const long long ch_stride = p.cl_out ? 1 : (p.od > 0 ? plane * p.od : plane);
         float* dst0 = p.cl_out ? p.out + (static_cast<long long>(img) * plane + static_cast<long long>(oh) * p.Q + ow) * p.conv_ktot
-                               : p.out + static_cast<long long>(img) * p.conv_ktot * plane + static_cast<long long>(oh) * p.Q + ow;
+                      : p.od > 0 ? p.out + (static_cast<long long>(img_n) * p.conv_ktot * p.od + img_d) * plane +
+                                       static_cast<long long>(oh) * p.Q + ow
+                                 : p.out + static_cast<long long>(img) * p.conv_ktot * plane + static_cast<long long>(oh) * p.Q + ow;
         for (int c = 0; c < p.bn; c += 32) {
           uint32_t v[32];
           tmem_ld_32x32(taddr + c, v);

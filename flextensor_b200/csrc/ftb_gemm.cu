@@ -1617,7 +1617,8 @@ int conv3d_generic(const float* in, const float* weight, const float* bias, floa
   if (user && (user->relu < 0 || user->relu > 1)) return FTB_E_BAD_CONFIG;
   if (user && (user->fp32_mode < 0 || user->fp32_mode > 1)) return FTB_E_BAD_CONFIG;
   if (user && (user->epilogue < 0 || user->epilogue > 1)) return FTB_E_BAD_CONFIG;
-  if (user && (user->algo < 0 || user->algo > 1)) return FTB_E_UNSUPPORTED;  // only the per-tap lowering
+  const int algo3 = user ? user->algo : 0;
+  if (algo3 == 3 || algo3 == 4 || algo3 < 0 || algo3 > 5) return FTB_E_UNSUPPORTED;
   const int relu = user ? user->relu : 0;
   if (relu && user->split_k > 1) return FTB_E_BAD_CONFIG;
   int rc = device_ok();
@@ -1632,6 +1633,75 @@ int conv3d_generic(const float* in, const float* weight, const float* bias, floa
   const bool split3 = user && user->fp32_mode == 1;
   const int num_sms = sm_count();
   const int stride_h = stride[1], stride_w = stride[2];
+
+  // Stride 1, one group: the slab kernel with a slab per (depth tap, channel chunk) and the filter
+  // streamed (27 taps never stay resident).  Taken by itself when the tile list keeps the SMs busy;
+  // shorter lists go to the per-tap lowering, which can split the reduction over CTAs.
+  if (algo3 != 1 && groups == 1 && !split3 && kg <= 256 && stride[0] == 1 && stride_h == 1 && stride_w == 1 &&
+      pad[0] <= (t - 1) * dil[0] && !(user && user->split_k > 1) && !(user && user->cluster == 2 && algo3 == 0)) {
+    ftb_config scfg;
+    memset(&scfg, 0, sizeof(scfg));
+    if (user) scfg = *user;
+    scfg.algo = 5;
+    SlabPlan sp = plan_slab(&scfg, n * OD, kg, P, Q, r, s, ws.cchunks, dil[1], dil[2], pad[1], pad[2],
+                            (reinterpret_cast<uintptr_t>(out) & 15) == 0, num_sms, false);
+    if (sp.ok && algo3 == 0 && 2ll * sp.p.tiles < num_sms) sp.ok = false;
+    if (!sp.ok && (algo3 == 2 || algo3 == 5)) return FTB_E_UNSUPPORTED;
+    if (sp.ok) {
+      rc = conv_prepass(in, weight, in_cl, w_packed, n, c, d * h, w, k, cg, t * r, s, ws, num_sms, stream_v, nullptr, 0,
+                        0, 0, 1, 1, false, prepacked ? 1 : 3);
+      if (rc) return rc;
+      sp.p.out = out;
+      sp.p.bias = bias;
+      sp.p.relu = relu;
+      sp.p.diag = 0;
+      sp.p.conv_ktot = static_cast<int>(k);
+      sp.p.num_dst = 1;
+      sp.p.od = static_cast<int>(OD);
+      sp.p.T = static_cast<int>(t);
+      sp.p.pad_d = pad[0];
+      sp.p.dil_d = dil[0];
+      sp.p.depth = static_cast<int>(d);
+      sp.p.status = status ? status : fallback_status();
+      if (!sp.p.status) return FTB_E_CUDA;
+      CUtensorMap tin, tw;
+      {
+        uint64_t dims[5] = {static_cast<uint64_t>(ws.cp), static_cast<uint64_t>(w), static_cast<uint64_t>(h),
+                            static_cast<uint64_t>(d), static_cast<uint64_t>(n)};
+        uint64_t strides[4] = {static_cast<uint64_t>(ws.cp) * 4, static_cast<uint64_t>(w) * ws.cp * 4,
+                               static_cast<uint64_t>(h) * w * ws.cp * 4, static_cast<uint64_t>(d) * h * w * ws.cp * 4};
+        uint32_t box[5] = {32, sp.box_w, sp.box_h, 1, 1};
+        const uint32_t ones[5] = {1, 1, 1, 1, 1};
+        rc = make_tmap(&tin, ki.dt, 5, in_cl, dims, strides, box, ones);
+        if (rc) return rc;
+      }
+      {
+        const uint64_t kdim = static_cast<uint64_t>(t * r * s * ws.cchunks) * 32;
+        uint64_t dims[3] = {kdim, static_cast<uint64_t>(kg), 1};
+        uint64_t strides[2] = {kdim * 4, kdim * 4 * kg};
+        uint32_t box[3] = {32, static_cast<uint32_t>(sp.pair ? sp.p.bn / 2 : sp.p.bn), 1};
+        const uint32_t ones[3] = {1, 1, 1};
+        rc = make_tmap(&tw, ki.dt, 3, w_packed, dims, strides, box, ones);
+        if (rc) return rc;
+      }
+      StoreMaps tout;
+      memset(&tout, 0, sizeof(tout));
+      if (sp.p.epi_bufs) {
+        // (w, h, depth, channel, image) view of the NCDHW result; a box is 32 channels of one output tile
+        uint64_t dims[5] = {static_cast<uint64_t>(Q), static_cast<uint64_t>(P), static_cast<uint64_t>(OD),
+                            static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+        uint64_t strides[4] = {static_cast<uint64_t>(Q) * 4, static_cast<uint64_t>(P) * Q * 4,
+                               static_cast<uint64_t>(OD) * P * Q * 4, static_cast<uint64_t>(k) * OD * P * Q * 4};
+        uint32_t box[5] = {static_cast<uint32_t>(sp.p.tile_w), static_cast<uint32_t>(sp.p.tile_h), 1, 32, 1};
+        const uint32_t ones[5] = {1, 1, 1, 1, 1};
+        rc = make_tmap(&tout.dst[0], ki.dt, 5, out, dims, strides, box, ones, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+      }
+      return launch_slab(tin, tw, tout, sp, static_cast<cudaStream_t>(stream_v));
+    }
+  } else if (algo3 == 2 || algo3 == 5) {
+    return FTB_E_UNSUPPORTED;
+  }
 
   int tile_w = static_cast<int>(Q < 128 ? Q : 128);
   if (tile_w * stride_w > 256) tile_w = 256 / stride_w;

@@ -388,7 +388,10 @@ def generate_space_intra_op_b200(op, down_graph=None):
         im2col_ok = one_group and rc <= 8 and taps >= 4
         algos = [1] + ([2, 5] if slab_ok else []) + ([3] if gemm_ok else []) + ([4] if im2col_ok else [])
         if form == "conv3d":
-            algos = [1]  # the per-tap lowering with its depth-tap loop
+            # the per-tap lowering with its depth-tap loop; at stride 1 also the slab kernel with one
+            # slab per (depth tap, channel chunk) and a streamed filter
+            unit3 = tuple(op.attrs.get("stride", (1, 1, 1))) == (1, 1, 1)
+            algos = [1] + ([5] if taps > 1 and one_group and k_out <= 256 and unit3 else [])
         elif form == "nhwc":
             algos = [1] + ([2, 5] if slab_ok else [])  # read in place: no NCHW batched GEMM, no im2col form
         space.add_subspace("algo", KnobSpace("algo", algos), "inline")

@@ -203,7 +203,8 @@ int ftb_conv2d_nhwc_f32(const float* in, const float* weight, const float* bias,
  * zero padding folded into the loads (flextensor/nn/ops.py:157-189 zero_pad3d + :689-751
  * conv3d_ncdhw).  stride_dhw / pad_dhw / dil_dhw point at three host ints each (depth, height,
  * width).  The same implicit-GEMM kernel as conv2d with a third tap loop; groups run as one launch
- * each.  Knobs as for conv2d, `algo` 0 or 1 only.  `workspace` as for conv2d, sized by
+ * each.  Knobs as for conv2d; `algo` 0, 1 or 5 (5: at stride 1 and one group, the slab kernel with one input
+ * slab per depth tap and channel chunk and the filter streamed; 0 picks it for long tile lists).  `workspace` as for conv2d, sized by
  * ftb_conv3d_workspace_bytes; `prepacked` != 0: it already holds this filter's packing from an earlier call
  * with the same shape arguments and knobs (weights are constant per task), only the input is laid out. */
 size_t ftb_conv3d_workspace_bytes(int64_t n, int64_t c, int64_t d, int64_t h, int64_t w, int64_t k, int64_t t,

@@ -118,6 +118,37 @@ def test_conv3d_shapes_and_knobs(B, status, shape, cfg):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("cfg", [{"algo": 5}, {"algo": 5, "cluster": 1}, {"algo": 5, "cluster": 2}, {"algo": 5, "tile_h": 1},
+                                 {"algo": 5, "epilogue": 1}, {"algo": 5, "relu": 1}, {}])
+@pytest.mark.parametrize("shape", [
+    # n, c, d, h, w, k, (t, r, s), padding, dilation  (stride 1)
+    (2, 64, 8, 28, 28, 64, (3, 3, 3), (1, 1, 1), (1, 1, 1)),      # the first layer of the reference's table, batch 2
+    (6, 32, 6, 16, 16, 48, (3, 3, 3), (1, 1, 1), (1, 1, 1)),      # enough tiles for the library to pick the slab kernel
+    (3, 40, 2, 9, 12, 136, (3, 3, 3), (1, 1, 1), (1, 1, 1)),      # two input planes under three depth taps
+    (2, 128, 1, 14, 14, 128, (3, 3, 3), (1, 1, 1), (1, 1, 1)),    # one input plane: two of three depth taps are padding
+    (2, 24, 7, 10, 11, 20, (2, 3, 2), (1, 0, 1), (2, 1, 1)),      # depth dilation 2, rows that bulk stores cannot address
+    (1, 96, 5, 12, 12, 72, (3, 1, 1), (0, 0, 0), (1, 1, 1)),      # depth taps only, no padding
+])
+def test_conv3d_on_the_slab_kernel(B, status, shape, cfg):
+    """Stride-1 conv3d with one input slab per (depth tap, channel chunk) and the filter streamed (algo 5),
+    single CTAs (which skip depth taps that fall into the padding) and CTA pairs (which load zeros there)."""
+    n, c, d, h, w, k, taps, pad, dil = shape
+    x, wt = _inputs(n, c, d, h, w, k, *taps, 1, seed=340)
+    bias = np.random.default_rng(341).standard_normal(k).astype(np.float32)
+    want = O.conv3d_ncdhw(x, wt, bias, 1, pad, dil, 1)
+    if cfg.get("relu"):
+        want = np.maximum(want, 0)
+    try:
+        got = run_conv3d(B, x, wt, bias, 1, pad, dil, 1, cfg=cfg, status=status, calls=2)
+    except B.FtbError as exc:
+        assert exc.code in (-2, -3), exc
+        pytest.skip("refused: %s" % exc)
+    assert got.shape == want.shape
+    assert not np.isnan(got).any()
+    assert O.normalised_error(got, want) <= TOL["conv2d_tf32"], (shape, cfg)
+    assert int(status.item()) == 0
+
+
 def test_conv3d_single_tap_is_the_batched_gemm(B, status):
     # 1x1x1, stride 1, no padding: a batched GEMM on the NCDHW tensors as they are
     x, wt = _inputs(2, 64, 4, 6, 8, 40, 1, 1, 1, 1, seed=320)
@@ -170,8 +201,8 @@ def test_conv3d_bad_arguments_are_refused(B):
     ws = torch.empty(B.conv3d_workspace_bytes(1, 8, 4, 4, 4, 8, 5, 5, 5, 1), dtype=torch.uint8, device="cuda")
     with pytest.raises(B.FtbError):   # a filter larger than the padded input
         B.conv3d_ncdhw_f32(x, torch.zeros(8, 8, 5, 5, 5, device="cuda"), out, workspace=ws)
-    with pytest.raises(B.FtbError):   # the slab algorithm does not take conv3d
-        B.conv3d_ncdhw_f32(x, w, out, workspace=ws, cfg={"algo": 2})
+    with pytest.raises(B.FtbError):   # the slab kernel takes conv3d at stride 1 only
+        B.conv3d_ncdhw_f32(x, w, torch.zeros(1, 8, 1, 1, 1, device="cuda"), stride=2, workspace=ws, cfg={"algo": 5})
     with pytest.raises(ValueError):
         B.conv3d_ncdhw_f32(x, torch.zeros(8, 4, 3, 3, 3, device="cuda"), out, workspace=ws)
 

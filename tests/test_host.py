@@ -180,7 +180,10 @@ def test_b200_space_per_family():
     c3 = flatten_graph(conv3d(1, 64, 8, 28, 28, 64, 3, 1, 1, 1, 1)[0])
     assert [op.kind for op in c3[0]] == ["pad2d", "conv2d"]
     c3s = SP.generate_space_intra_op(c3[0][1], c3[1], target="cuda")
-    assert [e[0] for e in c3s.subspaces["algo"].static_entities] == [1]      # per-tap lowering with a depth-tap loop
+    assert [e[0] for e in c3s.subspaces["algo"].static_entities] == [1, 5]   # per-tap with a depth-tap loop; slab kernel
+    c3_strided = flatten_graph(conv3d(1, 64, 8, 28, 28, 128, 3, 2, 1, 1, 1)[0])
+    assert [e[0] for e in SP.generate_space_intra_op(c3_strided[0][1], c3_strided[1], target="cuda")
+            .subspaces["algo"].static_entities] == [1]
     assert [e[0] for e in c3s.subspaces["tile_h"].static_entities] == [1, 2, 3, 4]   # rows of the 28 x 28 plane
     assert 9 in [e[0] for e in c3s.subspaces["split_k"].static_entities]      # 27 taps x 2 channel chunks
     dw = SP.generate_space_intra_op(flatten_graph(depthwise_conv2d(1, 256, 56, 56, 1, 3, 1, 1, 1)[0])[0][1], {},
