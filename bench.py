@@ -47,8 +47,10 @@ KNOBS_FUSED = {"cluster": 2, "tile_n": 512, "raster": 3, "group_m": 4}
 # Receive bandwidth per GPU (GB/s) when every rank pushes its slice into all the others at the same
 # time, by world size; 770 is the one-pair peer copy measured on this pool.
 ALL_TO_ALL_GBS = {2: 737.0, 4: 730.0, 8: 730.0}
-ALL_TO_ALL_SOURCE = ("`bench.py --link-ceiling --link-mib 256` on this pool: 737 GB/s at N=2, 730 GB/s at N=4; "
-                     "N=8 not measured (no 8-GPU slot was free), the N=4 figure is used")
+ALL_TO_ALL_SOURCE = ("`bench.py --link-ceiling --link-mib 256` on this pool: 737 GB/s at N=2, 730 GB/s at N=4; at N=8 "
+                     "the same pattern of device-to-device copies (56 at once) reaches only 503 GB/s per GPU, less "
+                     "than the fused kernel's own stores move there (622 GB/s), so it is no ceiling and the N=4 "
+                     "figure is used")
 
 
 def measured_peak():
