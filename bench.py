@@ -41,15 +41,18 @@ KNOBS = {"cluster": 2, "tile_n": 512, "raster": 3, "group_m": 8}
 # N > 1 with the fused gather: the epilogue's bulk stores cross NVLink and take longer.  The 256 x 512
 # tile overlaps its epilogue with the next main loop only half by half, and for as long as handing an
 # accumulator half back was slow the 256 x 256 tile (whole-tile overlap) was the faster one there; with
-# that fixed the wide tile leads again (20 steps: N = 2 0.483 ms against 0.492 ms, N = 4 0.657 against
-# 0.664 ms), with a shorter grouped-M walk because a rank owns fewer items.
+# that fixed the wide tile leads at N = 2 and 4 (20 steps: 0.483 ms against 0.492 ms, 0.657 against
+# 0.664 ms), with a shorter grouped-M walk because a rank owns fewer items.  At N = 8 a rank writes every
+# slab eight times and the step is all stores: there the tile with a spare accumulator still wins
+# (0.730 / 0.737 ms against 0.750 / 0.753 ms, runs alternated on one box).
 KNOBS_FUSED = {"cluster": 2, "tile_n": 512, "raster": 3, "group_m": 4}
+KNOBS_FUSED_8 = {"cluster": 2, "tile_n": 256, "raster": 3, "group_m": 4, "stages": 6, "release": 2}
 # Receive bandwidth per GPU (GB/s) when every rank pushes its slice into all the others at the same
 # time, by world size; 770 is the one-pair peer copy measured on this pool.
 ALL_TO_ALL_GBS = {2: 737.0, 4: 730.0, 8: 730.0}
 ALL_TO_ALL_SOURCE = ("`bench.py --link-ceiling --link-mib 256` on this pool: 737 GB/s at N=2, 730 GB/s at N=4; at N=8 "
                      "the same pattern of device-to-device copies (56 at once) reaches only 503 GB/s per GPU, less "
-                     "than the fused kernel's own stores move there (622 GB/s), so it is no ceiling and the N=4 "
+                     "than the fused kernel's own stores move there (643 GB/s), so it is no ceiling and the N=4 "
                      "figure is used")
 
 
@@ -552,7 +555,7 @@ def run_ours(args, rank, world, local_rank):
     # rank's shard.  N > 1: the output argument is this rank's slice of a buffer every rank holds and the
     # GEMM epilogue stores into all of them (fused gather), else one NCCL all-gather follows the call.
     fused_why = None
-    knobs = KNOBS if world == 1 else KNOBS_FUSED
+    knobs = KNOBS if world == 1 else KNOBS_FUSED if world < 8 else KNOBS_FUSED_8
     if args.knobs:
         knobs = json.loads(args.knobs)
     op = None
