@@ -1,5 +1,7 @@
 // conv2d (stride 1) on the tensor cores with the input staged once per channel chunk and
-// the filter held in shared memory for the whole kernel.
+// the filter held in shared memory for the whole kernel - or, when it does not fit, passed through
+// a ring of shared-memory stages (STREAM).  Also stride-1 conv3d (one slab per depth tap and
+// channel chunk, STREAM only) and channels-last results.
 //
 // The implicit-GEMM lowering in ftb_umma_kernel.cuh fetches one shifted copy of the input
 // tile per filter tap, so an R x S filter reads the same pixels R*S times from L2.  Here a
@@ -22,6 +24,12 @@
 //
 // CTAs with the same blockIdx.x % split share a subset of the taps and walk the tile list
 // with a stride of gridDim.x / split.
+//
+// STREAM = true: the filter is not resident.  The producer follows every slab with that channel
+// chunk's filter tiles, b_group taps per ring stage, and the issuer hands a stage back (one
+// tcgen05.commit) after its taps' MMAs.  A CTA then re-reads the filter from L2 for every tile -
+// a few KB per tap - instead of splitting the taps over CTAs, whose partial sums would have to be
+// added in global memory.
 //
 // PAIR = true runs two CTAs of a cluster as one tcgen05 `cta_group::2` unit on two consecutive
 // tiles (M = 256): each CTA stages the slab of its own tile and HALF of the filter's output
