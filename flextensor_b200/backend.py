@@ -47,11 +47,12 @@ class FtbConfig(ctypes.Structure):
         ("epilogue", ctypes.c_int32),
         ("release", ctypes.c_int32),
         ("relu", ctypes.c_int32),
-        ("reserved", ctypes.c_int32 * 2),
+        ("gather", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 1),
     ]
 
     KNOBS = ("tile_n", "stages", "raster", "group_m", "split_k", "fp32_mode", "ctas", "tile_h", "threads",
-             "cluster", "algo", "epilogue", "release", "relu")
+             "cluster", "algo", "epilogue", "release", "relu", "gather")
 
     @classmethod
     def from_dict(cls, knobs):

@@ -71,6 +71,11 @@ struct ConvSlabParams {
   // gets a slab of its own, from input plane `output depth - pad_d + depth tap * dil_d` (planes outside
   // the input read as zeros); input map (c, w, h, d, n), result map (w, h, d, k, n).
   int od, T, pad_d, dil_d, depth;
+  // GATHER instantiations: no channels-last copy of the input exists; eight loader warps build every
+  // slab from the NCHW tensor `in_nchw` [n_imgs][C][H][W] themselves (coalesced 32-byte reads along
+  // the rows, conflict-free 4-byte writes into the swizzled slab), zero-filling the padding.
+  const float* in_nchw;
+  int n_imgs, C, H, W;
   int cl_out;   // the result is channels-last [N][P][Q][K]: staged as [pixel][32 channels], stored through a
                 // (k, q, p, n) map
   uint32_t epi_buf_bytes;
@@ -83,8 +88,8 @@ struct ConvSlabParams {
   int* status;
 };
 
-template <bool PAIR, bool STREAM>
-__global__ void __launch_bounds__(192, 1)
+template <bool PAIR, bool STREAM, bool GATHER>
+__global__ void __launch_bounds__(GATHER ? 448 : 192, 1)
 conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ StoreMaps tmap_out,
                  const __grid_constant__ ConvSlabParams p) {
@@ -126,7 +131,9 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (uint32_t s = 0; s < a_stages; ++s) {
-      mbar_init(smem_u32(&bar_afull[s]), 1);
+      // a slab is complete when its TMA bytes have landed, or when every loader warp (of both CTAs
+      // of a pair) has written its part
+      mbar_init(smem_u32(&bar_afull[s]), GATHER ? (PAIR ? 16u : 8u) : 1u);
       mbar_init(smem_u32(&bar_aempty[s]), 1);
     }
     mbar_init(smem_u32(&bar_bfull), 1);
@@ -140,7 +147,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
     }
     fence_mbar_init();
     fence_proxy_async_smem();
-    prefetch_tmap(&tmap_in);
+    if constexpr (!GATHER) prefetch_tmap(&tmap_in);
     prefetch_tmap(&tmap_w);
     if (p.epi_bufs)
       for (int d = 0; d < p.num_dst; ++d) prefetch_tmap(&tmap_out.dst[d]);
@@ -218,6 +225,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         }
         const int tap_base = tap0 + td * (p.R * p.S);
         for (int cc = 0; cc < p.cchunks && ok; ++cc) {
+          if constexpr (!GATHER) {
           FTB_PROF_T0(prof_w0);
           if (!mbar_wait(aempty0 + 8 * s, ph ^ 1u, &abort_flag)) {
             atomicOr(p.status, FTB_DEV_WAIT_EMPTY);
@@ -240,6 +248,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             s = 0;
             ph ^= 1u;
             sa = a_base;
+          }
           }
           if (streamed) {
             // this chunk's filter tiles, b_group taps per stage, in the order the issuer takes them
@@ -422,6 +431,84 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       FTB_PROF_FLUSH(PROF_ISSUER_TEMPTY, prof_tempty);
       FTB_PROF_FLUSH(PROF_ISSUER_LOOP, prof_iloop);
       (void)prof_full; (void)prof_tempty; (void)prof_iloop;
+    }
+    __syncwarp();
+  } else if (GATHER && warp >= 6) {
+    // ------------------------------------------------------------ slab loader (NCHW input)
+    // 256 threads build the slab of every (tile, channel chunk): warp g takes the channels 4 g .. 4 g + 3
+    // of the chunk, its lanes 32 consecutive slab pixels, so that a warp-wide load is one 128-byte line
+    // of a channel plane (minus what falls into the padding).  The writes into the swizzled slab (16-byte
+    // chunk index = (channel / 4) ^ (pixel & 7)) collide four ways, which is nothing beside the loads'
+    // latency: eight of those are in flight per thread (sixteen, or asking the next tile's lines into
+    // L2 ahead of time, measured no better).
+    if (ntaps > 0) {
+      const int lt = static_cast<int>(threadIdx.x) - 192;
+      const int g = lt >> 5;
+      const int slab_px = (p.tile_h + (p.R - 1) * p.dil_h) * p.slab_w;
+      const long long plane = static_cast<long long>(p.H) * p.W;
+      const uint32_t afull_sig0 = PAIR ? map_to_cta(afull0, 0) : afull0;
+      uint32_t s = 0, ph = 0, sa = a_base;
+      bool ok = true;
+      for (int tp = walker; tp < steps && ok; tp += walkers) {
+        const int t = PAIR ? 2 * tp + static_cast<int>(cta_rank) : tp;
+        const int img = t / tiles_per_img;
+        const int rem = t - img * tiles_per_img;
+        const int th = rem / p.tiles_w, tw = rem - th * p.tiles_w;
+        const int h0 = th * p.tile_h - p.pad_h, w0 = tw * p.tile_w - p.pad_w;
+        const bool img_ok = img < p.n_imgs;
+        for (int cc = 0; cc < p.cchunks && ok; ++cc) {
+          if (lane == 0) ok = mbar_wait(aempty0 + 8 * s, ph ^ 1u, &abort_flag);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) {
+            if (lane == 0) {
+              atomicOr(p.status, FTB_DEV_WAIT_EMPTY);
+              abort_flag = 1;
+            }
+            break;
+          }
+          const int ch0 = cc * 32 + 4 * g;
+          const float* src = p.in_nchw + (static_cast<long long>(img) * p.C + ch0) * plane;
+          int sr = lane / p.slab_w, sc = lane - sr * p.slab_w;  // slab row and column of this lane's pixel
+          constexpr int kU = 2;  // pixel blocks per round: 4 * kU loads in flight per thread
+          for (int px = lane; px < slab_px; px += 32 * kU) {
+            float v[kU][4];
+            uint32_t dst[kU];
+#pragma unroll
+            for (int u = 0; u < kU; ++u) {
+              const int pxu = px + 32 * u;
+              const int h = h0 + sr, w = w0 + sc;
+              const bool inside = img_ok && pxu < slab_px && h >= 0 && h < p.H && w >= 0 && w < p.W;
+              const float* at = src + static_cast<long long>(h) * p.W + w;
+#pragma unroll
+              for (int qc = 0; qc < 4; ++qc) v[u][qc] = (inside && ch0 + qc < p.C) ? __ldg(at + qc * plane) : 0.0f;
+              dst[u] = pxu < slab_px ? sa + static_cast<uint32_t>(pxu) * 128u +
+                                           ((static_cast<uint32_t>(g) ^ static_cast<uint32_t>(pxu & 7)) << 4)
+                                     : 0u;
+              sc += 32;
+              while (sc >= p.slab_w) {
+                sc -= p.slab_w;
+                ++sr;
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < kU; ++u)
+              if (dst[u]) st_shared_v4(dst[u], __float_as_uint(v[u][0]), __float_as_uint(v[u][1]), __float_as_uint(v[u][2]),
+                                       __float_as_uint(v[u][3]));
+          }
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_cluster_release(afull_sig0 + 8 * s);
+            else mbar_arrive(afull0 + 8 * s);
+          }
+          sa += p.slab_alloc;
+          if (++s == a_stages) {
+            s = 0;
+            ph ^= 1u;
+            sa = a_base;
+          }
+        }
+      }
     }
     __syncwarp();
   } else {

@@ -905,6 +905,7 @@ static bool pick_small_conv(const ftb_config* user, long long groups, long long 
 struct SlabPlan {
   bool ok;
   bool pair;  // two CTAs of a cluster on two consecutive tiles (cta_group::2)
+  bool gather;  // slabs built from the NCHW tensor by loader warps (no channels-last copy)
   ConvSlabParams p;
   int ctas;
   size_t smem;
@@ -1073,11 +1074,15 @@ static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const Stor
     std::lock_guard<std::mutex> lock(mu);
     if (dev >= 0 && dev < 64 && !done[dev]) {
       cudaError_t attr_err = cudaSuccess;
-      const void* kernels[4] = {reinterpret_cast<const void*>(conv_slab_kernel<false, false>),
-                                reinterpret_cast<const void*>(conv_slab_kernel<false, true>),
-                                reinterpret_cast<const void*>(conv_slab_kernel<true, false>),
-                                reinterpret_cast<const void*>(conv_slab_kernel<true, true>)};
-      for (int i = 0; i < 4 && attr_err == cudaSuccess; ++i)
+      const void* kernels[8] = {reinterpret_cast<const void*>(conv_slab_kernel<false, false, false>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<false, true, false>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<true, false, false>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<true, true, false>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<false, false, true>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<false, true, true>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<true, false, true>),
+                                reinterpret_cast<const void*>(conv_slab_kernel<true, true, true>)};
+      for (int i = 0; i < 8 && attr_err == cudaSuccess; ++i)
         attr_err = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemLimit));
       if (attr_err != cudaSuccess) {
@@ -1091,7 +1096,7 @@ static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const Stor
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));
   lc.gridDim = dim3(static_cast<unsigned>(sp.ctas), 1, 1);
-  lc.blockDim = dim3(192, 1, 1);
+  lc.blockDim = dim3(sp.gather ? 448 : 192, 1, 1);
   lc.dynamicSmemBytes = sp.smem;
   lc.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -1105,12 +1110,16 @@ static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const Stor
     attr[1].val.clusterDim.y = 1;
     attr[1].val.clusterDim.z = 1;
     lc.numAttrs = 2;
-    if (sp.p.b_stages > 0) cudaLaunchKernelEx(&lc, conv_slab_kernel<true, true>, tin, tw, tout, sp.p);
-    else cudaLaunchKernelEx(&lc, conv_slab_kernel<true, false>, tin, tw, tout, sp.p);
-  } else {
-    if (sp.p.b_stages > 0) cudaLaunchKernelEx(&lc, conv_slab_kernel<false, true>, tin, tw, tout, sp.p);
-    else cudaLaunchKernelEx(&lc, conv_slab_kernel<false, false>, tin, tw, tout, sp.p);
   }
+  const bool streamed = sp.p.b_stages > 0;
+  if (sp.pair && streamed && sp.gather) cudaLaunchKernelEx(&lc, conv_slab_kernel<true, true, true>, tin, tw, tout, sp.p);
+  else if (sp.pair && streamed) cudaLaunchKernelEx(&lc, conv_slab_kernel<true, true, false>, tin, tw, tout, sp.p);
+  else if (sp.pair && sp.gather) cudaLaunchKernelEx(&lc, conv_slab_kernel<true, false, true>, tin, tw, tout, sp.p);
+  else if (sp.pair) cudaLaunchKernelEx(&lc, conv_slab_kernel<true, false, false>, tin, tw, tout, sp.p);
+  else if (streamed && sp.gather) cudaLaunchKernelEx(&lc, conv_slab_kernel<false, true, true>, tin, tw, tout, sp.p);
+  else if (streamed) cudaLaunchKernelEx(&lc, conv_slab_kernel<false, true, false>, tin, tw, tout, sp.p);
+  else if (sp.gather) cudaLaunchKernelEx(&lc, conv_slab_kernel<false, false, true>, tin, tw, tout, sp.p);
+  else cudaLaunchKernelEx(&lc, conv_slab_kernel<false, false, false>, tin, tw, tout, sp.p);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -1250,14 +1259,28 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
   // list is shorter than half the SM count (where a split reduction is wanted anyway); a long tile list
   // with the taps split would add every partial sum of a large result in global memory.
   if (sp.ok && algo == 0 && sp.p.split > 1 && 2ll * sp.p.tiles > num_sms) sp.ok = false;
+  if (user && (user->gather < 0 || user->gather > 2)) return FTB_E_BAD_CONFIG;
   if (sp.ok) {
     if (user) {
       rc = ftb_validate(3, user, n * P * Q, k, c * r * s);
       if (rc) return rc;
     }
+    // NCHW input: the slabs are either TMA loads from a channels-last copy made by the layout pass
+    // (default), or built from the NCHW tensor by loader warps inside the kernel (gather = 2: no copy,
+    // the input crosses HBM once instead of three times).  Measured, batch 64 / 16 layers, the two are
+    // level where the MMAs are wide (128 -> 128 at 28 x 28: 55.6 against 58.6 us; 256 -> 256 at 14 x 14:
+    // 45.6 against 47.8) and the layout pass wins where they are narrow and a tile's MMAs are over before
+    // the loader warps have the next slab (64 -> 64 at 56 x 56: 77.5-80 against 72.6 us).
+    sp.gather = !cl && user && user->gather == 2;
     rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v,
-                      (sp.p.split > 1 && !pack_only) ? out : nullptr, n * k * P * Q, 0, 0, 1, 1, false, parts);
+                      (sp.p.split > 1 && !pack_only) ? out : nullptr, n * k * P * Q, 0, 0, 1, 1, false,
+                      sp.gather ? (parts & ~1) : parts);
     if (rc || pack_only) return rc;
+    sp.p.in_nchw = in;
+    sp.p.n_imgs = static_cast<int>(n);
+    sp.p.C = static_cast<int>(c);
+    sp.p.H = static_cast<int>(h);
+    sp.p.W = static_cast<int>(w);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     sp.p.out = out;
     sp.p.bias = bias;
@@ -1267,7 +1290,8 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     sp.p.status = status ? status : fallback_status();
     if (!sp.p.status) return FTB_E_CUDA;
     CUtensorMap tin, tw;
-    {
+    memset(&tin, 0, sizeof(tin));
+    if (!sp.gather) {
       uint64_t dims[4] = {static_cast<uint64_t>(ws.cp), static_cast<uint64_t>(w), static_cast<uint64_t>(h),
                           static_cast<uint64_t>(n)};
       uint64_t strides[3] = {static_cast<uint64_t>(ws.cp) * 4, static_cast<uint64_t>(w) * ws.cp * 4,

@@ -240,6 +240,11 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// The same with a cluster-scope release: for shared-memory data written by this CTA's threads that the
+// waiter in the peer CTA orders work after (once per slab, not on a per-tile critical path).
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 // TMA load issued by one CTA of a pair: data lands in this CTA, completion bytes are
 // reported to `bar`, which may live in the peer CTA.
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0,

@@ -673,6 +673,41 @@ def test_conv2d_slab_kernel_as_cta_pairs(B, status, shape, extra):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("shape", [
+    # n, c, h, w, k, r, pad, dil
+    (5, 64, 56, 56, 64, 3, 1, 1),      # resident filter, slab ring and both accumulators wrap
+    (3, 128, 28, 28, 128, 3, 1, 1),    # streamed filter
+    (2, 40, 20, 24, 200, 3, 1, 2),     # channel counts that are no multiples of 32 (zero-filled chunk tail), dilation 2
+    (1, 8, 33, 130, 16, 5, 2, 1),      # 5x5, two tiles across the width, few channels
+    (2, 32, 14, 14, 48, 3, 1, 1),      # small planes, per-thread epilogue
+    (3, 20, 9, 7, 24, 3, 0, 1),        # no padding, a slab narrower than a warp's 32 pixels
+])
+@pytest.mark.parametrize("cfg", [{"algo": 2, "gather": 2}, {"algo": 2, "gather": 2, "cluster": 2}, {"algo": 5, "gather": 2},
+                                 {"algo": 2, "gather": 2, "split_k": 3}, {"algo": 2, "gather": 2, "relu": 1}])
+def test_conv2d_slab_kernel_gathers_its_slabs_from_nchw(B, status, shape, cfg):
+    """gather = 2: no channels-last copy; loader warps of the slab kernel build every slab from the NCHW
+    tensor (zero-filling padding, channel tails and, in a pair with an odd tile count, the tile past the end)."""
+    n, c, h, wd, k, r, pad, dil = shape
+    x, w = O.conv2d_inputs(n, c, h, wd, k, r, r, seed=61)
+    bias = np.random.default_rng(62).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, 1, pad, dil, 1)
+    if cfg.get("relu"):
+        want = np.maximum(want, 0)
+    try:
+        got = run_conv(B, x, w, bias, 1, pad, dil, 1, cfg=dict(cfg, fp32_mode=0), status=status)
+    except B.FtbError as exc:
+        assert exc.code in (-2, -3), exc
+        pytest.skip("refused: %s" % exc)
+    assert got.shape == want.shape
+    assert not np.isnan(got).any()
+    assert O.normalised_error(got, want) <= TOL["conv2d_tf32"], (shape, cfg)
+    # the same MMAs on the same operand bits as the layout-pass form; only where the library splits the taps
+    # over CTAs do partial sums meet in a different order
+    plain = run_conv(B, x, w, bias, 1, pad, dil, 1, cfg=dict(cfg, fp32_mode=0, gather=1), status=status)
+    assert O.normalised_error(got, plain) <= 1e-5
+    assert int(status.item()) == 0
+
+
 def test_conv2d_slab_algorithm_refuses_what_it_cannot_take(B, status):
     x, w = O.conv2d_inputs(1, 32, 16, 16, 32, 3, 3, seed=59)
     for kwargs, cfg in ((dict(stride=2), {"algo": 2}),                 # stride 2
