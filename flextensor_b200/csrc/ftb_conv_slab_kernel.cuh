@@ -439,13 +439,12 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
     // of the chunk, its lanes 32 consecutive slab pixels, so that a warp-wide load is one 128-byte line
     // of a channel plane (minus what falls into the padding).  The writes into the swizzled slab (16-byte
     // chunk index = (channel / 4) ^ (pixel & 7)) collide four ways, which is nothing beside the loads'
-    // latency: eight of those are in flight per thread (sixteen, or asking the next tile's lines into
-    // L2 ahead of time, measured no better).
+    // latency; sixteen loads are in flight per thread.
     if (ntaps > 0) {
       const int lt = static_cast<int>(threadIdx.x) - 192;
       const int g = lt >> 5;
-      const int slab_px = (p.tile_h + (p.R - 1) * p.dil_h) * p.slab_w;
-      const long long plane = static_cast<long long>(p.H) * p.W;
+      const int slab_h = p.tile_h + (p.R - 1) * p.dil_h;
+      const int plane = p.H * p.W;
       const uint32_t afull_sig0 = PAIR ? map_to_cta(afull0, 0) : afull0;
       uint32_t s = 0, ph = 0, sa = a_base;
       bool ok = true;
@@ -467,33 +466,38 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             break;
           }
           const int ch0 = cc * 32 + 4 * g;
-          const float* src = p.in_nchw + (static_cast<long long>(img) * p.C + ch0) * plane;
-          int sr = lane / p.slab_w, sc = lane - sr * p.slab_w;  // slab row and column of this lane's pixel
-          constexpr int kU = 2;  // pixel blocks per round: 4 * kU loads in flight per thread
-          for (int px = lane; px < slab_px; px += 32 * kU) {
-            float v[kU][4];
-            uint32_t dst[kU];
+          const float* src = p.in_nchw + (static_cast<long long>(img) * p.C + ch0) * static_cast<long long>(plane);
+          // rows of the slab in groups of kRows, a lane per slab column: the row tests are uniform over
+          // the warp and the address arithmetic is a few instructions per 4 * kRows loads (the loader is
+          // bound by instruction issue as much as by latency: a version that worked out row and column
+          // per pixel was half as fast)
+          constexpr int kRows = 4;
+          const bool c1 = ch0 + 1 < p.C, c2 = ch0 + 2 < p.C, c3 = ch0 + 3 < p.C;
+          const bool c0 = img_ok && ch0 < p.C;
+          for (int sr0 = 0; sr0 < slab_h; sr0 += kRows) {
+            for (int sc = lane; sc < p.slab_w; sc += 32) {
+              const int w = w0 + sc;
+              const bool col_ok = c0 && w >= 0 && w < p.W;
+              float v[kRows][4];
 #pragma unroll
-            for (int u = 0; u < kU; ++u) {
-              const int pxu = px + 32 * u;
-              const int h = h0 + sr, w = w0 + sc;
-              const bool inside = img_ok && pxu < slab_px && h >= 0 && h < p.H && w >= 0 && w < p.W;
-              const float* at = src + static_cast<long long>(h) * p.W + w;
+              for (int r = 0; r < kRows; ++r) {
+                const int h = h0 + sr0 + r;
+                const bool inside = col_ok && sr0 + r < slab_h && h >= 0 && h < p.H;
+                const float* at = src + h * p.W + w;
+                v[r][0] = inside ? __ldg(at) : 0.0f;
+                v[r][1] = (inside && c1) ? __ldg(at + plane) : 0.0f;
+                v[r][2] = (inside && c2) ? __ldg(at + 2 * plane) : 0.0f;
+                v[r][3] = (inside && c3) ? __ldg(at + 3 * plane) : 0.0f;
+              }
 #pragma unroll
-              for (int qc = 0; qc < 4; ++qc) v[u][qc] = (inside && ch0 + qc < p.C) ? __ldg(at + qc * plane) : 0.0f;
-              dst[u] = pxu < slab_px ? sa + static_cast<uint32_t>(pxu) * 128u +
-                                           ((static_cast<uint32_t>(g) ^ static_cast<uint32_t>(pxu & 7)) << 4)
-                                     : 0u;
-              sc += 32;
-              while (sc >= p.slab_w) {
-                sc -= p.slab_w;
-                ++sr;
+              for (int r = 0; r < kRows; ++r) {
+                if (sr0 + r < slab_h) {
+                  const uint32_t px = static_cast<uint32_t>((sr0 + r) * p.slab_w + sc);
+                  st_shared_v4(sa + px * 128u + ((static_cast<uint32_t>(g) ^ (px & 7u)) << 4), __float_as_uint(v[r][0]),
+                               __float_as_uint(v[r][1]), __float_as_uint(v[r][2]), __float_as_uint(v[r][3]));
+                }
               }
             }
-#pragma unroll
-            for (int u = 0; u < kU; ++u)
-              if (dst[u]) st_shared_v4(dst[u], __float_as_uint(v[u][0]), __float_as_uint(v[u][1]), __float_as_uint(v[u][2]),
-                                       __float_as_uint(v[u][3]));
           }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
           __syncwarp();

@@ -1265,13 +1265,15 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
       rc = ftb_validate(3, user, n * P * Q, k, c * r * s);
       if (rc) return rc;
     }
-    // NCHW input: the slabs are either TMA loads from a channels-last copy made by the layout pass
-    // (default), or built from the NCHW tensor by loader warps inside the kernel (gather = 2: no copy,
-    // the input crosses HBM once instead of three times).  Measured, batch 64 / 16 layers, the two are
-    // level where the MMAs are wide (128 -> 128 at 28 x 28: 55.6 against 58.6 us; 256 -> 256 at 14 x 14:
-    // 45.6 against 47.8) and the layout pass wins where they are narrow and a tile's MMAs are over before
-    // the loader warps have the next slab (64 -> 64 at 56 x 56: 77.5-80 against 72.6 us).
-    sp.gather = !cl && user && user->gather == 2;
+    // NCHW input: the slabs are either TMA loads from a channels-last copy made by the layout pass, or
+    // built from the NCHW tensor by loader warps inside the kernel (no copy: the input crosses HBM once
+    // instead of three times).  Left open, the gather is taken for long tile lists whose taps are not
+    // split and whose slab rows fit two warp-wide loads (64 -> 64 at 56 x 56, batch 64: 59.9 against
+    // 72.8 us; 128 -> 128 at 56 x 56: 161 against 187); short lists (batch 1: 9.3 against 8.9 us) and wide
+    // rows (64 -> 192 at 112 x 112, batch 8: 68.1 against 63.8) stay with the layout pass.
+    const int want_gather = user ? user->gather : 0;
+    sp.gather = !cl && (want_gather == 2 ||
+                        (want_gather == 0 && sp.p.split == 1 && sp.p.tiles >= 2 * num_sms && sp.p.slab_w <= 64));
     rc = conv_prepass(in, weight, in_nhwc, w_packed, n, c, h, w, k, cg, r, s, ws, num_sms, stream_v,
                       (sp.p.split > 1 && !pack_only) ? out : nullptr, n * k * P * Q, 0, 0, 1, 1, false,
                       sp.gather ? (parts & ~1) : parts);

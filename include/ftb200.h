@@ -72,9 +72,10 @@ typedef struct ftb_config {
                         per-tap conv kernels 2 on tiles of at most 128 output channels, else 1           */
   int32_t relu;      /* conv2d and depthwise: 1 = clamp the result at zero after the bias (the conv + bias +
                         ReLU chain of a network as one kernel); not a search knob                       */
-  int32_t gather;    /* conv2d on NCHW tensors, slab kernel: 0 or 1 = the layout pass writes a channels-last
-                        copy and the slabs are TMA loads; 2 = eight loader warps of the kernel build the
-                        slabs from the NCHW tensor themselves (no copy: the input crosses HBM once)           */
+  int32_t gather;    /* conv2d on NCHW tensors, slab kernel: 1 = the layout pass writes a channels-last copy and
+                        the slabs are TMA loads; 2 = eight loader warps of the kernel build the slabs from the
+                        NCHW tensor themselves (no copy: the input crosses HBM once); 0 = 2 for long tile lists
+                        with unsplit taps and slab rows of at most 64 pixels, else 1                          */
   int32_t reserved[1];
 } ftb_config;
 
