@@ -76,6 +76,12 @@ struct ConvSlabParams {
   // the rows, conflict-free 4-byte writes into the swizzled slab), zero-filling the padding.
   const float* in_nchw;
   int n_imgs, C, H, W;
+  // Two issuing threads (accumulators of at most 128 columns).  One thread gets a tcgen05.mma out about
+  // every 137 cycles whatever its shape (measured), which leaves a 64-column TF32 MMA's tensor pipe three
+  // quarters idle; a second thread issuing at the same time gets as many again.  The taps of every slab are
+  // dealt to the two threads alternately, each adds its taps into an accumulator of its own (128 columns
+  // apart) and the epilogue adds the two.  Used by a CTA whose share of the taps is at least two.
+  int dual;
   int cl_out;   // the result is channels-last [N][P][Q][K]: staged as [pixel][32 channels], stored through a
                 // (k, q, p, n) map
   uint32_t epi_buf_bytes;
@@ -88,8 +94,23 @@ struct ConvSlabParams {
   int* status;
 };
 
+// 32 columns of a tile's accumulator; with two issuing threads (`other` = the distance to the second
+// thread's accumulator, else 0) the sum of the two partial accumulators.
+__device__ __forceinline__ void slab_acc_ld(uint32_t taddr, uint32_t other, uint32_t (&v)[32]) {
+  tmem_ld_32x32(taddr, v);
+  if (other) {
+    uint32_t w[32];
+    tmem_ld_32x32(taddr + other, w);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(w[j]));
+  } else {
+    tmem_ld_wait();
+  }
+}
+
 template <bool PAIR, bool STREAM, bool GATHER>
-__global__ void __launch_bounds__(GATHER ? 448 : 192, 1)
+__global__ void __launch_bounds__(GATHER ? 480 : 224, 1)
 conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_constant__ CUtensorMap tmap_w,
                  const __grid_constant__ StoreMaps tmap_out,
                  const __grid_constant__ ConvSlabParams p) {
@@ -121,6 +142,9 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
   const int tap0 = ks * p.taps_per_split;
   const int tap1 = min(taps, tap0 + p.taps_per_split);
   const int ntaps = tap1 - tap0;
+  const bool dual = p.dual != 0 && ntaps >= 2;
+  constexpr int kIssuer2Warp = GATHER ? 14 : 6;   // the last warp of the CTA
+  constexpr uint32_t kDualCols = 128;             // columns between the two threads' accumulators
   // filter (or the ring its tiles stream through) first, slabs after it
   constexpr bool streamed = STREAM;  // p.b_stages > 0
   const uint32_t b_stage_bytes = static_cast<uint32_t>(p.b_group) * p.b_tile_bytes;
@@ -134,15 +158,15 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       // a slab is complete when its TMA bytes have landed, or when every loader warp (of both CTAs
       // of a pair) has written its part
       mbar_init(smem_u32(&bar_afull[s]), GATHER ? (PAIR ? 16u : 8u) : 1u);
-      mbar_init(smem_u32(&bar_aempty[s]), 1);
+      mbar_init(smem_u32(&bar_aempty[s]), dual ? 2 : 1);  // one commit per issuing thread
     }
     mbar_init(smem_u32(&bar_bfull), 1);
     for (int s = 0; s < p.b_stages; ++s) {
       mbar_init(smem_u32(&bar_bsfull[s]), 1);
-      mbar_init(smem_u32(&bar_bsempty[s]), 1);
+      mbar_init(smem_u32(&bar_bsempty[s]), dual ? 2 : 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&bar_tfull[a]), 1);
+      mbar_init(smem_u32(&bar_tfull[a]), dual ? 2 : 1);
       mbar_init(smem_u32(&bar_tempty[a]), PAIR ? 8 : 4);  // the leader's copy counts both CTAs' epilogue warps
     }
     fence_mbar_init();
@@ -289,9 +313,10 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       (void)prof_wait; (void)prof_loop;
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && ntaps > 0 && cta_rank == 0) {
+  } else if (warp == 1 || warp == kIssuer2Warp) {
+    // ------------------------------------------------------------ MMA issuer(s)
+    const uint32_t me = (warp == 1) ? 0u : 1u;  // this thread takes the taps of this parity when there are two
+    if (lane == 0 && ntaps > 0 && cta_rank == 0 && (me == 0 || dual)) {
       const uint32_t idesc = p.idesc;
       const uint32_t hi = smem_desc_hi(16, 1024, 2);
       const uint32_t b_tile_enc = p.b_tile_bytes >> 4;
@@ -322,7 +347,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
         }
         FTB_PROF_ADD(prof_tempty, prof_t0);
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kAccStride;
+        const uint32_t d_tmem = tmem_base + acc * kAccStride + me * kDualCols;
         uint32_t accumulate = 0;
         // conv3d: the same walk over depth taps as the producer's (skips included)
         const int depth_taps = STREAM && p.od > 0 ? p.T : 1;
@@ -364,10 +389,12 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
               const int nt = min(p.b_group, ntaps - g0);
               for (int j = 0; j < nt; ++j) {
                 const uint32_t ta_lo = a_lo + static_cast<uint32_t>(tr * p.dil_h * p.slab_w + ts * p.dil_w) * 8u;
+                if (!dual || (static_cast<uint32_t>(g0 + j) & 1u) == me) {
 #pragma unroll
-                for (int k = 0; k < kMmaPerKb; ++k) {
-                  umma<KIND_TF32, PAIR>(d_tmem, ta_lo + 2u * k, hi, b_lo + 2u * k, hi, idesc, accumulate);
-                  accumulate = 1;
+                  for (int k = 0; k < kMmaPerKb; ++k) {
+                    umma<KIND_TF32, PAIR>(d_tmem, ta_lo + 2u * k, hi, b_lo + 2u * k, hi, idesc, accumulate);
+                    accumulate = 1;
+                  }
                 }
                 b_lo += b_tile_enc;
                 if (++ts == p.S) {
@@ -398,10 +425,12 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             if (p.diag & 2) off &= ~7u;
 #endif
             const uint32_t ta_lo = a_lo + off * 8u;
+            if (!dual || (static_cast<uint32_t>(tap) & 1u) == me) {
 #pragma unroll
-            for (int k = 0; k < kMmaPerKb; ++k) {
-              umma<KIND_TF32, PAIR>(d_tmem, ta_lo + 2u * k, hi, b_lo + 2u * k, hi, idesc, accumulate);
-              accumulate = 1;
+              for (int k = 0; k < kMmaPerKb; ++k) {
+                umma<KIND_TF32, PAIR>(d_tmem, ta_lo + 2u * k, hi, b_lo + 2u * k, hi, idesc, accumulate);
+                accumulate = 1;
+              }
             }
             b_lo += static_cast<uint32_t>(p.cchunks) * b_tile_enc;
             if (++ts == p.S) {
@@ -427,13 +456,15 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       }
       long long prof_iloop = 0;
       FTB_PROF_ADD(prof_iloop, prof_iloop0);
-      FTB_PROF_FLUSH(PROF_ISSUER_FULL, prof_full);
-      FTB_PROF_FLUSH(PROF_ISSUER_TEMPTY, prof_tempty);
-      FTB_PROF_FLUSH(PROF_ISSUER_LOOP, prof_iloop);
+      if (me == 0) {
+        FTB_PROF_FLUSH(PROF_ISSUER_FULL, prof_full);
+        FTB_PROF_FLUSH(PROF_ISSUER_TEMPTY, prof_tempty);
+        FTB_PROF_FLUSH(PROF_ISSUER_LOOP, prof_iloop);
+      }
       (void)prof_full; (void)prof_tempty; (void)prof_iloop;
     }
     __syncwarp();
-  } else if (GATHER && warp >= 6) {
+  } else if (GATHER && warp >= 6 && warp < 14) {
     // ------------------------------------------------------------ slab loader (NCHW input)
     // 256 threads build the slab of every (tile, channel chunk): warp g takes the channels 4 g .. 4 g + 3
     // of the chunk, its lanes 32 consecutive slab pixels, so that a warp-wide load is one 128-byte line
@@ -515,7 +546,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -567,8 +598,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             }
             named_barrier_sync(1, 128);
             uint32_t v[32];
-            tmem_ld_32x32(taddr + c, v);
-            tmem_ld_wait();
+            slab_acc_ld(taddr + c, dual ? kDualCols : 0u, v);
             if (c + 32 >= p.bn) {
               tc_fence_before();
               __syncwarp();
@@ -625,8 +655,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
             }
             named_barrier_sync(1, 128);
             uint32_t v[32];
-            tmem_ld_32x32(taddr + c, v);
-            tmem_ld_wait();
+            slab_acc_ld(taddr + c, dual ? kDualCols : 0u, v);
             if (c + 32 >= p.bn) {
               tc_fence_before();
               __syncwarp();
@@ -676,8 +705,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
                                  : p.out + static_cast<long long>(img) * p.conv_ktot * plane + static_cast<long long>(oh) * p.Q + ow;
         for (int c = 0; c < p.bn; c += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
-          tmem_ld_wait();
+          slab_acc_ld(taddr + c, dual ? kDualCols : 0u, v);
           if (c + 32 >= p.bn) {
             tc_fence_before();
             __syncwarp();

@@ -243,7 +243,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const StoreMaps&
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));
   lc.gridDim = dim3(static_cast<unsigned>(ctas), 1, 1);
-  lc.blockDim = dim3((SPLIT3 || WIDE) ? 320 : 192, 1, 1);
+  lc.blockDim = dim3(WIDE ? 352 : SPLIT3 ? 320 : 192, 1, 1);
   lc.dynamicSmemBytes = smem;
   lc.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -484,6 +484,12 @@ int gemm_generic(int kind, int out, const void* a, const void* b, void* c, int64
   p.tma_store = (store_ok && p.bn % p.slab_cols == 0 &&
                  (p.split_k == 1 || (out == OUT_F32 && num_extra == 0))) ? 1 : 0;
   p.diag = user ? user->reserved[0] : 0;
+#ifdef FTB_PROFILE_WAITS
+  // diagnostic bit 3 (with bit 2): the free-running MMAs are issued as M = 64 instructions, to see what a
+  // narrower A operand costs (single-CTA tiles only; results are garbage by design)
+  if (((p.diag & 32) && p.bn > 64) || ((p.diag & 64) && p.bn > 128)) return FTB_E_BAD_CONFIG;  // columns past the allocation
+  if ((p.diag & 8) && !pair) p.idesc = make_idesc(ki, wide ? 256 : p.bn, a_mn, b_mn, 64);
+#endif
   if (user && (user->release < 0 || user->release > 2)) return FTB_E_BAD_CONFIG;
   // (the 256 x 512 tile keeps the per-stage hand-back: its four stages are too few to give one up)
   p.release_pairs = (user && user->release == 2 && !split3 && cfg.tile_n != 512 && cfg.stages % 2 == 0 &&
@@ -1047,6 +1053,7 @@ static SlabPlan plan_slab(const ftb_config* user, int64_t n, int64_t kg, int64_t
   p.slab_alloc = slab_stride;
   p.b_tile_bytes = b_tile;
   p.idesc = make_idesc(kind_info(KIND_TF32), bn, 0, 0, pair ? 2 * kTileM : kTileM);
+  p.dual = bn <= 128 ? 1 : 0;  // two accumulators per tile fit tensor memory's 512 columns twice over
   const long long units_avail = pair ? num_sms / 2 : num_sms;
   const long long steps = pair ? (tiles + 1) / 2 : tiles;
   long long walkers = units_avail / split;
@@ -1096,7 +1103,7 @@ static int launch_slab(const CUtensorMap& tin, const CUtensorMap& tw, const Stor
   cudaLaunchConfig_t lc;
   memset(&lc, 0, sizeof(lc));
   lc.gridDim = dim3(static_cast<unsigned>(sp.ctas), 1, 1);
-  lc.blockDim = dim3(sp.gather ? 448 : 192, 1, 1);
+  lc.blockDim = dim3(sp.gather ? 480 : 224, 1, 1);
   lc.dynamicSmemBytes = sp.smem;
   lc.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -1288,6 +1295,7 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
     sp.p.bias = bias;
     sp.p.relu = relu;
     sp.p.diag = user ? user->reserved[0] : 0;
+    if (sp.p.diag & 128) sp.p.dual = 0;  // (diagnostic: one issuing thread)
     sp.p.conv_ktot = static_cast<int>(k);
     sp.p.status = status ? status : fallback_status();
     if (!sp.p.status) return FTB_E_CUDA;

@@ -171,7 +171,7 @@ __device__ __forceinline__ TileCoord decode_tile(const UmmaParams& p, int t) {
 }
 
 template <int KIND, int OUT, bool SPLIT3, bool PAIR, bool WIDE = false>
-__global__ void __launch_bounds__((SPLIT3 || WIDE) ? 320 : 192, 1)
+__global__ void __launch_bounds__(WIDE ? 352 : SPLIT3 ? 320 : 192, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ StoreMaps tmap_c, const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -200,7 +200,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // `tempty` barrier the epilogue warps of both.
     for (uint32_t s = 0; s < stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
-      mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), WIDE ? 2 : 1);  // a wide tile's stage is read by two issuing threads
       mbar_init(smem_u32(&bar_split[s]), 4);
     }
     for (int a = 0; a < 2; ++a) {
@@ -292,7 +292,24 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int kb = kb0; kb < kb1; ++kb, kc += kblk) {
           FTB_PROF_T0(prof_w0);
 #ifdef FTB_PROFILE_WAITS
-          if (p.diag & 4) continue;
+          if (p.diag & 4) {
+            // diagnostic bit 6: this thread issues the same free-running MMAs as the issuer, into
+            // columns 128.. of tensor memory (tiles of at most 128 columns): do two issuing threads
+            // get twice the instruction rate of one?
+            if constexpr (!PAIR && !WIDE && !SPLIT3) {
+              if (p.diag & 64) {
+                const uint32_t xa_hi = smem_desc_hi(p.a_lbo, p.a_sbo, p.a_layout);
+                const uint32_t xb_hi = smem_desc_hi(p.b_lbo, p.b_sbo, p.b_layout);
+                const uint32_t xa = smem_desc_lo(smem_base, p.a_lbo);
+                const uint32_t xb = xa + (kATileBytes >> 4) + smem_desc_lo(0, p.b_lbo) - smem_desc_lo(0, p.a_lbo);
+#pragma unroll
+                for (int k = 0; k < kMmaPerKb; ++k)
+                  umma<KIND, false>(tmem_base + 128u, xa + k * (p.a_kadv >> 4), xa_hi, xb + k * (p.b_kadv >> 4), xb_hi,
+                                    p.idesc, 1u);
+              }
+            }
+            continue;
+          }
 #endif
           if ((!release_pairs || (s & 1u) == 0) &&
               !mbar_wait(empty0 + 8 * (release_pairs ? (s >> 1) : s), ph ^ 1u, &abort_flag)) {
@@ -390,6 +407,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
+#ifdef FTB_PROFILE_WAITS
+      if ((p.diag & 68) == 68 && !PAIR && !WIDE && !SPLIT3) {
+        // this thread's own MMAs are complete before the kernel gives tensor memory back
+        tc_commit(empty0);
+        mbar_wait(empty0, 0, &abort_flag);
+      }
+#endif
       long long prof_loop = 0;
       FTB_PROF_ADD(prof_loop, prof_loop0);
       FTB_PROF_FLUSH(PROF_PRODUCER_EMPTY, prof_wait);
@@ -398,8 +422,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       (void)prof_wait; (void)prof_loop;
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 1 || (WIDE && warp == 10)) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only in a pair)
+    // A wide tile has TWO issuing threads, one per accumulator half (warps 1 and 10).  Measured: one
+    // thread gets a tcgen05.mma out about every 137 cycles whatever its shape, and a second thread
+    // issuing at the same time gets as many again in the same time, so a single thread keeps the
+    // tensor pipe (128 cycles of math per 256-column MMA) at most 93 % busy.  Both threads read every
+    // stage (its `empty` barrier counts two commits); each owns one half's accumulator, waits for it
+    // and reports it complete by itself, so the second half trails the first by however long the
+    // epilogue held it back and the halves' drains do not fall together.
+    const uint32_t wide_half = (WIDE && warp == 10) ? 1u : 0u;
     if (lane == 0 && cta_rank == 0) {
       const uint32_t idesc = p.idesc;
       const uint32_t a_hi = smem_desc_hi(p.a_lbo, p.a_sbo, p.a_layout);
@@ -423,14 +455,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // barrier wait, about 80 per commit).  So it asks about the NEXT stage before it issues the
       // MMAs of the current one; the probe's latency then runs under the MMA issue.
       uint32_t ready = 0;
-      uint32_t pend_a = 0, pend_s = 0, pend_acc = 0;  // wide tiles: a K block whose second half is still to be issued
       const bool release_pairs = p.release_pairs != 0;
       for (int t = unit; t < total_tiles && ok; t += units, ++local) {
         const int ks = (p.split_k > 1) ? (t % p.split_k) : 0;
         const int kb0 = ks * kb_per_split;
         const int kb1 = min(num_kb, kb0 + kb_per_split);
         // Plain tiles alternate between the two accumulators; a wide tile owns both (one per half).
-        const uint32_t acc = WIDE ? 0u : (local & 1);
+        const uint32_t acc = WIDE ? wide_half : (local & 1);
         const uint32_t aph = WIDE ? (local & 1u) : ((local >> 1) & 1u);
         FTB_PROF_T0(prof_t0);
         if (!mbar_wait(smem_u32(&bar_tempty[acc]), aph ^ 1u, &abort_flag)) {
@@ -475,54 +506,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
 #endif
           if constexpr (WIDE) {
-            // Order of the two halves.  In the middle of a tile a K block feeds the first half, then
-            // the second.  At both ends of a tile two K blocks are taken together, first half twice,
-            // then second half twice: the first half then completes two K blocks' worth of MMAs
-            // (about a thousand cycles) before the second instead of one, and at the start of the
-            // next tile the second half is wanted that much later - time in which the epilogue warps,
-            // which serve both halves one after the other, drain them without the tensor pipe waiting.
-            const int j = kb - kb0, nkb = kb1 - kb0;
-            const bool skew = nkb >= 4;
-            const bool last = kb + 1 == kb1;
+            const uint32_t b_half = b_lo + wide_half * p.b_half_enc;  // this thread's 256 columns of B
 #pragma unroll
             for (int k = 0; k < kMmaPerKb; ++k)
-              umma<KIND, PAIR>(d_tmem, a_lo + k * a_k, a_hi, b_lo + k * b_k, b_hi, idesc, k > 0 ? 1u : accumulate);
-            if (last) tc_commit_pair_both(tfull0);  // the first half is complete
-            if (skew && (j == 0 || j == nkb - 2)) {
-              // this K block's second half is issued together with the next one's
-              pend_a = a_lo;
-              pend_s = s;
-              pend_acc = accumulate;
-            } else {
-              const bool with_pending = skew && (j == 1 || last);
-              if (j == (skew ? 1 : 0)) {
-                // the second half may still be draining the previous tile
-                FTB_PROF_T0(prof_t1);
-                if (!mbar_wait(smem_u32(&bar_tempty[1]), aph ^ 1u, &abort_flag)) {
-                  atomicOr(p.status, FTB_DEV_WAIT_TMEMFREE);
-                  abort_flag = 1;
-                  ok = false;
-                  break;
-                }
-                FTB_PROF_ADD(prof_tempty, prof_t1);
-                tc_fence_after();
-              }
-              if (with_pending) {
-                const uint32_t pb = pend_a + b_off + b_lbo_delta + p.b_half_enc;
-#pragma unroll
-                for (int k = 0; k < kMmaPerKb; ++k)
-                  umma<KIND, PAIR>(d_tmem + kAccStride, pend_a + k * a_k, a_hi, pb + k * b_k, b_hi, idesc,
-                                   k > 0 ? 1u : pend_acc);
-                tc_commit_pair_both(empty0 + 8 * pend_s);
-              }
-              const uint32_t b_half = b_lo + p.b_half_enc;
-              const uint32_t acc1 = with_pending ? 1u : accumulate;
-#pragma unroll
-              for (int k = 0; k < kMmaPerKb; ++k)
-                umma<KIND, PAIR>(d_tmem + kAccStride, a_lo + k * a_k, a_hi, b_half + k * b_k, b_hi, idesc,
-                                 k > 0 ? 1u : acc1);
-              tc_commit_pair_both(empty0 + 8 * s);
-            }
+              umma<KIND, PAIR>(d_tmem, a_lo + k * a_k, a_hi, b_half + k * b_k, b_hi, idesc, k > 0 ? 1u : accumulate);
+            tc_commit_pair_both(empty0 + 8 * s);
             accumulate = 1;
             a_lo += stage_enc;
             if (++s == stages) {
@@ -536,7 +524,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int k = 0; k < kMmaPerKb; ++k) {
               const uint32_t ak = a_lo + k * a_k;
               const uint32_t bk = b_lo + k * b_k;
+#ifdef FTB_PROFILE_WAITS
+              // diagnostic bits 4 and 5: consecutive MMAs go to two (four, tiles of at most 64 columns)
+              // different accumulators, so that no MMA adds to the result of the one before it
+              const uint32_t d_k = (p.diag & 32) ? d_tmem + 64u * k
+                                   : (p.diag & 16) ? tmem_base + ((acc ^ (k & 1u)) * kAccStride) : d_tmem;
+              umma<KIND, PAIR>(d_k, ak, a_hi, bk, b_hi, idesc, accumulate);
+#else
               umma<KIND, PAIR>(d_tmem, ak, a_hi, bk, b_hi, idesc, accumulate);
+#endif
               accumulate = 1;
               if constexpr (SPLIT3) {
                 umma<KIND, PAIR>(d_tmem, ak + lo_enc, a_hi, bk, b_hi, idesc, 1);  // A_lo * B_hi
@@ -564,9 +560,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
         if (ok) {
-          if constexpr (WIDE) {
-            tc_commit_pair_both(tfull0 + 8);
-          } else if constexpr (PAIR) {
+          if constexpr (PAIR) {
             tc_commit_pair_both(tfull0 + 8 * acc);
           } else {
             tc_commit(tfull0 + 8 * acc);
@@ -575,13 +569,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       long long prof_loop = 0;
       FTB_PROF_ADD(prof_loop, prof_loop0);
-      FTB_PROF_FLUSH(PROF_ISSUER_FULL, prof_full);
-      FTB_PROF_FLUSH(PROF_ISSUER_TEMPTY, prof_tempty);
-      FTB_PROF_FLUSH(PROF_ISSUER_LOOP, prof_loop);
+      if (wide_half == 0) {
+        FTB_PROF_FLUSH(PROF_ISSUER_FULL, prof_full);
+        FTB_PROF_FLUSH(PROF_ISSUER_TEMPTY, prof_tempty);
+        FTB_PROF_FLUSH(PROF_ISSUER_LOOP, prof_loop);
+      }
       (void)prof_full; (void)prof_tempty; (void)prof_loop;
     }
     __syncwarp();
-  } else if (warp < 6 || (WIDE && p.tma_store != 0)) {
+  } else if (warp < 6 || (WIDE && p.tma_store != 0 && warp < 10)) {
     // ------------------------------------------------------------ epilogue
     // A wide tile's staged epilogue runs on two groups of four warps (2-5 and 6-9): both read the
     // same accumulator half, each takes every other slab through its own staging buffer, so a half

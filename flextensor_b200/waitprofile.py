@@ -13,7 +13,9 @@ cycles each role of a CTA spent inside its barrier waits, per K block of the mai
 ``--diag`` adds runs whose results are garbage but whose timings separate the bounds: 1 = stages
 are signalled without being loaded (tensor pipe + epilogue only), 2 = stages are released without
 MMAs (loads only), 4 = MMAs back to back with no producer and no stage hand-off (the tensor
-pipe's own rate).
+pipe's own rate), 12 = the same with M = 64 instructions (single-CTA tiles), 20 / 36 = consecutive
+MMAs go to two / four accumulators in turn (36: tiles of at most 64 columns), 68 = a second thread
+issues the same MMAs at the same time (single-CTA tiles of at most 128 columns).
 """
 import argparse
 import json
