@@ -592,11 +592,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
           const uint32_t px_row = static_cast<uint32_t>(prow * p.tile_w + pcol) * 128u;
           for (int c = 0; c < p.bn; c += 32, ++epi_seq) {
             const uint32_t buf = epi_base + (p.epi_bufs == 2 ? (epi_seq & 1u) : 0u) * p.epi_buf_bytes;
-            if (leader) {
-              if (p.epi_bufs == 2) bulk_wait_group_read<1>();
-              else bulk_wait_group_read<0>();
-            }
-            named_barrier_sync(1, 128);
+            // the accumulator columns come into registers (and the accumulator goes back) while the previous
+            // bulk store is still reading the staging buffer
             uint32_t v[32];
             slab_acc_ld(taddr + c, dual ? kDualCols : 0u, v);
             if (c + 32 >= p.bn) {
@@ -607,6 +604,11 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
                 else mbar_arrive(tempty_sig0 + 8 * acc);
               }
             }
+            if (leader) {
+              if (p.epi_bufs == 2) bulk_wait_group_read<1>();
+              else bulk_wait_group_read<0>();
+            }
+            named_barrier_sync(1, 128);
             if (in_tile) {
               const bool add_bias = p.bias != nullptr && ks == 0;
 #pragma unroll
@@ -649,11 +651,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
           const uint32_t ch_stride = static_cast<uint32_t>(p.tile_h * p.tile_w) * 4u;
           for (int c = 0; c < p.bn; c += 32, ++epi_seq) {
             const uint32_t buf = epi_base + (p.epi_bufs == 2 ? (epi_seq & 1u) : 0u) * p.epi_buf_bytes;
-            if (leader) {
-              if (p.epi_bufs == 2) bulk_wait_group_read<1>();
-              else bulk_wait_group_read<0>();
-            }
-            named_barrier_sync(1, 128);
+            // the accumulator columns come into registers (and the accumulator goes back) while the previous
+            // bulk store is still reading the staging buffer
             uint32_t v[32];
             slab_acc_ld(taddr + c, dual ? kDualCols : 0u, v);
             if (c + 32 >= p.bn) {
@@ -664,6 +663,11 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
                 else mbar_arrive(tempty_sig0 + 8 * acc);
               }
             }
+            if (leader) {
+              if (p.epi_bufs == 2) bulk_wait_group_read<1>();
+              else bulk_wait_group_read<0>();
+            }
+            named_barrier_sync(1, 128);
             if (in_tile) {
               const bool add_bias = p.bias != nullptr && ks == 0;
 #pragma unroll

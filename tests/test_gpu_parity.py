@@ -469,6 +469,34 @@ def test_conv2d_slab_algorithm(B, status, shape, cfg):
 
 @pytest.mark.parametrize("shape", [
     # n, c, h, w, k, r, pad, dil
+    (5, 64, 56, 56, 64, 3, 1, 1),      # 64 accumulator columns, both accumulator pairs wrap
+    (2, 96, 28, 28, 128, 3, 1, 1),     # 128 columns: the four accumulators fill tensor memory
+    (1, 32, 40, 40, 48, 5, 2, 1),      # 25 taps
+    (2, 64, 28, 28, 256, 3, 1, 1),     # 256 columns: one issuing thread only
+])
+@pytest.mark.parametrize("cfg", [{"algo": 2}, {"algo": 2, "split_k": 5}, {"algo": 2, "split_k": 9}, {"algo": 2, "split_k": 2},
+                                 {"algo": 5}, {"algo": 2, "cluster": 2}, {"algo": 2, "gather": 2}, {"algo": 5, "gather": 2}])
+def test_conv2d_slab_kernel_with_two_issuing_threads(B, status, shape, cfg):
+    """Accumulators of at most 128 columns are filled by two MMA-issuing threads that take the taps of a slab
+    alternately and are summed in the epilogue.  Tap shares of 2, 2, 2, 2, 1 (split 5: the last CTA has one
+    thread's worth), of one tap each (split 9: single thread everywhere) and of 5 and 4 (split 2)."""
+    n, c, h, wd, k, r, pad, dil = shape
+    x, w = O.conv2d_inputs(n, c, h, wd, k, r, r, seed=61)
+    bias = np.random.default_rng(62).standard_normal(k).astype(np.float32)
+    want = O.conv2d_nchw(x, w, bias, 1, pad, dil, 1)
+    try:
+        got = run_conv(B, x, w, bias, 1, pad, dil, 1, cfg=dict(cfg, fp32_mode=0), status=status)
+    except B.FtbError as exc:
+        assert exc.code in (-2, -3), exc  # a knob set the shape cannot take is refused, never run wrong
+        pytest.skip("refused: %s" % exc)
+    assert got.shape == want.shape
+    assert not np.isnan(got).any()
+    assert O.normalised_error(got, want) <= TOL["conv2d_tf32"]
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("shape", [
+    # n, c, h, w, k, r, pad, dil
     (3, 128, 28, 28, 128, 3, 1, 1),    # 36 filter tiles of 16 KB: cannot stay resident
     (2, 256, 14, 14, 256, 3, 1, 1),    # 72 tiles of 32 KB
     (5, 64, 56, 56, 64, 3, 1, 1),      # would fit resident: streamed because asked for; ring and slabs wrap
