@@ -82,6 +82,7 @@ struct ConvSlabParams {
   // dealt to the two threads alternately, each adds its taps into an accumulator of its own (128 columns
   // apart) and the epilogue adds the two.  Used by a CTA whose share of the taps is at least two.
   int dual;
+  int cl_swz;   // channels-last staging rows are written in the 128-byte swizzle of their store map
   int cl_out;   // the result is channels-last [N][P][Q][K]: staged as [pixel][32 channels], stored through a
                 // (k, q, p, n) map
   uint32_t epi_buf_bytes;
@@ -590,6 +591,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
           // (a lane writes its pixel's 128 bytes) -> one bulk tensor store per 32 output channels
           const bool leader = (warp == 2 && lane == 0);
           const uint32_t px_row = static_cast<uint32_t>(prow * p.tile_w + pcol) * 128u;
+          const uint32_t px_swz = p.cl_swz ? (static_cast<uint32_t>(prow * p.tile_w + pcol) & 7u) : 0u;
           for (int c = 0; c < p.bn; c += 32, ++epi_seq) {
             const uint32_t buf = epi_base + (p.epi_bufs == 2 ? (epi_seq & 1u) : 0u) * p.epi_buf_bytes;
             // the accumulator columns come into registers (and the accumulator goes back) while the previous
@@ -618,12 +620,12 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmap_in, const __grid_const
                 if (p.relu) x = fmaxf(x, 0.0f);
                 v[j] = __float_as_uint(x);
               }
-              // (the lanes' 128-byte pitch makes these stores collide on their banks; they run beside
-              // the next tile's main loop and are a small part of a tile's time)
+              // (the lanes' 128-byte pitch would make these stores collide on their banks: chunk j of pixel
+              // px goes to position j ^ (px & 7), which the swizzled store map undoes)
 #pragma unroll
               for (int j = 0; j < 8; ++j)
-                st_shared_v4(buf + px_row + (static_cast<uint32_t>(j) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2],
-                             v[4 * j + 3]);
+                st_shared_v4(buf + px_row + ((static_cast<uint32_t>(j) ^ px_swz) << 4), v[4 * j], v[4 * j + 1],
+                             v[4 * j + 2], v[4 * j + 3]);
             }
             fence_proxy_async_smem();
             named_barrier_sync(1, 128);

@@ -1331,9 +1331,13 @@ int conv2d_generic(const float* in, const float* weight, const float* bias, floa
                              static_cast<uint64_t>(P) * Q * k * 4};
       uint32_t box[4] = {32, static_cast<uint32_t>(sp.p.tile_w), static_cast<uint32_t>(sp.p.tile_h), 1};
       const uint32_t ones[4] = {1, 1, 1, 1};
+      // A staging row is one pixel's 32 channels = 128 bytes: with the 128-byte swizzle the lanes of a warp,
+      // which hold consecutive pixels, write their 16-byte chunks without bank conflicts (staging buffers
+      // that start on 1024-byte boundaries).
+      sp.p.cl_swz = sp.p.epi_buf_bytes % 1024 == 0 ? 1 : 0;
       for (int d = 0; d < sp.p.num_dst; ++d) {
         rc = make_tmap(&tout.dst[d], ki.dt, 4, d == 0 ? out : extra_dst[d - 1], dims, strides, box, ones,
-                       CU_TENSOR_MAP_SWIZZLE_NONE);
+                       sp.p.cl_swz ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc) return rc;
       }
     } else if (sp.p.epi_bufs) {
